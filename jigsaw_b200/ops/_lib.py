@@ -1,0 +1,89 @@
+"""ctypes loader of the in-tree sm_100a kernel library.
+
+``lib()`` returns the loaded library or raises: on a machine with a CUDA device the
+kernels are the product, so a missing or stale ``libjb_kernels.so`` is an error, never a
+silent fall back to PyTorch ops.  ``available()`` answers without raising, for code that
+must also run on CPU-only machines.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_int, c_longlong, c_uint, c_void_p
+from functools import lru_cache
+
+import torch
+
+from . import _build
+
+
+class JbHalo(ctypes.Structure):
+    """Mirror of the C ``JbHalo`` struct: peer buffers / flags of the 3x3 neighbourhood."""
+
+    _fields_ = [
+        ("push_buf", c_void_p * 9),
+        ("push_flag", c_void_p * 9),
+        ("wait_flag", c_void_p * 9),
+        ("push_epoch", c_uint),
+        ("wait_epoch", c_uint),
+        ("push_enabled", c_uint),
+        ("wait_enabled", c_uint),
+    ]
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    L.jb_abi_version.restype = c_int
+    L.jb_gemm_bf16.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p,  # A B C bias
+        c_int, c_int, c_int,  # M N K
+        c_longlong, c_longlong, c_longlong,  # lda ldb ldc
+        c_int, c_int, c_int, c_int, c_int,  # a_mn b_mn act out_fp32 accumulate
+        c_int, c_void_p, c_void_p,  # sm_count status stream
+    ]
+    L.jb_gemm_bf16.restype = c_int
+    L.jb_conv3x3_c64.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p,  # in weights bias gelu_src
+        c_void_p, c_void_p, c_void_p,  # dense_pre padded_out dense_out
+        c_int, c_int, c_int,  # NB H W
+        c_int, c_int, c_int, c_int,  # nout_pad cout_real act mode
+        POINTER(JbHalo), c_void_p, c_void_p, c_int, c_void_p,  # halo done_counter status sm_count stream
+    ]
+    L.jb_conv3x3_c64.restype = c_int
+    L.jb_conv3x3_wgrad_scratch_floats.argtypes = [c_int]
+    L.jb_conv3x3_wgrad_scratch_floats.restype = c_longlong
+    L.jb_conv3x3_c64_wgrad.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # x gy gw gb scratch
+        c_int, c_int, c_int,  # NB H W
+        POINTER(JbHalo), c_void_p, c_int, c_void_p,  # halo status sm_count stream
+    ]
+    L.jb_conv3x3_c64_wgrad.restype = c_int
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    """Load (building first if the sources are newer) and return the kernel library."""
+    if not _build.is_fresh():
+        _build.build()
+    L = ctypes.CDLL(str(_build.LIB_PATH))
+    _declare(L)
+    return L
+
+
+def available() -> bool:
+    """True when a CUDA device is present and the kernel library loads."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        lib()
+    except (OSError, RuntimeError):
+        return False
+    return True
+
+
+@lru_cache(maxsize=8)
+def sm_count(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,775 @@
+// Halo-fused 3x3 convolution (stride 1, padding 1) for 64-channel NHWC bf16 tiles on
+// tcgen05 tensor cores: forward, data gradient and weight gradient.
+//
+// Data layout.  Every activation / gradient tile lives in a PADDED buffer
+//   [NB][H+2][W+2][64] bf16
+// whose one-pixel border is the halo.  The producer of a tile (the epilogue of the
+// previous convolution, or the pack kernel) writes the interior locally and stores
+// its edge rows / columns / corner pixels straight into the borders of the up to
+// eight neighbouring ranks' buffers over NVLink (plain peer stores), then publishes
+// an epoch in the neighbours' flag words.  A border on the edge of the global domain
+// is never written and stays zero, which is the convolution's zero padding.  The
+// consumer waits (bounded) for the flags and afterwards reads LOCAL memory only, so
+// every operand tile is fetched by TMA (no cluster multicast anywhere).
+//
+// Implicit GEMM.  An output tile is 128 consecutive pixels of one row: M = 128,
+// N = output channels, K = 9 taps x 64 input channels.  A CTA walks down a column
+// strip; input rows are kept in an 8-slot shared-memory window (130 pixels x 128 B,
+// 128-byte swizzle) so each input row is fetched from L2 about once, and the nine
+// taps are nine shifted views of three slots: the shift is applied to the start
+// address of the UMMA shared-memory descriptor.  The 9 x 64 x N weights stay resident
+// in shared memory for the life of the CTA.  Accumulators are double-buffered in TMEM
+// so the epilogue of row h overlaps the MMAs of row h+1.
+//
+// Capability parity: replaces halo_gather + F.conv2d, conv2d_input + halo_scatter_add
+// and conv2d_weight of the reference (jigsaw/modules/convolution/_conv/halo.py:66-251,
+// jigsaw/modules/convolution/_conv/distributed.py:212-396).
+
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace jb {
+
+constexpr int CV_TW = 128;                        // output pixels per tile
+constexpr int CV_BOXW = 130;                      // input pixels per slot (tile + 2)
+constexpr int CV_SLOT_BYTES = 136 * 128;          // 17 KiB, keeps slots 1024-byte aligned
+constexpr int CV_SLOTS = 8;
+constexpr int CV_CHUNK = 6;                       // output rows per window refill
+constexpr int CV_THREADS = 320;                   // producer, MMA, 8 epilogue warps
+constexpr int CV_EPI_WARPS = 8;
+
+struct HaloPush {
+  // Index (sy + 1) * 3 + (sx + 1); entry 4 (self) unused.  Null = no neighbour there.
+  void* buf[9];         // base of that neighbour's padded buffer (same shape as ours)
+  uint32_t* flag[9];    // flag word on that neighbour to set once all our stores are out
+  uint32_t epoch;       // value to publish
+  uint32_t enabled;     // 0: no neighbour at all (single rank)
+};
+
+struct HaloWait {
+  const uint32_t* flag[9];  // local flag words to wait for (null = none)
+  uint32_t epoch;
+  uint32_t enabled;
+};
+
+struct ConvArgs {
+  int NB, H, W;            // local tile
+  int tiles_w;             // ceil(W / 128)
+  int rows_per_strip;
+  int nstrips;
+  int cout_real;           // channels actually stored by the dense outputs
+  // epilogue
+  const float* bias;               // [N] fp32 or null
+  const __nv_bfloat16* gelu_src;   // dense [NB][H][W][64]: multiply result by GELU'(src) (data gradient)
+  __nv_bfloat16* dense_pre;        // dense [NB][H][W][64]: value before the activation (saved for backward)
+  int act;                         // 1: GELU after bias
+  __nv_bfloat16* padded_out;       // padded [NB][H+2][W+2][64] output (interior) + halo push
+  __nv_bfloat16* dense_out;        // dense [NB][H][W][cout_real] output
+  HaloPush push;
+  HaloWait wait;
+  unsigned int* done_counter;      // local scratch word, zero before the first launch
+  int* status;
+};
+
+__device__ __forceinline__ void halo_wait_all(const HaloWait& w, volatile int* abort_flag, int* status) {
+  if (!w.enabled) return;
+  const uint64_t t0 = globaltimer_ns();
+  for (int d = 0; d < 9; ++d) {
+    const uint32_t* f = w.flag[d];
+    if (f == nullptr) continue;
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (static_cast<int32_t>(v - w.epoch) >= 0) break;
+      if (*abort_flag) return;
+      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+        return;
+      }
+      __nanosleep(100);
+    }
+  }
+  // Peer data arrived through the generic proxy; the TMA engine reads through the async proxy.
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Called by every thread after the role loops.  The last CTA of the grid publishes the epoch.
+__device__ __forceinline__ void halo_publish(const HaloPush& p, unsigned int* done_counter) {
+  if (!p.enabled) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0u;
+      __threadfence_system();
+      for (int d = 0; d < 9; ++d) {
+        if (p.flag[d] != nullptr) {
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[d]), "r"(p.epoch) : "memory");
+        }
+      }
+    }
+  }
+}
+
+// Store 32 (or fewer) consecutive channels of one pixel into the interior of the local padded
+// buffer and, for pixels on the tile edge, into the matching border of the neighbours.
+template <int NV>  // NV = number of uint4 (8 channels each)
+__device__ __forceinline__ void store_padded_with_halo(const ConvArgs& a, const uint4 (&v)[NV], int n, int h, int w,
+                                                       int c0) {
+  const long long prow = static_cast<long long>(a.W + 2) * 64;
+  const long long pimg = static_cast<long long>(a.H + 2) * prow;
+  {
+    __nv_bfloat16* dst = a.padded_out + n * pimg + (h + 1) * prow + static_cast<long long>(w + 1) * 64 + c0;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) reinterpret_cast<uint4*>(dst)[j] = v[j];
+  }
+  if (!a.push.enabled) return;
+  const bool top = (h == 0), bot = (h == a.H - 1), lef = (w == 0), rig = (w == a.W - 1);
+  if (!(top || bot || lef || rig)) return;
+#pragma unroll
+  for (int sy = -1; sy <= 1; ++sy) {
+#pragma unroll
+    for (int sx = -1; sx <= 1; ++sx) {
+      if (sy == 0 && sx == 0) continue;
+      const int d = (sy + 1) * 3 + (sx + 1);
+      if (a.push.buf[d] == nullptr) continue;
+      const bool hit_y = (sy == -1) ? top : (sy == 1 ? bot : true);
+      const bool hit_x = (sx == -1) ? lef : (sx == 1 ? rig : true);
+      if (!(hit_y && hit_x)) continue;
+      // Our top row is the neighbour-above's bottom border, and so on.
+      const int dr = (sy == -1) ? (a.H + 1) : (sy == 1 ? 0 : h + 1);
+      const int dc = (sx == -1) ? (a.W + 1) : (sx == 1 ? 0 : w + 1);
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.push.buf[d]) + n * pimg + dr * prow +
+                           static_cast<long long>(dc) * 64 + c0;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) reinterpret_cast<uint4*>(dst)[j] = v[j];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward (B_MN = 0, weights [9][NOUT][64] = tap, cout, cin) and data gradient
+// (B_MN = 1, same weight tensor read as tap, K = cout, N = cin, taps mirrored).
+// ------------------------------------------------------------------------------------------
+template <int NOUT, int B_MN>
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
+                  const ConvArgs a) {
+  constexpr int WTAP_BYTES = (B_MN ? 64 : NOUT) * 128;
+  constexpr int W_BYTES = 9 * WTAP_BYTES;
+  constexpr uint32_t TMEM_COLS = (2 * NOUT <= 32) ? 32 : (2 * NOUT <= 64 ? 64 : (2 * NOUT <= 128 ? 128 : 256));
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* w_smem = smem;
+  uint8_t* slots = smem + ((W_BYTES + 1023) & ~1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + CV_SLOTS * CV_SLOT_BYTES);
+  uint64_t* full = bars;                  // [8]
+  uint64_t* empty = bars + 8;             // [8]
+  uint64_t* acc_full = bars + 16;         // [2]
+  uint64_t* acc_empty = bars + 18;        // [2]
+  uint64_t* wbar = bars + 20;             // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int items = a.NB * a.tiles_w * a.nstrips;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], CV_EPI_WARPS);
+    }
+    mbar_init(wbar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmIn);
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(wbar, W_BYTES);
+      for (int t = 0; t < 9; ++t) tma_load_2d(w_smem + t * WTAP_BYTES, &tmW, wbar, 0, t * (B_MN ? 64 : NOUT));
+      halo_wait_all(a.wait, abort_flag, a.status);
+      uint32_t eph = 0;  // per-slot phase bits of the empty barriers
+      bool ok = true;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int tw = (item / a.nstrips) % a.tiles_w;
+        const int n = item / (a.nstrips * a.tiles_w);
+        const int h0 = s * a.rows_per_strip;
+        const int h1 = min(a.H, h0 + a.rows_per_strip);
+        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+          const int nslots = min(CV_CHUNK, h1 - hc) + 2;
+          for (int j = 0; j < nslots; ++j) {
+            ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
+            if (!ok) break;
+            eph ^= (1u << j);
+            mbar_expect_tx(&full[j], CV_BOXW * 128);
+            tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, NOUT, 0, B_MN);
+      bool ok = mbar_wait(wbar, 0, abort_flag, a.status);
+      uint32_t fph = 0;  // per-slot phase bits of the full barriers
+      int it = 0;
+      const uint32_t w_addr = smem_u32(w_smem);
+      const uint32_t s_addr = smem_u32(slots);
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int h0 = s * a.rows_per_strip;
+        const int h1 = min(a.H, h0 + a.rows_per_strip);
+        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+          const int n_out = min(CV_CHUNK, h1 - hc);
+          for (int i = 0; i < n_out; ++i, ++it) {
+            const int as = it & 1;
+            const uint32_t aph = (it >> 1) & 1u;
+            ok = mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status);
+            if (!ok) break;
+            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
+              ok = mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
+              if (!ok) break;
+              fph ^= (1u << j);
+            }
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * NOUT);
+#pragma unroll
+            for (int dy = 0; dy < 3; ++dy) {
+#pragma unroll
+              for (int dx = 0; dx < 3; ++dx) {
+                const int wt = B_MN ? ((2 - dy) * 3 + (2 - dx)) : (dy * 3 + dx);
+                const uint32_t a_tap = s_addr + (i + dy) * CV_SLOT_BYTES + dx * 128;
+                const uint32_t b_tap = w_addr + wt * WTAP_BYTES;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint64_t ad = make_smem_desc_sw128(a_tap + k * 32, 16, 1024);
+                  const uint64_t bd = B_MN ? make_smem_desc_sw128(b_tap + k * 2048, 8192, 1024)
+                                           : make_smem_desc_sw128(b_tap + k * 32, 16, 1024);
+                  umma_f16(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
+                }
+              }
+            }
+            umma_commit(&acc_full[as]);
+            umma_commit(&empty[i]);
+            if (i == n_out - 1) {
+              umma_commit(&empty[i + 1]);
+              umma_commit(&empty[i + 2]);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (8 warps)
+    const int e = warp - 2;
+    const int quad = warp & 3;
+    const int half = e >> 2;
+    constexpr int CPW = (NOUT >= 64) ? 32 : NOUT;   // columns handled per warp
+    const bool active = (NOUT >= 64) || (half == 0);
+    const int c0 = half * 32;
+    int it = 0;
+    bool ok = true;
+    const long long drow = static_cast<long long>(a.W);
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const int s = item % a.nstrips;
+      const int tw = (item / a.nstrips) % a.tiles_w;
+      const int n = item / (a.nstrips * a.tiles_w);
+      const int h0 = s * a.rows_per_strip;
+      const int h1 = min(a.H, h0 + a.rows_per_strip);
+      for (int h = h0; h < h1; ++h, ++it) {
+        const int as = it & 1;
+        const uint32_t aph = (it >> 1) & 1u;
+        ok = mbar_wait(&acc_full[as], aph, abort_flag, a.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t r[CPW];
+        if (active) {
+          const uint32_t taddr =
+              tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(as * NOUT + c0);
+          if constexpr (CPW == 32) {
+            tmem_ld_32x32(taddr, r);
+          } else {
+            tmem_ld_32x16(taddr, r);
+          }
+          tmem_ld_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[as]);
+        const int w = tw * CV_TW + quad * 32 + lane;
+        if (!active || w >= a.W) continue;
+        const long long pix = (static_cast<long long>(n) * a.H + h) * drow + w;
+        float v[CPW];
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+          v[j] = __uint_as_float(r[j]);
+          if (a.bias != nullptr) v[j] += __ldg(a.bias + c0 + j);
+        }
+        if (a.gelu_src != nullptr) {
+          const uint4* src = reinterpret_cast<const uint4*>(a.gelu_src + pix * 64 + c0);
+#pragma unroll
+          for (int q = 0; q < CPW / 8; ++q) {
+            const uint4 u = __ldg(src + q);
+            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
+              v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
+              v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
+            }
+          }
+        }
+        if (a.dense_pre != nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
+#pragma unroll
+          for (int q = 0; q < CPW / 8; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            dst[q] = o;
+          }
+        }
+        if (a.act == 1) {
+#pragma unroll
+          for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (a.padded_out != nullptr) {
+          uint4 o[CPW / 8];
+#pragma unroll
+          for (int q = 0; q < CPW / 8; ++q) {
+            o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          }
+          store_padded_with_halo<CPW / 8>(a, o, n, h, w, c0);
+        }
+        if (a.dense_out != nullptr) {
+          __nv_bfloat16* dst = a.dense_out + pix * a.cout_real + c0;
+          if ((a.cout_real & 7) == 0 && c0 + CPW <= a.cout_real) {
+#pragma unroll
+            for (int q = 0; q < CPW / 8; ++q) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              reinterpret_cast<uint4*>(dst)[q] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CPW; ++j)
+              if (c0 + j < a.cout_real) dst[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  halo_publish(a.push, a.done_counter);
+}
+
+// ------------------------------------------------------------------------------------------
+// Weight gradient:  gW[tap][ci][co] = sum over pixels of  x[p + tap][ci] * gy[p][co]
+// M = 128 = two taps x 64 ci (two shifted views of the input window, MN-major),
+// N = 64 co (the gy tile, MN-major), K = pixels.  Nine taps make four full pairs plus one
+// tap paired with a tile of ones, whose 64 result rows are sum_p gy[p][co]: the bias
+// gradient falls out of the same accumulation.  Accumulators stay in TMEM (5 x 64 columns)
+// for the life of the CTA; one partial per CTA is written at the end and a second small
+// kernel sums the partials in a fixed order (deterministic).
+// ------------------------------------------------------------------------------------------
+constexpr int WG_GSTAGES = 3;
+constexpr int WG_THREADS = 192;
+constexpr int WG_PARTIAL_FLOATS = 5 * 128 * 64;
+
+struct WgradArgs {
+  int NB, H, W, tiles_w, rows_per_strip, nstrips;
+  float* partials;   // [gridDim.x][5][128][64] fp32 scratch
+  HaloWait wait;     // the input window reads halo pixels
+  int* status;
+};
+
+__global__ void __launch_bounds__(WG_THREADS, 1)
+conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
+                     const WgradArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* slots = smem;
+  uint8_t* gtiles = slots + CV_SLOTS * CV_SLOT_BYTES;
+  uint8_t* ones = gtiles + WG_GSTAGES * 16384;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ones + 2048);
+  uint64_t* full = bars;              // [8]
+  uint64_t* empty = bars + 8;         // [8]
+  uint64_t* gfull = bars + 16;        // [3]
+  uint64_t* gempty = bars + 19;       // [3]
+  uint64_t* acc_full = bars + 22;     // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  constexpr uint32_t TMEM_COLS = 512;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int items = a.NB * a.tiles_w * a.nstrips;
+
+  // Tile of bf16 ones (16 rows x 128 bytes); invariant under the swizzle.
+  for (int i = threadIdx.x; i < 2048 / 4; i += WG_THREADS) reinterpret_cast<uint32_t*>(ones)[i] = 0x3F803F80u;
+  fence_proxy_async_smem();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < WG_GSTAGES; ++s) {
+      mbar_init(&gfull[s], 1);
+      mbar_init(&gempty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmG);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      halo_wait_all(a.wait, abort_flag, a.status);
+      uint32_t eph = 0;
+      int gs = 0;
+      uint32_t gph = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int tw = (item / a.nstrips) % a.tiles_w;
+        const int n = item / (a.nstrips * a.tiles_w);
+        const int h0 = s * a.rows_per_strip;
+        const int h1 = min(a.H, h0 + a.rows_per_strip);
+        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+          const int n_out = min(CV_CHUNK, h1 - hc);
+          for (int i = 0; i < n_out && ok; ++i) {
+            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
+              ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
+              if (!ok) break;
+              eph ^= (1u << j);
+              mbar_expect_tx(&full[j], CV_BOXW * 128);
+              tma_load_4d(slots + j * CV_SLOT_BYTES, &tmX, &full[j], 0, tw * CV_TW, hc + j, n);
+            }
+            if (!ok) break;
+            ok = mbar_wait(&gempty[gs], gph ^ 1u, abort_flag, a.status);
+            if (!ok) break;
+            mbar_expect_tx(&gfull[gs], 16384);
+            // gy lives in a padded buffer too: interior pixel (h, w) is at (h + 1, w + 1).
+            tma_load_4d(gtiles + gs * 16384, &tmG, &gfull[gs], 0, tw * CV_TW + 1, hc + i + 1, n);
+            if (++gs == WG_GSTAGES) {
+              gs = 0;
+              gph ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
+      uint32_t fph = 0;
+      int gs = 0;
+      uint32_t gph = 0;
+      bool ok = true;
+      bool first = true;
+      const uint32_t s_addr = smem_u32(slots);
+      const uint32_t g_addr = smem_u32(gtiles);
+      const uint32_t ones_addr = smem_u32(ones);
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int h0 = s * a.rows_per_strip;
+        const int h1 = min(a.H, h0 + a.rows_per_strip);
+        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+          const int n_out = min(CV_CHUNK, h1 - hc);
+          for (int i = 0; i < n_out; ++i) {
+            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
+              ok = mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
+              if (!ok) break;
+              fph ^= (1u << j);
+            }
+            if (!ok) break;
+            ok = mbar_wait(&gfull[gs], gph, abort_flag, a.status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t g_tile = g_addr + gs * 16384;
+            const uint32_t r0 = s_addr + (i + 0) * CV_SLOT_BYTES;
+            const uint32_t r1 = s_addr + (i + 1) * CV_SLOT_BYTES;
+            const uint32_t r2 = s_addr + (i + 2) * CV_SLOT_BYTES;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t acc = (first && k == 0) ? 0u : 1u;
+              const uint32_t ko = k * 2048;  // 16 pixels x 128 bytes
+              const uint64_t bd = make_smem_desc_sw128(g_tile + ko, 8192, 1024);
+              // taps (dy,0) + (dy,1): second 64 rows of M are the view one pixel to the right.
+              umma_f16(tmem_base + 0, make_smem_desc_sw128(r0 + ko, 128, 1024), bd, idesc, acc);
+              umma_f16(tmem_base + 64, make_smem_desc_sw128(r1 + ko, 128, 1024), bd, idesc, acc);
+              umma_f16(tmem_base + 128, make_smem_desc_sw128(r2 + ko, 128, 1024), bd, idesc, acc);
+              // taps (0,2) + (1,2): second half is the same view one slot further.
+              umma_f16(tmem_base + 192, make_smem_desc_sw128(r0 + 256 + ko, CV_SLOT_BYTES, 1024), bd, idesc, acc);
+              // tap (2,2) + ones (bias gradient).
+              const uint32_t v22 = r2 + 256 + ko;
+              umma_f16(tmem_base + 256, make_smem_desc_sw128(v22, ones_addr - v22, 1024), bd, idesc, acc);
+            }
+            first = false;
+            umma_commit(&gempty[gs]);
+            if (++gs == WG_GSTAGES) {
+              gs = 0;
+              gph ^= 1u;
+            }
+            umma_commit(&empty[i]);
+            if (i == n_out - 1) {
+              umma_commit(&empty[i + 1]);
+              umma_commit(&empty[i + 2]);
+            }
+          }
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // epilogue: one pass at the end
+    const int quad = warp & 3;
+    if (mbar_wait(acc_full, 0, abort_flag, a.status)) {
+      tc_fence_after_sync();
+      const bool any = blockIdx.x < items;
+      float* dst = a.partials + static_cast<long long>(blockIdx.x) * WG_PARTIAL_FLOATS;
+      const int m = quad * 32 + lane;
+      for (int chain = 0; chain < 5; ++chain) {
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t r[32];
+          const uint32_t taddr =
+              tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chain * 64 + c0);
+          tmem_ld_32x32(taddr, r);
+          tmem_ld_wait();
+          float4* o = reinterpret_cast<float4*>(dst + (chain * 128 + m) * 64 + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            o[j] = any ? make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Sum the per-CTA partials in CTA order and emit the torch layouts:
+//   gw[co][ci][ty][tx] (fp32) and gb[co] (fp32).
+__global__ void conv3x3_wgrad_reduce_kernel(const float* __restrict__ partials, int nparts, float* __restrict__ gw,
+                                            float* __restrict__ gb) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;  // over 9*64*64 + 64
+  if (idx < 9 * 64 * 64) {
+    const int co = idx & 63;
+    const int ci = (idx >> 6) & 63;
+    const int tap = idx >> 12;
+    const int dy = tap / 3, dx = tap % 3;
+    int chain, halfm;
+    if (dx < 2) {
+      chain = dy;
+      halfm = dx;
+    } else if (dy < 2) {
+      chain = 3;
+      halfm = dy;
+    } else {
+      chain = 4;
+      halfm = 0;
+    }
+    const long long off = (static_cast<long long>(chain) * 128 + halfm * 64 + ci) * 64 + co;
+    float s = 0.f;
+    for (int p = 0; p < nparts; ++p) s += partials[static_cast<long long>(p) * WG_PARTIAL_FLOATS + off];
+    gw[((co * 64 + ci) * 3 + dy) * 3 + dx] = s;
+  } else if (idx < 9 * 64 * 64 + 64) {
+    const int co = idx - 9 * 64 * 64;
+    const long long off = (static_cast<long long>(4) * 128 + 64) * 64 + co;
+    float s = 0.f;
+    for (int p = 0; p < nparts; ++p) s += partials[static_cast<long long>(p) * WG_PARTIAL_FLOATS + off];
+    if (gb != nullptr) gb[co] = s;
+  }
+}
+
+static int padded_tmap(CUtensorMap* tm, const void* base, int NB, int H, int W, int boxw, int shrink_w) {
+  // dims (C, W + 2 - shrink_w, H + 2, NB); strides of the full padded buffer.
+  uint64_t dims[4] = {64, static_cast<uint64_t>(W + 2 - shrink_w), static_cast<uint64_t>(H + 2),
+                      static_cast<uint64_t>(NB)};
+  uint64_t strides[3] = {128, static_cast<uint64_t>(W + 2) * 128, static_cast<uint64_t>(H + 2) * (W + 2) * 128};
+  uint32_t box[4] = {64, static_cast<uint32_t>(boxw), 1, 1};
+  return make_tmap_bf16(tm, base, 4, dims, strides, box);
+}
+
+static void choose_strips(int H, int NB, int tiles_w, int sm_count, int* rows_per_strip, int* nstrips) {
+  // Strips of a multiple of CV_CHUNK rows; aim for >= 8 work items per CTA when the tile allows it.
+  int rps = 48;
+  while (rps > CV_CHUNK && static_cast<long long>(NB) * tiles_w * ((H + rps - 1) / rps) < 8LL * sm_count) rps -= CV_CHUNK;
+  if (rps > H) rps = ((H + CV_CHUNK - 1) / CV_CHUNK) * CV_CHUNK;
+  *rows_per_strip = rps;
+  *nstrips = (H + rps - 1) / rps;
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+struct JbHalo {          // C mirror passed from Python (ctypes)
+  void* push_buf[9];
+  void* push_flag[9];
+  void* wait_flag[9];
+  unsigned int push_epoch;
+  unsigned int wait_epoch;
+  unsigned int push_enabled;
+  unsigned int wait_enabled;
+};
+
+// Forward / data-gradient launcher.
+//  in_padded : [NB][H+2][W+2][64] bf16 (halo filled)        weights : [9][nout_pad][64] bf16
+//  mode 0 = forward (weights tap,cout,cin; nout_pad in {16, 64}); mode 1 = data gradient (nout_pad = 64).
+extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const float* bias, const void* gelu_src,
+                              void* dense_pre, void* padded_out, void* dense_out, int NB, int H, int W,
+                              int nout_pad, int cout_real, int act, int mode, const JbHalo* halo,
+                              unsigned int* done_counter, int* status, int sm_count, void* stream) {
+  if (nout_pad != 64 && nout_pad != 16) return -1;
+  if (mode == 1 && nout_pad != 64) return -1;
+  CUtensorMap tmIn, tmW;
+  if (padded_tmap(&tmIn, in_padded, NB, H, W, CV_BOXW, 0) != 0) return -2;
+  {
+    uint64_t dims[2] = {64, static_cast<uint64_t>(9 * nout_pad)};
+    uint64_t strides[1] = {128};
+    uint32_t box[2] = {64, static_cast<uint32_t>(mode == 1 ? 64 : nout_pad)};
+    if (make_tmap_bf16(&tmW, weights, 2, dims, strides, box) != 0) return -2;
+  }
+  ConvArgs a{};
+  a.NB = NB; a.H = H; a.W = W;
+  a.tiles_w = (W + CV_TW - 1) / CV_TW;
+  choose_strips(H, NB, a.tiles_w, sm_count, &a.rows_per_strip, &a.nstrips);
+  a.cout_real = cout_real;
+  a.bias = bias;
+  a.gelu_src = static_cast<const __nv_bfloat16*>(gelu_src);
+  a.dense_pre = static_cast<__nv_bfloat16*>(dense_pre);
+  a.act = act;
+  a.padded_out = static_cast<__nv_bfloat16*>(padded_out);
+  a.dense_out = static_cast<__nv_bfloat16*>(dense_out);
+  a.done_counter = done_counter;
+  a.status = status;
+  if (halo != nullptr) {
+    for (int d = 0; d < 9; ++d) {
+      a.push.buf[d] = halo->push_buf[d];
+      a.push.flag[d] = static_cast<uint32_t*>(halo->push_flag[d]);
+      a.wait.flag[d] = static_cast<const uint32_t*>(halo->wait_flag[d]);
+    }
+    a.push.epoch = halo->push_epoch;
+    a.push.enabled = halo->push_enabled;
+    a.wait.epoch = halo->wait_epoch;
+    a.wait.enabled = halo->wait_enabled;
+  }
+  const int items = NB * a.tiles_w * a.nstrips;
+  const int grid = items < sm_count ? items : sm_count;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  constexpr int SMEM64 = 9 * 8192 + CV_SLOTS * CV_SLOT_BYTES + 256 + 1024;
+  constexpr int SMEM16 = ((9 * 2048 + 1023) & ~1023) + CV_SLOTS * CV_SLOT_BYTES + 256 + 1024;
+  cudaError_t e;
+  if (mode == 1) {
+    auto k = conv3x3_tc_kernel<64, 1>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM64);
+    if (e != cudaSuccess) return -3;
+    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, a);
+  } else if (nout_pad == 64) {
+    auto k = conv3x3_tc_kernel<64, 0>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM64);
+    if (e != cudaSuccess) return -3;
+    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, a);
+  } else {
+    auto k = conv3x3_tc_kernel<16, 0>;
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM16);
+    if (e != cudaSuccess) return -3;
+    k<<<grid, CV_THREADS, SMEM16, st>>>(tmIn, tmW, a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Number of fp32 scratch elements jb_conv3x3_c64_wgrad needs for a given SM count.
+extern "C" long long jb_conv3x3_wgrad_scratch_floats(int sm_count) {
+  return static_cast<long long>(sm_count) * WG_PARTIAL_FLOATS;
+}
+
+// Weight (and bias) gradient.  x_padded: [NB][H+2][W+2][64] input of the layer (halo filled),
+// gy_padded: [NB][H+2][W+2][64] gradient of the layer output (interior used), gw: [64][64][3][3] fp32,
+// gb: [64] fp32 or null, scratch: jb_conv3x3_wgrad_scratch_floats(sm_count) floats.
+extern "C" int jb_conv3x3_c64_wgrad(const void* x_padded, const void* gy_padded, float* gw, float* gb,
+                                    float* scratch, int NB, int H, int W, const JbHalo* halo, int* status,
+                                    int sm_count, void* stream) {
+  CUtensorMap tmX, tmG;
+  if (padded_tmap(&tmX, x_padded, NB, H, W, CV_BOXW, 0) != 0) return -2;
+  // Hide the right border column of gy so that pixels beyond W read as zero.
+  if (padded_tmap(&tmG, gy_padded, NB, H, W, CV_TW, 1) != 0) return -2;
+  WgradArgs a{};
+  a.NB = NB; a.H = H; a.W = W;
+  a.tiles_w = (W + CV_TW - 1) / CV_TW;
+  choose_strips(H, NB, a.tiles_w, sm_count, &a.rows_per_strip, &a.nstrips);
+  a.partials = scratch;
+  a.status = status;
+  if (halo != nullptr) {
+    for (int d = 0; d < 9; ++d) a.wait.flag[d] = static_cast<const uint32_t*>(halo->wait_flag[d]);
+    a.wait.epoch = halo->wait_epoch;
+    a.wait.enabled = halo->wait_enabled;
+  }
+  const int items = NB * a.tiles_w * a.nstrips;
+  const int grid = items < sm_count ? items : sm_count;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  constexpr int SMEM = CV_SLOTS * CV_SLOT_BYTES + WG_GSTAGES * 16384 + 2048 + 256 + 1024;
+  if (cudaFuncSetAttribute(conv3x3_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+    return -3;
+  conv3x3_wgrad_kernel<<<grid, WG_THREADS, SMEM, st>>>(tmX, tmG, a);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  const int n = 9 * 64 * 64 + 64;
+  conv3x3_wgrad_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(scratch, grid, gw, gb);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

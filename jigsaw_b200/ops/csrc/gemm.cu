@@ -1,0 +1,314 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+//   C[M,N] = act(A * B + bias)        A, B bf16; accumulation fp32 in TMEM
+//
+// Both operands may be stored K-major (reduction index contiguous) or MN-major
+// (output index contiguous), so the three products a linear layer needs
+//   Y  = X  * W^T   (A K-major,  B K-major)
+//   dX = dY * W     (A K-major,  B MN-major)
+//   dW = dY^T * X   (A MN-major, B MN-major)
+// run from the stored tensors without a transpose pass.  A CTA is persistent over
+// 128 x BN output tiles; warp 0 issues TMA loads into a multi-stage shared-memory
+// ring, warp 1 issues tcgen05.mma into a double-buffered TMEM accumulator, warps
+// 2..5 drain finished accumulators (tcgen05.ld), apply bias / GELU and store.
+//
+// Capability parity: replaces the cuBLAS `torch.matmul` calls of the reference
+// (jigsaw/modules/linear/_distributed_matmul.py:100-110, 159-177).
+
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace jb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+
+struct GemmEpilogue {
+  void* c;            // output, row-major [M, ldc]
+  long long ldc;      // elements
+  const float* bias;  // [N] or nullptr
+  int act;            // 0 none, 1 GELU(erf)
+  int out_fp32;       // 0 -> bf16 output, 1 -> fp32 output
+  int accumulate;     // 1 -> C += result (fp32 output only)
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 GemmEpilogue ep, int M, int N, int K, int* status) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]
+  uint64_t* empty = bars + S::STAGES;       // [STAGES]
+  uint64_t* acc_full = bars + 2 * S::STAGES;      // [2]
+  uint64_t* acc_empty = bars + 2 * S::STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * GEMM_BM;
+        const int n0 = (t % tiles_n) * BN;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks && ok; ++kb) {
+          ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, status);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + S::A_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          const int k0 = kb * GEMM_BK;
+          if (A_MN == 0) {
+            tma_load_2d(a_dst, &tmA, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full[s], m0 + 64 * j, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(b_dst, &tmB, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full[s], n0 + 64 * j, k0);
+          }
+          if (++s == S::STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int as = it & 1;
+        const uint32_t aph = (it >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, status)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&full[s], ph, abort_flag, status);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // K-major: 16 K values = 32 bytes inside the swizzle row.
+            // MN-major: 16 K values = 16 rows of 128 bytes.
+            const uint64_t ad = A_MN ? make_smem_desc_sw128(a_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == S::STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int quad = warp & 3;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const int as = it & 1;
+      const uint32_t aph = (it >> 1) & 1u;
+      const int m0 = (t / tiles_n) * GEMM_BM;
+      const int n0 = (t % tiles_n) * BN;
+      if (!mbar_wait(&acc_full[as], aph, abort_flag, status)) break;
+      tc_fence_after_sync();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(as * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        if (row < M) {
+          const int col0 = n0 + c0;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]);
+            if (ep.bias != nullptr && col0 + j < N) x += __ldg(ep.bias + col0 + j);
+            if (ep.act == 1) x = gelu_erf(x);
+            v[j] = x;
+          }
+          if (ep.out_fp32) {
+            float* dst = reinterpret_cast<float*>(ep.c) + static_cast<long long>(row) * ep.ldc + col0;
+            if (col0 + 32 <= N && (ep.ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (ep.accumulate) {
+                  const float4 old = *reinterpret_cast<float4*>(dst + j);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = ep.accumulate ? dst[j] + v[j] : v[j];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.c) + static_cast<long long>(row) * ep.ldc + col0;
+            if (col0 + 32 <= N && (ep.ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int M, int N, int K, long long lda,
+                       long long ldb, int sm_count, int* status, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  CUtensorMap tmA, tmB;
+  {
+    // K-major: memory [rows = M][K contiguous]; MN-major: memory [rows = K][M contiguous].
+    uint64_t dims[2], strides[1];
+    uint32_t box[2];
+    if (A_MN == 0) {
+      dims[0] = K; dims[1] = M; box[0] = 64; box[1] = GEMM_BM;
+    } else {
+      dims[0] = M; dims[1] = K; box[0] = 64; box[1] = GEMM_BK;
+    }
+    strides[0] = static_cast<uint64_t>(lda) * 2;
+    if (make_tmap_bf16(&tmA, A, 2, dims, strides, box) != 0) return -2;
+    if (B_MN == 0) {
+      dims[0] = K; dims[1] = N; box[0] = 64; box[1] = BN;
+    } else {
+      dims[0] = N; dims[1] = K; box[0] = 64; box[1] = GEMM_BK;
+    }
+    strides[0] = static_cast<uint64_t>(ldb) * 2;
+    if (make_tmap_bf16(&tmB, B, 2, dims, strides, box) != 0) return -2;
+  }
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) return -3;
+    attr_set = true;
+  }
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, ep, M, N, K, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace jb
+
+// C ABI.  a_mn / b_mn select the stored layout of each operand:
+//   a_mn = 0: A is [M, K] row-major (lda = row stride);  a_mn = 1: A is [K, M] row-major.
+//   b_mn = 0: B is [N, K] row-major (ldb = row stride);  b_mn = 1: B is [K, N] row-major.
+// Leading dimensions must be multiples of 8 elements and base pointers 16-byte aligned.
+// Returns 0 on success, a negative code if the launch could not be set up.
+extern "C" int jb_gemm_bf16(const void* A, const void* B, void* C, const float* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int act,
+                            int out_fp32, int accumulate, int sm_count, int* status, void* stream) {
+  using namespace jb;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -1;
+  GemmEpilogue ep{C, ldc, bias, act, out_fp32, accumulate};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  // Tile width: wide tiles when N is large, narrower ones to fill the SMs otherwise.
+  const int tiles128 = ((M + 127) / 128) * ((N + 127) / 128);
+  const bool wide = (N >= 256) && (((M + 127) / 128) * ((N + 255) / 256) >= sm_count);
+  const bool narrow = (N <= 64) || (tiles128 < sm_count / 2 && N % 64 == 0);
+#define JB_GEMM_DISPATCH(BN)                                                                                   \
+  switch (key) {                                                                                                \
+    case 0: return launch_gemm<BN, 0, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                    \
+    case 1: return launch_gemm<BN, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                    \
+    case 2: return launch_gemm<BN, 1, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                    \
+    default: return launch_gemm<BN, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                   \
+  }
+  if (wide) {
+    JB_GEMM_DISPATCH(256)
+  } else if (narrow) {
+    JB_GEMM_DISPATCH(64)
+  } else {
+    JB_GEMM_DISPATCH(128)
+  }
+#undef JB_GEMM_DISPATCH
+}

@@ -1,0 +1,7 @@
+// Single translation unit of the sm_100a kernel library (C ABI, loaded with ctypes).
+// Build:  nvcc -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 \
+//              -shared -Xcompiler -fPIC -o libjb_kernels.so jb_kernels.cu
+#include "gemm.cu"
+#include "conv3x3.cu"
+
+extern "C" int jb_abi_version() { return 1; }
