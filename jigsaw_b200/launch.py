@@ -1,0 +1,118 @@
+"""Process launch and runtime set-up: launcher detection, device selection, seeds, TF32.
+
+Launcher precedence: SLURM (``SLURM_PROCID`` / ``SLURM_NTASKS`` / ``SLURM_LOCALID``),
+then torchrun (``RANK`` / ``WORLD_SIZE`` / ``LOCAL_RANK``), then a single process.
+
+Reference parity: jigsaw/launch.py:21-31 (seeds), :34-114 (launch env), :117-164
+(init_cuda), :167-177 (TF32 switch).
+"""
+
+from __future__ import annotations
+
+import os
+import subprocess
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import log
+
+__all__ = ["LaunchEnv", "init_cuda", "init_cpu", "resolve_launch_env", "set_all_seeds", "setup_precision"]
+
+
+def set_all_seeds(seed: int = 0) -> None:
+    """Seed the CPU and every CUDA generator of PyTorch."""
+    os.environ["PL_GLOBAL_SEED"] = str(seed)
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed)
+
+
+@dataclass(frozen=True)
+class LaunchEnv:
+    """Resolved launch parameters of this process."""
+
+    rank: int
+    world_size: int
+    local_rank: int
+    master_addr: str
+    master_port: str
+    source: str  # "slurm" | "torchrun" | "single"
+
+
+def _first_slurm_host(nodelist: str) -> str:
+    out = subprocess.check_output(["scontrol", "show", "hostnames", nodelist])
+    return out.decode().splitlines()[0].strip()
+
+
+def resolve_launch_env(strict: bool = False) -> LaunchEnv:
+    """Read rank / world size / local rank from the environment.
+
+    ``MASTER_ADDR`` (first SLURM node via ``scontrol`` when unset, else ``localhost``)
+    and ``MASTER_PORT`` (default 29500) are written back to ``os.environ`` so that
+    ``init_method="env://"`` works.  With ``strict`` a missing launcher raises
+    ``RuntimeError`` instead of assuming one process.
+    """
+    env = os.environ
+    if env.get("SLURM_PROCID") is not None:
+        source = "slurm"
+        rank = int(env["SLURM_PROCID"])
+        world = int(env.get("SLURM_NTASKS") or 1)
+        local = int(env.get("SLURM_LOCALID") or 0)
+    elif env.get("RANK") is not None:
+        source = "torchrun"
+        rank = int(env["RANK"])
+        world = int(env.get("WORLD_SIZE") or 1)
+        local = int(env.get("LOCAL_RANK") or 0)
+    elif strict:
+        raise RuntimeError(
+            "No distributed launcher detected: expected SLURM_PROCID (srun) or RANK (torchrun) "
+            "in the environment. Launch with srun or torchrun, or pass strict=False for a "
+            "single-process run."
+        )
+    else:
+        source, rank, world, local = "single", 0, 1, 0
+
+    addr = env.get("MASTER_ADDR", "")
+    if not addr:
+        nodelist = env.get("SLURM_JOB_NODELIST", "")
+        addr = _first_slurm_host(nodelist) if nodelist else "localhost"
+    port = env.get("MASTER_PORT", "29500")
+    env["MASTER_ADDR"] = addr
+    env["MASTER_PORT"] = port
+    return LaunchEnv(rank, world, local, addr, port, source)
+
+
+def init_cuda() -> tuple[torch.device, int, int, int]:
+    """Pick the local GPU, start the NCCL process group, return ``(device, local_rank, rank, world_size)``."""
+    e = resolve_launch_env()
+    log.configure_logging()
+    log.info_all("launch: rank %d/%d, local_rank %d, via %s", e.rank, e.world_size, e.local_rank, e.source)
+    index = e.local_rank if torch.cuda.device_count() != 1 else 0
+    device = torch.device("cuda", index)
+    torch.cuda.set_device(index)
+    dist.init_process_group(
+        backend="nccl", rank=e.rank, world_size=e.world_size, init_method="env://", device_id=device
+    )
+    log.info(
+        "process group up: torch rank %d, world size %d, backend %s",
+        dist.get_rank(),
+        dist.get_world_size(),
+        dist.get_backend(),
+    )
+    return device, e.local_rank, e.rank, e.world_size
+
+
+def init_cpu() -> tuple[torch.device, int, int, int]:
+    """Gloo counterpart of :func:`init_cuda` for CPU runs (tests, laptops)."""
+    e = resolve_launch_env()
+    log.configure_logging()
+    dist.init_process_group(backend="gloo", rank=e.rank, world_size=e.world_size, init_method="env://")
+    return torch.device("cpu"), e.local_rank, e.rank, e.world_size
+
+
+def setup_precision(tf32: bool) -> None:
+    """Allow or forbid TF32 in cuBLAS matmuls and cuDNN convolutions."""
+    torch.backends.cuda.matmul.allow_tf32 = bool(tf32)
+    torch.backends.cudnn.allow_tf32 = bool(tf32)

@@ -1,0 +1,289 @@
+"""``DistributedLinear`` and the ``(Distributed)MatMul{XWT,XW,XTW}`` modules.
+
+``DistributedLinear``: ``x`` holds tokens over ``row_group`` and features over
+``col_group``; the weight ``(out, in)`` is split into ``(out / Rw, in / C)`` blocks with
+``Rw = |model_group| / |col_group|`` (``Rw = 1``, i.e. replicated over ``row_group`` and
+marked, when ``model_group is col_group`` as in attention projections); the bias holds
+``out / C`` entries, replicated over ``row_group``.  The output is again (row, col)-blocked
+so layers chain without gathers.
+
+Forward = all-gather(x over col) -> all-gather(W block rows) -> one local GEMM (+ bias);
+any R x C that divides the shapes is accepted (the reference implements 1x1, 1x2, 2x2 and
+4x2 only).  On CUDA the local GEMM runs on the tcgen05 kernel of ``jigsaw_b200.ops``.
+
+Reference parity: jigsaw/modules/linear/_linear.py:55-594 (DistributedLinear), :597-761
+(DistributedMatMul*), :776-836 (MatMul*); jigsaw/modules/linear/_functional.py:113-466.
+"""
+
+from __future__ import annotations
+
+import math
+import warnings
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ... import init, parallel
+from ..._core.autocast import cast_to_autocast_dtype
+from ..._core.collectives import all_gather_cat
+from ..._core.config import check_config
+from ..._core.placement import check_divisible, gather_dim
+from ..._core.shard_repr import shard_repr
+from ._config import LinearConfig, default_grid
+from ._functional import block_matmul
+
+
+def _local_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor:
+    if x.is_cuda:
+        from ...ops import linear_fused
+
+        out = linear_fused.maybe_fused_linear(x, w, b)
+        if out is not None:
+            return out
+    return torch.nn.functional.linear(x, w, b)
+
+
+class DistributedLinear(torch.nn.Module):
+    def __init__(
+        self,
+        in_dim: int,
+        out_dim: int,
+        device: torch.device | str,
+        model_group: dist.ProcessGroup,
+        row_group: dist.ProcessGroup,
+        col_group: dist.ProcessGroup,
+        bias: bool = True,
+        config: LinearConfig | None = None,
+        dtype: torch.dtype = torch.float32,
+        *,
+        local_rank: int | None = None,
+    ) -> None:
+        super().__init__()
+        if local_rank is not None:
+            warnings.warn("local_rank is deprecated and ignored", DeprecationWarning, stacklevel=2)
+        self.in_dim, self.out_dim = in_dim, out_dim
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self._bind_groups(model_group, row_group, col_group)
+        if config is not None:
+            check_config(config, {"model group size": model_group.size(), "linear_layer": True})
+        self.config = config or LinearConfig(model_group, linear_layer=True, device=self.device)
+        self.global_weight_shape = (out_dim, in_dim)
+        self.weight = torch.nn.Parameter(
+            torch.empty(out_dim // self.row_split, in_dim // self.col_split, device=self.device, dtype=dtype)
+        )
+        self.bias = (
+            torch.nn.Parameter(torch.empty(out_dim // self.col_split, device=self.device, dtype=dtype)) if bias else None
+        )
+        self.reset_parameters()
+        self._mark()
+
+    def _bind_groups(self, model_group: dist.ProcessGroup, row_group: dist.ProcessGroup, col_group: dist.ProcessGroup) -> None:
+        self.model_group, self.row_group, self.col_group = model_group, row_group, col_group
+        self._model_is_col = model_group is col_group
+        C = col_group.size()
+        if model_group.size() % C:
+            raise ValueError("model group size must be a multiple of the column group size")
+        self.col_split = C
+        self.row_split = model_group.size() // C       # weight row blocks
+        self.weight_replicated_over_rows = self.row_split == 1
+        if self.row_split > 1 and self.row_split != row_group.size():
+            raise NotImplementedError(
+                f"weight rows are split {self.row_split}-way but row_group has {row_group.size()} ranks; "
+                "model_group must span row_group x col_group or equal col_group"
+            )
+        check_divisible(self.in_dim, C, "in_dim")
+        check_divisible(self.out_dim, C, "out_dim")
+        check_divisible(self.out_dim, self.row_split, "out_dim")
+
+    def _mark(self) -> None:
+        """Bias is always replicated over ``row_group``; the weight too when its rows are not split."""
+        targets = []
+        if self.bias is not None:
+            targets.append(self.bias)
+        if self.weight_replicated_over_rows:
+            targets.append(self.weight)
+        for p in targets:
+            if not parallel.replica_groups(p):
+                parallel.mark_replicated(p, [self.row_group])
+        if self.row_group.size() > 1:
+            with torch.no_grad():
+                for p in targets:
+                    dist.broadcast(p.data, group_src=0, group=self.row_group)
+
+    def reset_parameters(self) -> None:
+        """Same distributions as ``torch.nn.Linear`` (fans from the global shape)."""
+        init.kaiming_uniform_(self.weight, a=math.sqrt(5), global_shape=self.global_weight_shape)
+        if self.bias is not None:
+            bound = 1.0 / math.sqrt(self.in_dim) if self.in_dim > 0 else 0.0
+            init.uniform_(self.bias, -bound, bound)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w, b = parallel.sync_grad(self.weight, self.bias)
+        x_full = all_gather_cat(x, self.col_group, -1)                     # (.., M/R, K)
+        w_rows = all_gather_cat(w, self.col_group, 1)                       # (N/Rw, K)
+        j = self.col_group.rank()
+        n = self.out_dim // self.col_split
+        if self.row_split > 1:
+            w_all = all_gather_cat(w_rows, self.row_group, 0)               # (N, K)
+            w_j = w_all.narrow(0, j * n, n)
+        else:
+            w_j = w_rows.narrow(0, j * n, n)
+        return _local_linear(x_full, w_j, b)
+
+    # ------------------------------------------------------------------ conversion
+    @classmethod
+    def convert_to_jigsaw(
+        cls, model: torch.nn.Linear, process_mesh_dict: dict, device: torch.device | str, row_kw: str = "row",
+        col_kw: str = "col", model_kw: str = "model", comm: str = "auto", **kwargs: Any,
+    ) -> "DistributedLinear":
+        mg = process_mesh_dict[model_kw]
+        layer = cls(
+            model.in_features, model.out_features, device, mg, process_mesh_dict[row_kw], process_mesh_dict[col_kw],
+            bias=model.bias is not None, dtype=model.weight.dtype,
+            config=LinearConfig(mg, linear_layer=True, device=device, comm=comm),
+        )
+        layer._load_global(model.weight.data, None if model.bias is None else model.bias.data)
+        return layer
+
+    def _load_global(self, weight: torch.Tensor, bias: torch.Tensor | None) -> None:
+        i = self.row_group.rank() if self.row_split > 1 else 0
+        j = self.col_group.rank()
+        rb, cb = self.out_dim // self.row_split, self.in_dim // self.col_split
+        with torch.no_grad():
+            self.weight.data = weight[i * rb : (i + 1) * rb, j * cb : (j + 1) * cb].clone().to(self.device).contiguous()
+            if bias is not None and self.bias is not None:
+                nb = self.out_dim // self.col_split
+                self.bias.data = bias[j * nb : (j + 1) * nb].clone().to(self.device)
+
+    def merge_weights(
+        self, from_process_mesh_dict: dict, row_kw: str = "row", col_kw: str = "col", model_kw: str = "model"
+    ) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """Global weight and bias from the shards (collective over the row and column groups)."""
+        col = from_process_mesh_dict[col_kw]
+        with torch.no_grad():
+            w = gather_dim(self.weight.detach(), col, 1)
+            if self.row_split > 1:
+                w = gather_dim(w, from_process_mesh_dict[row_kw], 0)
+            b = None if self.bias is None else gather_dim(self.bias.detach(), col, 0)
+        return w, b
+
+    def convert_to_torch(self, process_mesh_dict: dict, row_kw: str = "row", col_kw: str = "col", model_kw: str = "model") -> torch.nn.Linear:
+        w, b = self.merge_weights(process_mesh_dict, row_kw, col_kw, model_kw)
+        layer = torch.nn.Linear(self.in_dim, self.out_dim, bias=b is not None, device=self.device, dtype=w.dtype)
+        layer.weight.data = w
+        if b is not None:
+            layer.bias.data = b
+        return layer
+
+    def reshard_parameters(
+        self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, pm_row_key: str = "row", pm_col_key: str = "col",
+        pm_model_key: str = "model",
+    ) -> None:
+        w, b = self.merge_weights(from_process_mesh_dict, pm_row_key, pm_col_key, pm_model_key)
+        # a projection built with model_group = col_group keeps its weight unsplit over rows
+        new_model = to_process_mesh_dict[pm_col_key] if self._model_is_col else to_process_mesh_dict[pm_model_key]
+        self._bind_groups(new_model, to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key])
+        self.config = LinearConfig(new_model, linear_layer=True, device=self.device, comm=self.config.comm)
+        self.weight = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))
+        if self.bias is not None:
+            self.bias = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))
+        self._load_global(w, b)
+        self._mark()
+
+    def get_parameter_count(self) -> int:
+        return self.in_dim * self.out_dim + (self.out_dim if self.bias is not None else 0)
+
+    def extra_repr(self) -> str:
+        return (
+            f"in_features={self.in_dim}, out_features={self.out_dim}, bias={self.bias is not None}, "
+            + shard_repr(row=self.row_split, col=self.col_group)
+        )
+
+
+class _DistributedMatMul(torch.nn.Module):
+    _kind = "xwt"
+
+    def __init__(self, device: torch.device | str, model_group: dist.ProcessGroup, config: LinearConfig | None = None,
+                 *, local_rank: int | None = None) -> None:
+        super().__init__()
+        if local_rank is not None:
+            warnings.warn("local_rank is deprecated and ignored", DeprecationWarning, stacklevel=2)
+        self.device = torch.device(device)
+        self.model_group = model_group
+        self.grid = default_grid(model_group.size())
+        if config is not None:
+            check_config(config, {"model group size": model_group.size(), "linear_layer": False})
+        self.config = config or LinearConfig(model_group, linear_layer=False, device=self.device)
+
+    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return block_matmul(self._kind, x, w, self.model_group, *self.grid)
+
+    def get_parameter_count(self) -> int:
+        return 0
+
+    def extra_repr(self) -> str:
+        return shard_repr(row=self.grid[0], col=self.grid[1])
+
+
+class DistributedMatMulXWT(_DistributedMatMul):
+    """``Y = X W^T`` on 2-D block-distributed operands."""
+
+    _kind = "xwt"
+
+
+class DistributedMatMulXW(_DistributedMatMul):
+    """``Y = X W`` on 2-D block-distributed operands."""
+
+    _kind = "xw"
+
+
+class DistributedMatMulXTW(_DistributedMatMul):
+    """``Y = X^T W`` on 2-D block-distributed operands."""
+
+    _kind = "xtw"
+
+
+class _MatMul(torch.nn.Module):
+    def get_parameter_count(self) -> int:
+        return 0
+
+
+class MatMulXWT(_MatMul):
+    """Serial ``X W^T`` (convertible to :class:`DistributedMatMulXWT`)."""
+
+    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        x, w = cast_to_autocast_dtype(x, w)
+        return torch.matmul(x, w.transpose(-1, -2))
+
+
+class MatMulXW(_MatMul):
+    """Serial ``X W``."""
+
+    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        x, w = cast_to_autocast_dtype(x, w)
+        return torch.matmul(x, w)
+
+
+class MatMulXTW(_MatMul):
+    """Serial ``X^T W``."""
+
+    def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        x, w = cast_to_autocast_dtype(x, w)
+        return torch.matmul(x.transpose(-1, -2), w)
+
+
+def _convert_matmul(dist_cls: type) -> Any:
+    def convert(cls: type, model: torch.nn.Module, process_mesh_dict: dict, device: torch.device | str,
+                row_kw: str = "row", col_kw: str = "col", model_kw: str = "model", comm: str = "auto", **kw: Any) -> Any:
+        mg = process_mesh_dict[model_kw]
+        return dist_cls(device, mg, LinearConfig(mg, linear_layer=False, device=device, comm=comm))
+
+    return classmethod(convert)
+
+
+for _serial, _dist in ((MatMulXWT, DistributedMatMulXWT), (MatMulXW, DistributedMatMulXW), (MatMulXTW, DistributedMatMulXTW)):
+    _dist.convert_to_jigsaw = _convert_matmul(_dist)
+    _dist.convert_to_torch = (lambda s: (lambda self, *a, **k: s()))(_serial)

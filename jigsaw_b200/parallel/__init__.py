@@ -1,0 +1,28 @@
+"""Replica marks, gradient synchronisation, DDP composition and gradient clipping.
+
+Reference parity: jigsaw/parallel/__init__.py:24-37 (the twelve public names).
+"""
+
+from .._core.public import set_module
+from ._clip import clip_grad_norm_
+from ._ddp import check_ddp, wrap_ddp
+from ._joint import JointCommHookState, joint_comm_hook, register_joint_comm_hook
+from ._replicas import broadcast_replicas, mark_replicated, replica_groups
+from ._sync import sync_grad, synced_call, synced_parameters
+
+__all__ = [
+    "JointCommHookState",
+    "broadcast_replicas",
+    "check_ddp",
+    "clip_grad_norm_",
+    "joint_comm_hook",
+    "mark_replicated",
+    "register_joint_comm_hook",
+    "replica_groups",
+    "sync_grad",
+    "synced_call",
+    "synced_parameters",
+    "wrap_ddp",
+]
+
+set_module(globals(), __all__)

@@ -1,0 +1,132 @@
+"""In-graph gradient synchronisation of replicated parameters.
+
+``sync_grad(w, b)`` returns views whose backward sums the incoming gradients over the
+replica groups of each marked parameter: one flat all-reduce per (groups, dtype) bucket
+and group.  Under a DDP with the joint hook registered the sum is replaced by a scale
+(the hook reduces).  The returned tensors carry no mark, so nested or re-entered
+forwards never reduce twice.
+
+Setting ``JIGSAW_DISABLE_GRAD_SYNC=1`` turns the function into a pass-through: a mutation
+switch for tests that must *fail* when synchronisation is missing.
+
+Reference parity: jigsaw/parallel/_sync.py:13-16 (switch), :19-53 (_SyncGrad), :56-83
+(_ScaleGrad), :86-132 (sync_grad), :135-194 (synced_parameters / synced_call).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ._ddp import check_active_ddp
+from ._joint import JointCommHookState, active_joint_state, joint_state_of
+from ._replicas import Groups, replica_groups
+
+_SYNC_DISABLED = os.environ.get("JIGSAW_DISABLE_GRAD_SYNC", "") == "1"
+
+
+def _reduce_flat(flat: torch.Tensor, groups: Groups) -> None:
+    for g in groups:
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=g)
+
+
+class _SumGradOverGroups(torch.autograd.Function):
+    """Identity forward; backward = SUM all-reduce of all gradients, flattened together."""
+
+    @staticmethod
+    def forward(groups: Groups, *tensors: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: tuple) -> None:
+        ctx.groups = inputs[0]
+
+    @staticmethod
+    def backward(ctx: Any, *grads: torch.Tensor) -> tuple:
+        if len(grads) == 1:
+            flat = grads[0].contiguous().clone().view(-1)
+        else:
+            flat = torch.cat([g.reshape(-1) for g in grads])
+        _reduce_flat(flat, ctx.groups)
+        outs, offset = [], 0
+        for g in grads:
+            outs.append(flat[offset : offset + g.numel()].view_as(g))
+            offset += g.numel()
+        return (None, *outs)
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, groups: Groups, *tensors: Any) -> tuple:
+        # elementwise in the batch: reduce the stacked members in one go
+        return _SumGradOverGroups.apply(groups, *tensors), tuple(in_dims[1:])
+
+
+class _ScaleGrad(torch.autograd.Function):
+    """Identity forward; backward multiplies by ``factor`` (the joint hook does the sum)."""
+
+    @staticmethod
+    def forward(factor: float, *tensors: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: tuple) -> None:
+        ctx.factor = inputs[0]
+
+    @staticmethod
+    def backward(ctx: Any, *grads: torch.Tensor) -> tuple:
+        return (None, *(g * ctx.factor for g in grads))
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, factor: float, *tensors: Any) -> tuple:
+        return _ScaleGrad.apply(factor, *tensors), tuple(in_dims[1:])
+
+
+def sync_grad(*tensors: torch.Tensor | None) -> tuple[torch.Tensor | None, ...]:
+    """Route marked parameters through the in-graph gradient sum (or scale, see module doc).
+
+    Unmarked tensors, ``None``, tensors that do not require grad and everything under
+    ``torch.no_grad()`` pass through untouched.
+    """
+    check_active_ddp()
+    result = list(tensors)
+    if _SYNC_DISABLED or not torch.is_grad_enabled():
+        return tuple(result)
+    joint = active_joint_state()
+    buckets: dict[tuple[Groups, torch.dtype, JointCommHookState | None], list[int]] = {}
+    for i, t in enumerate(tensors):
+        if t is None or not t.requires_grad:
+            continue
+        groups = replica_groups(t)
+        if not groups:
+            continue
+        buckets.setdefault((groups, t.dtype, joint_state_of(t, joint)), []).append(i)
+    for (groups, _, state), idx in buckets.items():
+        members = [tensors[i] for i in idx]
+        if state is None:
+            routed = _SumGradOverGroups.apply(groups, *members)
+        else:
+            routed = _ScaleGrad.apply(state.factor(groups), *members)
+        for i, r in zip(idx, routed):
+            result[i] = r
+    return tuple(result)
+
+
+def synced_parameters(module: torch.nn.Module) -> dict[str, torch.Tensor]:
+    """``{name: synced tensor}`` for the marked parameters of ``module`` (empty when none,
+    or when grad mode is off), for ``torch.func.functional_call``."""
+    marked = {n: p for n, p in module.named_parameters() if replica_groups(p)}
+    if not marked:
+        return {}
+    routed = sync_grad(*marked.values())
+    return {n: r for (n, p), r in zip(marked.items(), routed) if r is not None and r is not p}
+
+
+def synced_call(module: torch.nn.Module, *args: Any, **kwargs: Any) -> Any:
+    """Call a foreign ``module`` (e.g. a plain ``nn.LayerNorm`` whose parameters were marked
+    by hand) with its marked parameters routed through :func:`sync_grad`."""
+    routed = synced_parameters(module)
+    if not routed:
+        return module(*args, **kwargs)
+    return torch.func.functional_call(module, routed, args, kwargs)
