@@ -57,6 +57,23 @@ def _declare(L: ctypes.CDLL) -> None:
         POINTER(JbHalo), c_void_p, c_int, c_void_p,  # halo status sm_count stream
     ]
     L.jb_conv3x3_c64_wgrad.restype = c_int
+    L.jb_halo_pack.argtypes = [
+        c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_longlong,  # src is_fp32 strides
+        c_int, c_int, c_int, c_int, c_int,  # NB C H W CP
+        c_void_p, POINTER(JbHalo), c_void_p, c_void_p,  # dst halo done_counter stream
+    ]
+    L.jb_halo_pack.restype = c_int
+    L.jb_conv3x3_thin.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # in w bias gelu_src pre padded dense
+        c_int, c_int, c_int, c_int,  # NB H W act
+        POINTER(JbHalo), c_void_p, c_void_p, c_int, c_void_p,
+    ]
+    L.jb_conv3x3_thin.restype = c_int
+    L.jb_wgrad_thin.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,  # big small out NB H W sign
+        POINTER(JbHalo), c_void_p, c_int, c_void_p,
+    ]
+    L.jb_wgrad_thin.restype = c_int
 
 
 @lru_cache(maxsize=1)

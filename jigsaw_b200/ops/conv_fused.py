@@ -1,7 +1,300 @@
-"""Bindings of the halo-fused convolution kernels (filled in by the kernel layer)."""
+"""Fused halo-exchange convolution chains on the sm_100a kernels.
+
+A *chain* is a sequence of 3x3 / stride 1 / padding 1 convolutions, each optionally followed
+by GELU, whose channel counts fit the kernels: a thin first layer (<= 4 input channels to 64),
+any number of 64 -> 64 layers, and optionally a thin last layer (64 to <= 4 channels).  A single
+layer is a chain of length one.  The whole chain runs in bf16 with fp32 accumulation (the
+numerics of ``torch.autocast(dtype=bfloat16)``), fp32 master weights and fp32 weight
+gradients.
+
+Forward.  The input is packed once into a padded NHWC buffer; every layer's epilogue writes
+the next layer's padded input (bias + GELU fused) and stores its edge pixels directly into
+the neighbouring ranks' buffers, so no halo exchange, padded copy, activation kernel or
+layout change runs between the layers.  Backward.  The data-gradient kernel of layer ``i``
+multiplies by GELU'(pre-activation of layer ``i - 1``) in its epilogue and writes the padded
+gradient (with halo push) that both the weight-gradient kernel of layer ``i - 1`` and the next
+data-gradient kernel consume; the halo scatter-add of the reference disappears because the
+gradient halo is read instead.  The weight-gradient kernel also yields the bias gradient.
+
+Reference parity: jigsaw/modules/convolution/_conv/distributed.py:212-396 (forward and
+backward with halo exchange), _conv/functional.py:28-169 (autograd Function).
+"""
 
 from __future__ import annotations
 
+import ctypes
+from typing import Any
 
-def maybe_fused_conv2d(layer, x, w, b):
-    return None
+import torch
+import torch.distributed as dist
+
+from . import _lib, symm
+
+
+def _p(t: torch.Tensor | None) -> ctypes.c_void_p | None:
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _bp(b: "symm.Block | None") -> ctypes.c_void_p | None:
+    return None if b is None else ctypes.c_void_p(b.ptr)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launch failed ({what}): code {rc}")
+
+
+class Geometry:
+    """Local tile shape plus the neighbourhood it exchanges halos with."""
+
+    def __init__(self, NB: int, H: int, W: int, device: torch.device, group_h: Any, group_w: Any) -> None:
+        self.NB, self.H, self.W = NB, H, W
+        self.device = device
+        self.arena = symm.arena(device)
+        self.nbrs = symm.neighbour_table(group_h, group_w)
+        self.sm = _lib.sm_count(device.index if device.index is not None else torch.cuda.current_device())
+
+    def padded(self, channels: int) -> "symm.Block":
+        n = self.NB * (self.H + 2) * (self.W + 2) * channels * 2
+        return self.arena.alloc(n, tag=("padded", self.NB, self.H, self.W, channels))
+
+    def halo(self, produce: "symm.Block | None", consume: "symm.Block | None") -> Any:
+        return symm.make_halo(self.arena, self.nbrs, produce, consume)
+
+
+def chain_kinds(channels: list[tuple[int, int]]) -> list[str] | None:
+    """Classify the layers of a chain or return ``None`` if the kernels do not cover it."""
+    kinds = []
+    for i, (cin, cout) in enumerate(channels):
+        if cin == 64 and cout == 64:
+            kinds.append("mid")
+        elif cin <= 4 and cout == 64 and i == 0:
+            kinds.append("thin_in")
+        elif cin == 64 and cout <= 4 and i == len(channels) - 1:
+            kinds.append("thin_out")
+        else:
+            return None
+    return kinds
+
+
+def _prep_weights(kind: str, w: torch.Tensor, b: torch.Tensor | None) -> dict:
+    """Kernel-side weight layouts of one layer (small tensors, rebuilt every step)."""
+    dev = w.device
+    cout, cin = w.shape[0], w.shape[1]
+    out: dict = {}
+    if kind == "mid":
+        out["w"] = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16).contiguous()          # [3,3,co,ci]
+        out["b"] = None if b is None else b.detach().float().contiguous()
+    elif kind == "thin_in":
+        t = torch.zeros(3, 3, 4, 64, device=dev, dtype=torch.float32)
+        t[:, :, :cin] = w.detach().float().permute(2, 3, 1, 0)
+        out["w"] = t                                                                        # [tap, ci, co]
+        out["b"] = None if b is None else b.detach().float().contiguous()
+    else:  # thin_out
+        t = torch.zeros(3, 3, 16, 64, device=dev, dtype=torch.bfloat16)
+        t[:, :, :cout] = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16)
+        out["w"] = t                                                                        # [tap, co(16), ci]
+        bb = torch.zeros(16, device=dev, dtype=torch.float32)
+        if b is not None:
+            bb[:cout] = b.detach().float()
+        out["b"] = bb
+        d = torch.zeros(3, 3, 4, 64, device=dev, dtype=torch.float32)
+        d[:, :, :cout] = w.detach().float().flip(2, 3).permute(2, 3, 0, 1)
+        out["w_dgrad"] = d                                                                  # mirrored taps, [tap, co, ci]
+    return out
+
+
+class _BlockHolder:
+    """Returns the saved padded buffers to the arena after backward, or when the autograd
+    graph that owns them is dropped without a backward pass."""
+
+    def __init__(self, ar: "symm.PeerArena", blocks: list) -> None:
+        self.ar, self.blocks = ar, list(blocks)
+
+    def release(self) -> None:
+        for b in self.blocks:
+            self.ar.free(b)
+        self.blocks = []
+
+    def __del__(self) -> None:
+        self.release()
+
+
+class _ConvChain(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, geom: Geometry, kinds: tuple, acts: tuple, *params: torch.Tensor | None) -> torch.Tensor:
+        L = _lib.lib()
+        ar, st = geom.arena, _lib.stream_ptr()
+        NB, H, W = geom.NB, geom.H, geom.W
+        n = len(kinds)
+        weights = [params[2 * i] for i in range(n)]
+        biases = [params[2 * i + 1] for i in range(n)]
+        need_grad = any(ctx.needs_input_grad)      # grad mode itself is always off inside forward
+        if acts[-1]:
+            raise ValueError("the last layer of a fused chain must not have an activation")
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.float()
+        prep = [_prep_weights(kinds[i], weights[i], biases[i]) for i in range(n)]
+        cin0 = weights[0].shape[1]
+        cp0 = 4 if kinds[0] == "thin_in" else 64
+        # ---- pack the input into the padded layout (+ halo push)
+        a = geom.padded(cp0)
+        sn, sc, sh, sw = x.stride()
+        _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, cp0, _bp(a),
+                              geom.halo(a, None), _p(ar.done_counter), st), "halo_pack")
+        acts_in: list[symm.Block] = [a]
+        pres: list[torch.Tensor | None] = []
+        out = None
+        for i in range(n):
+            last = i == n - 1
+            cout = weights[i].shape[0]
+            nxt = None if last else geom.padded(64)
+            pre = None
+            if need_grad and not last and acts[i]:
+                pre = torch.empty(NB, H, W, 64, device=x.device, dtype=torch.bfloat16)
+            if last:
+                out = torch.empty(NB, H, W, cout, device=x.device, dtype=torch.bfloat16)
+            halo = geom.halo(nxt, acts_in[i])
+            act = 1 if acts[i] else 0
+            if kinds[i] == "thin_in":
+                _check(L.jb_conv3x3_thin(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
+                                         _p(out) if last else None, NB, H, W, act, halo, _p(ar.done_counter),
+                                         _p(ar.status), geom.sm, st), "conv3x3_thin")
+            else:
+                nout = 16 if kinds[i] == "thin_out" else 64
+                _check(L.jb_conv3x3_c64(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
+                                        _p(out) if last else None, NB, H, W, nout, cout, act, 0, halo,
+                                        _p(ar.done_counter), _p(ar.status), geom.sm, st), "conv3x3_c64")
+            pres.append(pre)
+            if nxt is not None:
+                acts_in.append(nxt)
+        if need_grad:
+            ctx.geom, ctx.kinds, ctx.acts, ctx.prep = geom, kinds, acts, prep
+            ctx.acts_in, ctx.pres = acts_in, pres
+            ctx.shapes = [tuple(w.shape) for w in weights]
+            ctx.has_bias = [b is not None for b in biases]
+            ctx.x_needs_grad = ctx.needs_input_grad[0]
+            ctx.holder = _BlockHolder(ar, acts_in)
+        else:
+            for blk in acts_in:
+                ar.free(blk)
+        return out.permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx: Any, gout: torch.Tensor) -> tuple:
+        L = _lib.lib()
+        geom: Geometry = ctx.geom
+        ar, st = geom.arena, _lib.stream_ptr()
+        NB, H, W = geom.NB, geom.H, geom.W
+        kinds, acts, prep, acts_in, pres = ctx.kinds, ctx.acts, ctx.prep, ctx.acts_in, ctx.pres
+        n = len(kinds)
+        dev = gout.device
+        grads: list[torch.Tensor | None] = [None] * (2 * n)
+        cout_last = ctx.shapes[-1][0]
+        cpg = 4 if kinds[-1] == "thin_out" else 64
+        g = geom.padded(cpg)
+        sn, sc, sh, sw = gout.stride()
+        _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, cpg,
+                              _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
+        scratch = None
+        gx = None
+        for i in range(n - 1, -1, -1):
+            kind = kinds[i]
+            cout, cin = ctx.shapes[i][0], ctx.shapes[i][1]
+            # gradient of the layer above flows through the GELU that precedes this layer's input
+            src = pres[i - 1] if i > 0 else None
+            # ---- weight / bias gradient
+            if kind == "mid":
+                gw = torch.empty(64, 64, 3, 3, device=dev, dtype=torch.float32)
+                gb = torch.empty(64, device=dev, dtype=torch.float32)
+                if scratch is None:
+                    scratch = torch.empty(L.jb_conv3x3_wgrad_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
+                _check(L.jb_conv3x3_c64_wgrad(_bp(acts_in[i]), _bp(g), _p(gw), _p(gb), _p(scratch), NB, H, W,
+                                              geom.halo(None, g), _p(ar.status), geom.sm, st), "wgrad")
+            else:
+                raw = torch.empty(28, 64, device=dev, dtype=torch.float32)
+                if kind == "thin_in":
+                    _check(L.jb_wgrad_thin(_bp(g), _bp(acts_in[i]), _p(raw), NB, H, W, 1, geom.halo(None, acts_in[i]),
+                                           _p(ar.status), geom.sm, st), "wgrad_thin")
+                    gw = raw[:27].view(9, 3, 64)[:, :cin].permute(2, 1, 0).reshape(64, cin, 3, 3).contiguous()
+                    gb = raw[27].clone()
+                else:
+                    _check(L.jb_wgrad_thin(_bp(acts_in[i]), _bp(g), _p(raw), NB, H, W, -1, geom.halo(None, g),
+                                           _p(ar.status), geom.sm, st), "wgrad_thin")
+                    gw = raw[:27].view(9, 3, 64)[:, :cout].permute(1, 2, 0).reshape(cout, 64, 3, 3).contiguous()
+                    gb = gout.float().sum(dim=(0, 2, 3))
+            grads[2 * i] = gw
+            grads[2 * i + 1] = gb if ctx.has_bias[i] else None
+            # ---- data gradient
+            if i == 0:
+                if ctx.x_needs_grad and kind == "mid":
+                    gx = torch.empty(NB, H, W, 64, device=dev, dtype=torch.bfloat16)
+                    _check(L.jb_conv3x3_c64(_bp(g), _p(prep[i]["w"]), None, None, None, None, _p(gx), NB, H, W, 64, 64, 0,
+                                            1, geom.halo(None, g), _p(ar.done_counter), _p(ar.status), geom.sm, st),
+                           "dgrad(input)")
+                    gx = gx.permute(0, 3, 1, 2)
+                ar.free(g)
+                break
+            gnext = geom.padded(64)
+            halo = geom.halo(gnext, g)
+            gsrc = src if acts[i - 1] else None
+            if kind == "thin_out":
+                _check(L.jb_conv3x3_thin(_bp(g), _p(prep[i]["w_dgrad"]), None, _p(gsrc), None, _bp(gnext), None, NB, H, W,
+                                         0, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad_thin")
+            else:
+                _check(L.jb_conv3x3_c64(_bp(g), _p(prep[i]["w"]), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 64, 64,
+                                        0, 1, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
+            ar.free(g)
+            g = gnext
+        ctx.holder.release()
+        return (gx, None, None, None, *grads)
+
+
+def conv_chain(x: torch.Tensor, geom: Geometry, kinds: list[str], acts: list[bool], weights: list, biases: list) -> torch.Tensor:
+    """Run an eligible chain on the fused kernels.  ``x``: ``(N, C, H, W)`` local tile (any
+    strides, fp32 or bf16).  Returns the output tile as a bf16 ``(N, C_out, H, W)`` tensor in
+    channels-last memory."""
+    flat: list = []
+    for w, b in zip(weights, biases):
+        flat += [w, b]
+    return _ConvChain.apply(x, geom, tuple(kinds), tuple(acts), *flat)
+
+
+_geoms: dict[tuple, Geometry] = {}
+
+
+def geometry_for(x: torch.Tensor, group_h: Any, group_w: Any) -> Geometry:
+    key = (x.shape[0], x.shape[2], x.shape[3], x.device.index, id(group_h), id(group_w))
+    if key not in _geoms:
+        _geoms[key] = Geometry(x.shape[0], x.shape[2], x.shape[3], x.device, group_h, group_w)
+    return _geoms[key]
+
+
+def layer_is_eligible(layer: Any, x: torch.Tensor) -> bool:
+    """3x3 / stride 1 / padding 1 / dilation 1 / groups 1, unsplit channels, bf16 numerics."""
+    if not (x.is_cuda and x.dim() == 4 and layer._n_spatial == 2 and not layer._transposed):
+        return False
+    if layer.kernel_size != (3, 3) or layer.stride != (1, 1) or layer.padding != (1, 1) or layer.dilation != (1, 1):
+        return False
+    if layer.groups != 1 or layer.channel_group.size() != 1:
+        return False
+    bf16 = x.dtype == torch.bfloat16 or (
+        torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+    )
+    if not bf16 or x.shape[2] > 65535 or x.shape[0] > 65535:
+        return False
+    return _lib.available()
+
+
+def maybe_fused_conv2d(layer: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
+    """Single-layer entry point used by ``DistributedConv2d.forward``."""
+    if not layer_is_eligible(layer, x):
+        return None
+    kinds = chain_kinds([(layer.in_channels, layer.out_channels)])
+    if kinds is None:
+        return None
+    if kinds[0] != "mid" and x.requires_grad:
+        return None
+    gh, gw = layer.spatial_groups
+    geom = geometry_for(x, gh, gw)
+    return conv_chain(x, geom, kinds, [False], [w], [b])

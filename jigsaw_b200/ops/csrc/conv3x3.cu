@@ -150,6 +150,77 @@ __device__ __forceinline__ void store_padded_with_halo(const ConvArgs& a, const 
   }
 }
 
+
+// Shared epilogue of the convolution kernels: CPW consecutive output channels (starting at
+// c0) of pixel (n, h, w) held in fp32 registers.
+template <int CPW>
+__device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW], int n, int h, int w, int c0) {
+  const long long pix = (static_cast<long long>(n) * a.H + h) * static_cast<long long>(a.W) + w;
+  if (a.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) v[j] += __ldg(a.bias + c0 + j);
+  }
+  if (a.gelu_src != nullptr) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.gelu_src + pix * 64 + c0);
+#pragma unroll
+    for (int q = 0; q < CPW / 8; ++q) {
+      const uint4 u = __ldg(src + q);
+      const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
+        v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
+        v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
+      }
+    }
+  }
+  if (a.dense_pre != nullptr) {
+    uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
+#pragma unroll
+    for (int q = 0; q < CPW / 8; ++q) {
+      uint4 o;
+      o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+      o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+      o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+      o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+      dst[q] = o;
+    }
+  }
+  if (a.act == 1) {
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+  }
+  if (a.padded_out != nullptr) {
+    uint4 o[CPW / 8];
+#pragma unroll
+    for (int q = 0; q < CPW / 8; ++q) {
+      o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+      o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+      o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+      o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+    }
+    store_padded_with_halo<CPW / 8>(a, o, n, h, w, c0);
+  }
+  if (a.dense_out != nullptr) {
+    __nv_bfloat16* dst = a.dense_out + pix * a.cout_real + c0;
+    if ((a.cout_real & 7) == 0 && c0 + CPW <= a.cout_real) {
+#pragma unroll
+      for (int q = 0; q < CPW / 8; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        reinterpret_cast<uint4*>(dst)[q] = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CPW; ++j)
+        if (c0 + j < a.cout_real) dst[j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Forward (B_MN = 0, weights [9][NOUT][64] = tap, cout, cin) and data gradient
 // (B_MN = 1, same weight tensor read as tap, K = cout, N = cin, taps mirrored).
@@ -292,7 +363,6 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     const int c0 = half * 32;
     int it = 0;
     bool ok = true;
-    const long long drow = static_cast<long long>(a.W);
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const int s = item % a.nstrips;
       const int tw = (item / a.nstrips) % a.tiles_w;
@@ -321,72 +391,10 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         if (lane == 0) mbar_arrive(&acc_empty[as]);
         const int w = tw * CV_TW + quad * 32 + lane;
         if (!active || w >= a.W) continue;
-        const long long pix = (static_cast<long long>(n) * a.H + h) * drow + w;
         float v[CPW];
 #pragma unroll
-        for (int j = 0; j < CPW; ++j) {
-          v[j] = __uint_as_float(r[j]);
-          if (a.bias != nullptr) v[j] += __ldg(a.bias + c0 + j);
-        }
-        if (a.gelu_src != nullptr) {
-          const uint4* src = reinterpret_cast<const uint4*>(a.gelu_src + pix * 64 + c0);
-#pragma unroll
-          for (int q = 0; q < CPW / 8; ++q) {
-            const uint4 u = __ldg(src + q);
-            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
-              v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
-              v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
-            }
-          }
-        }
-        if (a.dense_pre != nullptr) {
-          uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
-#pragma unroll
-          for (int q = 0; q < CPW / 8; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-            o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-            o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-            o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-            dst[q] = o;
-          }
-        }
-        if (a.act == 1) {
-#pragma unroll
-          for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
-        }
-        if (a.padded_out != nullptr) {
-          uint4 o[CPW / 8];
-#pragma unroll
-          for (int q = 0; q < CPW / 8; ++q) {
-            o[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-            o[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-            o[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-            o[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-          }
-          store_padded_with_halo<CPW / 8>(a, o, n, h, w, c0);
-        }
-        if (a.dense_out != nullptr) {
-          __nv_bfloat16* dst = a.dense_out + pix * a.cout_real + c0;
-          if ((a.cout_real & 7) == 0 && c0 + CPW <= a.cout_real) {
-#pragma unroll
-            for (int q = 0; q < CPW / 8; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              reinterpret_cast<uint4*>(dst)[q] = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < CPW; ++j)
-              if (c0 + j < a.cout_real) dst[j] = __float2bfloat16(v[j]);
-          }
-        }
+        for (int j = 0; j < CPW; ++j) v[j] = __uint_as_float(r[j]);
+        conv_epilogue<CPW>(a, v, n, h, w, c0);
       }
     }
   }

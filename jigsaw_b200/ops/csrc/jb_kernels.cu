@@ -3,5 +3,6 @@
 //              -shared -Xcompiler -fPIC -o libjb_kernels.so jb_kernels.cu
 #include "gemm.cu"
 #include "conv3x3.cu"
+#include "conv_thin.cu"
 
 extern "C" int jb_abi_version() { return 1; }

@@ -1,0 +1,223 @@
+"""Peer-memory runtime: symmetric buffers, flag slots and neighbour tables for the fused kernels.
+
+Every rank of the job allocates the same sequence of blocks from a :class:`PeerArena`, so a
+block has the same offset on every rank and a kernel can address a neighbour's copy as
+``peer_base[rank] + offset``.  The arena grows in segments; each segment is one symmetric
+allocation (``torch.distributed._symmetric_memory``: CUDA VMM allocation plus handle
+exchange over the process group), so growing is a collective that all ranks reach together
+because they run the same program.  Blocks are recycled through exact-size free lists, which
+keeps the allocation sequence deterministic across ranks.
+
+Signalling: each padded buffer owns a *slot* of 16 flag words in a small symmetric flag
+segment.  A producer kernel publishes a monotonically increasing epoch into the slot of each
+neighbour once its peer stores are visible; a consumer kernel waits (bounded) until the flags
+of all its neighbours reach the epoch.  With one rank, no symmetric memory is used at all.
+
+Reference parity: the reference has no peer-memory layer; it moves halos with
+``all_to_all_single`` (jigsaw/modules/convolution/_common/halo.py:7-63).  This module is the
+B200-native replacement of that transport.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ._lib import JbHalo
+
+_ALIGN = 1024
+_FLAG_WORDS = 16
+_MAX_SLOTS = 4096
+
+
+def _round_up(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class Block:
+    """A sub-range of the arena: same offset on every rank."""
+
+    __slots__ = ("arena", "segment", "offset", "nbytes", "slot", "epoch", "tensor", "tag")
+
+    def __init__(self, arena: "PeerArena", segment: int, offset: int, nbytes: int, tensor: torch.Tensor) -> None:
+        self.arena, self.segment, self.offset, self.nbytes = arena, segment, offset, nbytes
+        self.tensor = tensor
+        self.slot = -1
+        self.epoch = 0
+        self.tag: object = None
+
+    @property
+    def ptr(self) -> int:
+        return self.tensor.data_ptr()
+
+    def peer_ptr(self, world_rank: int) -> int:
+        return self.arena.peer_base(self.segment, world_rank) + self.offset
+
+    def view(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self.tensor.view(dtype)[: int(torch.Size(shape).numel())].view(shape)
+
+
+class PeerArena:
+    """Symmetric block allocator shared by all ranks of the default process group."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.symmetric = self.world > 1
+        self._segments: list[dict] = []
+        self._free: dict[tuple, list[Block]] = {}
+        self._free_slots = list(range(_MAX_SLOTS - 1, -1, -1))
+        self._slot_epoch = [0] * _MAX_SLOTS
+        self.done_counter = torch.zeros(4, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self._flags = None
+        if self.symmetric:
+            self._flags = self._new_symmetric(_MAX_SLOTS * _FLAG_WORDS * 4)
+            self._flags["tensor"].zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier()
+
+    # ------------------------------------------------------------------ segments
+    def _new_symmetric(self, nbytes: int) -> dict:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        handle = symm_mem.rendezvous(t, group=dist.group.WORLD)
+        return {"tensor": t, "handle": handle, "ptrs": [int(p) for p in handle.buffer_ptrs], "used": 0, "size": nbytes}
+
+    def _new_segment(self, at_least: int) -> int:
+        default = int(float(os.environ.get("JIGSAW_B200_ARENA_SEGMENT_GB", "1")) * (1 << 30))
+        nbytes = _round_up(max(at_least, default), 1 << 21)
+        if self.symmetric:
+            seg = self._new_symmetric(nbytes)
+        else:
+            t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            seg = {"tensor": t, "handle": None, "ptrs": [t.data_ptr()], "used": 0, "size": nbytes}
+        self._segments.append(seg)
+        return len(self._segments) - 1
+
+    def peer_base(self, segment: int, world_rank: int) -> int:
+        ptrs = self._segments[segment]["ptrs"]
+        return ptrs[world_rank if self.symmetric else 0]
+
+    # ------------------------------------------------------------------ blocks
+    def alloc(self, nbytes: int, zero: bool = False, tag: object = None) -> Block:
+        """A block of at least ``nbytes`` (1 KiB aligned).  A recycled block is only handed to a
+        request with the same ``tag`` (callers tag padded buffers with their geometry, so the
+        never-written zero border of a recycled buffer is still in the right place) and keeps
+        its contents unless ``zero``; fresh segments come zero-filled."""
+        size = _round_up(nbytes, _ALIGN)
+        pool = self._free.get((size, tag))
+        if pool:
+            blk = pool.pop()
+            if zero:
+                blk.tensor.zero_()
+            return blk
+        for i, seg in enumerate(self._segments):
+            if seg["size"] - seg["used"] >= size:
+                break
+        else:
+            i = self._new_segment(size)
+            self._segments[i]["tensor"].zero_()
+            if self.symmetric:
+                torch.cuda.synchronize(self.device)
+                dist.barrier()
+        seg = self._segments[i]
+        off = seg["used"]
+        seg["used"] += size
+        blk = Block(self, i, off, size, seg["tensor"][off : off + size])
+        blk.tag = tag
+        return blk
+
+    def free(self, blk: Block) -> None:
+        if blk.slot >= 0:
+            self._free_slots.append(blk.slot)
+            blk.slot = -1
+        self._free.setdefault((blk.nbytes, blk.tag), []).append(blk)
+
+    # ------------------------------------------------------------------ flags
+    def bind_slot(self, blk: Block) -> None:
+        if blk.slot < 0:
+            blk.slot = self._free_slots.pop()
+
+    def next_epoch(self, blk: Block) -> int:
+        """Advance and return the epoch of the block's slot (one per production of its content)."""
+        self.bind_slot(blk)
+        self._slot_epoch[blk.slot] += 1
+        blk.epoch = self._slot_epoch[blk.slot]
+        return blk.epoch
+
+    def flag_ptr(self, world_rank: int, slot: int, direction: int) -> int:
+        return self._flags["ptrs"][world_rank] + (slot * _FLAG_WORDS + direction) * 4
+
+    def check_status(self) -> None:
+        """Raise if any kernel recorded a bounded-wait timeout (synchronises the device)."""
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            names = {1: "an mbarrier wait timed out", 2: "a cross-GPU flag wait timed out", 3: "bad argument"}
+            raise RuntimeError(f"jigsaw_b200 kernel error {code}: {names.get(code, 'unknown')}")
+
+
+_arenas: dict[int, PeerArena] = {}
+
+
+def arena(device: torch.device) -> PeerArena:
+    """The arena of ``device`` (created on first use; collective when the job has several ranks)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _arenas:
+        _arenas[idx] = PeerArena(torch.device("cuda", idx))
+    return _arenas[idx]
+
+
+# --------------------------------------------------------------------------- neighbours
+def neighbour_table(group_h: dist.ProcessGroup | None, group_w: dist.ProcessGroup | None) -> list[int | None]:
+    """World rank of the tile at ``(sy, sx)`` relative to this rank for the 3x3 neighbourhood
+    (index ``(sy + 1) * 3 + (sx + 1)``), ``None`` outside the tile grid.  Process meshes are
+    regular grids, so a diagonal neighbour follows from the strides of the two axes."""
+
+    def axis(g: dist.ProcessGroup | None) -> tuple[int, int, int]:
+        if g is None or g.size() == 1:
+            return 0, 1, 0
+        ranks = dist.get_process_group_ranks(g)
+        return g.rank(), g.size(), ranks[1] - ranks[0]
+
+    rh, nh, sh = axis(group_h)
+    rw, nw, sw = axis(group_w)
+    me = dist.get_rank() if dist.is_initialized() else 0
+    table: list[int | None] = []
+    for sy in (-1, 0, 1):
+        for sx in (-1, 0, 1):
+            if (sy, sx) == (0, 0) or not (0 <= rh + sy < nh and 0 <= rw + sx < nw):
+                table.append(None)
+            else:
+                table.append(me + sy * sh + sx * sw)
+    return table
+
+
+def make_halo(
+    ar: PeerArena, nbrs: list[int | None], produce: Block | None, consume: Block | None
+) -> "ctypes.pointer[JbHalo] | None":
+    """Descriptor for one kernel launch: where to push the edges of ``produce`` (a new epoch is
+    taken for it) and which flags to wait for before reading ``consume``."""
+    if not ar.symmetric or all(n is None for n in nbrs):
+        return None
+    h = JbHalo()
+    if produce is not None:
+        h.push_epoch = ar.next_epoch(produce)
+        h.push_enabled = 1
+        for d, n in enumerate(nbrs):
+            if n is not None:
+                h.push_buf[d] = produce.peer_ptr(n)
+                h.push_flag[d] = ar.flag_ptr(n, produce.slot, 8 - d)
+    if consume is not None and consume.slot >= 0:
+        h.wait_epoch = consume.epoch
+        h.wait_enabled = 1
+        for d, n in enumerate(nbrs):
+            if n is not None:
+                h.wait_flag[d] = ar.flag_ptr(ar.rank, consume.slot, d)
+    return ctypes.pointer(h)
