@@ -104,3 +104,12 @@ def sm_count(device_index: int) -> int:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+#: Number of kernels of this library launched so far in this process (benchmarks report it).
+LAUNCHES = 0
+
+
+def count_launches(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n

@@ -40,6 +40,7 @@ def _bp(b: "symm.Block | None") -> ctypes.c_void_p | None:
 
 
 def _check(rc: int, what: str) -> None:
+    _lib.count_launches(2 if what == "wgrad" else 1)
     if rc != 0:
         raise RuntimeError(f"jigsaw_b200 kernel launch failed ({what}): code {rc}")
 
