@@ -306,8 +306,10 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       bool ok = mbar_wait(wbar, 0, abort_flag, a.status);
       uint32_t fph = 0;  // per-slot phase bits of the full barriers
       int it = 0;
-      const uint32_t w_addr = smem_u32(w_smem);
-      const uint32_t s_addr = smem_u32(slots);
+      // Descriptors of slot 0 / tap 0; every other operand is a constant byte offset away.
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(slots), 16, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(w_smem), 8192, 1024)
+                                    : make_smem_desc_sw128(smem_u32(w_smem), 16, 1024);
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int h0 = s * a.rows_per_strip;
@@ -327,18 +329,16 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * NOUT);
+            const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
 #pragma unroll
             for (int dy = 0; dy < 3; ++dy) {
 #pragma unroll
               for (int dx = 0; dx < 3; ++dx) {
                 const int wt = B_MN ? ((2 - dy) * 3 + (2 - dx)) : (dy * 3 + dx);
-                const uint32_t a_tap = s_addr + (i + dy) * CV_SLOT_BYTES + dx * 128;
-                const uint32_t b_tap = w_addr + wt * WTAP_BYTES;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                  const uint64_t ad = make_smem_desc_sw128(a_tap + k * 32, 16, 1024);
-                  const uint64_t bd = B_MN ? make_smem_desc_sw128(b_tap + k * 2048, 8192, 1024)
-                                           : make_smem_desc_sw128(b_tap + k * 32, 16, 1024);
+                  const uint64_t ad = desc_advance(a_row, dy * CV_SLOT_BYTES + dx * 128 + k * 32);
+                  const uint64_t bd = desc_advance(b_desc0, wt * WTAP_BYTES + k * (B_MN ? 2048 : 32));
                   umma_f16(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
                 }
               }
@@ -523,8 +523,10 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       bool ok = true;
       bool first = true;
       const uint32_t s_addr = smem_u32(slots);
-      const uint32_t g_addr = smem_u32(gtiles);
       const uint32_t ones_addr = smem_u32(ones);
+      const uint64_t g_desc0 = make_smem_desc_sw128(smem_u32(gtiles), 8192, 1024);
+      const uint64_t x_desc128 = make_smem_desc_sw128(s_addr, 128, 1024);            // pair = next pixel
+      const uint64_t x_descslot = make_smem_desc_sw128(s_addr, CV_SLOT_BYTES, 1024); // pair = next slot
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int h0 = s * a.rows_per_strip;
@@ -541,24 +543,23 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             ok = mbar_wait(&gfull[gs], gph, abort_flag, a.status);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t g_tile = g_addr + gs * 16384;
-            const uint32_t r0 = s_addr + (i + 0) * CV_SLOT_BYTES;
-            const uint32_t r1 = s_addr + (i + 1) * CV_SLOT_BYTES;
-            const uint32_t r2 = s_addr + (i + 2) * CV_SLOT_BYTES;
+            const uint64_t bd0 = desc_advance(g_desc0, static_cast<uint32_t>(gs * 16384));
+            const uint64_t r0 = desc_advance(x_desc128, static_cast<uint32_t>(i * CV_SLOT_BYTES));
+            const uint64_t q0 = desc_advance(x_descslot, static_cast<uint32_t>(i * CV_SLOT_BYTES + 256));
+            const uint32_t v22 = s_addr + (i + 2) * CV_SLOT_BYTES + 256;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t acc = (first && k == 0) ? 0u : 1u;
               const uint32_t ko = k * 2048;  // 16 pixels x 128 bytes
-              const uint64_t bd = make_smem_desc_sw128(g_tile + ko, 8192, 1024);
+              const uint64_t bd = desc_advance(bd0, ko);
               // taps (dy,0) + (dy,1): second 64 rows of M are the view one pixel to the right.
-              umma_f16(tmem_base + 0, make_smem_desc_sw128(r0 + ko, 128, 1024), bd, idesc, acc);
-              umma_f16(tmem_base + 64, make_smem_desc_sw128(r1 + ko, 128, 1024), bd, idesc, acc);
-              umma_f16(tmem_base + 128, make_smem_desc_sw128(r2 + ko, 128, 1024), bd, idesc, acc);
+              umma_f16(tmem_base + 0, desc_advance(r0, ko), bd, idesc, acc);
+              umma_f16(tmem_base + 64, desc_advance(r0, CV_SLOT_BYTES + ko), bd, idesc, acc);
+              umma_f16(tmem_base + 128, desc_advance(r0, 2 * CV_SLOT_BYTES + ko), bd, idesc, acc);
               // taps (0,2) + (1,2): second half is the same view one slot further.
-              umma_f16(tmem_base + 192, make_smem_desc_sw128(r0 + 256 + ko, CV_SLOT_BYTES, 1024), bd, idesc, acc);
-              // tap (2,2) + ones (bias gradient).
-              const uint32_t v22 = r2 + 256 + ko;
-              umma_f16(tmem_base + 256, make_smem_desc_sw128(v22, ones_addr - v22, 1024), bd, idesc, acc);
+              umma_f16(tmem_base + 192, desc_advance(q0, ko), bd, idesc, acc);
+              // tap (2,2) + ones (bias gradient): the distance to the ones tile shrinks with k.
+              umma_f16(tmem_base + 256, make_smem_desc_sw128(v22 + ko, ones_addr - (v22 + ko), 1024), bd, idesc, acc);
             }
             first = false;
             umma_commit(&gempty[gs]);

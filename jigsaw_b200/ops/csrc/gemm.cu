@@ -132,6 +132,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
+      const uint32_t a_addr0 = smem_u32(smem);
+      const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(a_addr0, 8192, 1024) : make_smem_desc_sw128(a_addr0, 16, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(a_addr0 + S::A_BYTES, 8192, 1024)
+                                    : make_smem_desc_sw128(a_addr0 + S::A_BYTES, 16, 1024);
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
         const int as = it & 1;
         const uint32_t aph = (it >> 1) & 1u;
@@ -143,17 +147,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ok = mbar_wait(&full[s], ph, abort_flag, status);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + S::A_BYTES;
+          const uint64_t ad0 = desc_advance(a_desc0, static_cast<uint32_t>(s * S::STAGE_BYTES));
+          const uint64_t bd0 = desc_advance(b_desc0, static_cast<uint32_t>(s * S::STAGE_BYTES));
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k) {
             // K-major: 16 K values = 32 bytes inside the swizzle row.
             // MN-major: 16 K values = 16 rows of 128 bytes.
-            const uint64_t ad = A_MN ? make_smem_desc_sw128(a_addr + k * 2048, 8192, 1024)
-                                     : make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t bd = B_MN ? make_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
-                                     : make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, desc_advance(ad0, k * (A_MN ? 2048 : 32)), desc_advance(bd0, k * (B_MN ? 2048 : 32)), idesc,
+                     (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);
           if (++s == S::STAGES) {
