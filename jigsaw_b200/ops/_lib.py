@@ -9,6 +9,7 @@ must also run on CPU-only machines.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_int, c_longlong, c_uint, c_void_p
 from functools import lru_cache
 
@@ -79,6 +80,11 @@ def _declare(L: ctypes.CDLL) -> None:
 @lru_cache(maxsize=1)
 def lib() -> ctypes.CDLL:
     """Load (building first if the sources are newer) and return the kernel library."""
+    override = os.environ.get("JIGSAW_B200_LIB")     # a pre-built library to load instead
+    if override:
+        L = ctypes.CDLL(override)
+        _declare(L)
+        return L
     if not _build.is_fresh():
         _build.build()
     L = ctypes.CDLL(str(_build.LIB_PATH))

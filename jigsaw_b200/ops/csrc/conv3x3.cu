@@ -25,6 +25,8 @@
 // and conv2d_weight of the reference (jigsaw/modules/convolution/_conv/halo.py:66-251,
 // jigsaw/modules/convolution/_conv/distributed.py:212-396).
 
+#include <stdlib.h>
+
 #include "ptx.cuh"
 #include "tmap.cuh"
 
@@ -35,8 +37,15 @@ constexpr int CV_BOXW = 130;                      // input pixels per slot (tile
 constexpr int CV_SLOT_BYTES = 136 * 128;          // 17 KiB, keeps slots 1024-byte aligned
 constexpr int CV_SLOTS = 8;
 constexpr int CV_CHUNK = 6;                       // output rows per window refill
-constexpr int CV_THREADS = 320;                   // producer, MMA, 8 epilogue warps
-constexpr int CV_EPI_WARPS = 8;
+#ifndef JB_CV_EPI_WARPS
+#define JB_CV_EPI_WARPS 16
+#endif
+#ifndef JB_CV_ACC_STAGES
+#define JB_CV_ACC_STAGES 4
+#endif
+constexpr int CV_EPI_WARPS = JB_CV_EPI_WARPS;      // a multiple of four: one set per TMEM lane quadrant
+constexpr int CV_THREADS = 64 + 32 * CV_EPI_WARPS; // producer, MMA, epilogue warps
+constexpr int CV_ACC_STAGES = JB_CV_ACC_STAGES;    // accumulator buffers in TMEM
 
 struct HaloPush {
   // Index (sy + 1) * 3 + (sx + 1); entry 4 (self) unused.  Null = no neighbour there.
@@ -69,6 +78,8 @@ struct ConvArgs {
   HaloWait wait;
   unsigned int* done_counter;      // local scratch word, zero before the first launch
   int* status;
+  int debug;
+  long long* prof;                 // optional [gridDim.x][8] clock totals of the MMA warp (diagnostics)
 };
 
 __device__ __forceinline__ void halo_wait_all(const HaloWait& w, volatile int* abort_flag, int* status) {
@@ -153,18 +164,35 @@ __device__ __forceinline__ void store_padded_with_halo(const ConvArgs& a, const 
 
 // Shared epilogue of the convolution kernels: CPW consecutive output channels (starting at
 // c0) of pixel (n, h, w) held in fp32 registers.
+// Bias values of the CPW channels a thread owns; they are the same for every tile, so the
+// kernels load them once into registers.
 template <int CPW>
-__device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW], int n, int h, int w, int c0) {
-  const long long pix = (static_cast<long long>(n) * a.H + h) * static_cast<long long>(a.W) + w;
-  if (a.bias != nullptr) {
+__device__ __forceinline__ void load_bias_regs(const ConvArgs& a, int c0, float (&b)[CPW]) {
 #pragma unroll
-    for (int j = 0; j < CPW; ++j) v[j] += __ldg(a.bias + c0 + j);
-  }
+  for (int j = 0; j < CPW; ++j) b[j] = (a.bias != nullptr) ? __ldg(a.bias + c0 + j) : 0.f;
+}
+
+// The GELU'(src) operand of a pixel, fetched early (before waiting for the accumulator) so
+// that its latency hides behind the wait.
+template <int CPW>
+__device__ __forceinline__ void prefetch_gelu_src(const ConvArgs& a, int n, int h, int w, int c0, uint4 (&g)[CPW / 8]) {
+  if (a.gelu_src == nullptr || w >= a.W) return;
+  const long long pix = (static_cast<long long>(n) * a.H + h) * static_cast<long long>(a.W) + w;
+  const uint4* src = reinterpret_cast<const uint4*>(a.gelu_src + pix * 64 + c0);
+#pragma unroll
+  for (int q = 0; q < CPW / 8; ++q) g[q] = __ldg(src + q);
+}
+
+template <int CPW>
+__device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW], const float (&bias)[CPW],
+                                              const uint4 (&gsrc)[CPW / 8], int n, int h, int w, int c0) {
+  const long long pix = (static_cast<long long>(n) * a.H + h) * static_cast<long long>(a.W) + w;
+#pragma unroll
+  for (int j = 0; j < CPW; ++j) v[j] += bias[j];
   if (a.gelu_src != nullptr) {
-    const uint4* src = reinterpret_cast<const uint4*>(a.gelu_src + pix * 64 + c0);
 #pragma unroll
     for (int q = 0; q < CPW / 8; ++q) {
-      const uint4 u = __ldg(src + q);
+      const uint4 u = gsrc[q];
       const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
@@ -231,7 +259,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
                   const ConvArgs a) {
   constexpr int WTAP_BYTES = (B_MN ? 64 : NOUT) * 128;
   constexpr int W_BYTES = 9 * WTAP_BYTES;
-  constexpr uint32_t TMEM_COLS = (2 * NOUT <= 32) ? 32 : (2 * NOUT <= 64 ? 64 : (2 * NOUT <= 128 ? 128 : 256));
+  constexpr uint32_t TMEM_COLS = (CV_ACC_STAGES * NOUT <= 32) ? 32 : (CV_ACC_STAGES * NOUT <= 64 ? 64 : (CV_ACC_STAGES * NOUT <= 128 ? 128 : 256));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_smem = smem;
@@ -239,10 +267,10 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(slots + CV_SLOTS * CV_SLOT_BYTES);
   uint64_t* full = bars;                  // [8]
   uint64_t* empty = bars + 8;             // [8]
-  uint64_t* acc_full = bars + 16;         // [2]
-  uint64_t* acc_empty = bars + 18;        // [2]
-  uint64_t* wbar = bars + 20;             // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* acc_full = bars + 16;         // [CV_ACC_STAGES]
+  uint64_t* acc_empty = bars + 20;        // [CV_ACC_STAGES]
+  uint64_t* wbar = bars + 24;             // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -254,7 +282,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < CV_ACC_STAGES; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], CV_EPI_WARPS);
     }
@@ -293,6 +321,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
             ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
             if (!ok) break;
             eph ^= (1u << j);
+            if ((a.debug & 1) && (item != blockIdx.x || hc != h0)) { mbar_arrive(&full[j]); continue; }
             mbar_expect_tx(&full[j], CV_BOXW * 128);
             tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
           }
@@ -301,11 +330,13 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- UMMA issuer
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc_bf16(128, NOUT, 0, B_MN);
       bool ok = mbar_wait(wbar, 0, abort_flag, a.status);
       uint32_t fph = 0;  // per-slot phase bits of the full barriers
       int it = 0;
+      long long pr0 = 0, pr1 = 0, pr2 = 0, pr3 = 0, pr4 = 0;
+      const long long t_begin = clock64();
       // Descriptors of slot 0 / tap 0; every other operand is a constant byte offset away.
       const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(slots), 16, 1024);
       const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(w_smem), 8192, 1024)
@@ -317,10 +348,12 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
           const int n_out = min(CV_CHUNK, h1 - hc);
           for (int i = 0; i < n_out; ++i, ++it) {
-            const int as = it & 1;
-            const uint32_t aph = (it >> 1) & 1u;
+            const int as = it % CV_ACC_STAGES;
+            const uint32_t aph = (it / CV_ACC_STAGES) & 1u;
+            const long long c0 = clock64();
             ok = mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status);
             if (!ok) break;
+            const long long c1 = clock64();
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
               ok = mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
               if (!ok) break;
@@ -328,6 +361,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
             }
             if (!ok) break;
             tc_fence_after_sync();
+            const long long c2 = clock64();
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * NOUT);
             const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
 #pragma unroll
@@ -337,41 +371,55 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
                 const int wt = B_MN ? ((2 - dy) * 3 + (2 - dx)) : (dy * 3 + dx);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                  const uint64_t ad = desc_advance(a_row, dy * CV_SLOT_BYTES + dx * 128 + k * 32);
+                  if ((a.debug & 4) && (dy | dx) != 0) continue;
+                  const uint64_t ad = desc_advance(a_row, ((a.debug & 8) ? 0 : dy) * CV_SLOT_BYTES + ((a.debug & 8) ? 0 : dx) * 128 + k * 32);
                   const uint64_t bd = desc_advance(b_desc0, wt * WTAP_BYTES + k * (B_MN ? 2048 : 32));
-                  umma_f16(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
+                  umma_f16_elect(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
                 }
               }
             }
-            umma_commit(&acc_full[as]);
-            umma_commit(&empty[i]);
+            const long long c3 = clock64();
+            umma_commit_elect(&acc_full[as]);
+            umma_commit_elect(&empty[i]);
             if (i == n_out - 1) {
-              umma_commit(&empty[i + 1]);
-              umma_commit(&empty[i + 2]);
+              umma_commit_elect(&empty[i + 1]);
+              umma_commit_elect(&empty[i + 2]);
             }
+            const long long c4 = clock64();
+            pr0 += c1 - c0; pr1 += c2 - c1; pr2 += c3 - c2; pr3 += c4 - c3; pr4 += 1;
           }
         }
       }
+      if (a.prof != nullptr && lane == 0) {
+        long long* o = a.prof + blockIdx.x * 8;
+        o[0] = pr0; o[1] = pr1; o[2] = pr2; o[3] = pr3; o[4] = pr4; o[5] = clock64() - t_begin;
+      }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (8 warps)
+    // ---------------------------------------------------------------- epilogue (16 warps)
+    // Warp e drains TMEM lane quadrant (warp % 4) and the 16 accumulator columns of group e / 4.
     const int e = warp - 2;
     const int quad = warp & 3;
     const int half = e >> 2;
-    constexpr int CPW = (NOUT >= 64) ? 32 : NOUT;   // columns handled per warp
-    const bool active = (NOUT >= 64) || (half == 0);
-    const int c0 = half * 32;
+    constexpr int CPW = (CV_EPI_WARPS == 16) ? 16 : ((NOUT >= 64) ? 32 : NOUT);   // columns per warp
+    const bool active = (half * CPW) < NOUT;
+    const int c0 = half * CPW;
     int it = 0;
     bool ok = true;
+    float bias_r[CPW];
+    load_bias_regs<CPW>(a, c0, bias_r);
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const int s = item % a.nstrips;
       const int tw = (item / a.nstrips) % a.tiles_w;
       const int n = item / (a.nstrips * a.tiles_w);
       const int h0 = s * a.rows_per_strip;
       const int h1 = min(a.H, h0 + a.rows_per_strip);
+      const int w = tw * CV_TW + quad * 32 + lane;
       for (int h = h0; h < h1; ++h, ++it) {
-        const int as = it & 1;
-        const uint32_t aph = (it >> 1) & 1u;
+        const int as = it % CV_ACC_STAGES;
+        const uint32_t aph = (it / CV_ACC_STAGES) & 1u;
+        uint4 gsrc[CPW / 8];
+        if (active) prefetch_gelu_src<CPW>(a, n, h, w, c0, gsrc);
         ok = mbar_wait(&acc_full[as], aph, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after_sync();
@@ -389,12 +437,11 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[as]);
-        const int w = tw * CV_TW + quad * 32 + lane;
-        if (!active || w >= a.W) continue;
+        if (!active || w >= a.W || (a.debug & 2)) continue;
         float v[CPW];
 #pragma unroll
         for (int j = 0; j < CPW; ++j) v[j] = __uint_as_float(r[j]);
-        conv_epilogue<CPW>(a, v, n, h, w, c0);
+        conv_epilogue<CPW>(a, v, bias_r, gsrc, n, h, w, c0);
       }
     }
   }
@@ -515,7 +562,7 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
       uint32_t fph = 0;
       int gs = 0;
@@ -553,29 +600,29 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
               const uint32_t ko = k * 2048;  // 16 pixels x 128 bytes
               const uint64_t bd = desc_advance(bd0, ko);
               // taps (dy,0) + (dy,1): second 64 rows of M are the view one pixel to the right.
-              umma_f16(tmem_base + 0, desc_advance(r0, ko), bd, idesc, acc);
-              umma_f16(tmem_base + 64, desc_advance(r0, CV_SLOT_BYTES + ko), bd, idesc, acc);
-              umma_f16(tmem_base + 128, desc_advance(r0, 2 * CV_SLOT_BYTES + ko), bd, idesc, acc);
+              umma_f16_elect(tmem_base + 0, desc_advance(r0, ko), bd, idesc, acc);
+              umma_f16_elect(tmem_base + 64, desc_advance(r0, CV_SLOT_BYTES + ko), bd, idesc, acc);
+              umma_f16_elect(tmem_base + 128, desc_advance(r0, 2 * CV_SLOT_BYTES + ko), bd, idesc, acc);
               // taps (0,2) + (1,2): second half is the same view one slot further.
-              umma_f16(tmem_base + 192, desc_advance(q0, ko), bd, idesc, acc);
+              umma_f16_elect(tmem_base + 192, desc_advance(q0, ko), bd, idesc, acc);
               // tap (2,2) + ones (bias gradient): the distance to the ones tile shrinks with k.
-              umma_f16(tmem_base + 256, make_smem_desc_sw128(v22 + ko, ones_addr - (v22 + ko), 1024), bd, idesc, acc);
+              umma_f16_elect(tmem_base + 256, make_smem_desc_sw128(v22 + ko, ones_addr - (v22 + ko), 1024), bd, idesc, acc);
             }
             first = false;
-            umma_commit(&gempty[gs]);
+            umma_commit_elect(&gempty[gs]);
             if (++gs == WG_GSTAGES) {
               gs = 0;
               gph ^= 1u;
             }
-            umma_commit(&empty[i]);
+            umma_commit_elect(&empty[i]);
             if (i == n_out - 1) {
-              umma_commit(&empty[i + 1]);
-              umma_commit(&empty[i + 2]);
+              umma_commit_elect(&empty[i + 1]);
+              umma_commit_elect(&empty[i + 2]);
             }
           }
         }
       }
-      umma_commit(acc_full);
+      umma_commit_elect(acc_full);
     }
   } else {
     // epilogue: one pass at the end
@@ -708,6 +755,12 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
   a.dense_out = static_cast<__nv_bfloat16*>(dense_out);
   a.done_counter = done_counter;
   a.status = status;
+  {
+    const char* dbg = getenv("JB_CONV_DEBUG");
+    a.debug = dbg ? atoi(dbg) : 0;
+    const char* prof = getenv("JB_CONV_PROF_PTR");
+    a.prof = prof ? reinterpret_cast<long long*>(strtoull(prof, nullptr, 10)) : nullptr;
+  }
   if (halo != nullptr) {
     for (int d = 0; d < 9; ++d) {
       a.push.buf[d] = halo->push_buf[d];
@@ -722,8 +775,8 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
   const int items = NB * a.tiles_w * a.nstrips;
   const int grid = items < sm_count ? items : sm_count;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  constexpr int SMEM64 = 9 * 8192 + CV_SLOTS * CV_SLOT_BYTES + 256 + 1024;
-  constexpr int SMEM16 = ((9 * 2048 + 1023) & ~1023) + CV_SLOTS * CV_SLOT_BYTES + 256 + 1024;
+  constexpr int SMEM64 = 9 * 8192 + CV_SLOTS * CV_SLOT_BYTES + 512 + 1024;
+  constexpr int SMEM16 = ((9 * 2048 + 1023) & ~1023) + CV_SLOTS * CV_SLOT_BYTES + 512 + 1024;
   cudaError_t e;
   if (mode == 1) {
     auto k = conv3x3_tc_kernel<64, 1>;

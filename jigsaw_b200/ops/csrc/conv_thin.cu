@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(256) conv3x3_thin_kernel(const __nv_bfloat16* 
   const int c0 = half * 32;
   const long long prow = static_cast<long long>(a.W + 2) * 4;
   const long long pimg = static_cast<long long>(a.H + 2) * prow;
+  float bias_r[32];
+  load_bias_regs<32>(a, c0, bias_r);
   const int segs = a.tiles_w;
   const long long total = static_cast<long long>(a.NB) * a.H * segs;
   for (long long item = blockIdx.x; item < total; item += gridDim.x) {
@@ -174,7 +176,9 @@ __global__ void __launch_bounds__(256) conv3x3_thin_kernel(const __nv_bfloat16* 
         }
       }
     }
-    conv_epilogue<32>(a, v, n, h, wpix, c0);
+    uint4 gsrc[4];
+    prefetch_gelu_src<32>(a, n, h, wpix, c0, gsrc);
+    conv_epilogue<32>(a, v, bias_r, gsrc, n, h, wpix, c0);
   }
   halo_publish(a.push, a.done_counter);
 }

@@ -127,7 +127,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, A_MN, B_MN);
       int s = 0;
       uint32_t ph = 0;
@@ -153,17 +153,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < GEMM_BK / 16; ++k) {
             // K-major: 16 K values = 32 bytes inside the swizzle row.
             // MN-major: 16 K values = 16 rows of 128 bytes.
-            umma_f16(d_tmem, desc_advance(ad0, k * (A_MN ? 2048 : 32)), desc_advance(bd0, k * (B_MN ? 2048 : 32)), idesc,
+            umma_f16_elect(d_tmem, desc_advance(ad0, k * (A_MN ? 2048 : 32)), desc_advance(bd0, k * (B_MN ? 2048 : 32)), idesc,
                      (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty[s]);
+          umma_commit_elect(&empty[s]);
           if (++s == S::STAGES) {
             s = 0;
             ph ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(&acc_full[as]);
+        umma_commit_elect(&acc_full[as]);
       }
     }
   } else {

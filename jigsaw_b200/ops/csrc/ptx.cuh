@@ -159,6 +159,16 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Warp-convergent issue: the whole warp runs the (uniform) address arithmetic so that the
+// compiler can keep descriptors in uniform registers; one elected lane issues the instruction.
+__device__ __forceinline__ void umma_f16_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  if (elect_one()) umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  if (elect_one()) umma_commit(bar);
+}
+
 // 32 lanes x 32 columns of fp32 accumulators -> 32 registers per thread.  The warp
 // reads the TMEM lane quadrant (warp_idx % 4); taddr = (lane << 16) | column.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -165,6 +165,14 @@ def joint_comm_hook(state: JointCommHookState, bucket: Any) -> "torch.futures.Fu
     return works[-1].get_future().then(done)
 
 
+# DDP validates the hook's annotations as objects, not strings.
+joint_comm_hook.__annotations__ = {
+    "state": JointCommHookState,
+    "bucket": dist.GradBucket,
+    "return": torch.futures.Future[torch.Tensor],
+}
+
+
 def register_joint_comm_hook(
     ddp: DistributedDataParallel, wrapper: Callable[[Callable], Callable] | None = None
 ) -> JointCommHookState:
