@@ -57,13 +57,14 @@ def _dense_attention(q, k, v, scale: float, dropout_p: float, backend: AttnBacke
 
 
 def _math_autograd(q, k, v, scale, p, mask):
-    s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * scale
+    acc = torch.promote_types(q.dtype, torch.float32)
+    s = torch.matmul(q.to(acc), k.to(acc).transpose(-1, -2)) * scale
     if mask is not None:
-        s = s + mask.float() if mask.dtype != torch.bool else s.masked_fill(~mask, float("-inf"))
+        s = s + mask.to(acc) if mask.dtype != torch.bool else s.masked_fill(~mask, float("-inf"))
     a = torch.softmax(s, dim=-1)
     if p > 0.0:
         a = F.dropout(a, p)
-    return torch.matmul(a, v.float()).to(q.dtype)
+    return torch.matmul(a, v.to(acc)).to(q.dtype)
 
 
 def _split_heads(qkv: torch.Tensor, heads: int, bshd: bool) -> torch.Tensor:

@@ -39,19 +39,21 @@ class MathCore:
 
     @staticmethod
     def forward(q, k, v, scale: float, dropout_p: float = 0.0, seed: int = 0) -> tuple[torch.Tensor, torch.Tensor, Any]:
-        s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * scale
+        acc = torch.promote_types(q.dtype, torch.float32)
+        s = torch.matmul(q.to(acc), k.to(acc).transpose(-1, -2)) * scale
         lse = torch.logsumexp(s, dim=-1)
         p = torch.exp(s - lse.unsqueeze(-1))
         if dropout_p > 0.0:
             p = p * _dropout_mask(p.shape, dropout_p, seed, p.device)
-        out = torch.matmul(p, v.float())
+        out = torch.matmul(p, v.to(acc))
         return out.to(q.dtype), lse, seed
 
     @staticmethod
     def backward(dout, q, k, v, out, lse, scale: float, dropout_p: float = 0.0, rng_state: Any = 0):
-        qf, kf, vf, do = q.float(), k.float(), v.float(), dout.float()
-        p = torch.exp(torch.matmul(qf, kf.transpose(-1, -2)) * scale - lse.unsqueeze(-1))
-        delta = (do * out.float()).sum(dim=-1, keepdim=True)
+        acc = torch.promote_types(q.dtype, torch.float32)
+        qf, kf, vf, do = q.to(acc), k.to(acc), v.to(acc), dout.to(acc)
+        p = torch.exp(torch.matmul(qf, kf.transpose(-1, -2)) * scale - lse.to(acc).unsqueeze(-1))
+        delta = (do * out.to(acc)).sum(dim=-1, keepdim=True)
         dp = torch.matmul(do, vf.transpose(-1, -2))
         if dropout_p > 0.0:
             mask = _dropout_mask(p.shape, dropout_p, rng_state, p.device)

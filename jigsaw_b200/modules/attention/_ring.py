@@ -122,8 +122,9 @@ class _RingAttention(torch.autograd.Function):
         fetch = _Fetcher(payload, group, cfg)
         P, me = fetch.P, fetch.me
         base_seed = int(torch.randint(0, 2**31 - 1, (1,)).item()) if dropout_p > 0.0 else 0
-        out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-        lse = torch.full(q.shape[:-1], float("-inf"), dtype=torch.float32, device=q.device)
+        acc = torch.promote_types(q.dtype, torch.float32)
+        out = torch.zeros(q.shape, dtype=acc, device=q.device)
+        lse = torch.full(q.shape[:-1], float("-inf"), dtype=acc, device=q.device)
         saved: list[Any] = []
         rng: list[Any] = []
         keep_all = save_chunks and cfg.save_scope is SaveScope.GLOBAL
@@ -136,7 +137,7 @@ class _RingAttention(torch.autograd.Function):
                 kj, vj = chunk[0], chunk[1]
             seed = chunk_seed(base_seed, me, fetch.owner(me, s))
             out_j, lse_j, state = core.forward(q, kj, vj, scale, dropout_p, seed)
-            out, lse = merge_chunks(out, lse, out_j, lse_j.float())
+            out, lse = merge_chunks(out, lse, out_j, lse_j.to(acc))
             rng.append(state)
             if keep_all:
                 if cfg.offload is Offload.CPU and fetch.owner(me, s) != me:
@@ -161,14 +162,15 @@ class _RingAttention(torch.autograd.Function):
         fetch = _Fetcher(payload, group, cfg)
         P, me = fetch.P, fetch.me
         dout = dout.contiguous()
-        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-        d_own = torch.zeros(payload.shape, dtype=torch.float32, device=q.device)
+        acc = torch.promote_types(q.dtype, torch.float32)
+        dq = torch.zeros(q.shape, dtype=acc, device=q.device)
+        d_own = torch.zeros(payload.shape, dtype=acc, device=q.device)
         gathered = (
-            torch.zeros((P, *payload.shape), dtype=torch.float32, device=q.device)
+            torch.zeros((P, *payload.shape), dtype=acc, device=q.device)
             if cfg.send_backward is SendBackward.GATHER_DKV
             else None
         )
-        dw = torch.zeros_like(w_qkv, dtype=torch.float32) if ctx.send_x else None
+        dw = torch.zeros_like(w_qkv, dtype=acc) if ctx.send_x else None
         nxt = None
         for s in range(P):
             if ctx.saved_chunks is not None:
@@ -187,16 +189,16 @@ class _RingAttention(torch.autograd.Function):
             else:
                 kj, vj = chunk[0], chunk[1]
             dq_j, dk_j, dv_j = core.backward(dout, q, kj, vj, out, lse, ctx.scale, ctx.dropout_p, ctx.rng[s])
-            dq += dq_j.float()
+            dq += dq_j.to(acc)
             if ctx.send_x:
                 e = w_qkv.shape[0] // 3
-                merge = lambda t: t.float().transpose(-3, -2).reshape(*chunk.shape[:-1], e)  # noqa: E731
+                merge = lambda t: t.to(acc).transpose(-3, -2).reshape(*chunk.shape[:-1], e)  # noqa: E731
                 dkv = torch.cat((merge(dk_j), merge(dv_j)), dim=-1)                    # (..., s, 2E)
-                contrib = torch.matmul(dkv, w_qkv[e:].float())                            # (..., s, in)
+                contrib = torch.matmul(dkv, w_qkv[e:].to(acc))                            # (..., s, in)
                 flat_dkv = dkv.reshape(-1, 2 * e)
-                dw[e:] += torch.matmul(flat_dkv.t(), chunk.float().reshape(-1, chunk.shape[-1]))
+                dw[e:] += torch.matmul(flat_dkv.t(), chunk.to(acc).reshape(-1, chunk.shape[-1]))
             else:
-                contrib = torch.stack((dk_j, dv_j)).float()
+                contrib = torch.stack((dk_j, dv_j)).to(acc)
             if gathered is not None:
                 gathered[fetch.owner(me, s)] += contrib
             else:

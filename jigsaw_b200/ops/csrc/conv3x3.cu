@@ -25,8 +25,6 @@
 // and conv2d_weight of the reference (jigsaw/modules/convolution/_conv/halo.py:66-251,
 // jigsaw/modules/convolution/_conv/distributed.py:212-396).
 
-#include <stdlib.h>
-
 #include "ptx.cuh"
 #include "tmap.cuh"
 
@@ -37,15 +35,9 @@ constexpr int CV_BOXW = 130;                      // input pixels per slot (tile
 constexpr int CV_SLOT_BYTES = 136 * 128;          // 17 KiB, keeps slots 1024-byte aligned
 constexpr int CV_SLOTS = 8;
 constexpr int CV_CHUNK = 6;                       // output rows per window refill
-#ifndef JB_CV_EPI_WARPS
-#define JB_CV_EPI_WARPS 16
-#endif
-#ifndef JB_CV_ACC_STAGES
-#define JB_CV_ACC_STAGES 4
-#endif
-constexpr int CV_EPI_WARPS = JB_CV_EPI_WARPS;      // a multiple of four: one set per TMEM lane quadrant
-constexpr int CV_THREADS = 64 + 32 * CV_EPI_WARPS; // producer, MMA, epilogue warps
-constexpr int CV_ACC_STAGES = JB_CV_ACC_STAGES;    // accumulator buffers in TMEM
+constexpr int CV_MMA_WARPS = 4;                   // MMA-issuing warps = accumulator buffers in TMEM
+constexpr int CV_EPI_WARPS = 8;                   // two per TMEM lane quadrant
+constexpr int CV_THREADS = 32 * (1 + CV_MMA_WARPS + CV_EPI_WARPS);  // + one TMA producer warp
 
 struct HaloPush {
   // Index (sy + 1) * 3 + (sx + 1); entry 4 (self) unused.  Null = no neighbour there.
@@ -78,8 +70,6 @@ struct ConvArgs {
   HaloWait wait;
   unsigned int* done_counter;      // local scratch word, zero before the first launch
   int* status;
-  int debug;
-  long long* prof;                 // optional [gridDim.x][8] clock totals of the MMA warp (diagnostics)
 };
 
 __device__ __forceinline__ void halo_wait_all(const HaloWait& w, volatile int* abort_flag, int* status) {
@@ -259,16 +249,17 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
                   const ConvArgs a) {
   constexpr int WTAP_BYTES = (B_MN ? 64 : NOUT) * 128;
   constexpr int W_BYTES = 9 * WTAP_BYTES;
-  constexpr uint32_t TMEM_COLS = (CV_ACC_STAGES * NOUT <= 32) ? 32 : (CV_ACC_STAGES * NOUT <= 64 ? 64 : (CV_ACC_STAGES * NOUT <= 128 ? 128 : 256));
+  constexpr uint32_t ACC_COLS = CV_MMA_WARPS * NOUT;
+  constexpr uint32_t TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_smem = smem;
   uint8_t* slots = smem + ((W_BYTES + 1023) & ~1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(slots + CV_SLOTS * CV_SLOT_BYTES);
-  uint64_t* full = bars;                  // [8]
-  uint64_t* empty = bars + 8;             // [8]
-  uint64_t* acc_full = bars + 16;         // [CV_ACC_STAGES]
-  uint64_t* acc_empty = bars + 20;        // [CV_ACC_STAGES]
+  uint64_t* full = bars;                  // [8]   TMA landed in window slot j
+  uint64_t* empty = bars + 8;             // [8]   the (up to) three rows reading slot j are done
+  uint64_t* acc_full = bars + 16;         // [CV_MMA_WARPS]
+  uint64_t* acc_empty = bars + 20;        // [CV_MMA_WARPS]
   uint64_t* wbar = bars + 24;             // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -280,9 +271,9 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], 3);
     }
-    for (int s = 0; s < CV_ACC_STAGES; ++s) {
+    for (int s = 0; s < CV_MMA_WARPS; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], CV_EPI_WARPS);
     }
@@ -308,107 +299,97 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       for (int t = 0; t < 9; ++t) tma_load_2d(w_smem + t * WTAP_BYTES, &tmW, wbar, 0, t * (B_MN ? 64 : NOUT));
       halo_wait_all(a.wait, abort_flag, a.status);
       uint32_t eph = 0;  // per-slot phase bits of the empty barriers
-      bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int tw = (item / a.nstrips) % a.tiles_w;
         const int n = item / (a.nstrips * a.tiles_w);
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+        for (int hc = h0; hc < h1; hc += CV_CHUNK) {
           const int nslots = min(CV_CHUNK, h1 - hc) + 2;
           for (int j = 0; j < nslots; ++j) {
-            ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
-            if (!ok) break;
+            mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
             eph ^= (1u << j);
-            if ((a.debug & 1) && (item != blockIdx.x || hc != h0)) { mbar_arrive(&full[j]); continue; }
             mbar_expect_tx(&full[j], CV_BOXW * 128);
             tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
           }
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- UMMA issuer
-    {
-      constexpr uint32_t idesc = make_idesc_bf16(128, NOUT, 0, B_MN);
-      bool ok = mbar_wait(wbar, 0, abort_flag, a.status);
-      uint32_t fph = 0;  // per-slot phase bits of the full barriers
-      int it = 0;
-      long long pr0 = 0, pr1 = 0, pr2 = 0, pr3 = 0, pr4 = 0;
-      const long long t_begin = clock64();
-      // Descriptors of slot 0 / tap 0; every other operand is a constant byte offset away.
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(slots), 16, 1024);
-      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(w_smem), 8192, 1024)
-                                    : make_smem_desc_sw128(smem_u32(w_smem), 16, 1024);
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        const int s = item % a.nstrips;
-        const int h0 = s * a.rows_per_strip;
-        const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
-          const int n_out = min(CV_CHUNK, h1 - hc);
-          for (int i = 0; i < n_out; ++i, ++it) {
-            const int as = it % CV_ACC_STAGES;
-            const uint32_t aph = (it / CV_ACC_STAGES) & 1u;
-            const long long c0 = clock64();
-            ok = mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, a.status);
-            if (!ok) break;
-            const long long c1 = clock64();
-            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
-              ok = mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
-              if (!ok) break;
-              fph ^= (1u << j);
-            }
-            if (!ok) break;
-            tc_fence_after_sync();
-            const long long c2 = clock64();
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * NOUT);
-            const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
+  } else if (warp <= CV_MMA_WARPS) {
+    // ---------------------------------------------------------------- UMMA issuers
+    // Issuing one tcgen05.mma costs a warp on the order of a hundred cycles, three times the
+    // 32 cycles a 128x64x16 MMA occupies the tensor core.  Four warps therefore issue in
+    // parallel: warp m owns accumulator buffer m and every fourth output row, so no two warps
+    // ever touch the same accumulator.  The whole warp runs the loop (uniform trip counts,
+    // descriptors in uniform registers); one elected lane issues.
+    const int mi = warp - 1;
+    constexpr uint32_t idesc = make_idesc_bf16(128, NOUT, 0, B_MN);
+    mbar_wait(wbar, 0, abort_flag, a.status);
+    uint32_t fph = 0;  // per-slot phase bits of the full barriers
+    int it = 0;
+    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(mi * NOUT);
+    // Descriptors of slot 0 / tap 0; every other operand is a constant byte offset away.
+    const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(slots), 16, 1024);
+    const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem_u32(w_smem), 8192, 1024)
+                                  : make_smem_desc_sw128(smem_u32(w_smem), 16, 1024);
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int s = item % a.nstrips;
+      const int h0 = s * a.rows_per_strip;
+      const int h1 = min(a.H, h0 + a.rows_per_strip);
+      for (int hc = h0; hc < h1; hc += CV_CHUNK) {
+        const int n_out = min(CV_CHUNK, h1 - hc);
+        for (int i = 0; i < n_out; ++i, ++it) {
+          if ((it % CV_MMA_WARPS) != mi) continue;
+          const uint32_t aph = (it / CV_MMA_WARPS) & 1u;
+          mbar_wait(&acc_empty[mi], aph ^ 1u, abort_flag, a.status);
 #pragma unroll
-            for (int dy = 0; dy < 3; ++dy) {
+          for (int d = 0; d < 3; ++d) mbar_wait(&full[i + d], (fph >> (i + d)) & 1u, abort_flag, a.status);
+          tc_fence_after_sync();
+          const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
 #pragma unroll
-              for (int dx = 0; dx < 3; ++dx) {
-                const int wt = B_MN ? ((2 - dy) * 3 + (2 - dx)) : (dy * 3 + dx);
+          for (int dy = 0; dy < 3; ++dy) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  if ((a.debug & 4) && (dy | dx) != 0) continue;
-                  const uint64_t ad = desc_advance(a_row, ((a.debug & 8) ? 0 : dy) * CV_SLOT_BYTES + ((a.debug & 8) ? 0 : dx) * 128 + k * 32);
-                  const uint64_t bd = desc_advance(b_desc0, wt * WTAP_BYTES + k * (B_MN ? 2048 : 32));
-                  umma_f16_elect(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
-                }
+            for (int dx = 0; dx < 3; ++dx) {
+              const int wt = B_MN ? ((2 - dy) * 3 + (2 - dx)) : (dy * 3 + dx);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t ad = desc_advance(a_row, dy * CV_SLOT_BYTES + dx * 128 + k * 32);
+                const uint64_t bd = desc_advance(b_desc0, wt * WTAP_BYTES + k * (B_MN ? 2048 : 32));
+                umma_f16_elect(d_tmem, ad, bd, idesc, (dy | dx | k) != 0 ? 1u : 0u);
               }
             }
-            const long long c3 = clock64();
-            umma_commit_elect(&acc_full[as]);
-            umma_commit_elect(&empty[i]);
-            if (i == n_out - 1) {
-              umma_commit_elect(&empty[i + 1]);
-              umma_commit_elect(&empty[i + 2]);
+          }
+          umma_commit_elect(&acc_full[mi]);
+          // Release the three window slots this row read.  A slot needs three arrivals per
+          // refill; near the ends of a chunk fewer rows read it, and the first reader supplies
+          // the missing ones.
+#pragma unroll
+          for (int d = 0; d < 3; ++d) {
+            const int j = i + d;
+            const int lo = max(0, j - 2), hi = min(n_out - 1, j);
+            umma_commit_elect(&empty[j]);
+            if (i == lo && lane == 0) {
+              for (int e = hi - lo + 1; e < 3; ++e) mbar_arrive(&empty[j]);
             }
-            const long long c4 = clock64();
-            pr0 += c1 - c0; pr1 += c2 - c1; pr2 += c3 - c2; pr3 += c4 - c3; pr4 += 1;
           }
         }
-      }
-      if (a.prof != nullptr && lane == 0) {
-        long long* o = a.prof + blockIdx.x * 8;
-        o[0] = pr0; o[1] = pr1; o[2] = pr2; o[3] = pr3; o[4] = pr4; o[5] = clock64() - t_begin;
+        fph ^= (1u << (n_out + 2)) - 1u;
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (16 warps)
-    // Warp e drains TMEM lane quadrant (warp % 4) and the 16 accumulator columns of group e / 4.
-    const int e = warp - 2;
+    // ---------------------------------------------------------------- epilogue (8 warps)
+    // Warp e drains TMEM lane quadrant (warp % 4) and one half of the accumulator columns.
+    const int e = warp - (1 + CV_MMA_WARPS);
     const int quad = warp & 3;
     const int half = e >> 2;
-    constexpr int CPW = (CV_EPI_WARPS == 16) ? 16 : ((NOUT >= 64) ? 32 : NOUT);   // columns per warp
+    constexpr int CPW = (NOUT >= 64) ? 32 : NOUT;   // columns handled per warp
     const bool active = (half * CPW) < NOUT;
     const int c0 = half * CPW;
     int it = 0;
-    bool ok = true;
     float bias_r[CPW];
     load_bias_regs<CPW>(a, c0, bias_r);
-    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
       const int s = item % a.nstrips;
       const int tw = (item / a.nstrips) % a.tiles_w;
       const int n = item / (a.nstrips * a.tiles_w);
@@ -416,12 +397,11 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       const int h1 = min(a.H, h0 + a.rows_per_strip);
       const int w = tw * CV_TW + quad * 32 + lane;
       for (int h = h0; h < h1; ++h, ++it) {
-        const int as = it % CV_ACC_STAGES;
-        const uint32_t aph = (it / CV_ACC_STAGES) & 1u;
+        const int as = it % CV_MMA_WARPS;
+        const uint32_t aph = (it / CV_MMA_WARPS) & 1u;
         uint4 gsrc[CPW / 8];
         if (active) prefetch_gelu_src<CPW>(a, n, h, w, c0, gsrc);
-        ok = mbar_wait(&acc_full[as], aph, abort_flag, a.status);
-        if (!ok) break;
+        mbar_wait(&acc_full[as], aph, abort_flag, a.status);
         tc_fence_after_sync();
         uint32_t r[CPW];
         if (active) {
@@ -437,7 +417,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[as]);
-        if (!active || w >= a.W || (a.debug & 2)) continue;
+        if (!active || w >= a.W) continue;
         float v[CPW];
 #pragma unroll
         for (int j = 0; j < CPW; ++j) v[j] = __uint_as_float(r[j]);
@@ -567,28 +547,24 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       uint32_t fph = 0;
       int gs = 0;
       uint32_t gph = 0;
-      bool ok = true;
       bool first = true;
       const uint32_t s_addr = smem_u32(slots);
       const uint32_t ones_addr = smem_u32(ones);
       const uint64_t g_desc0 = make_smem_desc_sw128(smem_u32(gtiles), 8192, 1024);
       const uint64_t x_desc128 = make_smem_desc_sw128(s_addr, 128, 1024);            // pair = next pixel
       const uint64_t x_descslot = make_smem_desc_sw128(s_addr, CV_SLOT_BYTES, 1024); // pair = next slot
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
+        for (int hc = h0; hc < h1; hc += CV_CHUNK) {
           const int n_out = min(CV_CHUNK, h1 - hc);
           for (int i = 0; i < n_out; ++i) {
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
-              ok = mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
-              if (!ok) break;
+              mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
               fph ^= (1u << j);
             }
-            if (!ok) break;
-            ok = mbar_wait(&gfull[gs], gph, abort_flag, a.status);
-            if (!ok) break;
+            mbar_wait(&gfull[gs], gph, abort_flag, a.status);
             tc_fence_after_sync();
             const uint64_t bd0 = desc_advance(g_desc0, static_cast<uint32_t>(gs * 16384));
             const uint64_t r0 = desc_advance(x_desc128, static_cast<uint32_t>(i * CV_SLOT_BYTES));
@@ -755,12 +731,6 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
   a.dense_out = static_cast<__nv_bfloat16*>(dense_out);
   a.done_counter = done_counter;
   a.status = status;
-  {
-    const char* dbg = getenv("JB_CONV_DEBUG");
-    a.debug = dbg ? atoi(dbg) : 0;
-    const char* prof = getenv("JB_CONV_PROF_PTR");
-    a.prof = prof ? reinterpret_cast<long long*>(strtoull(prof, nullptr, 10)) : nullptr;
-  }
   if (halo != nullptr) {
     for (int d = 0; d < 9; ++d) {
       a.push.buf[d] = halo->push_buf[d];

@@ -139,13 +139,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
         const int as = it & 1;
         const uint32_t aph = (it >> 1) & 1u;
-        if (!mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, status)) break;
+        mbar_wait(&acc_empty[as], aph ^ 1u, abort_flag, status);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
-        bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb) {
-          ok = mbar_wait(&full[s], ph, abort_flag, status);
-          if (!ok) break;
+          mbar_wait(&full[s], ph, abort_flag, status);
           tc_fence_after_sync();
           const uint64_t ad0 = desc_advance(a_desc0, static_cast<uint32_t>(s * S::STAGE_BYTES));
           const uint64_t bd0 = desc_advance(b_desc0, static_cast<uint32_t>(s * S::STAGE_BYTES));
@@ -162,7 +160,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ph ^= 1u;
           }
         }
-        if (!ok) break;
         umma_commit_elect(&acc_full[as]);
       }
     }

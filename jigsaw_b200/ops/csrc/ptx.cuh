@@ -74,10 +74,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait on an mbarrier phase.  `abort_flag` lives in shared memory and is
 // set by whichever wait of the CTA gives up first; once set, every later wait
-// returns false at once so that all roles fall through to the teardown.
+// returns false at once.  Callers do NOT branch on the result: the role loops keep their
+// uniform trip counts (which lets the compiler hold descriptors and loop state in uniform
+// registers) and simply run to the end without waiting, on whatever data is there; the
+// host sees the error code in the status word and discards the result.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;   // an earlier wait of this CTA gave up: drain without waiting
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {

@@ -1,0 +1,141 @@
+"""Attention parity on CPU/gloo ranks: ring (every topology / save scope / dK-dV routing),
+Ulysses (flat and hierarchical), circulated-input mode, head-parallel projections, masks,
+and conversion to / from the serial layer."""
+
+import itertools
+
+import pytest
+import torch
+
+from dist_utils import assert_close, run_distributed, split
+
+
+def _serial_and_grads(att, x, mask=None):
+    xr = x.clone().requires_grad_(True)
+    y = att(xr, mask) if mask is not None else att(xr)
+    gy = torch.randn(y.shape, generator=torch.Generator().manual_seed(7), dtype=y.dtype)
+    y.backward(gy)
+    return xr, y.detach(), gy
+
+
+def _compare(layer, att, x, xr, y_ref, gy, mesh, what, tol=1e-9):
+    row, col = mesh["row"], mesh["col"]
+    spec = {1: row, 2: col}
+    xl = split(x, spec).requires_grad_(True)
+    y = layer(xl)
+    assert_close(y, split(y_ref, spec), f"{what}: output", tol, tol)
+    y.backward(split(gy, spec))
+    assert_close(xl.grad, split(xr.grad, spec), f"{what}: dx", tol, tol)
+    back = layer.convert_to_torch(mesh)
+    assert_close(back.qkv.weight.data, att.qkv.weight.data, f"{what}: qkv round trip", 0, 0)
+    # parameter gradients: compare through the merged layout
+    C = col.size()
+    gq = layer.qkv.weight.grad
+    if C > 1:
+        from jigsaw_b200._core.placement import gather_dim
+
+        gq = gather_dim(gq, col, 1)
+    heads_local = att.heads // C
+    gq = gq.view(C, 3, heads_local, att.head_dim, att.in_dim).transpose(0, 1).reshape(3 * att.embed_dim, att.in_dim)
+    assert_close(gq, att.qkv.weight.grad, f"{what}: dW_qkv", tol, tol)
+
+
+def _worker_ring(rank, world):
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention, RingAttentionConfig
+
+    mesh = jb.make_process_mesh({"row": 4, "col": 1})
+    torch.manual_seed(0)
+    att = Attention(8, 16, 8, 4, "cpu", dtype=torch.float64, attn_backend="math")
+    x = torch.randn(2, 16, 8, dtype=torch.float64)
+    xr, y_ref, gy = _serial_and_grads(att, x)
+    combos = itertools.product(("ring", "broadcast", "hybrid", "hybrid_broadcast"), ("local", "global"),
+                               ("send_dkv", "gather_dkv"), (False, True))
+    for send_op, scope, back, overlap in combos:
+        cfg = RingAttentionConfig(device="cpu", send_in_forward="kv", send_op=send_op, save_scope=scope,
+                                  send_backward=back, intra_size=2, attn_backend="math", overlap_comm=overlap)
+        layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
+        att.zero_grad()
+        xr, y_ref, gy = _serial_and_grads(att, x)
+        _compare(layer, att, x, xr, y_ref, gy, mesh, f"ring {send_op}/{scope}/{back}/overlap={overlap}")
+    # the layer input circulates and K/V are re-projected on arrival
+    cfg = RingAttentionConfig(device="cpu", send_in_forward="x", attn_backend="math")
+    layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
+    att.zero_grad()
+    xr, y_ref, gy = _serial_and_grads(att, x)
+    _compare(layer, att, x, xr, y_ref, gy, mesh, "ring send_in_forward=X")
+    # no-grad forward keeps nothing
+    with torch.no_grad():
+        y = layer(split(x, {1: mesh["row"]}))
+    assert_close(y, split(y_ref, {1: mesh["row"]}), "ring no_grad", 1e-9, 1e-9)
+    # guards
+    with pytest.raises(ValueError):
+        jb.modules.DistributedAttention(8, 16, 8, 4, 0, "cpu", mesh["col"], mesh["col"], ring=True)
+    with pytest.raises(ValueError):
+        jb.modules.DistributedAttention(8, 16, 8, 4, 0, "cpu", mesh["row"], mesh["col"], ring=True, ulysses=True)
+    with pytest.raises(ValueError):
+        RingAttentionConfig(device="cpu", send_op="nonsense")
+
+
+def _worker_ulysses(rank, world):
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention
+
+    mesh = jb.make_process_mesh({"row": 4, "col": 1})
+    torch.manual_seed(1)
+    att = Attention(8, 32, 8, 8, "cpu", dtype=torch.float64, attn_backend="math", qk_norm=True)
+    x = torch.randn(2, 16, 8, dtype=torch.float64)
+    xr, y_ref, gy = _serial_and_grads(att, x)
+    layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=False, ulysses=True, attn_backend="math")
+    _compare(layer, att, x, xr, y_ref, gy, mesh, "ulysses")
+    for scope in ("local", "global"):
+        att.zero_grad()
+        xr, y_ref, gy = _serial_and_grads(att, x)
+        layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=False, ulysses=True, ulysses_intra_size=2,
+                                            ulysses_inter_save_scope=scope, attn_backend="math")
+        _compare(layer, att, x, xr, y_ref, gy, mesh, f"hierarchical ulysses {scope}")
+    with pytest.raises(ValueError):
+        jb.modules.DistributedAttention(8, 24, 8, 6, 0, "cpu", mesh["row"], mesh["col"], ulysses=True)
+
+
+def _worker_heads(rank, world):
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    torch.manual_seed(2)
+    att = Attention(8, 16, 12, 4, "cpu", dtype=torch.float64, attn_backend="math")
+    x = torch.randn(2, 8, 8, dtype=torch.float64)
+    xr, y_ref, gy = _serial_and_grads(att, x)
+    layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, attn_backend="math")
+    assert layer.heads == 2 and isinstance(layer.qkv, jb.modules.DistributedLinear)
+    _compare(layer, att, x, xr, y_ref, gy, mesh, "ring + head parallel")
+    att.zero_grad()
+    xr, y_ref, gy = _serial_and_grads(att, x)
+    layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=False, ulysses=True, attn_backend="math")
+    _compare(layer, att, x, xr, y_ref, gy, mesh, "ulysses + head parallel")
+    # window attention: no sequence parallelism, extra window axis, additive mask
+    mesh1 = {"row": mesh["col"], "col": mesh["col"]}
+    xw = torch.randn(2, 3, 8, 8, dtype=torch.float64)
+    mask = torch.randn(3, 1, 8, 8, dtype=torch.float64)
+    att.zero_grad()
+    xr = xw.clone().requires_grad_(True)
+    y_ref = att(xr, mask)
+    layer = jb.modules.DistributedAttention(8, 16, 12, 4, 0, "cpu", mesh["row"], mesh["col"], attn_backend="math",
+                                            dtype=torch.float64)
+    conv = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=False, attn_backend="math")
+    y = conv(split(xw, {3: mesh["col"]}), mask)
+    assert_close(y, split(y_ref.detach(), {3: mesh["col"]}), "window attention with mask", 1e-9, 1e-9)
+    assert "ring=False" in repr(conv) and conv.get_parameter_count() == 0
+
+
+def test_ring_attention_all_policies():
+    run_distributed(_worker_ring, 4, timeout=400)
+
+
+def test_ulysses_and_hierarchical():
+    run_distributed(_worker_ulysses, 4)
+
+
+def test_head_parallel_and_window_attention():
+    run_distributed(_worker_heads, 4)
