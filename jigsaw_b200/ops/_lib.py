@@ -60,7 +60,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_conv3x3_c64_wgrad.restype = c_int
     L.jb_halo_pack.argtypes = [
         c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_longlong,  # src is_fp32 strides
-        c_int, c_int, c_int, c_int, c_int,  # NB C H W CP
+        c_int, c_int, c_int, c_int, c_int, c_int,  # NB C H W CP CW
         c_void_p, POINTER(JbHalo), c_void_p, c_void_p,  # dst halo done_counter stream
     ]
     L.jb_halo_pack.restype = c_int

@@ -55,9 +55,11 @@ class Geometry:
         self.nbrs = symm.neighbour_table(group_h, group_w)
         self.sm = _lib.sm_count(device.index if device.index is not None else torch.cuda.current_device())
 
-    def padded(self, channels: int) -> "symm.Block":
+    def padded(self, channels: int, live: int | None = None) -> "symm.Block":
+        """A padded buffer.  ``live`` (< channels) asks for one whose channels beyond ``live`` are
+        and stay zero: such buffers are only ever recycled among themselves."""
         n = self.NB * (self.H + 2) * (self.W + 2) * channels * 2
-        return self.arena.alloc(n, tag=("padded", self.NB, self.H, self.W, channels))
+        return self.arena.alloc(n, tag=("padded", self.NB, self.H, self.W, channels, live))
 
     def halo(self, produce: "symm.Block | None", consume: "symm.Block | None") -> Any:
         return symm.make_halo(self.arena, self.nbrs, produce, consume)
@@ -79,29 +81,35 @@ def chain_kinds(channels: list[tuple[int, int]]) -> list[str] | None:
 
 
 def _prep_weights(kind: str, w: torch.Tensor, b: torch.Tensor | None) -> dict:
-    """Kernel-side weight layouts of one layer (small tensors, rebuilt every step)."""
+    """Kernel-side weight layouts of one layer (small tensors, rebuilt every step).
+
+    Thin layers run on the 64-channel tensor-core kernels with their missing channels
+    zero-filled: the tensor cores have ample headroom there (these layers are bound by the
+    64-channel tensor they read or write), and it keeps every layer on one code path.
+    """
     dev = w.device
     cout, cin = w.shape[0], w.shape[1]
     out: dict = {}
+    wt = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16)                                  # [3,3,co,ci]
     if kind == "mid":
-        out["w"] = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16).contiguous()          # [3,3,co,ci]
+        out["w"] = wt.contiguous()
         out["b"] = None if b is None else b.detach().float().contiguous()
     elif kind == "thin_in":
-        t = torch.zeros(3, 3, 4, 64, device=dev, dtype=torch.float32)
-        t[:, :, :cin] = w.detach().float().permute(2, 3, 1, 0)
-        out["w"] = t                                                                        # [tap, ci, co]
+        t = torch.zeros(3, 3, 64, 64, device=dev, dtype=torch.bfloat16)
+        t[:, :, :, :cin] = wt
+        out["w"] = t
         out["b"] = None if b is None else b.detach().float().contiguous()
     else:  # thin_out
         t = torch.zeros(3, 3, 16, 64, device=dev, dtype=torch.bfloat16)
-        t[:, :, :cout] = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16)
-        out["w"] = t                                                                        # [tap, co(16), ci]
+        t[:, :, :cout] = wt
+        out["w"] = t                                                                        # forward: 16 output columns
         bb = torch.zeros(16, device=dev, dtype=torch.float32)
         if b is not None:
             bb[:cout] = b.detach().float()
         out["b"] = bb
-        d = torch.zeros(3, 3, 4, 64, device=dev, dtype=torch.float32)
-        d[:, :, :cout] = w.detach().float().flip(2, 3).permute(2, 3, 0, 1)
-        out["w_dgrad"] = d                                                                  # mirrored taps, [tap, co, ci]
+        d = torch.zeros(3, 3, 64, 64, device=dev, dtype=torch.bfloat16)
+        d[:, :, :cout] = wt
+        out["w_dgrad"] = d                                                                  # backward: 64 (zero-filled) gradient channels
     return out
 
 
@@ -137,11 +145,12 @@ class _ConvChain(torch.autograd.Function):
             x = x.float()
         prep = [_prep_weights(kinds[i], weights[i], biases[i]) for i in range(n)]
         cin0 = weights[0].shape[1]
-        cp0 = 4 if kinds[0] == "thin_in" else 64
+        cp0 = 64
         # ---- pack the input into the padded layout (+ halo push)
-        a = geom.padded(cp0)
+        cw0 = min(64, (cin0 + 3) // 4 * 4)
+        a = geom.padded(cp0, None if cw0 == 64 else cw0)
         sn, sc, sh, sw = x.stride()
-        _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, cp0, _bp(a),
+        _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, cp0, cw0, _bp(a),
                               geom.halo(a, None), _p(ar.done_counter), st), "halo_pack")
         acts_in: list[symm.Block] = [a]
         pres: list[torch.Tensor | None] = []
@@ -157,15 +166,10 @@ class _ConvChain(torch.autograd.Function):
                 out = torch.empty(NB, H, W, cout, device=x.device, dtype=torch.bfloat16)
             halo = geom.halo(nxt, acts_in[i])
             act = 1 if acts[i] else 0
-            if kinds[i] == "thin_in":
-                _check(L.jb_conv3x3_thin(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
-                                         _p(out) if last else None, NB, H, W, act, halo, _p(ar.done_counter),
-                                         _p(ar.status), geom.sm, st), "conv3x3_thin")
-            else:
-                nout = 16 if kinds[i] == "thin_out" else 64
-                _check(L.jb_conv3x3_c64(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
-                                        _p(out) if last else None, NB, H, W, nout, cout, act, 0, halo,
-                                        _p(ar.done_counter), _p(ar.status), geom.sm, st), "conv3x3_c64")
+            nout = 16 if kinds[i] == "thin_out" else 64
+            _check(L.jb_conv3x3_c64(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
+                                    _p(out) if last else None, NB, H, W, nout, cout, act, 0, halo,
+                                    _p(ar.done_counter), _p(ar.status), geom.sm, st), "conv3x3_c64")
             pres.append(pre)
             if nxt is not None:
                 acts_in.append(nxt)
@@ -192,10 +196,11 @@ class _ConvChain(torch.autograd.Function):
         dev = gout.device
         grads: list[torch.Tensor | None] = [None] * (2 * n)
         cout_last = ctx.shapes[-1][0]
-        cpg = 4 if kinds[-1] == "thin_out" else 64
-        g = geom.padded(cpg)
+        cpg = 64
+        cwg = min(64, (cout_last + 3) // 4 * 4)
+        g = geom.padded(cpg, None if cwg == 64 else cwg)
         sn, sc, sh, sw = gout.stride()
-        _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, cpg,
+        _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, cpg, cwg,
                               _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
         scratch = None
         gx = None
@@ -205,25 +210,16 @@ class _ConvChain(torch.autograd.Function):
             # gradient of the layer above flows through the GELU that precedes this layer's input
             src = pres[i - 1] if i > 0 else None
             # ---- weight / bias gradient
-            if kind == "mid":
-                gw = torch.empty(64, 64, 3, 3, device=dev, dtype=torch.float32)
-                gb = torch.empty(64, device=dev, dtype=torch.float32)
-                if scratch is None:
-                    scratch = torch.empty(L.jb_conv3x3_wgrad_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
-                _check(L.jb_conv3x3_c64_wgrad(_bp(acts_in[i]), _bp(g), _p(gw), _p(gb), _p(scratch), NB, H, W,
-                                              geom.halo(None, g), _p(ar.status), geom.sm, st), "wgrad")
-            else:
-                raw = torch.empty(28, 64, device=dev, dtype=torch.float32)
-                if kind == "thin_in":
-                    _check(L.jb_wgrad_thin(_bp(g), _bp(acts_in[i]), _p(raw), NB, H, W, 1, geom.halo(None, acts_in[i]),
-                                           _p(ar.status), geom.sm, st), "wgrad_thin")
-                    gw = raw[:27].view(9, 3, 64)[:, :cin].permute(2, 1, 0).reshape(64, cin, 3, 3).contiguous()
-                    gb = raw[27].clone()
-                else:
-                    _check(L.jb_wgrad_thin(_bp(acts_in[i]), _bp(g), _p(raw), NB, H, W, -1, geom.halo(None, g),
-                                           _p(ar.status), geom.sm, st), "wgrad_thin")
-                    gw = raw[:27].view(9, 3, 64)[:, :cout].permute(1, 2, 0).reshape(cout, 64, 3, 3).contiguous()
-                    gb = gout.float().sum(dim=(0, 2, 3))
+            gw = torch.empty(64, 64, 3, 3, device=dev, dtype=torch.float32)
+            gb = torch.empty(64, device=dev, dtype=torch.float32)
+            if scratch is None:
+                scratch = torch.empty(L.jb_conv3x3_wgrad_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
+            _check(L.jb_conv3x3_c64_wgrad(_bp(acts_in[i]), _bp(g), _p(gw), _p(gb), _p(scratch), NB, H, W,
+                                          geom.halo(None, g), _p(ar.status), geom.sm, st), "wgrad")
+            if kind == "thin_in":
+                gw = gw[:, :cin].contiguous()
+            elif kind == "thin_out":
+                gw, gb = gw[:cout].contiguous(), gb[:cout].contiguous()
             grads[2 * i] = gw
             grads[2 * i + 1] = gb if ctx.has_bias[i] else None
             # ---- data gradient
@@ -239,12 +235,9 @@ class _ConvChain(torch.autograd.Function):
             gnext = geom.padded(64)
             halo = geom.halo(gnext, g)
             gsrc = src if acts[i - 1] else None
-            if kind == "thin_out":
-                _check(L.jb_conv3x3_thin(_bp(g), _p(prep[i]["w_dgrad"]), None, _p(gsrc), None, _bp(gnext), None, NB, H, W,
-                                         0, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad_thin")
-            else:
-                _check(L.jb_conv3x3_c64(_bp(g), _p(prep[i]["w"]), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 64, 64,
-                                        0, 1, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
+            wd = prep[i]["w_dgrad"] if kind == "thin_out" else prep[i]["w"]
+            _check(L.jb_conv3x3_c64(_bp(g), _p(wd), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 64, 64,
+                                    0, 1, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
             ar.free(g)
             g = gnext
         ctx.holder.release()

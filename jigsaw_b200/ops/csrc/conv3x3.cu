@@ -36,7 +36,10 @@ constexpr int CV_SLOT_BYTES = 136 * 128;          // 17 KiB, keeps slots 1024-by
 constexpr int CV_SLOTS = 8;
 constexpr int CV_CHUNK = 6;                       // output rows per window refill
 constexpr int CV_MMA_WARPS = 4;                   // MMA-issuing warps = accumulator buffers in TMEM
-constexpr int CV_EPI_WARPS = 8;                   // two per TMEM lane quadrant
+#ifndef JB_CV_EPI_WARPS
+#define JB_CV_EPI_WARPS 8
+#endif
+constexpr int CV_EPI_WARPS = JB_CV_EPI_WARPS;      // two or four per TMEM lane quadrant
 constexpr int CV_THREADS = 32 * (1 + CV_MMA_WARPS + CV_EPI_WARPS);  // + one TMA producer warp
 
 struct HaloPush {
@@ -383,7 +386,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     const int e = warp - (1 + CV_MMA_WARPS);
     const int quad = warp & 3;
     const int half = e >> 2;
-    constexpr int CPW = (NOUT >= 64) ? 32 : NOUT;   // columns handled per warp
+    constexpr int CPW = (NOUT >= 64) ? (NOUT * 4 / CV_EPI_WARPS) : NOUT;   // columns handled per warp
     const bool active = (half * CPW) < NOUT;
     const int c0 = half * CPW;
     int it = 0;

@@ -22,7 +22,9 @@ struct PackArgs {
   int src_is_fp32;
   long long sn, sc, sh, sw;   // element strides of the source
   int NB, C, H, W;            // logical shape
-  int CP;                     // channels of the padded buffer (>= C, multiple of 4)
+  int CP;                     // channels (pixel stride) of the padded buffer, multiple of 4
+  int CW;                     // channels actually written (>= C, multiple of 4, <= CP); the rest of a
+                              // pixel is left as it is (callers keep such buffers zero there)
   __nv_bfloat16* dst;         // [NB][H+2][W+2][CP]
   HaloPush push;
   unsigned int* done_counter;
@@ -31,15 +33,15 @@ struct PackArgs {
 // One block handles 32 pixels of one row for all channels, going through shared memory so that
 // both the (possibly channel-strided) reads and the channel-contiguous writes are coalesced.
 __global__ void __launch_bounds__(256) halo_pack_kernel(const PackArgs a) {
-  extern __shared__ float tile[];  // [32 pixels][CP + 1]
+  extern __shared__ float tile[];  // [32 pixels][CW + 1]
   const int wt = blockIdx.x, h = blockIdx.y, n = blockIdx.z;
   const int w0 = wt * 32;
-  const int ld = a.CP + 1;
+  const int ld = a.CW + 1;
   const int tid = threadIdx.x;
   if (a.sc == 1) {
     // channel-contiguous source: consecutive threads read consecutive channels
-    for (int i = tid; i < 32 * a.CP; i += 256) {
-      const int p = i / a.CP, c = i % a.CP;
+    for (int i = tid; i < 32 * a.CW; i += 256) {
+      const int p = i / a.CW, c = i % a.CW;
       float v = 0.f;
       if (c < a.C && w0 + p < a.W) {
         const long long off = n * a.sn + c * a.sc + h * a.sh + static_cast<long long>(w0 + p) * a.sw;
@@ -50,7 +52,7 @@ __global__ void __launch_bounds__(256) halo_pack_kernel(const PackArgs a) {
     }
   } else {
     // pixel-contiguous source (NCHW): consecutive threads read consecutive pixels
-    for (int i = tid; i < 32 * a.CP; i += 256) {
+    for (int i = tid; i < 32 * a.CW; i += 256) {
       const int c = i / 32, p = i % 32;
       float v = 0.f;
       if (c < a.C && w0 + p < a.W) {
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(256) halo_pack_kernel(const PackArgs a) {
   __syncthreads();
   const long long prow = static_cast<long long>(a.W + 2) * a.CP;
   const long long pimg = static_cast<long long>(a.H + 2) * prow;
-  const int groups = a.CP / 4;  // 4 channels = 8 bytes per store
+  const int groups = a.CW / 4;  // 4 channels = 8 bytes per store
   for (int i = tid; i < 32 * groups; i += 256) {
     const int p = i / groups, g = i % groups;
     const int w = w0 + p;
@@ -266,21 +268,22 @@ static void fill_halo(HaloPush* push, HaloWait* wait, const JbHalo* halo) {
 }
 
 // Copy a strided (NB, C, H, W) tensor into a padded NHWC bf16 buffer [NB][H+2][W+2][CP] and push
-// the edge pixels to the neighbours.  Strides are in elements.  CP in {4, 64} (multiple of 4).
+// the edge pixels to the neighbours.  Strides are in elements.  Only the first CW channels of a pixel
+// are written.
 extern "C" int jb_halo_pack(const void* src, int src_is_fp32, long long sn, long long sc, long long sh,
-                            long long sw, int NB, int C, int H, int W, int CP, void* dst, const JbHalo* halo,
+                            long long sw, int NB, int C, int H, int W, int CP, int CW, void* dst, const JbHalo* halo,
                             unsigned int* done_counter, void* stream) {
-  if (CP % 4 != 0 || C > CP || CP > 256) return -1;
+  if (CP % 4 != 0 || CW % 4 != 0 || C > CW || CW > CP || CP > 256) return -1;
   PackArgs a{};
   a.src = src; a.src_is_fp32 = src_is_fp32;
   a.sn = sn; a.sc = sc; a.sh = sh; a.sw = sw;
-  a.NB = NB; a.C = C; a.H = H; a.W = W; a.CP = CP;
+  a.NB = NB; a.C = C; a.H = H; a.W = W; a.CP = CP; a.CW = CW;
   a.dst = static_cast<__nv_bfloat16*>(dst);
   a.done_counter = done_counter;
   fill_halo(&a.push, nullptr, halo);
   dim3 grid((W + 31) / 32, H, NB);
   if (grid.y > 65535 || grid.z > 65535) return -1;
-  halo_pack_kernel<<<grid, 256, 32 * (CP + 1) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
+  halo_pack_kernel<<<grid, 256, 32 * (CW + 1) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
