@@ -128,7 +128,9 @@ def sparse_exchange(
     recvs = {p: t for p, t in recvs.items() if p != me and t.numel() > 0}
     works: list[dist.Work | None] = []
     if comm is CommOp.ALL_TO_ALL:
-        some = next(iter(sends.values()), None) or next(iter(recvs.values()), None)
+        some = next(iter(sends.values()), None)
+        if some is None:
+            some = next(iter(recvs.values()), None)
         if some is None:
             # keep the collective matched on every rank: an all-empty all-to-all
             dev = get_device_of_process_group(group)
