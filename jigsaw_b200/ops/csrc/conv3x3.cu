@@ -33,8 +33,11 @@ namespace jb {
 constexpr int CV_TW = 128;                        // output pixels per tile
 constexpr int CV_BOXW = 130;                      // input pixels per slot (tile + 2)
 constexpr int CV_SLOT_BYTES = 136 * 128;          // 17 KiB, keeps slots 1024-byte aligned
-constexpr int CV_SLOTS = 8;
-constexpr int CV_CHUNK = 6;                       // output rows per window refill
+constexpr int CV_SLOTS = 7;                       // window slots of the forward / data-gradient kernel
+constexpr int CV_CHUNK = 5;                       // output rows per window refill (slots - 2)
+constexpr int WG_SLOTS = 8;                       // window of the weight-gradient kernel
+constexpr int WG_CHUNK = 6;
+constexpr int CV_STAGE_BYTES = 128 * 128;         // one 128-pixel x 64-channel bf16 tile
 constexpr int CV_MMA_WARPS = 4;                   // MMA-issuing warps = accumulator buffers in TMEM
 #ifndef JB_CV_EPI_WARPS
 #define JB_CV_EPI_WARPS 8
@@ -120,12 +123,12 @@ __device__ __forceinline__ void halo_publish(const HaloPush& p, unsigned int* do
 
 // Store 32 (or fewer) consecutive channels of one pixel into the interior of the local padded
 // buffer and, for pixels on the tile edge, into the matching border of the neighbours.
-template <int NV>  // NV = number of uint4 (8 channels each)
+template <int NV, bool LOCAL = true>  // NV = number of uint4 (8 channels each); LOCAL: also store the interior
 __device__ __forceinline__ void store_padded_with_halo(const ConvArgs& a, const uint4 (&v)[NV], int n, int h, int w,
                                                        int c0) {
   const long long prow = static_cast<long long>(a.W + 2) * 64;
   const long long pimg = static_cast<long long>(a.H + 2) * prow;
-  {
+  if (LOCAL) {
     __nv_bfloat16* dst = a.padded_out + n * pimg + (h + 1) * prow + static_cast<long long>(w + 1) * 64 + c0;
 #pragma unroll
     for (int j = 0; j < NV; ++j) reinterpret_cast<uint4*>(dst)[j] = v[j];
@@ -249,27 +252,37 @@ __device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW]
 template <int NOUT, int B_MN>
 __global__ void __launch_bounds__(CV_THREADS, 1)
 conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
+                  const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmAux,
                   const ConvArgs a) {
   constexpr int WTAP_BYTES = (B_MN ? 64 : NOUT) * 128;
   constexpr int W_BYTES = 9 * WTAP_BYTES;
   constexpr uint32_t ACC_COLS = CV_MMA_WARPS * NOUT;
   constexpr uint32_t TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
+  // Wide layers stage their output tiles in shared memory and write them with TMA stores
+  // (full lines, one request per tile); they also fetch the GELU'-source tile with TMA.
+  constexpr bool STAGED = (NOUT == 64);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_smem = smem;
   uint8_t* slots = smem + ((W_BYTES + 1023) & ~1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + CV_SLOTS * CV_SLOT_BYTES);
+  uint8_t* stage_out = slots + CV_SLOTS * CV_SLOT_BYTES;           // [128 px][64 ch] padded-output tile
+  uint8_t* stage_aux = stage_out + (STAGED ? CV_STAGE_BYTES : 0);  // dense output tile, or GELU'-source tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_aux + (STAGED ? CV_STAGE_BYTES : 0));
   uint64_t* full = bars;                  // [8]   TMA landed in window slot j
   uint64_t* empty = bars + 8;             // [8]   the (up to) three rows reading slot j are done
   uint64_t* acc_full = bars + 16;         // [CV_MMA_WARPS]
   uint64_t* acc_empty = bars + 20;        // [CV_MMA_WARPS]
   uint64_t* wbar = bars + 24;             // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
+  uint64_t* src_full = bars + 25;         // [1]   GELU'-source tile landed
+  uint64_t* src_empty = bars + 26;        // [1]   ... and has been read by every epilogue warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 27);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int items = a.NB * a.tiles_w * a.nstrips;
+  const bool has_src = STAGED && a.gelu_src != nullptr;
+  const bool aux_out = STAGED && (a.dense_pre != nullptr || a.dense_out != nullptr);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) {
@@ -281,6 +294,8 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       mbar_init(&acc_empty[s], CV_EPI_WARPS);
     }
     mbar_init(wbar, 1);
+    mbar_init(src_full, 1);
+    mbar_init(src_empty, CV_EPI_WARPS);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmIn);
@@ -301,7 +316,8 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       mbar_expect_tx(wbar, W_BYTES);
       for (int t = 0; t < 9; ++t) tma_load_2d(w_smem + t * WTAP_BYTES, &tmW, wbar, 0, t * (B_MN ? 64 : NOUT));
       halo_wait_all(a.wait, abort_flag, a.status);
-      uint32_t eph = 0;  // per-slot phase bits of the empty barriers
+      uint32_t eph = 0;   // per-slot phase bits of the empty barriers
+      uint32_t sph = 0;   // phase of src_empty
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int tw = (item / a.nstrips) % a.tiles_w;
@@ -309,12 +325,22 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
         for (int hc = h0; hc < h1; hc += CV_CHUNK) {
-          const int nslots = min(CV_CHUNK, h1 - hc) + 2;
-          for (int j = 0; j < nslots; ++j) {
-            mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
-            eph ^= (1u << j);
-            mbar_expect_tx(&full[j], CV_BOXW * 128);
-            tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
+          const int n_out = min(CV_CHUNK, h1 - hc);
+          for (int i = 0; i < n_out; ++i) {
+            if (*abort_flag) break;          // after a timeout: issue nothing more
+            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
+              mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status, 10 + j);
+              eph ^= (1u << j);
+              mbar_expect_tx(&full[j], CV_BOXW * 128);
+              tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
+            }
+            if (has_src) {
+              mbar_wait(src_empty, sph ^ 1u, abort_flag, a.status, 20);
+              if (*abort_flag) break;
+              sph ^= 1u;
+              mbar_expect_tx(src_full, CV_STAGE_BYTES);
+              tma_load_4d(stage_aux, &tmAux, src_full, 0, tw * CV_TW, hc + i, n);
+            }
           }
         }
       }
@@ -328,7 +354,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     // descriptors in uniform registers); one elected lane issues.
     const int mi = warp - 1;
     constexpr uint32_t idesc = make_idesc_bf16(128, NOUT, 0, B_MN);
-    mbar_wait(wbar, 0, abort_flag, a.status);
+    mbar_wait(wbar, 0, abort_flag, a.status, 1);
     uint32_t fph = 0;  // per-slot phase bits of the full barriers
     int it = 0;
     const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(mi * NOUT);
@@ -343,11 +369,15 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       for (int hc = h0; hc < h1; hc += CV_CHUNK) {
         const int n_out = min(CV_CHUNK, h1 - hc);
         for (int i = 0; i < n_out; ++i, ++it) {
+          // Every issuing warp follows every refill of every slot, also for rows it does not
+          // own: a parity wait can only tell the current phase from the previous one, so a warp
+          // that skipped a refill could mistake a stale phase for the one it needs.
+          for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j)
+            mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status, 40 + j);
           if ((it % CV_MMA_WARPS) != mi) continue;
           const uint32_t aph = (it / CV_MMA_WARPS) & 1u;
-          mbar_wait(&acc_empty[mi], aph ^ 1u, abort_flag, a.status);
-#pragma unroll
-          for (int d = 0; d < 3; ++d) mbar_wait(&full[i + d], (fph >> (i + d)) & 1u, abort_flag, a.status);
+          mbar_wait(&acc_empty[mi], aph ^ 1u, abort_flag, a.status, 30 + mi);
+          if (*abort_flag) continue;         // after a timeout: issue nothing more
           tc_fence_after_sync();
           const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
 #pragma unroll
@@ -382,14 +412,19 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- epilogue (8 warps)
-    // Warp e drains TMEM lane quadrant (warp % 4) and one half of the accumulator columns.
+    // Warp e drains TMEM lane quadrant (warp % 4) and one half of the accumulator columns:
+    // thread = (pixel quad * 32 + lane, CPW consecutive channels).
     const int e = warp - (1 + CV_MMA_WARPS);
     const int quad = warp & 3;
     const int half = e >> 2;
     constexpr int CPW = (NOUT >= 64) ? (NOUT * 4 / CV_EPI_WARPS) : NOUT;   // columns handled per warp
+    constexpr int EPI_THREADS = 32 * CV_EPI_WARPS;
     const bool active = (half * CPW) < NOUT;
     const int c0 = half * CPW;
+    const bool leader = (e == 0 && lane == 0);
+    const int m = quad * 32 + lane;                     // pixel of the tile = row of the staging tiles
     int it = 0;
+    uint32_t sfph = 0;                                  // phase of src_full
     float bias_r[CPW];
     load_bias_regs<CPW>(a, c0, bias_r);
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
@@ -398,13 +433,28 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
       const int n = item / (a.nstrips * a.tiles_w);
       const int h0 = s * a.rows_per_strip;
       const int h1 = min(a.H, h0 + a.rows_per_strip);
-      const int w = tw * CV_TW + quad * 32 + lane;
+      const int w = tw * CV_TW + m;
       for (int h = h0; h < h1; ++h, ++it) {
         const int as = it % CV_MMA_WARPS;
         const uint32_t aph = (it / CV_MMA_WARPS) & 1u;
         uint4 gsrc[CPW / 8];
-        if (active) prefetch_gelu_src<CPW>(a, n, h, w, c0, gsrc);
-        mbar_wait(&acc_full[as], aph, abort_flag, a.status);
+        if constexpr (STAGED) {
+          if (has_src) {
+            // the tile of pre-activations whose GELU' multiplies this gradient tile
+            mbar_wait(src_full, sfph, abort_flag, a.status, 50);
+            sfph ^= 1u;
+#pragma unroll
+            for (int q = 0; q < CPW / 8; ++q) {
+              const int chunk = (c0 / 8 + q) ^ (m & 7);
+              gsrc[q] = *reinterpret_cast<const uint4*>(stage_aux + m * 128 + chunk * 16);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(src_empty);
+          }
+        } else {
+          if (active) prefetch_gelu_src<CPW>(a, n, h, w, c0, gsrc);
+        }
+        mbar_wait(&acc_full[as], aph, abort_flag, a.status, 60 + as);
         tc_fence_after_sync();
         uint32_t r[CPW];
         if (active) {
@@ -420,13 +470,72 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[as]);
-        if (!active || w >= a.W) continue;
         float v[CPW];
 #pragma unroll
         for (int j = 0; j < CPW; ++j) v[j] = __uint_as_float(r[j]);
-        conv_epilogue<CPW>(a, v, bias_r, gsrc, n, h, w, c0);
+        if constexpr (!STAGED) {
+          if (!active || w >= a.W) continue;
+          conv_epilogue<CPW>(a, v, bias_r, gsrc, n, h, w, c0);
+        } else {
+          // ---- math in registers
+#pragma unroll
+          for (int j = 0; j < CPW; ++j) v[j] += bias_r[j];
+          if (has_src) {
+#pragma unroll
+            for (int q = 0; q < CPW / 8; ++q) {
+              const uint32_t uu[4] = {gsrc[q].x, gsrc[q].y, gsrc[q].z, gsrc[q].w};
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
+                v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
+                v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
+              }
+            }
+          }
+          uint4 aux_v[CPW / 8], out_v[CPW / 8];
+          const bool aux_is_pre = a.dense_pre != nullptr;
+          if (aux_out && aux_is_pre) {
+#pragma unroll
+            for (int q = 0; q < CPW / 8; ++q) {
+              aux_v[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              aux_v[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              aux_v[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              aux_v[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            }
+          }
+          if (a.act == 1) {
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+          }
+#pragma unroll
+          for (int q = 0; q < CPW / 8; ++q) {
+            out_v[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            out_v[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            out_v[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            out_v[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          }
+          // ---- staging tiles: wait until the previous tile's TMA stores have read them
+          if (leader) bulk_wait_read_all();
+          named_barrier(1, EPI_THREADS);
+#pragma unroll
+          for (int q = 0; q < CPW / 8; ++q) {
+            const int chunk = (c0 / 8 + q) ^ (m & 7);
+            if (a.padded_out != nullptr) *reinterpret_cast<uint4*>(stage_out + m * 128 + chunk * 16) = out_v[q];
+            if (aux_out) *reinterpret_cast<uint4*>(stage_aux + m * 128 + chunk * 16) = aux_is_pre ? aux_v[q] : out_v[q];
+          }
+          // edge pixels go straight to the neighbours' borders
+          if (a.padded_out != nullptr && w < a.W) store_padded_with_halo<CPW / 8, false>(a, out_v, n, h, w, c0);
+          fence_proxy_async_smem();
+          named_barrier(2, EPI_THREADS);
+          if (leader) {
+            if (a.padded_out != nullptr) tma_store_4d(&tmOut, stage_out, 0, tw * CV_TW + 1, h + 1, n);
+            if (aux_out) tma_store_4d(&tmAux, stage_aux, 0, tw * CV_TW, h, n);
+            bulk_commit_group();
+          }
+        }
       }
     }
+    if (STAGED && leader) bulk_wait_all();
   }
 
   tc_fence_before_sync();
@@ -464,7 +573,7 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* slots = smem;
-  uint8_t* gtiles = slots + CV_SLOTS * CV_SLOT_BYTES;
+  uint8_t* gtiles = slots + WG_SLOTS * CV_SLOT_BYTES;
   uint8_t* ones = gtiles + WG_GSTAGES * 16384;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ones + 2048);
   uint64_t* full = bars;              // [8]
@@ -520,8 +629,8 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         const int n = item / (a.nstrips * a.tiles_w);
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1 && ok; hc += CV_CHUNK) {
-          const int n_out = min(CV_CHUNK, h1 - hc);
+        for (int hc = h0; hc < h1 && ok; hc += WG_CHUNK) {
+          const int n_out = min(WG_CHUNK, h1 - hc);
           for (int i = 0; i < n_out && ok; ++i) {
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
               ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
@@ -560,8 +669,8 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         const int s = item % a.nstrips;
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1; hc += CV_CHUNK) {
-          const int n_out = min(CV_CHUNK, h1 - hc);
+        for (int hc = h0; hc < h1; hc += WG_CHUNK) {
+          const int n_out = min(WG_CHUNK, h1 - hc);
           for (int i = 0; i < n_out; ++i) {
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
               mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
@@ -681,11 +790,11 @@ static int padded_tmap(CUtensorMap* tm, const void* base, int NB, int H, int W, 
   return make_tmap_bf16(tm, base, 4, dims, strides, box);
 }
 
-static void choose_strips(int H, int NB, int tiles_w, int sm_count, int* rows_per_strip, int* nstrips) {
-  // Strips of a multiple of CV_CHUNK rows; aim for >= 8 work items per CTA when the tile allows it.
-  int rps = 48;
-  while (rps > CV_CHUNK && static_cast<long long>(NB) * tiles_w * ((H + rps - 1) / rps) < 8LL * sm_count) rps -= CV_CHUNK;
-  if (rps > H) rps = ((H + CV_CHUNK - 1) / CV_CHUNK) * CV_CHUNK;
+static void choose_strips(int H, int NB, int tiles_w, int sm_count, int chunk, int* rows_per_strip, int* nstrips) {
+  // Strips of a multiple of `chunk` rows; aim for >= 8 work items per CTA when the tile allows it.
+  int rps = 8 * chunk;
+  while (rps > chunk && static_cast<long long>(NB) * tiles_w * ((H + rps - 1) / rps) < 8LL * sm_count) rps -= chunk;
+  if (rps > H) rps = ((H + chunk - 1) / chunk) * chunk;
   *rows_per_strip = rps;
   *nstrips = (H + rps - 1) / rps;
 }
@@ -724,7 +833,7 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
   ConvArgs a{};
   a.NB = NB; a.H = H; a.W = W;
   a.tiles_w = (W + CV_TW - 1) / CV_TW;
-  choose_strips(H, NB, a.tiles_w, sm_count, &a.rows_per_strip, &a.nstrips);
+  choose_strips(H, NB, a.tiles_w, sm_count, CV_CHUNK, &a.rows_per_strip, &a.nstrips);
   a.cout_real = cout_real;
   a.bias = bias;
   a.gelu_src = static_cast<const __nv_bfloat16*>(gelu_src);
@@ -745,27 +854,42 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
     a.wait.epoch = halo->wait_epoch;
     a.wait.enabled = halo->wait_enabled;
   }
+  // Output / auxiliary tensor maps of the staged (64-column) kernels.
+  CUtensorMap tmOut = tmIn, tmAux = tmIn;
+  if (nout_pad == 64) {
+    const void* aux = gelu_src ? gelu_src : (dense_pre ? static_cast<const void*>(dense_pre) : static_cast<const void*>(dense_out));
+    const int n_aux = (gelu_src != nullptr) + (dense_pre != nullptr) + (dense_out != nullptr);
+    if (n_aux > 1 || (dense_out != nullptr && cout_real != 64)) return -1;
+    // hide the right border column so that a partial last tile never writes into the halo
+    if (padded_out != nullptr && padded_tmap(&tmOut, padded_out, NB, H, W, CV_TW, 1) != 0) return -2;
+    if (aux != nullptr) {
+      uint64_t dims[4] = {64, static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(NB)};
+      uint64_t strides[3] = {128, static_cast<uint64_t>(W) * 128, static_cast<uint64_t>(H) * W * 128};
+      uint32_t box[4] = {64, CV_TW, 1, 1};
+      if (make_tmap_bf16(&tmAux, aux, 4, dims, strides, box) != 0) return -2;
+    }
+  }
   const int items = NB * a.tiles_w * a.nstrips;
   const int grid = items < sm_count ? items : sm_count;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  constexpr int SMEM64 = 9 * 8192 + CV_SLOTS * CV_SLOT_BYTES + 512 + 1024;
+  constexpr int SMEM64 = 9 * 8192 + CV_SLOTS * CV_SLOT_BYTES + 2 * CV_STAGE_BYTES + 512 + 1024;
   constexpr int SMEM16 = ((9 * 2048 + 1023) & ~1023) + CV_SLOTS * CV_SLOT_BYTES + 512 + 1024;
   cudaError_t e;
   if (mode == 1) {
     auto k = conv3x3_tc_kernel<64, 1>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM64);
     if (e != cudaSuccess) return -3;
-    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, a);
+    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, tmOut, tmAux, a);
   } else if (nout_pad == 64) {
     auto k = conv3x3_tc_kernel<64, 0>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM64);
     if (e != cudaSuccess) return -3;
-    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, a);
+    k<<<grid, CV_THREADS, SMEM64, st>>>(tmIn, tmW, tmOut, tmAux, a);
   } else {
     auto k = conv3x3_tc_kernel<16, 0>;
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM16);
     if (e != cudaSuccess) return -3;
-    k<<<grid, CV_THREADS, SMEM16, st>>>(tmIn, tmW, a);
+    k<<<grid, CV_THREADS, SMEM16, st>>>(tmIn, tmW, tmOut, tmAux, a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -788,7 +912,7 @@ extern "C" int jb_conv3x3_c64_wgrad(const void* x_padded, const void* gy_padded,
   WgradArgs a{};
   a.NB = NB; a.H = H; a.W = W;
   a.tiles_w = (W + CV_TW - 1) / CV_TW;
-  choose_strips(H, NB, a.tiles_w, sm_count, &a.rows_per_strip, &a.nstrips);
+  choose_strips(H, NB, a.tiles_w, sm_count, WG_CHUNK, &a.rows_per_strip, &a.nstrips);
   a.partials = scratch;
   a.status = status;
   if (halo != nullptr) {
@@ -799,7 +923,7 @@ extern "C" int jb_conv3x3_c64_wgrad(const void* x_padded, const void* gy_padded,
   const int items = NB * a.tiles_w * a.nstrips;
   const int grid = items < sm_count ? items : sm_count;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  constexpr int SMEM = CV_SLOTS * CV_SLOT_BYTES + WG_GSTAGES * 16384 + 2048 + 256 + 1024;
+  constexpr int SMEM = WG_SLOTS * CV_SLOT_BYTES + WG_GSTAGES * 16384 + 2048 + 256 + 1024;
   if (cudaFuncSetAttribute(conv3x3_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
     return -3;
   conv3x3_wgrad_kernel<<<grid, WG_THREADS, SMEM, st>>>(tmX, tmG, a);

@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // registers) and simply run to the end without waiting, on whatever data is there; the
 // host sees the error code in the status word and discards the result.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+                                          int* status, int where = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;   // an earlier wait of this CTA gave up: drain without waiting
   const uint64_t t0 = globaltimer_ns();
@@ -90,7 +90,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, JB_OK, JB_ERR_MBAR_TIMEOUT);
+        if (status && atomicCAS(status, JB_OK, JB_ERR_MBAR_TIMEOUT) == JB_OK) {
+          status[1] = where;                 // which wait gave up (kernel-specific code)
+          status[2] = static_cast<int>(blockIdx.x);
+          status[3] = static_cast<int>(threadIdx.x);
+        }
         return false;
       }
     }
@@ -131,6 +135,23 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// TMA store of a shared-memory tile (bulk async-group completion).  Coordinates beyond the
+// tensor's extents are clipped, never written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(m), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All committed bulk stores have finished READING their shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All committed bulk stores have completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Barrier among `count` threads (a multiple of 32) of the CTA; id 1..15 (0 is __syncthreads).
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // ---------------------------------------------------------------- TMEM
