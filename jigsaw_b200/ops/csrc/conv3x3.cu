@@ -40,7 +40,7 @@ constexpr int WG_CHUNK = 6;
 constexpr int CV_STAGE_BYTES = 128 * 128;         // one 128-pixel x 64-channel bf16 tile
 constexpr int CV_MMA_WARPS = 4;                   // MMA-issuing warps = accumulator buffers in TMEM
 #ifndef JB_CV_EPI_WARPS
-#define JB_CV_EPI_WARPS 8
+#define JB_CV_EPI_WARPS 16
 #endif
 constexpr int CV_EPI_WARPS = JB_CV_EPI_WARPS;      // two or four per TMEM lane quadrant
 constexpr int CV_THREADS = 32 * (1 + CV_MMA_WARPS + CV_EPI_WARPS);  // + one TMA producer warp
@@ -67,8 +67,9 @@ struct ConvArgs {
   int cout_real;           // channels actually stored by the dense outputs
   // epilogue
   const float* bias;               // [N] fp32 or null
-  const __nv_bfloat16* gelu_src;   // dense [NB][H][W][64]: multiply result by GELU'(src) (data gradient)
-  __nv_bfloat16* dense_pre;        // dense [NB][H][W][64]: value before the activation (saved for backward)
+  const __nv_bfloat16* gelu_src;   // dense [NB][H][W][64]: multiply the result by it (data gradient: the saved
+                                   // derivative of the activation that follows the previous layer)
+  __nv_bfloat16* dense_pre;        // dense [NB][H][W][64]: act'(value before the activation), saved for backward
   int act;                         // 1: GELU after bias
   __nv_bfloat16* padded_out;       // padded [NB][H+2][W+2][64] output (interior) + halo push
   __nv_bfloat16* dense_out;        // dense [NB][H][W][cout_real] output
@@ -193,26 +194,27 @@ __device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW]
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
         const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
-        v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
-        v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
+        v[q * 8 + 2 * p] *= __low2float(b2);
+        v[q * 8 + 2 * p + 1] *= __high2float(b2);
       }
     }
   }
-  if (a.dense_pre != nullptr) {
-    uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
-#pragma unroll
-    for (int q = 0; q < CPW / 8; ++q) {
-      uint4 o;
-      o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-      o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-      o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-      o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-      dst[q] = o;
-    }
-  }
   if (a.act == 1) {
+    float d[CPW];
 #pragma unroll
-    for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+    for (int j = 0; j < CPW; ++j) gelu_erf_with_grad(v[j], v[j], d[j]);
+    if (a.dense_pre != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
+#pragma unroll
+      for (int q = 0; q < CPW / 8; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(d[q * 8 + 0], d[q * 8 + 1]);
+        o.y = pack_bf16x2(d[q * 8 + 2], d[q * 8 + 3]);
+        o.z = pack_bf16x2(d[q * 8 + 4], d[q * 8 + 5]);
+        o.w = pack_bf16x2(d[q * 8 + 6], d[q * 8 + 7]);
+        dst[q] = o;
+      }
+    }
   }
   if (a.padded_out != nullptr) {
     uint4 o[CPW / 8];
@@ -487,25 +489,27 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
 #pragma unroll
               for (int p = 0; p < 4; ++p) {
                 const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&uu[p]);
-                v[q * 8 + 2 * p] *= gelu_erf_grad(__low2float(b2));
-                v[q * 8 + 2 * p + 1] *= gelu_erf_grad(__high2float(b2));
+                v[q * 8 + 2 * p] *= __low2float(b2);
+                v[q * 8 + 2 * p + 1] *= __high2float(b2);
               }
             }
           }
           uint4 aux_v[CPW / 8], out_v[CPW / 8];
           const bool aux_is_pre = a.dense_pre != nullptr;
-          if (aux_out && aux_is_pre) {
-#pragma unroll
-            for (int q = 0; q < CPW / 8; ++q) {
-              aux_v[q].x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              aux_v[q].y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              aux_v[q].z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              aux_v[q].w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-            }
-          }
-          if (a.act == 1) {
+          if (a.act == 1 && !aux_is_pre) {
 #pragma unroll
             for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+          } else if (a.act == 1) {
+            float d[CPW];
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) gelu_erf_with_grad(v[j], v[j], d[j]);
+#pragma unroll
+            for (int q = 0; q < CPW / 8; ++q) {
+              aux_v[q].x = pack_bf16x2(d[q * 8 + 0], d[q * 8 + 1]);
+              aux_v[q].y = pack_bf16x2(d[q * 8 + 2], d[q * 8 + 3]);
+              aux_v[q].z = pack_bf16x2(d[q * 8 + 4], d[q * 8 + 5]);
+              aux_v[q].w = pack_bf16x2(d[q * 8 + 6], d[q * 8 + 7]);
+            }
           }
 #pragma unroll
           for (int q = 0; q < CPW / 8; ++q) {
@@ -822,6 +826,7 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
                               unsigned int* done_counter, int* status, int sm_count, void* stream) {
   if (nout_pad != 64 && nout_pad != 16) return -1;
   if (mode == 1 && nout_pad != 64) return -1;
+  if (dense_pre != nullptr && act != 1) return -1;   // the saved tensor is the activation's derivative
   CUtensorMap tmIn, tmW;
   if (padded_tmap(&tmIn, in_padded, NB, H, W, CV_BOXW, 0) != 0) return -2;
   {

@@ -297,6 +297,16 @@ __device__ __forceinline__ float gelu_erf_grad(float x) {
   du = (t < 25.0f) ? du : 0.0f;
   return fmaf(x * (2.0f * du), P * (1.0f - P), P);
 }
+// GELU(x) and GELU'(x) together (they share Phi): the forward epilogue stores the derivative
+// so that the backward pass only multiplies.
+__device__ __forceinline__ void gelu_erf_with_grad(float x, float& y, float& dy) {
+  float t;
+  const float P = normal_cdf_fast(x, t);
+  float du = fmaf(t, fmaf(t, fmaf(t, 7.0f * JB_GELU_C3, 5.0f * JB_GELU_C2), 3.0f * JB_GELU_C1), JB_GELU_C0);
+  du = (t < 25.0f) ? du : 0.0f;
+  y = x * P;
+  dy = fmaf(x * (2.0f * du), P * (1.0f - P), P);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
