@@ -561,7 +561,8 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
 // kernel sums the partials in a fixed order (deterministic).
 // ------------------------------------------------------------------------------------------
 constexpr int WG_GSTAGES = 3;
-constexpr int WG_THREADS = 192;
+constexpr int WG_MMA_WARPS = 5;                    // one per accumulator chain
+constexpr int WG_THREADS = 32 * (1 + WG_MMA_WARPS + 4);
 constexpr int WG_PARTIAL_FLOATS = 5 * 128 * 64;
 
 struct WgradArgs {
@@ -581,10 +582,10 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   uint8_t* ones = gtiles + WG_GSTAGES * 16384;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ones + 2048);
   uint64_t* full = bars;              // [8]
-  uint64_t* empty = bars + 8;         // [8]
+  uint64_t* empty = bars + 8;         // [8]  3 rows x 5 issuing warps arrive per refill
   uint64_t* gfull = bars + 16;        // [3]
-  uint64_t* gempty = bars + 19;       // [3]
-  uint64_t* acc_full = bars + 22;     // [1]
+  uint64_t* gempty = bars + 19;       // [3]  5 issuing warps arrive
+  uint64_t* acc_full = bars + 22;     // [1]  5 issuing warps arrive
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   constexpr uint32_t TMEM_COLS = 512;
@@ -599,13 +600,13 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], 3 * WG_MMA_WARPS);
     }
     for (int s = 0; s < WG_GSTAGES; ++s) {
       mbar_init(&gfull[s], 1);
-      mbar_init(&gempty[s], 1);
+      mbar_init(&gempty[s], WG_MMA_WARPS);
     }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, WG_MMA_WARPS);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmX);
@@ -621,31 +622,30 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       halo_wait_all(a.wait, abort_flag, a.status);
       uint32_t eph = 0;
       int gs = 0;
       uint32_t gph = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int s = item % a.nstrips;
         const int tw = (item / a.nstrips) % a.tiles_w;
         const int n = item / (a.nstrips * a.tiles_w);
         const int h0 = s * a.rows_per_strip;
         const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1 && ok; hc += WG_CHUNK) {
+        for (int hc = h0; hc < h1; hc += WG_CHUNK) {
           const int n_out = min(WG_CHUNK, h1 - hc);
-          for (int i = 0; i < n_out && ok; ++i) {
+          for (int i = 0; i < n_out; ++i) {
+            if (*abort_flag) break;
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
-              ok = mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status);
-              if (!ok) break;
+              mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status, 110 + j);
               eph ^= (1u << j);
               mbar_expect_tx(&full[j], CV_BOXW * 128);
               tma_load_4d(slots + j * CV_SLOT_BYTES, &tmX, &full[j], 0, tw * CV_TW, hc + j, n);
             }
-            if (!ok) break;
-            ok = mbar_wait(&gempty[gs], gph ^ 1u, abort_flag, a.status);
-            if (!ok) break;
+            mbar_wait(&gempty[gs], gph ^ 1u, abort_flag, a.status, 120 + gs);
+            if (*abort_flag) break;
             mbar_expect_tx(&gfull[gs], 16384);
             // gy lives in a padded buffer too: interior pixel (h, w) is at (h + 1, w + 1).
             tma_load_4d(gtiles + gs * 16384, &tmG, &gfull[gs], 0, tw * CV_TW + 1, hc + i + 1, n);
@@ -657,87 +657,93 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         }
       }
     }
-  } else if (warp == 1) {
-    {
-      constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
-      uint32_t fph = 0;
-      int gs = 0;
-      uint32_t gph = 0;
-      bool first = true;
-      const uint32_t s_addr = smem_u32(slots);
-      const uint32_t ones_addr = smem_u32(ones);
-      const uint64_t g_desc0 = make_smem_desc_sw128(smem_u32(gtiles), 8192, 1024);
-      const uint64_t x_desc128 = make_smem_desc_sw128(s_addr, 128, 1024);            // pair = next pixel
-      const uint64_t x_descslot = make_smem_desc_sw128(s_addr, CV_SLOT_BYTES, 1024); // pair = next slot
-      for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        const int s = item % a.nstrips;
-        const int h0 = s * a.rows_per_strip;
-        const int h1 = min(a.H, h0 + a.rows_per_strip);
-        for (int hc = h0; hc < h1; hc += WG_CHUNK) {
-          const int n_out = min(WG_CHUNK, h1 - hc);
-          for (int i = 0; i < n_out; ++i) {
-            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
-              mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status);
-              fph ^= (1u << j);
-            }
-            mbar_wait(&gfull[gs], gph, abort_flag, a.status);
+  } else if (warp <= WG_MMA_WARPS) {
+    // ---------------------------------------------------------------- UMMA issuers
+    // One warp per accumulator chain (issue cost, not the tensor core, bounds a single
+    // issuing warp).  Chain c accumulates into TMEM columns [64 c, 64 c + 64):
+    //   c = 0,1,2 : taps (c,0) + (c,1)   (second 64 rows of M = the view one pixel to the right)
+    //   c = 3     : taps (0,2) + (1,2)   (second half = the same view one slot further)
+    //   c = 4     : tap  (2,2) + ones    (bias gradient)
+    const int c = warp - 1;
+    constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
+    uint32_t fph = 0;
+    int gs = 0;
+    uint32_t gph = 0;
+    bool first = true;
+    const uint32_t s_addr = smem_u32(slots);
+    const uint32_t ones_addr = smem_u32(ones);
+    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(64 * c);
+    const uint64_t g_desc0 = make_smem_desc_sw128(smem_u32(gtiles), 8192, 1024);
+    // A-operand view of this chain relative to the first slot of the row
+    const uint32_t view_off = (c < 3) ? static_cast<uint32_t>(c * CV_SLOT_BYTES)
+                                      : (c == 3 ? 256u : static_cast<uint32_t>(2 * CV_SLOT_BYTES + 256));
+    const uint32_t pair_lbo = (c < 3) ? 128u : static_cast<uint32_t>(CV_SLOT_BYTES);
+    const uint64_t a_desc0 = make_smem_desc_sw128(s_addr + view_off, pair_lbo, 1024);
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int s = item % a.nstrips;
+      const int h0 = s * a.rows_per_strip;
+      const int h1 = min(a.H, h0 + a.rows_per_strip);
+      for (int hc = h0; hc < h1; hc += WG_CHUNK) {
+        const int n_out = min(WG_CHUNK, h1 - hc);
+        for (int i = 0; i < n_out; ++i) {
+          for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j)
+            mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status, 140 + j);
+          mbar_wait(&gfull[gs], gph, abort_flag, a.status, 150 + gs);
+          if (!*abort_flag) {
             tc_fence_after_sync();
             const uint64_t bd0 = desc_advance(g_desc0, static_cast<uint32_t>(gs * 16384));
-            const uint64_t r0 = desc_advance(x_desc128, static_cast<uint32_t>(i * CV_SLOT_BYTES));
-            const uint64_t q0 = desc_advance(x_descslot, static_cast<uint32_t>(i * CV_SLOT_BYTES + 256));
+            const uint64_t ad0 = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
             const uint32_t v22 = s_addr + (i + 2) * CV_SLOT_BYTES + 256;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t acc = (first && k == 0) ? 0u : 1u;
               const uint32_t ko = k * 2048;  // 16 pixels x 128 bytes
               const uint64_t bd = desc_advance(bd0, ko);
-              // taps (dy,0) + (dy,1): second 64 rows of M are the view one pixel to the right.
-              umma_f16_elect(tmem_base + 0, desc_advance(r0, ko), bd, idesc, acc);
-              umma_f16_elect(tmem_base + 64, desc_advance(r0, CV_SLOT_BYTES + ko), bd, idesc, acc);
-              umma_f16_elect(tmem_base + 128, desc_advance(r0, 2 * CV_SLOT_BYTES + ko), bd, idesc, acc);
-              // taps (0,2) + (1,2): second half is the same view one slot further.
-              umma_f16_elect(tmem_base + 192, desc_advance(q0, ko), bd, idesc, acc);
-              // tap (2,2) + ones (bias gradient): the distance to the ones tile shrinks with k.
-              umma_f16_elect(tmem_base + 256, make_smem_desc_sw128(v22 + ko, ones_addr - (v22 + ko), 1024), bd, idesc, acc);
+              // chain 4 pairs its tap with the tile of ones: the distance shrinks as k advances
+              const uint64_t ad = (c == 4) ? make_smem_desc_sw128(v22 + ko, ones_addr - (v22 + ko), 1024)
+                                           : desc_advance(ad0, ko);
+              umma_f16_elect(d_tmem, ad, bd, idesc, acc);
             }
             first = false;
             umma_commit_elect(&gempty[gs]);
-            if (++gs == WG_GSTAGES) {
-              gs = 0;
-              gph ^= 1u;
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+              const int j = i + d;
+              const int lo = max(0, j - 2), hi = min(n_out - 1, j);
+              umma_commit_elect(&empty[j]);
+              if (i == lo && lane == 0) {
+                for (int e = hi - lo + 1; e < 3; ++e) mbar_arrive(&empty[j]);
+              }
             }
-            umma_commit_elect(&empty[i]);
-            if (i == n_out - 1) {
-              umma_commit_elect(&empty[i + 1]);
-              umma_commit_elect(&empty[i + 2]);
-            }
+          }
+          if (++gs == WG_GSTAGES) {
+            gs = 0;
+            gph ^= 1u;
           }
         }
+        fph ^= (1u << (n_out + 2)) - 1u;
       }
-      umma_commit_elect(acc_full);
     }
+    umma_commit_elect(acc_full);
   } else {
-    // epilogue: one pass at the end
+    // ---------------------------------------------------------------- epilogue: one pass at the end
     const int quad = warp & 3;
-    if (mbar_wait(acc_full, 0, abort_flag, a.status)) {
-      tc_fence_after_sync();
-      const bool any = blockIdx.x < items;
-      float* dst = a.partials + static_cast<long long>(blockIdx.x) * WG_PARTIAL_FLOATS;
-      const int m = quad * 32 + lane;
-      for (int chain = 0; chain < 5; ++chain) {
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t r[32];
-          const uint32_t taddr =
-              tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chain * 64 + c0);
-          tmem_ld_32x32(taddr, r);
-          tmem_ld_wait();
-          float4* o = reinterpret_cast<float4*>(dst + (chain * 128 + m) * 64 + c0);
+    mbar_wait(acc_full, 0, abort_flag, a.status, 160);
+    tc_fence_after_sync();
+    float* dst = a.partials + static_cast<long long>(blockIdx.x) * WG_PARTIAL_FLOATS;
+    const int m = quad * 32 + lane;
+    for (int chain = 0; chain < 5; ++chain) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr =
+            tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(chain * 64 + c0);
+        tmem_ld_32x32(taddr, r);
+        tmem_ld_wait();
+        float4* o = reinterpret_cast<float4*>(dst + (chain * 128 + m) * 64 + c0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            o[j] = any ? make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]))
-                       : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+        for (int j = 0; j < 8; ++j) {
+          o[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                             __uint_as_float(r[4 * j + 3]));
         }
       }
     }
