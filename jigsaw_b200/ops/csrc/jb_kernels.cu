@@ -4,5 +4,6 @@
 #include "gemm.cu"
 #include "conv3x3.cu"
 #include "conv_thin.cu"
+#include "wgrad_noalloc.cu"
 
 extern "C" int jb_abi_version() { return 1; }
