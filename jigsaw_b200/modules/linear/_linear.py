@@ -65,6 +65,10 @@ class DistributedLinear(torch.nn.Module):
         self.in_dim, self.out_dim = in_dim, out_dim
         self.device = torch.device(device)
         self.dtype = dtype
+        # a layer whose model group is the column group of a mesh with several rows keeps its
+        # weight unsplit over rows, and stays that way when resharded; on a one-row mesh the two
+        # groups cannot be told apart and the layer counts as fully model-parallel
+        self._model_is_col = model_group is col_group and row_group.size() > 1
         self._bind_groups(model_group, row_group, col_group)
         if config is not None:
             check_config(config, {"model group size": model_group.size(), "linear_layer": True})
@@ -81,7 +85,6 @@ class DistributedLinear(torch.nn.Module):
 
     def _bind_groups(self, model_group: dist.ProcessGroup, row_group: dist.ProcessGroup, col_group: dist.ProcessGroup) -> None:
         self.model_group, self.row_group, self.col_group = model_group, row_group, col_group
-        self._model_is_col = model_group is col_group
         C = col_group.size()
         if model_group.size() % C:
             raise ValueError("model group size must be a multiple of the column group size")
