@@ -325,6 +325,25 @@ class DistributedAttention(torch.nn.Module):
                 out.k_norm.load_state_dict(self.k_norm.state_dict())
         return out
 
+    def row_order_tags(self) -> dict[str, str]:
+        """The qkv rows are stored channel-rank-major (``C, 3, heads / C, head_dim``), which
+        depends on the channel split; a checkpoint records the split so that another mesh can
+        reorder the rows (:meth:`reorder_rows`)."""
+        return {"qkv.weight": f"qkv:{self.channel_group.size()}:{self.heads * self.channel_group.size()}:{self.head_dim}"}
+
+    @staticmethod
+    def reorder_rows(tensor: torch.Tensor, from_tag: str, to_tag: str) -> torch.Tensor:
+        """Global qkv weight written under one channel split, reordered for another."""
+        _, c_from, heads, hd = from_tag.split(":")
+        _, c_to, heads_to, hd_to = to_tag.split(":")
+        if (heads, hd) != (heads_to, hd_to):
+            raise ValueError(f"attention shapes differ: {from_tag} vs {to_tag}")
+        c_from, c_to, heads, hd = int(c_from), int(c_to), int(heads), int(hd)
+        rest = tensor.shape[1:]
+        t = tensor.view(c_from, 3, heads // c_from, hd, *rest).transpose(0, 1).reshape(3, heads, hd, *rest)
+        t = t.view(3, c_to, heads // c_to, hd, *rest).transpose(0, 1)
+        return t.reshape(3 * heads * hd, *rest).contiguous()
+
     def get_parameter_count(self) -> int:
         """Parameters owned directly (the q/k norms); the projections report their own."""
         return 4 * self.head_dim if self.qk_norm else 0

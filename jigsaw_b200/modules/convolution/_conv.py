@@ -164,6 +164,10 @@ class _DistributedConvBase(torch.nn.Module):
         """Number of spatial ranks the parameters are replicated over."""
         return math.prod(g.size() for g in self._spatial_sync_groups)
 
+    def shard_spec(self) -> dict:
+        """Which dimension of which parameter is cut over which group (sharded checkpoints)."""
+        return {"weight": ((self._weight_shard_dim, self.channel_group),), "bias": ((0, self.channel_group),)}
+
     def get_parameter_count(self) -> int:
         """Global (unsharded) number of weight and bias elements; no communication."""
         nb = math.prod(self.global_bias_shape) if self.bias is not None else 0

@@ -196,6 +196,13 @@ class DistributedLinear(torch.nn.Module):
         self._load_global(w, b)
         self._mark()
 
+    def shard_spec(self) -> dict[str, tuple[tuple[int, dist.ProcessGroup], ...]]:
+        """Which dimension of which parameter is cut over which group (sharded checkpoints)."""
+        w = [(1, self.col_group)]
+        if self.row_split > 1:
+            w.append((0, self.row_group))
+        return {"weight": tuple(w), "bias": ((0, self.col_group),)}
+
     def get_parameter_count(self) -> int:
         return self.in_dim * self.out_dim + (self.out_dim if self.bias is not None else 0)
 

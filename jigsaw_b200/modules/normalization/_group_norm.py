@@ -140,6 +140,11 @@ class DistributedGroupNorm(torch.nn.Module):
         self._load_global(w, b)
         self._mark()
 
+    def shard_spec(self) -> dict:
+        """Which dimension of which parameter is cut over which group (sharded checkpoints)."""
+        cut = () if self.channel_group is None else ((0, self.channel_group),)
+        return {"weight": cut, "bias": cut}
+
     def get_parameter_count(self) -> int:
         if not self.affine:
             return 0

@@ -129,6 +129,11 @@ class DistributedLayerNorm(torch.nn.Module):
         self._load_global(w, b)
         self._mark()
 
+    def shard_spec(self) -> dict:
+        """Which dimension of which parameter is cut over which group (sharded checkpoints)."""
+        cut = () if self.col_group is None else ((0, self.col_group),)
+        return {"weight": cut, "bias": cut}
+
     def get_parameter_count(self) -> int:
         if not self.elementwise_affine:
             return 0

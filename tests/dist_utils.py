@@ -123,3 +123,16 @@ def assert_close(a: torch.Tensor, b: torch.Tensor, what: str, rtol: float = 1e-4
         detail = f" shapes {tuple(a.shape)} vs {tuple(b.shape)}"
     if not all_ok(ok):
         raise AssertionError(f"{what}: mismatch on some rank (rank {dist.get_rank()}: ok={ok}{detail})")
+
+
+def singleton_mesh(*axes):
+    """``{axis: group holding only this rank}`` plus "model" (collective: every rank creates
+    the singleton groups of all ranks in the same order)."""
+    import torch.distributed as dist
+
+    mine = None
+    for r in range(dist.get_world_size()):
+        g = dist.new_group([r])
+        if r == dist.get_rank():
+            mine = g
+    return {a: mine for a in (*axes, "model")}

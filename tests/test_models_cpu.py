@@ -1,0 +1,175 @@
+"""Model families on CPU/gloo: every sharded model against the same model on one rank
+(weights moved through the checkpoint module), and sharded checkpoints across meshes."""
+
+import pytest
+import torch
+
+from dist_utils import assert_close, merge, run_distributed, singleton_mesh, split
+
+
+def _grads_full(model):
+    """Global gradients, assembled the same way as the global parameters."""
+    from jigsaw_b200 import checkpoint
+
+    layout = checkpoint.parameter_layout(model)
+    out = {}
+    for name, p in model.named_parameters():
+        g = p.grad
+        for dim, group in layout[name]:
+            g = checkpoint.gather_dim(g, group, dim)
+        out[name] = g
+    return out
+
+
+def _compare(dist_model, serial_model, y, y_ref_local, what, rtol=2e-4, atol=2e-5):
+    from jigsaw_b200 import checkpoint
+
+    assert_close(y, y_ref_local, f"{what}: output", rtol, atol)
+    g_dist = _grads_full(dist_model)
+    serial_grads = dict(serial_model.named_parameters())
+    for name, g in g_dist.items():
+        assert_close(g, serial_grads[name].grad, f"{what}: grad of {name}", 5 * rtol, 5 * atol)
+
+
+def _worker_vit(rank, world):
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import ViT, ViTConfig
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    solo = singleton_mesh("row", "col")
+    torch.manual_seed(1)
+    x = torch.randn(2, 4, 16, 32)
+    for seq, classes in (("ring", None), ("ulysses", 10)):
+        cfg = ViTConfig(image_size=(16, 32), depth=2, num_classes=classes, sequence_parallel=seq, attn_backend="math")
+        jb.launch.set_all_seeds(100 + mesh["model"].rank())
+        model = ViT(mesh, "cpu", cfg)
+        serial = ViT(solo, "cpu", cfg)
+        # attention stores its qkv rows per channel rank: move it through the serial layout
+        state = checkpoint.full_state_dict(model)
+        checkpoint.load_full_state_dict(serial, state)
+        xl = split(x, {1: mesh["col"], 3: mesh["row"]})
+        y = model(xl)
+        y_ref = serial(x)
+        if classes is None:
+            target = torch.zeros_like(x)
+            loss = jb.modules.DistributedMSELoss(reduce_groups=(mesh["row"], mesh["col"]))(
+                y, split(target, {1: mesh["col"], 3: mesh["row"]}))
+            loss_ref = torch.nn.functional.mse_loss(y_ref, target)
+            y_ref_local = split(y_ref.detach(), {1: mesh["col"], 3: mesh["row"]})
+        else:
+            labels = torch.tensor([3, 7])
+            loss = jb.modules.DistributedCrossEntropyLoss(mesh["col"], (mesh["row"],))(y, labels)
+            loss_ref = torch.nn.functional.cross_entropy(y_ref, labels)
+            y_ref_local = split(y_ref.detach(), {1: mesh["col"]})
+        assert_close(loss.detach(), loss_ref.detach(), f"vit {seq}: loss", 1e-4, 1e-6)
+        loss.backward()
+        loss_ref.backward()
+        # compare gradients in the serial layout
+        g = {n: p.grad for n, p in model.named_parameters()}
+        for p in model.parameters():
+            p.data, p.grad = p.grad, None
+        g_full = checkpoint.full_state_dict(model)
+        assert_close(y.detach(), y_ref_local, f"vit {seq}: output", 2e-4, 2e-5)
+        for name, p in serial.named_parameters():
+            assert_close(g_full[name], p.grad, f"vit {seq}: grad of {name}", 1e-3, 1e-5)
+
+
+def test_vit_ring_and_ulysses_match_serial():
+    run_distributed(_worker_vit, 4)
+
+
+def _worker_swin(rank, world, axes):
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import Swin, SwinConfig
+
+    mesh = jb.make_process_mesh(axes)
+    solo = singleton_mesh("sh", "sw", "col")
+    for classes in (None, 6):
+        cfg = SwinConfig(image_size=(32, 32), in_channels=2, patch=2, dims=(8, 16), heads=(2, 4), depths=(2, 2), window=4,
+                         num_classes=classes)
+        jb.launch.set_all_seeds(7 + mesh["col"].rank())
+        model = Swin(mesh, "cpu", cfg)
+        serial = Swin(solo, "cpu", cfg)
+        checkpoint.load_full_state_dict(serial, checkpoint.full_state_dict(model))
+        torch.manual_seed(3)
+        x = torch.randn(2, 2, 32, 32)
+        cuts = {1: mesh["col"], 2: mesh["sh"], 3: mesh["sw"]}
+        y = model(split(x, cuts))
+        y_ref = serial(x)
+        assert_close(y.detach(), split(y_ref.detach(), cuts), f"swin {axes} classes={classes}: output", 2e-4, 2e-5)
+        (y * split(torch.linspace(0, 1, y_ref.numel()).view_as(y_ref), cuts)).sum().backward()
+        (y_ref * torch.linspace(0, 1, y_ref.numel()).view_as(y_ref)).sum().backward()
+        for p in model.parameters():
+            p.data, p.grad = p.grad, None
+        g_full = checkpoint.full_state_dict(model)
+        for name, p in serial.named_parameters():
+            assert_close(g_full[name], p.grad, f"swin {axes}: grad of {name}", 2e-3, 2e-4)
+
+
+@pytest.mark.parametrize("axes", [{"sh": 2, "sw": 2, "col": 1}, {"sh": 2, "sw": 1, "col": 2}])
+def test_swin_matches_serial(axes):
+    run_distributed(_worker_swin, 4, axes)
+
+
+def _worker_unet(rank, world):
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import UNet3d, UNet3dConfig
+
+    mesh = jb.make_process_mesh({"sh": 2, "sw": 2, "col": 1})
+    solo = singleton_mesh("sh", "sw", "col")
+    cfg = UNet3dConfig(widths=(8, 16), norm_groups=4)
+    jb.launch.set_all_seeds(11)
+    model, serial = UNet3d(mesh, "cpu", cfg), UNet3d(solo, "cpu", cfg)
+    checkpoint.load_full_state_dict(serial, checkpoint.full_state_dict(model))
+    torch.manual_seed(5)
+    x = torch.randn(1, 1, 8, 16, 16)
+    t = (torch.rand(1, 1, 8, 16, 16) > 0.5).float()
+    cuts = {3: mesh["sh"], 4: mesh["sw"]}
+    y = model(split(x, cuts))
+    y_ref = serial(x)
+    loss = jb.modules.DistributedBCEWithLogitsLoss(reduce_groups=(mesh["sh"], mesh["sw"]))(y, split(t, cuts))
+    loss_ref = torch.nn.functional.binary_cross_entropy_with_logits(y_ref, t)
+    assert_close(y.detach(), split(y_ref.detach(), cuts), "unet3d: output", 2e-4, 2e-5)
+    assert_close(loss.detach(), loss_ref.detach(), "unet3d: loss", 1e-5, 1e-6)
+    loss.backward()
+    loss_ref.backward()
+    for (n, p), (_, q) in zip(model.named_parameters(), serial.named_parameters()):
+        assert_close(p.grad, q.grad, f"unet3d: grad of {n}", 2e-3, 1e-5)
+
+
+def test_unet3d_matches_serial():
+    run_distributed(_worker_unet, 4)
+
+
+def _worker_checkpoint(rank, world, tmp):
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import ViT, ViTConfig
+
+    cfg = ViTConfig(image_size=(16, 32), depth=1, attn_backend="math")
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    jb.launch.set_all_seeds(40 + rank)
+    model = ViT(mesh, "cpu", cfg)
+    torch.manual_seed(0)
+    x = torch.randn(1, 4, 16, 32)
+    y = merge(model(split(x, {1: mesh["col"], 3: mesh["row"]})).detach(), {1: mesh["col"], 3: mesh["row"]})
+    checkpoint.save_sharded(model, mesh, tmp, extra={"step": 12})
+    import os
+
+    assert sorted(f for f in os.listdir(tmp) if f.endswith(".pt")) == [f"shard-col{c}-row{r}.pt" for c in (0, 1) for r in (0, 1)]
+    for axes in ({"row": 2, "col": 2}, {"row": 4, "col": 1}, {"row": 1, "col": 4}, {"dp": 2, "row": 1, "col": 2}):
+        kw = {"model_parallel_axes": ("row", "col")} if "dp" in axes else {}
+        mesh2 = jb.make_process_mesh(axes, **kw)
+        other = ViT(mesh2, "cpu", cfg)
+        extra = checkpoint.load_sharded(other, mesh2, tmp)
+        assert extra == {"step": 12}
+        cuts = {1: mesh2["col"], 3: mesh2["row"]}
+        y2 = merge(other(split(x, cuts)).detach(), cuts)
+        assert_close(y2, y, f"checkpoint read back on {axes}", 2e-4, 2e-5)
+
+
+def test_sharded_checkpoint_across_meshes(tmp_path):
+    run_distributed(_worker_checkpoint, 4, str(tmp_path))
