@@ -10,19 +10,22 @@ peer memory over NVLink; on CPU (gloo) the same layers run on ``torch.distribute
 Reference parity: jigsaw/__init__.py:3-17.
 """
 
-from . import convert, debug, gather, init, launch, log, modules, parallel
+from . import checkpoint, convert, data, debug, gather, init, launch, log, models, modules, parallel
 from ._core.public import set_module
 from .mesh import ProcessMesh, make_process_mesh
 
 __all__ = [
     "ProcessMesh",
     "make_process_mesh",
+    "checkpoint",
     "convert",
+    "data",
     "debug",
     "gather",
     "init",
     "launch",
     "log",
+    "models",
     "modules",
     "parallel",
 ]
