@@ -148,7 +148,15 @@ def _norm_groups(groups: Any) -> tuple:
         return ()
     if isinstance(groups, dist.ProcessGroup):
         groups = (groups,)
-    return tuple(g for g in groups if _live(g))
+    gs = tuple(g for g in groups if _live(g))
+    if len(gs) > 1:
+        # axes that tile a whole model replica: one collective over the flattened group
+        from ..parallel._replicas import merged_group
+
+        whole = merged_group(gs)
+        if whole is not None:
+            return (whole,)
+    return gs
 
 
 def all_gather_cat(x: torch.Tensor, group: dist.ProcessGroup | None, dim: int) -> torch.Tensor:

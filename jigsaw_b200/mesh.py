@@ -136,4 +136,8 @@ def make_process_mesh(
             device_type, (world // model_n, model_n), mesh_dim_names=("replica", model_key)
         )
     mesh[model_key] = flat.get_group(model_key)
+    from .parallel._replicas import register_merged_group
+
+    # every subset of the model axes that tiles the whole replica reduces in one collective
+    register_merged_group([mesh[a] for a in model_axes], mesh[model_key])
     return mesh

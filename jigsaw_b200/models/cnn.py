@@ -63,9 +63,8 @@ class DomainCNN(nn.Module):
         kinds = conv_fused.chain_kinds([(c.in_channels, c.out_channels) for c in self.convs])
         if kinds is None:
             return None
-        params = []
-        for c in self.convs:
-            params += list(parallel.sync_grad(c.weight, c.bias))
+        # one call: all replicated gradients travel in a single flattened all-reduce per group
+        params = list(parallel.sync_grad(*[t for c in self.convs for t in (c.weight, c.bias)]))
         geom = conv_fused.geometry_for(x, *self.spatial)
         acts = [True] * (len(self.convs) - 1) + [False]
         return conv_fused.conv_chain(x, geom, kinds, acts, params[0::2], params[1::2])

@@ -69,7 +69,7 @@ def _elementwise_loss(fn, input, target, reduction, reduce_groups, **kw):
     with torch.autocast(input.device.type, enabled=False):
         acc = torch.promote_types(input.dtype, torch.float32)
         total = fn(input.to(acc), target.to(acc), reduction="sum", **kw)
-    count = torch.tensor(float(input.numel()), dtype=torch.float32, device=input.device)
+    count = torch.full((), float(input.numel()), dtype=torch.float32, device=input.device)   # device-side fill: capturable
     return reduce_scalar_loss(total, count, reduction, reduce_groups).to(input.dtype)
 
 
@@ -164,7 +164,7 @@ def distributed_cross_entropy(
             elem = redundant_all_reduce(-(target.to(logp.dtype) * logp).sum(dim=dim), channel_group)
             if reduction == "none":
                 return elem.to(in_dtype)
-            count = torch.tensor(float(elem.numel()), device=elem.device)
+            count = torch.full((), float(elem.numel()), device=elem.device)
             return reduce_scalar_loss(elem.sum(), count, reduction, reduce_groups).to(in_dtype)
         if label_smoothing != 0.0 and weight is not None:
             raise NotImplementedError("label_smoothing together with weight is not supported")

@@ -29,6 +29,9 @@ class JbHalo(ctypes.Structure):
         ("wait_epoch", c_uint),
         ("push_enabled", c_uint),
         ("wait_enabled", c_uint),
+        ("push_stride", c_uint),
+        ("wait_stride", c_uint),
+        ("replay", c_void_p),
     ]
 
 

@@ -49,15 +49,26 @@ struct HaloPush {
   // Index (sy + 1) * 3 + (sx + 1); entry 4 (self) unused.  Null = no neighbour there.
   void* buf[9];         // base of that neighbour's padded buffer (same shape as ours)
   uint32_t* flag[9];    // flag word on that neighbour to set once all our stores are out
-  uint32_t epoch;       // value to publish
+  uint32_t epoch;       // value to publish (plus stride * *replay when the launch sits in a replayed CUDA graph)
   uint32_t enabled;     // 0: no neighbour at all (single rank)
+  uint32_t stride;      // productions of this flag slot per replay of the graph
+  const uint32_t* replay;  // device counter of graph replays, or null outside a graph
 };
 
 struct HaloWait {
   const uint32_t* flag[9];  // local flag words to wait for (null = none)
   uint32_t epoch;
   uint32_t enabled;
+  uint32_t stride;          // as in HaloPush
+  const uint32_t* replay;
 };
+
+// The launch arguments of a kernel inside a CUDA graph are frozen, but every replay must publish and
+// await a later epoch.  The graph bumps a device counter once per replay; the epoch of this launch is
+// its captured value plus (replays * productions of the slot per replay).
+__device__ __forceinline__ uint32_t live_epoch(uint32_t epoch, uint32_t stride, const uint32_t* replay) {
+  return replay == nullptr ? epoch : epoch + stride * __ldg(replay);
+}
 
 struct ConvArgs {
   int NB, H, W;            // local tile
@@ -82,13 +93,14 @@ struct ConvArgs {
 __device__ __forceinline__ void halo_wait_all(const HaloWait& w, volatile int* abort_flag, int* status) {
   if (!w.enabled) return;
   const uint64_t t0 = globaltimer_ns();
+  const uint32_t want = live_epoch(w.epoch, w.stride, w.replay);
   for (int d = 0; d < 9; ++d) {
     const uint32_t* f = w.flag[d];
     if (f == nullptr) continue;
     while (true) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if (static_cast<int32_t>(v - w.epoch) >= 0) break;
+      if (static_cast<int32_t>(v - want) >= 0) break;
       if (*abort_flag) return;
       if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
         *abort_flag = 1;
@@ -113,9 +125,10 @@ __device__ __forceinline__ void halo_publish(const HaloPush& p, unsigned int* do
     if (prev == gridDim.x - 1) {
       *done_counter = 0u;
       __threadfence_system();
+      const uint32_t epoch = live_epoch(p.epoch, p.stride, p.replay);
       for (int d = 0; d < 9; ++d) {
         if (p.flag[d] != nullptr) {
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[d]), "r"(p.epoch) : "memory");
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[d]), "r"(epoch) : "memory");
         }
       }
     }
@@ -821,6 +834,9 @@ struct JbHalo {          // C mirror passed from Python (ctypes)
   unsigned int wait_epoch;
   unsigned int push_enabled;
   unsigned int wait_enabled;
+  unsigned int push_stride;      // CUDA-graph replays: see live_epoch()
+  unsigned int wait_stride;
+  const unsigned int* replay;    // null outside a graph
 };
 
 // Forward / data-gradient launcher.
@@ -862,8 +878,12 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
     }
     a.push.epoch = halo->push_epoch;
     a.push.enabled = halo->push_enabled;
+    a.push.stride = halo->push_stride;
+    a.push.replay = halo->replay;
     a.wait.epoch = halo->wait_epoch;
     a.wait.enabled = halo->wait_enabled;
+    a.wait.stride = halo->wait_stride;
+    a.wait.replay = halo->replay;
   }
   // Output / auxiliary tensor maps of the staged (64-column) kernels.
   CUtensorMap tmOut = tmIn, tmAux = tmIn;
@@ -930,6 +950,8 @@ extern "C" int jb_conv3x3_c64_wgrad(const void* x_padded, const void* gy_padded,
     for (int d = 0; d < 9; ++d) a.wait.flag[d] = static_cast<const uint32_t*>(halo->wait_flag[d]);
     a.wait.epoch = halo->wait_epoch;
     a.wait.enabled = halo->wait_enabled;
+    a.wait.stride = halo->wait_stride;
+    a.wait.replay = halo->replay;
   }
   const int items = NB * a.tiles_w * a.nstrips;
   const int grid = items < sm_count ? items : sm_count;

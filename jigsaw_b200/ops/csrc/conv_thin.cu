@@ -30,84 +30,79 @@ struct PackArgs {
   unsigned int* done_counter;
 };
 
-// One block handles 32 pixels of one row for all channels, going through shared memory so that
-// both the (possibly channel-strided) reads and the channel-contiguous writes are coalesced.
-__global__ void __launch_bounds__(256) halo_pack_kernel(const PackArgs a) {
-  extern __shared__ float tile[];  // [32 pixels][CW + 1]
-  const int wt = blockIdx.x, h = blockIdx.y, n = blockIdx.z;
-  const int w0 = wt * 32;
-  const int ld = a.CW + 1;
+// One thread per pixel, PACK_PIX pixels of one row per thread, channels in groups of four.  For a
+// pixel-contiguous source (NCHW) the reads of a warp are coalesced per channel; for a
+// channel-contiguous source (NHWC) each thread reads its pixel's channels from one short run.
+// Only blocks that stored into a neighbour's memory pay for a system-scope fence.
+constexpr int PACK_THREADS = 256;
+constexpr int PACK_PIX = 4;
+
+__global__ void __launch_bounds__(PACK_THREADS) halo_pack_kernel(const PackArgs a) {
+  const int h = blockIdx.y, n = blockIdx.z;
   const int tid = threadIdx.x;
-  if (a.sc == 1) {
-    // channel-contiguous source: consecutive threads read consecutive channels
-    for (int i = tid; i < 32 * a.CW; i += 256) {
-      const int p = i / a.CW, c = i % a.CW;
-      float v = 0.f;
-      if (c < a.C && w0 + p < a.W) {
-        const long long off = n * a.sn + c * a.sc + h * a.sh + static_cast<long long>(w0 + p) * a.sw;
-        v = a.src_is_fp32 ? static_cast<const float*>(a.src)[off]
-                          : __bfloat162float(static_cast<const __nv_bfloat16*>(a.src)[off]);
-      }
-      tile[p * ld + c] = v;
-    }
-  } else {
-    // pixel-contiguous source (NCHW): consecutive threads read consecutive pixels
-    for (int i = tid; i < 32 * a.CW; i += 256) {
-      const int c = i / 32, p = i % 32;
-      float v = 0.f;
-      if (c < a.C && w0 + p < a.W) {
-        const long long off = n * a.sn + c * a.sc + h * a.sh + static_cast<long long>(w0 + p) * a.sw;
-        v = a.src_is_fp32 ? static_cast<const float*>(a.src)[off]
-                          : __bfloat162float(static_cast<const __nv_bfloat16*>(a.src)[off]);
-      }
-      tile[p * ld + c] = v;
-    }
-  }
-  __syncthreads();
   const long long prow = static_cast<long long>(a.W + 2) * a.CP;
   const long long pimg = static_cast<long long>(a.H + 2) * prow;
   const int groups = a.CW / 4;  // 4 channels = 8 bytes per store
-  for (int i = tid; i < 32 * groups; i += 256) {
-    const int p = i / groups, g = i % groups;
-    const int w = w0 + p;
+  const bool top = (h == 0), bot = (h == a.H - 1);
+  bool pushed = false;
+  const long long src_row = n * a.sn + h * a.sh;
+#pragma unroll
+  for (int k = 0; k < PACK_PIX; ++k) {
+    const int w = (blockIdx.x * PACK_PIX + k) * PACK_THREADS + tid;
     if (w >= a.W) continue;
-    const float* t = tile + p * ld + g * 4;
-    uint2 o;
-    o.x = pack_bf16x2(t[0], t[1]);
-    o.y = pack_bf16x2(t[2], t[3]);
-    *reinterpret_cast<uint2*>(a.dst + n * pimg + (h + 1) * prow + static_cast<long long>(w + 1) * a.CP + g * 4) = o;
-    if (!a.push.enabled) continue;
-    const bool top = (h == 0), bot = (h == a.H - 1), lef = (w == 0), rig = (w == a.W - 1);
-    if (!(top || bot || lef || rig)) continue;
-    for (int sy = -1; sy <= 1; ++sy) {
-      for (int sx = -1; sx <= 1; ++sx) {
-        if (sy == 0 && sx == 0) continue;
-        const int d = (sy + 1) * 3 + (sx + 1);
-        if (a.push.buf[d] == nullptr) continue;
-        const bool hit_y = (sy == -1) ? top : (sy == 1 ? bot : true);
-        const bool hit_x = (sx == -1) ? lef : (sx == 1 ? rig : true);
-        if (!(hit_y && hit_x)) continue;
-        const int dr = (sy == -1) ? (a.H + 1) : (sy == 1 ? 0 : h + 1);
-        const int dc = (sx == -1) ? (a.W + 1) : (sx == 1 ? 0 : w + 1);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.push.buf[d]) + n * pimg + dr * prow +
-                                  static_cast<long long>(dc) * a.CP + g * 4) = o;
+    const long long src_pix = src_row + static_cast<long long>(w) * a.sw;
+    __nv_bfloat16* out_pix = a.dst + n * pimg + (h + 1) * prow + static_cast<long long>(w + 1) * a.CP;
+    const bool lef = (w == 0), rig = (w == a.W - 1);
+    const bool edge = a.push.enabled && (top || bot || lef || rig);
+    for (int g = 0; g < groups; ++g) {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = g * 4 + j;
+        v[j] = 0.f;
+        if (c < a.C) {
+          const long long off = src_pix + c * a.sc;
+          v[j] = a.src_is_fp32 ? static_cast<const float*>(a.src)[off]
+                               : __bfloat162float(static_cast<const __nv_bfloat16*>(a.src)[off]);
+        }
+      }
+      uint2 o;
+      o.x = pack_bf16x2(v[0], v[1]);
+      o.y = pack_bf16x2(v[2], v[3]);
+      *reinterpret_cast<uint2*>(out_pix + g * 4) = o;
+      if (!edge) continue;
+      for (int sy = -1; sy <= 1; ++sy) {
+        for (int sx = -1; sx <= 1; ++sx) {
+          if (sy == 0 && sx == 0) continue;
+          const int d = (sy + 1) * 3 + (sx + 1);
+          if (a.push.buf[d] == nullptr) continue;
+          const bool hit_y = (sy == -1) ? top : (sy == 1 ? bot : true);
+          const bool hit_x = (sx == -1) ? lef : (sx == 1 ? rig : true);
+          if (!(hit_y && hit_x)) continue;
+          const int dr = (sy == -1) ? (a.H + 1) : (sy == 1 ? 0 : h + 1);
+          const int dc = (sx == -1) ? (a.W + 1) : (sx == 1 ? 0 : w + 1);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.push.buf[d]) + n * pimg + dr * prow +
+                                    static_cast<long long>(dc) * a.CP + g * 4) = o;
+          pushed = true;
+        }
       }
     }
   }
   // publish: same protocol as the convolution kernels (last block of the grid sets the flags)
   if (a.push.enabled) {
-    __threadfence_system();
+    if (pushed) __threadfence_system();      // this thread's peer stores are visible before the count
     __syncthreads();
     if (tid == 0) {
-      __threadfence_system();
       const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+      __threadfence();
       const unsigned int prev = atomicAdd(a.done_counter, 1u);
       if (prev == total - 1) {
         *a.done_counter = 0u;
         __threadfence_system();
+        const uint32_t epoch = live_epoch(a.push.epoch, a.push.stride, a.push.replay);
         for (int d = 0; d < 9; ++d)
           if (a.push.flag[d] != nullptr)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.push.flag[d]), "r"(a.push.epoch) : "memory");
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.push.flag[d]), "r"(epoch) : "memory");
       }
     }
   }
@@ -260,10 +255,14 @@ static void fill_halo(HaloPush* push, HaloWait* wait, const JbHalo* halo) {
   if (push) {
     push->epoch = halo->push_epoch;
     push->enabled = halo->push_enabled;
+    push->stride = halo->push_stride;
+    push->replay = halo->replay;
   }
   if (wait) {
     wait->epoch = halo->wait_epoch;
     wait->enabled = halo->wait_enabled;
+    wait->stride = halo->wait_stride;
+    wait->replay = halo->replay;
   }
 }
 
@@ -281,9 +280,9 @@ extern "C" int jb_halo_pack(const void* src, int src_is_fp32, long long sn, long
   a.dst = static_cast<__nv_bfloat16*>(dst);
   a.done_counter = done_counter;
   fill_halo(&a.push, nullptr, halo);
-  dim3 grid((W + 31) / 32, H, NB);
+  dim3 grid((W + PACK_THREADS * PACK_PIX - 1) / (PACK_THREADS * PACK_PIX), H, NB);
   if (grid.y > 65535 || grid.z > 65535) return -1;
-  halo_pack_kernel<<<grid, 256, 32 * (CW + 1) * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
+  halo_pack_kernel<<<grid, PACK_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -74,6 +74,11 @@ class PeerArena:
         self._slot_epoch = [0] * _MAX_SLOTS
         self.done_counter = torch.zeros(4, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        # CUDA-graph support: kernels inside a captured step take their epochs as
+        # ``captured value + replays * productions of the slot per step`` (see begin_capture)
+        self.replay = torch.zeros(1, dtype=torch.int32, device=device)
+        self._capture_stride: int | None = None
+        self._capture_slots: set[int] = set()
         self._flags = None
         if self.symmetric:
             self._flags = self._new_symmetric(_MAX_SLOTS * _FLAG_WORDS * 4)
@@ -147,9 +152,30 @@ class PeerArena:
     def next_epoch(self, blk: Block) -> int:
         """Advance and return the epoch of the block's slot (one per production of its content)."""
         self.bind_slot(blk)
+        if self._capture_stride is not None:
+            self._capture_slots.add(blk.slot)
         self._slot_epoch[blk.slot] += 1
         blk.epoch = self._slot_epoch[blk.slot]
         return blk.epoch
+
+    def begin_capture(self, stride: int) -> None:
+        """From now on halo descriptors refer to the replay counter: a launch captured with
+        epoch ``e`` publishes / awaits ``e + replays * stride``.  ``stride`` must exceed the
+        number of times any one slot is produced between two replays (captured step plus
+        eager steps in between); which buffer gets which slot may differ from step to step,
+        so one generous stride serves all slots."""
+        self._capture_stride = int(stride)
+        self._capture_slots = set()
+
+    def end_capture(self) -> set[int]:
+        """Leave capture mode; returns the flag slots the captured step produces."""
+        self._capture_stride = None
+        return set(self._capture_slots)
+
+    def advance(self, slots: set[int], stride: int) -> None:
+        """Account on the host for one replay of a captured step."""
+        for slot in slots:
+            self._slot_epoch[slot] += stride
 
     def flag_ptr(self, world_rank: int, slot: int, direction: int) -> int:
         return self._flags["ptrs"][world_rank] + (slot * _FLAG_WORDS + direction) * 4
@@ -220,4 +246,7 @@ def make_halo(
         for d, n in enumerate(nbrs):
             if n is not None:
                 h.wait_flag[d] = ar.flag_ptr(ar.rank, consume.slot, d)
+    if ar._capture_stride is not None:
+        h.replay = ar.replay.data_ptr()
+        h.push_stride = h.wait_stride = ar._capture_stride
     return ctypes.pointer(h)

@@ -21,6 +21,30 @@ MARK_ATTR = "_jigsaw_replica_groups"
 Groups = tuple[dist.ProcessGroup, ...]
 
 
+# A set of orthogonal axis groups that together tile one bigger group (the axes of a model
+# replica and its flattened ``model`` group) can be reduced in one collective over that group.
+_MERGED: dict[frozenset, "dist.ProcessGroup"] = {}
+
+
+def register_merged_group(parts: "Sequence[dist.ProcessGroup]", whole: "dist.ProcessGroup") -> None:
+    """Record that SUM over every group of ``parts`` in turn equals SUM over ``whole``."""
+    live = [g for g in parts if g is not None and g.size() > 1]
+    if len(live) < 2:
+        return
+    n = 1
+    for g in live:
+        n *= g.size()
+    if n != whole.size():
+        return
+    _MERGED[frozenset(tuple(dist.get_process_group_ranks(g)) for g in live)] = whole
+
+
+def merged_group(groups: "Sequence[dist.ProcessGroup]") -> "dist.ProcessGroup | None":
+    if len(groups) < 2 or not _MERGED:
+        return None
+    return _MERGED.get(frozenset(tuple(dist.get_process_group_ranks(g)) for g in groups))
+
+
 def _real_groups(groups: "dist.ProcessGroup | Iterable[dist.ProcessGroup | None] | None") -> Groups:
     if groups is None:
         return ()

@@ -23,12 +23,16 @@ import torch.distributed as dist
 
 from ._ddp import check_active_ddp
 from ._joint import JointCommHookState, active_joint_state, joint_state_of
-from ._replicas import Groups, replica_groups
+from ._replicas import Groups, merged_group, replica_groups
 
 _SYNC_DISABLED = os.environ.get("JIGSAW_DISABLE_GRAD_SYNC", "") == "1"
 
 
 def _reduce_flat(flat: torch.Tensor, groups: Groups) -> None:
+    whole = merged_group(groups)
+    if whole is not None:
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=whole)
+        return
     for g in groups:
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=g)
 

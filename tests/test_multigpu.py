@@ -61,3 +61,75 @@ def test_fused_chain_two_gpus_cols():
 @pytest.mark.multigpu(4)
 def test_fused_chain_four_gpus_with_corners():
     run_distributed(_worker_chain, 4, (2, 2), backend="nccl", timeout=300)
+
+
+def _worker_graphed_step(rank, world, mesh_shape):
+    """A whole training step replayed as a CUDA graph must follow the eager run bit for bit
+    (same kernels, same order), halo epochs included, and eager steps may follow replays."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.models import DomainCNN
+    from jigsaw_b200.ops import symm
+    from jigsaw_b200.utils import GraphedStep
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"sh": mesh_shape[0], "sw": mesh_shape[1], "col": 1})
+    loss_fn = jb.modules.DistributedMSELoss(reduce_groups=(mesh["sh"], mesh["sw"]))
+    g = torch.Generator().manual_seed(5 + rank)
+    xs = [torch.randn(1, 3, 64, 136, generator=g).to(dev) for _ in range(4)]
+    ys = [torch.randn(1, 3, 64, 136, generator=g).to(dev) for _ in range(4)]
+
+    def make():
+        torch.manual_seed(0)
+        m = DomainCNN(mesh, dev, depth=4)
+        o = torch.optim.Adam(m.parameters(), lr=1e-3, fused=True, capturable=True)
+
+        def step(x, y):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = m(x)
+            loss = loss_fn(out.float(), y)
+            o.zero_grad(set_to_none=True)
+            loss.backward()
+            o.step()
+            return loss
+
+        return m, step
+
+    side = torch.cuda.Stream(dev)
+    order = [0, 0, 0, 0, 1, 2, 3]            # GraphedStep: 3 warm-up steps and one counting step on batch 0
+    m1, eager = make()
+    with torch.cuda.stream(side):
+        ref = [float(eager(xs[i], ys[i])) for i in order]
+    m2, step2 = make()
+    xi, yi = xs[0].clone(), ys[0].clone()
+    graphed = GraphedStep(step2, (xi, yi), warmup=3)
+    assert graphed.launches_per_step > 0
+    got = []
+    for i in order[4:]:
+        xi.copy_(xs[i])
+        yi.copy_(ys[i])
+        got.append(float(graphed.replay()))
+    with torch.cuda.stream(side):
+        after_ref, after_got = float(eager(xs[0], ys[0])), float(step2(xs[0], ys[0]))
+    symm.arena(dev).check_status()
+    assert got == ref[4:], (got, ref[4:])
+    assert after_got == after_ref
+    for p, q in zip(m1.parameters(), m2.parameters()):
+        assert torch.equal(p, q)
+    graphed.close()
+
+
+def test_graphed_step_one_gpu():
+    run_distributed(_worker_graphed_step, 1, (1, 1), backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(2)
+def test_graphed_step_two_gpus():
+    run_distributed(_worker_graphed_step, 2, (2, 1), backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_graphed_step_four_gpus():
+    run_distributed(_worker_graphed_step, 4, (2, 2), backend="nccl", timeout=300)
