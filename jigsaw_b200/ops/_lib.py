@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_int, c_longlong, c_uint, c_void_p
+from ctypes import POINTER, c_int, c_longlong, c_uint, c_void_p, c_float
 from functools import lru_cache
 
 import torch
@@ -32,6 +32,22 @@ class JbHalo(ctypes.Structure):
         ("push_stride", c_uint),
         ("wait_stride", c_uint),
         ("replay", c_void_p),
+    ]
+
+
+class JbLnExchange(ctypes.Structure):
+    """Mirror of the C ``JbLnExchange`` struct: inboxes / flags of the column ranks of a LayerNorm."""
+
+    _fields_ = [
+        ("inbox_local", c_void_p),
+        ("inbox_peer", c_void_p * 8),
+        ("flag_local", c_void_p),
+        ("flag_peer", c_void_p * 8),
+        ("epoch", c_uint),
+        ("stride", c_uint),
+        ("replay", c_void_p),
+        ("parts", c_int),
+        ("me", c_int),
     ]
 
 
@@ -78,6 +94,20 @@ def _declare(L: ctypes.CDLL) -> None:
         POINTER(JbHalo), c_void_p, c_int, c_void_p,
     ]
     L.jb_wgrad_thin.restype = c_int
+    L.jb_layer_norm_grid.argtypes = [c_int, c_int]
+    L.jb_layer_norm_grid.restype = c_int
+    L.jb_layer_norm_fwd.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,  # x x_bf16 y y_bf16 w b
+        c_void_p, c_void_p, c_int, c_int, c_float,  # mean rstd R n eps
+        POINTER(JbLnExchange), c_void_p, c_int, c_void_p,  # exchange status sm_count stream
+    ]
+    L.jb_layer_norm_fwd.restype = c_int
+    L.jb_layer_norm_bwd.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,  # x g dx (+ bf16 flags)
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # w mean rstd dw db scratch
+        c_int, c_int, POINTER(JbLnExchange), c_void_p, c_int, c_void_p,  # R n exchange status sm_count stream
+    ]
+    L.jb_layer_norm_bwd.restype = c_int
 
 
 @lru_cache(maxsize=1)

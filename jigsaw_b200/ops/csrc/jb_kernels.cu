@@ -5,5 +5,6 @@
 #include "conv3x3.cu"
 #include "conv_thin.cu"
 #include "wgrad_noalloc.cu"
+#include "norm.cu"
 
 extern "C" int jb_abi_version() { return 1; }

@@ -1,0 +1,370 @@
+// LayerNorm over a feature dimension that is split across GPUs, forward and backward, each as ONE
+// kernel: local row statistics -> exchange with the other column ranks through peer memory ->
+// normalisation.  The exchange is a push: every rank stores its per-row partials straight into the
+// inboxes of its peers (plain stores over NVLink), publishes an epoch flag per CTA, and waits
+// (bounded) for the flags of the same CTA index on the peers, which by construction handles the same
+// rows.  Grids never exceed the number of co-resident CTAs, so a waiting CTA cannot starve the CTA
+// it waits for.  Rows are re-read from L2 for the second phase.
+//
+// Statistics are combined with the parallel-variance formula (equal counts per rank):
+//   mean = sum_p mean_p / P,   M2 = sum_p M2_p + n * sum_p (mean_p - mean)^2,   var = M2 / (n P)
+// which matches the two-pass (mean, then centred second moment) definition.
+//
+// Backward: dx = rstd * (g w - S1 / N - xhat * S2 / N) with S1 = sum g w, S2 = sum g w xhat over the
+// global feature dimension (exchanged the same way); dw = sum_rows g xhat and db = sum_rows g are
+// accumulated per CTA in shared memory and reduced by a second small kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace jb {
+
+constexpr int LN_THREADS = 256;
+constexpr int LN_WARPS = LN_THREADS / 32;
+constexpr int LN_MAX_PARTS = 8;
+
+struct LnExchange {
+  float* inbox_local;               // [2][P][R][2] this rank's inbox (parity, source rank, row, value)
+  float* inbox_peer[LN_MAX_PARTS];  // the same buffer on every column rank (entry of this rank unused)
+  uint32_t* flag_local;             // [P][grid]
+  uint32_t* flag_peer[LN_MAX_PARTS];
+  uint32_t epoch;                   // value to publish; its parity selects the inbox half
+  uint32_t stride;                  // CUDA-graph replays: see live_epoch()
+  const uint32_t* replay;
+  int parts, me;
+};
+
+struct LnArgs {
+  const void* x; int x_bf16;
+  const void* g; int g_bf16;        // backward only: upstream gradient
+  void* out; int out_bf16;          // forward: y; backward: dx
+  const float* w; const float* b;   // local slices, may be null
+  float* mean; float* rstd;         // [R]: written by forward, read by backward
+  float* dw_part; float* db_part;   // backward: [grid][n]
+  int R, n;
+  float eps;
+  LnExchange ex;
+  int* status;
+};
+
+__device__ __forceinline__ float4 ln_load4(const void* base, int is_bf16, long long idx) {
+  if (is_bf16) {
+    const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+}
+
+__device__ __forceinline__ void ln_store4(void* base, int is_bf16, long long idx, float4 v) {
+  if (is_bf16) {
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + idx) = o;
+  } else {
+    *reinterpret_cast<float4*>(static_cast<float*>(base) + idx) = v;
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Publish this CTA's partials and wait for the same CTA of every peer.  Returns false after a
+// timeout (status is set; the caller still finishes with whatever is in the inbox).
+__device__ __forceinline__ bool ln_exchange(const LnExchange& ex, uint32_t epoch, int* status) {
+  __threadfence_system();          // this thread's peer stores first
+  __syncthreads();
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < ex.parts && static_cast<int>(threadIdx.x) != ex.me) {
+    const int p = threadIdx.x;
+    uint32_t* out = ex.flag_peer[p] + static_cast<size_t>(ex.me) * gridDim.x + blockIdx.x;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(out), "r"(epoch) : "memory");
+    const uint32_t* in = ex.flag_local + static_cast<size_t>(p) * gridDim.x + blockIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(in) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+        if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+        ok = 0;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+// rows of this CTA: a contiguous chunk
+__device__ __forceinline__ void ln_rows(int R, int* r0, int* r1) {
+  const int per = (R + gridDim.x - 1) / gridDim.x;
+  *r0 = min(R, static_cast<int>(blockIdx.x) * per);
+  *r1 = min(R, *r0 + per);
+}
+
+__global__ void __launch_bounds__(LN_THREADS) ln_fwd_kernel(const LnArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int r0, r1;
+  ln_rows(a.R, &r0, &r1);
+  const LnExchange& ex = a.ex;
+  const int P = ex.parts;
+  const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
+  const size_t half = static_cast<size_t>(epoch & 1u) * P * a.R * 2;
+  const float inv_n = 1.f / static_cast<float>(a.n);
+  // ---- phase 1: local mean and centred second moment of every row
+  for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+    const long long base = static_cast<long long>(r) * a.n;
+    float s = 0.f;
+    for (int i = lane * 4; i < a.n; i += 128) {
+      const float4 v = ln_load4(a.x, a.x_bf16, base + i);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    const float mean_l = warp_sum(s) * inv_n;
+    float q = 0.f;
+    for (int i = lane * 4; i < a.n; i += 128) {
+      const float4 v = ln_load4(a.x, a.x_bf16, base + i);
+      const float d0 = v.x - mean_l, d1 = v.y - mean_l, d2 = v.z - mean_l, d3 = v.w - mean_l;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+    const float m2_l = warp_sum(q);
+    if (P == 1) {
+      if (lane == 0) {
+        a.mean[r] = mean_l;
+        a.rstd[r] = rsqrtf(m2_l * inv_n + a.eps);
+      }
+    } else if (lane < P) {
+      const size_t slot = half + (static_cast<size_t>(ex.me) * a.R + r) * 2;
+      float* dst = (lane == ex.me) ? ex.inbox_local : ex.inbox_peer[lane];
+      *reinterpret_cast<float2*>(dst + slot) = make_float2(mean_l, m2_l);
+    }
+  }
+  if (P > 1) {
+    ln_exchange(ex, epoch, a.status);
+    for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+      float mp = 0.f, m2p = 0.f;
+      if (lane < P) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(
+            ex.inbox_local + half + (static_cast<size_t>(lane) * a.R + r) * 2));
+        mp = v.x;
+        m2p = v.y;
+      }
+      const float mean = warp_sum(mp) / static_cast<float>(P);
+      const float d = (lane < P) ? (mp - mean) : 0.f;
+      const float m2 = warp_sum(m2p + static_cast<float>(a.n) * d * d);
+      if (lane == 0) {
+        a.mean[r] = mean;
+        a.rstd[r] = rsqrtf(m2 * inv_n / static_cast<float>(P) + a.eps);
+      }
+    }
+  }
+  __syncwarp();
+  // ---- phase 2: normalise (each warp re-reads the statistics it wrote itself)
+  for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+    const long long base = static_cast<long long>(r) * a.n;
+    const float mean = a.mean[r], rstd = a.rstd[r];
+    for (int i = lane * 4; i < a.n; i += 128) {
+      float4 v = ln_load4(a.x, a.x_bf16, base + i);
+      v.x = (v.x - mean) * rstd; v.y = (v.y - mean) * rstd; v.z = (v.z - mean) * rstd; v.w = (v.w - mean) * rstd;
+      if (a.w != nullptr) {
+        const float4 w = *reinterpret_cast<const float4*>(a.w + i);
+        v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+      }
+      if (a.b != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(a.b + i);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      ln_store4(a.out, a.out_bf16, base + i, v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
+  extern __shared__ float acc[];   // [2][n]: dw, db partials of this CTA
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int r0, r1;
+  ln_rows(a.R, &r0, &r1);
+  const LnExchange& ex = a.ex;
+  const int P = ex.parts;
+  const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
+  const size_t half = static_cast<size_t>(epoch & 1u) * P * a.R * 2;
+  const bool want_dw = a.dw_part != nullptr;
+  if (want_dw)
+    for (int i = threadIdx.x; i < 2 * a.n; i += LN_THREADS) acc[i] = 0.f;
+  __syncthreads();
+  const float inv_N = 1.f / (static_cast<float>(a.n) * static_cast<float>(P));
+  // ---- phase 1: S1 = sum g w, S2 = sum g w xhat per row (local part); dw / db partials
+  for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+    const long long base = static_cast<long long>(r) * a.n;
+    const float mean = a.mean[r], rstd = a.rstd[r];
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = lane * 4; i < a.n; i += 128) {
+      const float4 x = ln_load4(a.x, a.x_bf16, base + i);
+      const float4 g = ln_load4(a.g, a.g_bf16, base + i);
+      float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (a.w != nullptr) w = *reinterpret_cast<const float4*>(a.w + i);
+      const float h0 = (x.x - mean) * rstd, h1 = (x.y - mean) * rstd, h2 = (x.z - mean) * rstd, h3 = (x.w - mean) * rstd;
+      const float gw0 = g.x * w.x, gw1 = g.y * w.y, gw2 = g.z * w.z, gw3 = g.w * w.w;
+      s1 += (gw0 + gw1) + (gw2 + gw3);
+      s2 += (gw0 * h0 + gw1 * h1) + (gw2 * h2 + gw3 * h3);
+      if (want_dw) {
+        atomicAdd(acc + i + 0, g.x * h0); atomicAdd(acc + i + 1, g.y * h1);
+        atomicAdd(acc + i + 2, g.z * h2); atomicAdd(acc + i + 3, g.w * h3);
+        atomicAdd(acc + a.n + i + 0, g.x); atomicAdd(acc + a.n + i + 1, g.y);
+        atomicAdd(acc + a.n + i + 2, g.z); atomicAdd(acc + a.n + i + 3, g.w);
+      }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane < P) {
+      const size_t slot = half + (static_cast<size_t>(ex.me) * a.R + r) * 2;
+      float* dst = (P == 1 || lane == ex.me) ? ex.inbox_local : ex.inbox_peer[lane];
+      *reinterpret_cast<float2*>(dst + slot) = make_float2(s1, s2);
+    }
+  }
+  if (P > 1) ln_exchange(ex, epoch, a.status);
+  else __syncwarp();
+  // ---- phase 2: dx
+  for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+    const long long base = static_cast<long long>(r) * a.n;
+    const float mean = a.mean[r], rstd = a.rstd[r];
+    float p1 = 0.f, p2 = 0.f;
+    if (lane < P) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(
+          ex.inbox_local + half + (static_cast<size_t>(lane) * a.R + r) * 2));
+      p1 = v.x;
+      p2 = v.y;
+    }
+    const float S1 = warp_sum(p1) * inv_N, S2 = warp_sum(p2) * inv_N;
+    for (int i = lane * 4; i < a.n; i += 128) {
+      const float4 x = ln_load4(a.x, a.x_bf16, base + i);
+      const float4 g = ln_load4(a.g, a.g_bf16, base + i);
+      float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (a.w != nullptr) w = *reinterpret_cast<const float4*>(a.w + i);
+      float4 d;
+      d.x = rstd * (g.x * w.x - S1 - (x.x - mean) * rstd * S2);
+      d.y = rstd * (g.y * w.y - S1 - (x.y - mean) * rstd * S2);
+      d.z = rstd * (g.z * w.z - S1 - (x.z - mean) * rstd * S2);
+      d.w = rstd * (g.w * w.w - S1 - (x.w - mean) * rstd * S2);
+      ln_store4(a.out, a.out_bf16, base + i, d);
+    }
+  }
+  if (want_dw) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.n; i += LN_THREADS) {
+      a.dw_part[static_cast<size_t>(blockIdx.x) * a.n + i] = acc[i];
+      a.db_part[static_cast<size_t>(blockIdx.x) * a.n + i] = acc[a.n + i];
+    }
+  }
+}
+
+// out[i] = sum_g part[g][i]   (deterministic order)
+__global__ void ln_colsum_kernel(const float* __restrict__ p0, const float* __restrict__ p1, int G, int n,
+                                 float* __restrict__ o0, float* __restrict__ o1) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s0 = 0.f, s1 = 0.f;
+  for (int g = 0; g < G; ++g) {
+    s0 += p0[static_cast<size_t>(g) * n + i];
+    s1 += p1[static_cast<size_t>(g) * n + i];
+  }
+  if (o0) o0[i] = s0;
+  if (o1) o1[i] = s1;
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+struct JbLnExchange {          // C mirror passed from Python (ctypes)
+  void* inbox_local;
+  void* inbox_peer[8];
+  void* flag_local;
+  void* flag_peer[8];
+  unsigned int epoch;
+  unsigned int stride;
+  const unsigned int* replay;
+  int parts, me;
+};
+
+static int ln_fill(LnArgs* a, const JbLnExchange* ex) {
+  a->ex.parts = 1;
+  if (ex == nullptr || ex->parts <= 1) {
+    if (ex != nullptr) a->ex.inbox_local = static_cast<float*>(ex->inbox_local);
+    return 0;
+  }
+  if (ex->parts > LN_MAX_PARTS) return -1;
+  a->ex.inbox_local = static_cast<float*>(ex->inbox_local);
+  a->ex.flag_local = static_cast<uint32_t*>(ex->flag_local);
+  for (int p = 0; p < ex->parts; ++p) {
+    a->ex.inbox_peer[p] = static_cast<float*>(ex->inbox_peer[p]);
+    a->ex.flag_peer[p] = static_cast<uint32_t*>(ex->flag_peer[p]);
+  }
+  a->ex.epoch = ex->epoch;
+  a->ex.stride = ex->stride;
+  a->ex.replay = ex->replay;
+  a->ex.parts = ex->parts;
+  a->ex.me = ex->me;
+  return 0;
+}
+
+// Number of CTAs a LayerNorm launch uses for R rows (the caller sizes flags and partials with it).
+extern "C" int jb_layer_norm_grid(int R, int sm_count) {
+  const int want = (R + LN_WARPS - 1) / LN_WARPS;
+  return want < sm_count ? (want < 1 ? 1 : want) : sm_count;
+}
+
+// y = LayerNorm(x) over the last dimension of x [R][n] (n = local slice, n % 4 == 0); saves mean / rstd.
+extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16, const float* w, const float* b,
+                                 float* mean, float* rstd, int R, int n, float eps, const JbLnExchange* ex,
+                                 int* status, int sm_count, void* stream) {
+  if (n % 4 != 0 || R <= 0) return -1;
+  LnArgs a{};
+  a.x = x; a.x_bf16 = x_bf16; a.out = y; a.out_bf16 = y_bf16; a.w = w; a.b = b;
+  a.mean = mean; a.rstd = rstd; a.R = R; a.n = n; a.eps = eps; a.status = status;
+  if (ln_fill(&a, ex) != 0) return -1;
+  const int grid = jb_layer_norm_grid(R, sm_count);
+  ln_fwd_kernel<<<grid, LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// dx, dw, db of the same.  scratch: 2 * grid * n floats.  The exchange needs an inbox even with one part.
+extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g_bf16, void* dx, int dx_bf16,
+                                 const float* w, const float* mean, const float* rstd, float* dw, float* db,
+                                 float* scratch, int R, int n, const JbLnExchange* ex, int* status, int sm_count,
+                                 void* stream) {
+  if (n % 4 != 0 || R <= 0 || n > 12000 || ex == nullptr || ex->inbox_local == nullptr) return -1;
+  LnArgs a{};
+  a.x = x; a.x_bf16 = x_bf16; a.g = g; a.g_bf16 = g_bf16; a.out = dx; a.out_bf16 = dx_bf16; a.w = w;
+  a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd); a.R = R; a.n = n; a.status = status;
+  if (ln_fill(&a, ex) != 0) return -1;
+  const int grid = jb_layer_norm_grid(R, sm_count);
+  const bool want = dw != nullptr || db != nullptr;
+  if (want) {
+    a.dw_part = scratch;
+    a.db_part = scratch + static_cast<size_t>(grid) * n;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int smem = want ? 2 * n * static_cast<int>(sizeof(float)) : 0;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(ln_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return -3;
+  ln_bwd_kernel<<<grid, LN_THREADS, smem, st>>>(a);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (want) {
+    ln_colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(a.dw_part, a.db_part, grid, n, dw, db);
+    if (cudaGetLastError() != cudaSuccess) return -4;
+  }
+  return 0;
+}

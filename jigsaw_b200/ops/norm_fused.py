@@ -1,9 +1,138 @@
-"""Bindings of the fused kernels (see the package docstring)."""
+"""Fused LayerNorm over a feature dimension split across GPUs (``csrc/norm.cu``).
+
+Forward and backward are one kernel each: local row statistics, exchange of the per-row
+partials with the other column ranks through peer memory (stores over NVLink + an epoch flag
+per CTA), normalisation.  With an unsplit feature dimension the same kernels run without the
+exchange.  Falls back (returns ``None``) for shapes / dtypes the kernels do not cover; the
+caller then takes the ``torch.distributed`` path.
+
+Reference parity: jigsaw/modules/normalization/_functional.py:45-59 (forward: two blocking
+all-reduces) and :136-177 (backward: two more); here each direction is a single launch.
+"""
 
 from __future__ import annotations
 
+import ctypes
+from typing import Any
 
-def __getattr__(name: str):
-    if name.startswith("maybe_fused_"):
-        return lambda *a, **k: None
-    raise AttributeError(name)
+import torch
+import torch.distributed as dist
+
+from . import _lib, symm
+
+_OK = (torch.float32, torch.bfloat16)
+
+
+def _p(t: torch.Tensor | None) -> ctypes.c_void_p | None:
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launcher {what} failed with code {rc}")
+
+
+class _Exchange:
+    """Inbox + flags of one launch.  With several column ranks they live in a symmetric arena
+    block (same offset on every rank); the block goes back to the arena right after the launch
+    is queued (reuse is ordered by the stream, the inbox halves alternate with the epoch)."""
+
+    def __init__(self, device: torch.device, group: dist.ProcessGroup | None, rows: int, grid: int) -> None:
+        parts = 1 if group is None else group.size()
+        self.desc = _lib.JbLnExchange()
+        self.desc.parts, self.desc.me = parts, 0 if group is None else group.rank()
+        self.block = None
+        flag_bytes = (parts * grid * 4 + 255) // 256 * 256
+        inbox_bytes = 2 * parts * rows * 2 * 4
+        if parts == 1:
+            self.local = torch.empty(inbox_bytes // 4, dtype=torch.float32, device=device)
+            self.desc.inbox_local = self.local.data_ptr()
+            return
+        ar = symm.arena(device)
+        self.block = ar.alloc(flag_bytes + inbox_bytes, tag=("layer_norm", parts, rows, grid))
+        self.desc.flag_local = self.block.ptr
+        self.desc.inbox_local = self.block.ptr + flag_bytes
+        for i, r in enumerate(dist.get_process_group_ranks(group)):
+            self.desc.flag_peer[i] = self.block.peer_ptr(r)
+            self.desc.inbox_peer[i] = self.block.peer_ptr(r) + flag_bytes
+        self.desc.epoch = ar.next_own_epoch(self.block)
+        if ar.capture_stride is not None:
+            self.desc.stride = ar.capture_stride
+            self.desc.replay = ar.replay.data_ptr()
+        self.arena = ar
+
+    def done(self) -> None:
+        if self.block is not None:
+            self.arena.free(self.block)
+            self.block = None
+
+
+class _FusedLayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None, group: Any, eps: float,
+                out_dtype: torch.dtype) -> torch.Tensor:
+        L = _lib.lib()
+        dev = x.device
+        n = x.shape[-1]
+        x2 = x.reshape(-1, n)
+        R = x2.shape[0]
+        sm = _lib.sm_count(dev.index)
+        grid = L.jb_layer_norm_grid(R, sm)
+        y = torch.empty(x.shape, dtype=out_dtype, device=dev)
+        mean = torch.empty(R, dtype=torch.float32, device=dev)
+        rstd = torch.empty(R, dtype=torch.float32, device=dev)
+        ex = _Exchange(dev, group, R, grid)
+        status = symm.arena(dev).status
+        _check(L.jb_layer_norm_fwd(_p(x2), int(x.dtype == torch.bfloat16), _p(y), int(out_dtype == torch.bfloat16), _p(w),
+                                   _p(b), _p(mean), _p(rstd), R, n, float(eps), ctypes.byref(ex.desc), _p(status), sm,
+                                   _lib.stream_ptr()), "layer_norm_fwd")
+        ex.done()
+        _lib.count_launches(1)
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.group, ctx.has_b, ctx.shape = group, b is not None, x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        L = _lib.lib()
+        x2, w, mean, rstd = ctx.saved_tensors
+        dev = x2.device
+        R, n = x2.shape
+        if g.dtype not in _OK:
+            g = g.float()
+        g2 = g.reshape(R, n).contiguous()
+        sm = _lib.sm_count(dev.index)
+        grid = L.jb_layer_norm_grid(R, sm)
+        dx = torch.empty_like(x2)
+        want_w = w is not None and ctx.needs_input_grad[1]
+        want_b = ctx.has_b and ctx.needs_input_grad[2]
+        dw = torch.empty(n, dtype=torch.float32, device=dev) if want_w else None
+        db = torch.empty(n, dtype=torch.float32, device=dev) if want_b else None
+        scratch = torch.empty(2 * grid * n, dtype=torch.float32, device=dev) if (want_w or want_b) else None
+        ex = _Exchange(dev, ctx.group, R, grid)
+        status = symm.arena(dev).status
+        _check(L.jb_layer_norm_bwd(_p(x2), int(x2.dtype == torch.bfloat16), _p(g2), int(g2.dtype == torch.bfloat16), _p(dx),
+                                   int(dx.dtype == torch.bfloat16), _p(w), _p(mean), _p(rstd), _p(dw), _p(db), _p(scratch),
+                                   R, n, ctypes.byref(ex.desc), _p(status), sm, _lib.stream_ptr()), "layer_norm_bwd")
+        ex.done()
+        _lib.count_launches(2 if scratch is not None else 1)
+        return dx.view(ctx.shape), dw, db, None, None, None
+
+
+def maybe_fused_layer_norm(x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None,
+                           col_group: dist.ProcessGroup | None, eps: float) -> torch.Tensor | None:
+    """LayerNorm of the last dimension of ``x`` (split over ``col_group``) with the fused
+    kernels, or ``None`` when they do not apply."""
+    if not x.is_cuda or x.dtype not in _OK or x.dim() < 2 or x.shape[-1] % 4 or x.shape[-1] > 12000 or x.numel() == 0:
+        return None
+    if any(t is not None and (t.dtype != torch.float32 or not t.is_contiguous()) for t in (w, b)):
+        return None
+    if b is not None and w is None:
+        return None
+    parts = 1 if col_group is None else col_group.size()
+    if parts > 8 or torch._C._functorch.is_batchedtensor(x):
+        return None
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    out_dtype = torch.float32 if torch.is_autocast_enabled("cuda") else x.dtype
+    return _FusedLayerNorm.apply(x.contiguous(), w, b, col_group if parts > 1 else None, eps, out_dtype)

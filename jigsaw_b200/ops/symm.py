@@ -40,13 +40,14 @@ def _round_up(n: int, a: int) -> int:
 class Block:
     """A sub-range of the arena: same offset on every rank."""
 
-    __slots__ = ("arena", "segment", "offset", "nbytes", "slot", "epoch", "tensor", "tag")
+    __slots__ = ("arena", "segment", "offset", "nbytes", "slot", "epoch", "tensor", "tag", "own_epoch")
 
     def __init__(self, arena: "PeerArena", segment: int, offset: int, nbytes: int, tensor: torch.Tensor) -> None:
         self.arena, self.segment, self.offset, self.nbytes = arena, segment, offset, nbytes
         self.tensor = tensor
         self.slot = -1
         self.epoch = 0
+        self.own_epoch = 0          # epoch of flags that live inside the block itself
         self.tag: object = None
 
     @property
@@ -79,6 +80,7 @@ class PeerArena:
         self.replay = torch.zeros(1, dtype=torch.int32, device=device)
         self._capture_stride: int | None = None
         self._capture_slots: set[int] = set()
+        self._capture_blocks: list[Block] = []
         self._flags = None
         if self.symmetric:
             self._flags = self._new_symmetric(_MAX_SLOTS * _FLAG_WORDS * 4)
@@ -166,16 +168,33 @@ class PeerArena:
         so one generous stride serves all slots."""
         self._capture_stride = int(stride)
         self._capture_slots = set()
+        self._capture_blocks = []
 
-    def end_capture(self) -> set[int]:
-        """Leave capture mode; returns the flag slots the captured step produces."""
+    def end_capture(self) -> tuple[set[int], list[Block]]:
+        """Leave capture mode; returns the flag slots and the self-flagged blocks that the
+        captured step produces."""
         self._capture_stride = None
-        return set(self._capture_slots)
+        return set(self._capture_slots), list(self._capture_blocks)
 
-    def advance(self, slots: set[int], stride: int) -> None:
+    def advance(self, produced: tuple[set[int], list[Block]], stride: int) -> None:
         """Account on the host for one replay of a captured step."""
+        slots, blocks = produced
         for slot in slots:
             self._slot_epoch[slot] += stride
+        for blk in blocks:
+            blk.own_epoch += stride
+
+    def next_own_epoch(self, blk: Block) -> int:
+        """Advance and return the epoch of flags kept inside ``blk`` (blocks are the same on
+        every rank, so their counters agree without communication)."""
+        blk.own_epoch += 1
+        if self._capture_stride is not None and not any(b is blk for b in self._capture_blocks):
+            self._capture_blocks.append(blk)
+        return blk.own_epoch
+
+    @property
+    def capture_stride(self) -> int | None:
+        return self._capture_stride
 
     def flag_ptr(self, world_rank: int, slot: int, direction: int) -> int:
         return self._flags["ptrs"][world_rank] + (slot * _FLAG_WORDS + direction) * 4

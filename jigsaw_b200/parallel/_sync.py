@@ -93,8 +93,10 @@ def sync_grad(*tensors: torch.Tensor | None) -> tuple[torch.Tensor | None, ...]:
     Unmarked tensors, ``None``, tensors that do not require grad and everything under
     ``torch.no_grad()`` pass through untouched.
     """
-    check_active_ddp()
     result = list(tensors)
+    if not dist.is_initialized():        # a single process: nothing is replicated
+        return tuple(result)
+    check_active_ddp()
     if _SYNC_DISABLED or not torch.is_grad_enabled():
         return tuple(result)
     joint = active_joint_state()

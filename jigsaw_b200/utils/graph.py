@@ -53,7 +53,7 @@ class GraphedStep:
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self._graph = torch.cuda.CUDAGraph()
-        self._slots: set[int] = set()
+        self._slots = (set(), [])
         self._arena.begin_capture(EPOCH_STRIDE)
         try:
             with torch.cuda.graph(self._graph):

@@ -133,3 +133,49 @@ def test_graphed_step_two_gpus():
 @pytest.mark.multigpu(4)
 def test_graphed_step_four_gpus():
     run_distributed(_worker_graphed_step, 4, (2, 2), backend="nccl", timeout=300)
+
+
+def _worker_layer_norm(rank, world):
+    """LayerNorm over a feature dimension cut over two GPUs: the fused kernels (statistics
+    exchanged through peer memory) against the undivided torch op, twice in a row and in both
+    directions (the inbox halves alternate from launch to launch)."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": 1, "col": world})
+    col = mesh["col"]
+    torch.manual_seed(0)
+    n = 256
+    full = torch.nn.LayerNorm(n, device=dev)
+    with torch.no_grad():
+        full.weight.uniform_(0.5, 1.5)
+        full.bias.normal_()
+    ln = jb.modules.DistributedLayerNorm.convert_to_jigsaw(full, mesh, dev)
+    for it, rows in enumerate((777, 777, 64)):
+        x = torch.randn(rows, n, device=dev) * 3 + 1
+        g = torch.randn(rows, n, device=dev)
+        xl = x[:, rank * n // world:(rank + 1) * n // world].contiguous().requires_grad_(True)
+        before = _lib.LAUNCHES
+        y = ln(xl)
+        assert _lib.LAUNCHES == before + 1
+        y.backward(g[:, rank * n // world:(rank + 1) * n // world].contiguous())
+        symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        full.zero_grad()
+        yr = full(xr)
+        yr.backward(g)
+        sl = slice(rank * n // world, (rank + 1) * n // world)
+        assert_close(y.detach(), yr.detach()[:, sl], f"call {it}: output", 1e-4, 1e-4)
+        assert_close(xl.grad, xr.grad[:, sl], f"call {it}: input gradient", 1e-4, 1e-4)
+        assert_close(ln.weight.grad, full.weight.grad[sl], f"call {it}: weight gradient", 1e-4, 1e-3)
+        assert_close(ln.bias.grad, full.bias.grad[sl], f"call {it}: bias gradient", 1e-4, 1e-3)
+        ln.zero_grad()
+
+
+@pytest.mark.multigpu(2)
+def test_fused_layer_norm_two_gpus():
+    run_distributed(_worker_layer_norm, 2, backend="nccl", timeout=300)
