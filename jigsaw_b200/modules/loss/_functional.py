@@ -66,9 +66,15 @@ def _elementwise_loss(fn, input, target, reduction, reduce_groups, **kw):
     _check_reduction(reduction)
     if reduction == "none":
         return fn(input, target, reduction="none", **kw)
-    with torch.autocast(input.device.type, enabled=False):
-        acc = torch.promote_types(input.dtype, torch.float32)
-        total = fn(input.to(acc), target.to(acc), reduction="sum", **kw)
+    total = None
+    if fn is F.mse_loss and input.is_cuda and not kw:
+        from ...ops import loss_fused
+
+        total = loss_fused.maybe_fused_sq_diff_sum(input, target)     # one kernel, any strides / bf16 input
+    if total is None:
+        with torch.autocast(input.device.type, enabled=False):
+            acc = torch.promote_types(input.dtype, torch.float32)
+            total = fn(input.to(acc), target.to(acc), reduction="sum", **kw)
     count = torch.full((), float(input.numel()), dtype=torch.float32, device=input.device)   # device-side fill: capturable
     return reduce_scalar_loss(total, count, reduction, reduce_groups).to(input.dtype)
 

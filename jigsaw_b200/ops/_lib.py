@@ -51,6 +51,19 @@ class JbLnExchange(ctypes.Structure):
     ]
 
 
+class JbStrided4(ctypes.Structure):
+    """A tensor of up to four dimensions: base pointer, element type, element strides."""
+
+    _fields_ = [("ptr", c_void_p), ("is_bf16", c_int), ("stride", c_longlong * 4)]
+
+
+class JbAdamTensors(ctypes.Structure):
+    """Parameter / gradient / moment pointers of up to 48 fp32 tensors."""
+
+    _fields_ = [("p", c_void_p * 48), ("g", c_void_p * 48), ("m", c_void_p * 48), ("v", c_void_p * 48),
+                ("numel", c_longlong * 48), ("count", c_int)]
+
+
 def _declare(L: ctypes.CDLL) -> None:
     L.jb_abi_version.restype = c_int
     L.jb_gemm_bf16.argtypes = [
@@ -94,6 +107,25 @@ def _declare(L: ctypes.CDLL) -> None:
         POINTER(JbHalo), c_void_p, c_int, c_void_p,
     ]
     L.jb_wgrad_thin.restype = c_int
+    L.jb_merge_chunks.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p]
+    L.jb_merge_chunks.restype = c_int
+    L.jb_mse_grid.argtypes = [c_longlong, c_int]
+    L.jb_mse_grid.restype = c_int
+    L.jb_mse_sum.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_void_p, c_void_p, c_void_p, c_int,
+                             c_void_p]
+    L.jb_mse_sum.restype = c_int
+    L.jb_mse_grad.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_void_p, c_void_p, c_int, c_int,
+                              c_void_p]
+    L.jb_mse_grad.restype = c_int
+    L.jb_increment.argtypes = [c_void_p, c_void_p]
+    L.jb_increment.restype = c_int
+    L.jb_adam_multi.argtypes = [POINTER(JbAdamTensors), c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p,
+                                c_void_p, c_void_p]
+    L.jb_adam_multi.restype = c_int
+    L.jb_sumsq_multi.argtypes = [POINTER(JbAdamTensors), c_void_p, c_void_p, c_void_p, c_void_p]
+    L.jb_sumsq_multi.restype = c_int
+    L.jb_chunks.argtypes = [c_longlong]
+    L.jb_chunks.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [

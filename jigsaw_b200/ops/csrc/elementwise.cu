@@ -1,0 +1,346 @@
+// Memory-bound helper kernels: online-softmax merge of attention chunks, fused squared-error loss
+// (forward sum and backward gradient on strided tensors), multi-tensor Adam / AdamW.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace jb {
+
+// ------------------------------------------------------------------------------------------
+// Merge the result (o2, l2) of a new key/value chunk into the running state (o1 fp32, l1):
+//   w = sigmoid(l2 - l1);  o1 += w (o2 - o1);  l1 = max(l1, l2) + log1p(exp(-|l1 - l2|))
+// One warp per row (a query of one head); rows = b * h * s.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o1, float* __restrict__ l1,
+                                                    const void* __restrict__ o2, int o2_bf16,
+                                                    const float* __restrict__ l2, long long rows, int d) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float a = l1[row], b = l2[row];
+  // a = -inf (nothing merged yet) gives w = 1; both -inf keeps the state
+  const float diff = b - a;
+  const float w = (b == -INFINITY) ? 0.f : 1.f / (1.f + __expf(-diff));
+  float* po = o1 + row * d;
+  if (o2_bf16) {
+    const __nv_bfloat16* pn = static_cast<const __nv_bfloat16*>(o2) + row * d;
+    for (int i = lane; i < d; i += 32) {
+      const float cur = po[i];
+      po[i] = cur + w * (__bfloat162float(pn[i]) - cur);
+    }
+  } else {
+    const float* pn = static_cast<const float*>(o2) + row * d;
+    for (int i = lane; i < d; i += 32) {
+      const float cur = po[i];
+      po[i] = cur + w * (pn[i] - cur);
+    }
+  }
+  if (lane == 0) {
+    const float m = fmaxf(a, b);
+    l1[row] = (m == -INFINITY) ? m : m + log1pf(__expf(-fabsf(diff)));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Squared-error loss on tensors of up to four dimensions with arbitrary strides.
+//   forward : out[0] = sum (a - b)^2          (deterministic two-level reduction)
+//   backward: ga = scale[0] * 2 (a - b), written with the strides of a
+// ------------------------------------------------------------------------------------------
+struct Strided4 {
+  const void* ptr;
+  int is_bf16;
+  long long stride[4];
+};
+
+struct MseArgs {
+  Strided4 a, b;
+  int size[4];          // logical shape (leading dimensions padded with 1)
+  long long numel;
+  float* partial;       // [grid]
+  float* out;           // scalar
+  unsigned int* counter;
+  const float* scale;   // backward: upstream gradient (device scalar)
+  void* ga;             // backward: gradient of a (strides of a)
+  int ga_bf16;
+};
+
+__device__ __forceinline__ float load_strided(const Strided4& t, long long off) {
+  return t.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(t.ptr)[off])
+                   : static_cast<const float*>(t.ptr)[off];
+}
+
+// Elements are visited in the memory order of `a` when `order_a`, so that its accesses coalesce.
+__device__ __forceinline__ void mse_offsets(const MseArgs& p, long long i, long long* oa, long long* ob) {
+  const int s3 = p.size[3], s2 = p.size[2], s1 = p.size[1];
+  const int i3 = static_cast<int>(i % s3);
+  long long r = i / s3;
+  const int i2 = static_cast<int>(r % s2);
+  r /= s2;
+  const int i1 = static_cast<int>(r % s1);
+  const long long i0 = r / s1;
+  *oa = i0 * p.a.stride[0] + i1 * p.a.stride[1] + i2 * p.a.stride[2] + i3 * p.a.stride[3];
+  *ob = i0 * p.b.stride[0] + i1 * p.b.stride[1] + i2 * p.b.stride[2] + i3 * p.b.stride[3];
+}
+
+__global__ void __launch_bounds__(256) mse_fwd_kernel(const MseArgs p) {
+  float s = 0.f;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    long long oa, ob;
+    mse_offsets(p, i, &oa, &ob);
+    const float d = load_strided(p.a, oa) - load_strided(p.b, ob);
+    s += d * d;
+  }
+  __shared__ float red[8];
+  __shared__ bool last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    p.partial[blockIdx.x] = t;
+    __threadfence();
+    last = atomicAdd(p.counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < 32) {          // the last block adds the partials in a fixed order
+    __threadfence();
+    float t = 0.f;
+    for (unsigned int g = threadIdx.x; g < gridDim.x; g += 32) t += __ldcg(p.partial + g);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) {
+      *p.out = t;
+      *p.counter = 0u;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) mse_bwd_kernel(const MseArgs p) {
+  const float k = 2.f * __ldg(p.scale);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    long long oa, ob;
+    mse_offsets(p, i, &oa, &ob);
+    const float g = k * (load_strided(p.a, oa) - load_strided(p.b, ob));
+    if (p.ga_bf16) static_cast<__nv_bfloat16*>(p.ga)[oa] = __float2bfloat16(g);
+    else static_cast<float*>(p.ga)[oa] = g;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Multi-tensor Adam / AdamW: one launch updates up to ADAM_MAX_TENSORS fp32 parameters.
+// `step` is a device scalar holding the number of the step being taken (already incremented),
+// so the launch can sit in a CUDA graph.
+// ------------------------------------------------------------------------------------------
+constexpr int ADAM_MAX_TENSORS = 48;
+constexpr int ADAM_CHUNK = 4096;   // elements per block
+
+struct AdamTable {
+  float* p[ADAM_MAX_TENSORS];
+  const float* g[ADAM_MAX_TENSORS];
+  float* m[ADAM_MAX_TENSORS];
+  float* v[ADAM_MAX_TENSORS];
+  int first_chunk[ADAM_MAX_TENSORS + 1];   // prefix sums of chunks per tensor
+  long long numel[ADAM_MAX_TENSORS];
+  int count;
+};
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, weight_decay;
+  int decoupled;          // 1: AdamW
+  int maximize;
+  const float* step;      // device scalar
+  const float* grad_scale;  // optional device scalar multiplied into every gradient (clipping), may be null
+};
+
+__global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamTable t, const AdamHyper h) {
+  // which tensor does this block's chunk belong to (few tensors: linear scan)
+  int ti = 0;
+  while (ti + 1 < t.count && static_cast<int>(blockIdx.x) >= t.first_chunk[ti + 1]) ++ti;
+  const long long base = static_cast<long long>(blockIdx.x - t.first_chunk[ti]) * ADAM_CHUNK;
+  const long long n = t.numel[ti];
+  const float step = __ldg(h.step);
+  const float c1 = 1.f - __powf(h.beta1, step);
+  const float c2 = 1.f - __powf(h.beta2, step);
+  const float step_size = h.lr / c1;
+  const float inv_sqrt_c2 = rsqrtf(c2);
+  const float gs = h.grad_scale != nullptr ? __ldg(h.grad_scale) : 1.f;
+  float* p = t.p[ti];
+  const float* g = t.g[ti];
+  float* m = t.m[ti];
+  float* v = t.v[ti];
+  for (long long i = base + threadIdx.x; i < n && i < base + ADAM_CHUNK; i += 256) {
+    float grad = g[i] * gs;
+    if (h.maximize) grad = -grad;
+    float w = p[i];
+    if (h.weight_decay != 0.f) {
+      if (h.decoupled) w *= 1.f - h.lr * h.weight_decay;
+      else grad += h.weight_decay * w;
+    }
+    const float mi = h.beta1 * m[i] + (1.f - h.beta1) * grad;
+    const float vi = h.beta2 * v[i] + (1.f - h.beta2) * grad * grad;
+    m[i] = mi;
+    v[i] = vi;
+    p[i] = w - step_size * mi / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
+  }
+}
+
+// Sum of squares of up to ADAM_MAX_TENSORS tensors (gradient norm): per-block partials, then the
+// last block reduces them in a fixed order and accumulates into out[0].
+__global__ void __launch_bounds__(256) sumsq_kernel(const __grid_constant__ AdamTable t, float* partial,
+                                                    unsigned int* counter, float* out) {
+  int ti = 0;
+  while (ti + 1 < t.count && static_cast<int>(blockIdx.x) >= t.first_chunk[ti + 1]) ++ti;
+  const long long base = static_cast<long long>(blockIdx.x - t.first_chunk[ti]) * ADAM_CHUNK;
+  const long long n = t.numel[ti];
+  const float* g = t.g[ti];
+  float s = 0.f;
+  for (long long i = base + threadIdx.x; i < n && i < base + ADAM_CHUNK; i += 256) s += g[i] * g[i];
+  __shared__ float red[8];
+  __shared__ bool last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float r = 0.f;
+    for (int w = 0; w < 8; ++w) r += red[w];
+    partial[blockIdx.x] = r;
+    __threadfence();
+    last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < 32) {
+    __threadfence();
+    float r = 0.f;
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += 32) r += __ldcg(partial + b);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    if (threadIdx.x == 0) {
+      *out += r;
+      *counter = 0u;
+    }
+  }
+}
+
+__global__ void incr_kernel(float* x) { *x += 1.f; }
+
+}  // namespace jb
+
+using namespace jb;
+
+extern "C" int jb_merge_chunks(float* o1, float* l1, const void* o2, int o2_bf16, const float* l2, long long rows,
+                               int d, void* stream) {
+  if (rows <= 0 || d <= 0) return -1;
+  const long long threads = rows * 32;
+  const unsigned int grid = static_cast<unsigned int>((threads + 255) / 256);
+  merge_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(o1, l1, o2, o2_bf16, l2, rows, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+struct JbStrided4 {
+  const void* ptr;
+  int is_bf16;
+  long long stride[4];
+};
+
+static void mse_fill(MseArgs* p, const JbStrided4* a, const JbStrided4* b, const int* size) {
+  p->a.ptr = a->ptr; p->a.is_bf16 = a->is_bf16;
+  p->b.ptr = b->ptr; p->b.is_bf16 = b->is_bf16;
+  p->numel = 1;
+  for (int i = 0; i < 4; ++i) {
+    p->a.stride[i] = a->stride[i];
+    p->b.stride[i] = b->stride[i];
+    p->size[i] = size[i];
+    p->numel *= size[i];
+  }
+}
+
+extern "C" int jb_mse_grid(long long numel, int sm_count) {
+  const long long want = (numel + 256 * 8 - 1) / (256 * 8);
+  const long long cap = static_cast<long long>(sm_count) * 8;
+  return static_cast<int>(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+// out[0] = sum (a - b)^2.  partial: jb_mse_grid() floats; counter: zeroed word (left zero).
+extern "C" int jb_mse_sum(const JbStrided4* a, const JbStrided4* b, const int* size, float* partial,
+                          unsigned int* counter, float* out, int sm_count, void* stream) {
+  MseArgs p{};
+  mse_fill(&p, a, b, size);
+  if (p.numel <= 0) return -1;
+  p.partial = partial; p.counter = counter; p.out = out;
+  mse_fwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// ga = 2 * scale[0] * (a - b), written with the strides of a.
+extern "C" int jb_mse_grad(const JbStrided4* a, const JbStrided4* b, const int* size, const float* scale, void* ga,
+                           int ga_bf16, int sm_count, void* stream) {
+  MseArgs p{};
+  mse_fill(&p, a, b, size);
+  if (p.numel <= 0) return -1;
+  p.scale = scale; p.ga = ga; p.ga_bf16 = ga_bf16;
+  mse_bwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+struct JbAdamTensors {
+  void* p[48];
+  const void* g[48];
+  void* m[48];
+  void* v[48];
+  long long numel[48];
+  int count;
+};
+
+static int adam_table(AdamTable* t, const JbAdamTensors* in) {
+  if (in->count <= 0 || in->count > ADAM_MAX_TENSORS) return -1;
+  t->count = in->count;
+  int chunks = 0;
+  for (int i = 0; i < in->count; ++i) {
+    t->p[i] = static_cast<float*>(in->p[i]);
+    t->g[i] = static_cast<const float*>(in->g[i]);
+    t->m[i] = static_cast<float*>(in->m[i]);
+    t->v[i] = static_cast<float*>(in->v[i]);
+    t->numel[i] = in->numel[i];
+    t->first_chunk[i] = chunks;
+    chunks += static_cast<int>((in->numel[i] + ADAM_CHUNK - 1) / ADAM_CHUNK);
+  }
+  t->first_chunk[in->count] = chunks;
+  return chunks;
+}
+
+extern "C" int jb_increment(float* x, void* stream) {
+  incr_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(x);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// One Adam / AdamW step for up to 48 fp32 tensors; `step` holds the (already incremented) step number.
+extern "C" int jb_adam_multi(const JbAdamTensors* tensors, float lr, float beta1, float beta2, float eps,
+                             float weight_decay, int decoupled, int maximize, const float* step,
+                             const float* grad_scale, void* stream) {
+  AdamTable t{};
+  const int chunks = adam_table(&t, tensors);
+  if (chunks <= 0) return -1;
+  AdamHyper h{lr, beta1, beta2, eps, weight_decay, decoupled, maximize, step, grad_scale};
+  adam_kernel<<<chunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(t, h);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// out[0] += sum over the tensors' g of g^2.  partial: one float per chunk (jb_chunks()); counter zeroed.
+extern "C" int jb_sumsq_multi(const JbAdamTensors* tensors, float* partial, unsigned int* counter, float* out,
+                              void* stream) {
+  AdamTable t{};
+  const int chunks = adam_table(&t, tensors);
+  if (chunks <= 0) return -1;
+  sumsq_kernel<<<chunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(t, partial, counter, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int jb_chunks(long long numel) { return static_cast<int>((numel + ADAM_CHUNK - 1) / ADAM_CHUNK); }

@@ -6,5 +6,6 @@
 #include "conv_thin.cu"
 #include "wgrad_noalloc.cu"
 #include "norm.cu"
+#include "elementwise.cu"
 
 extern "C" int jb_abi_version() { return 1; }

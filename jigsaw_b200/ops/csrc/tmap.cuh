@@ -25,6 +25,26 @@ inline EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// The encoder is a driver-API call and needs a current context on the calling thread.  A thread
+// that has only used cached allocations so far (an autograd worker, for instance) may not have one;
+// creating and destroying an event through the runtime binds the device's primary context and is
+// legal while another stream is being captured.
+inline void ensure_current_context() {
+  typedef CUresult (*GetCurrentFn)(CUcontext*);
+  static GetCurrentFn get_current = nullptr;
+  if (get_current == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      get_current = reinterpret_cast<GetCurrentFn>(p);
+  }
+  CUcontext ctx = nullptr;
+  if (get_current != nullptr && get_current(&ctx) == CUDA_SUCCESS && ctx != nullptr) return;
+  cudaEvent_t ev;
+  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) cudaEventDestroy(ev);
+}
+
 // rank <= 5.  dims[0] is the innermost (contiguous) extent in elements; strides_bytes[i]
 // is the byte stride of dims[i+1] (rank-1 entries, each a multiple of 16); box[] is the
 // tile copied per request (box[0]*2 bytes == 128 for the 128-byte swizzle used here).
@@ -33,6 +53,7 @@ inline int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const ui
                           const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true) {
   EncodeTiledFn fn = get_encode_tiled();
   if (fn == nullptr) return -1;
+  ensure_current_context();
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bx[5];

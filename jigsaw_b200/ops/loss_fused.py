@@ -1,9 +1,111 @@
-"""Bindings of the fused kernels (see the package docstring)."""
+"""Fused squared-error loss (``csrc/elementwise.cu``): one kernel sums ``(input - target)^2`` over
+tensors of any strides (the bf16 channels-last output of a fused convolution chain against an
+fp32 NCHW target, for instance) and one writes the gradient with the strides and dtype of the
+input, so nothing is copied, cast or re-laid-out between the model and the loss.
+
+Reference parity: ``F.mse_loss(reduction="sum")`` in
+jigsaw/modules/loss/_regression/functional.py:23-28 (ATen elementwise + reduce there).
+"""
 
 from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from . import _lib
+
+_OK = (torch.float32, torch.bfloat16)
 
 
 def __getattr__(name: str):
     if name.startswith("maybe_fused_"):
         return lambda *a, **k: None
     raise AttributeError(name)
+
+
+def _desc(t: torch.Tensor) -> "_lib.JbStrided4":
+    d = _lib.JbStrided4()
+    d.ptr, d.is_bf16 = t.data_ptr(), int(t.dtype == torch.bfloat16)
+    pad = 4 - t.dim()
+    for i in range(4):
+        d.stride[i] = 0 if i < pad else t.stride(i - pad)
+    return d
+
+
+def _sizes(t: torch.Tensor):
+    pad = 4 - t.dim()
+    return (ctypes.c_int * 4)(*([1] * pad + list(t.shape)))
+
+
+_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _scratch_for(dev: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    if dev.index not in _scratch:
+        _scratch[dev.index] = (torch.empty(_lib.sm_count(dev.index) * 8, dtype=torch.float32, device=dev),
+                               torch.zeros(1, dtype=torch.int32, device=dev))
+    return _scratch[dev.index]
+
+
+def _dense(t: torch.Tensor) -> bool:
+    """True when the elements of ``t`` tile one block of memory without gaps or overlaps (any
+    dimension order)."""
+    expect = 1
+    for size, stride in sorted(((sz, st) for sz, st in zip(t.shape, t.stride()) if sz != 1), key=lambda p: p[1]):
+        if stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+class _SqDiffSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        L, dev = _lib.lib(), a.device
+        partial, counter = _scratch_for(dev)
+        out = torch.empty((), dtype=torch.float32, device=dev)
+        da, db = _desc(a), _desc(b)
+        rc = L.jb_mse_sum(ctypes.byref(da), ctypes.byref(db), _sizes(a), ctypes.c_void_p(partial.data_ptr()),
+                          ctypes.c_void_p(counter.data_ptr()), ctypes.c_void_p(out.data_ptr()), _lib.sm_count(dev.index),
+                          _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher mse_sum failed with code {rc}")
+        _lib.count_launches(1)
+        ctx.save_for_backward(a, b)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        a, b = ctx.saved_tensors
+        L, dev = _lib.lib(), a.device
+        ga = gb = None
+        scale = g.float().contiguous()
+        if ctx.needs_input_grad[0]:
+            ga = torch.empty_strided(a.shape, a.stride(), dtype=a.dtype, device=dev)
+            da, db = _desc(a), _desc(b)
+            rc = L.jb_mse_grad(ctypes.byref(da), ctypes.byref(db), _sizes(a), ctypes.c_void_p(scale.data_ptr()),
+                               ctypes.c_void_p(ga.data_ptr()), int(ga.dtype == torch.bfloat16), _lib.sm_count(dev.index),
+                               _lib.stream_ptr())
+            if rc != 0:
+                raise RuntimeError(f"jigsaw_b200 kernel launcher mse_grad failed with code {rc}")
+            _lib.count_launches(1)
+        if ctx.needs_input_grad[1]:
+            gb = (-2.0 * scale) * (a.float() - b.float()).to(b.dtype)
+        return ga, gb
+
+
+def maybe_fused_sq_diff_sum(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor | None:
+    """``sum((a - b)^2)`` as an fp32 scalar (differentiable in ``a``), or ``None`` when the
+    kernel does not apply."""
+    if not a.is_cuda or a.shape != b.shape or a.dim() > 4 or a.dim() == 0 or a.numel() == 0:
+        return None
+    if a.dtype not in _OK or b.dtype not in _OK or torch._C._functorch.is_batchedtensor(a):
+        return None
+    # the gradient is written with the strides of ``a``: they must address distinct elements
+    if not _dense(a):
+        return None
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    return _SqDiffSum.apply(a, b)
