@@ -144,7 +144,12 @@ def main() -> None:
     ph, pw = MESHES[args.gpus]
     model, loss_fn, mesh = build(args.impl, (ph, pw), dev)
     graphed = args.impl == "ours" and not args.no_graph
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True, capturable=graphed)
+    if args.impl == "ours":
+        from jigsaw_b200.optim import FusedAdam
+
+        opt = FusedAdam(model.parameters(), lr=1e-3)          # multi-tensor kernel, device-side step counter
+    else:
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True)
     H, W = args.image // ph, args.image // pw
     # every rank draws its own tile (synthetic data; the global image is 1 x 3 x image x image)
     g = torch.Generator().manual_seed(1234 + rank)
@@ -155,7 +160,8 @@ def main() -> None:
     def step(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         with torch.autocast("cuda", dtype=torch.bfloat16):
             out = model(x)
-        loss = loss_fn(out.float(), y)
+        # the reference's loss wants fp32 predictions; ours reads the bf16 channels-last output in place
+        loss = loss_fn(out if args.impl == "ours" else out.float(), y)
         opt.zero_grad(set_to_none=True)
         loss.backward()
         opt.step()

@@ -159,6 +159,15 @@ def distributed_cross_entropy(
     _check_reduction(reduction)
     dim = dim % input.dim()
     in_dtype = input.dtype
+    if input.is_cuda and not target.is_floating_point() and weight is None and label_smoothing == 0.0:
+        from ...ops import loss_fused
+
+        elem = loss_fused.maybe_fused_cross_entropy(input, target, dim, channel_group, ignore_index)
+        if elem is not None:
+            if reduction == "none":
+                return elem.to(in_dtype)
+            wt = (target != ignore_index).to(torch.float32)
+            return reduce_scalar_loss(elem.sum(), wt.sum(), reduction, reduce_groups).to(in_dtype)
     with torch.autocast(input.device.type, enabled=False):
         logits = input.to(torch.promote_types(in_dtype, torch.float32))
         logp = distributed_log_softmax(logits, dim, channel_group)

@@ -126,6 +126,14 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_sumsq_multi.restype = c_int
     L.jb_chunks.argtypes = [c_longlong]
     L.jb_chunks.restype = c_int
+    L.jb_cross_entropy_grid.argtypes = [c_int, c_int, c_int, c_int]
+    L.jb_cross_entropy_grid.restype = c_int
+    L.jb_cross_entropy_fwd.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                       POINTER(JbLnExchange), c_void_p, c_int, c_void_p]
+    L.jb_cross_entropy_fwd.restype = c_int
+    L.jb_cross_entropy_bwd.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_int, c_void_p]
+    L.jb_cross_entropy_bwd.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [

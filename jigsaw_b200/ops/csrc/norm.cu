@@ -283,6 +283,128 @@ __global__ void ln_colsum_kernel(const float* __restrict__ p0, const float* __re
   if (o1) o1[i] = s1;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Softmax cross-entropy over a class dimension that is split across GPUs (index targets).
+// logits are viewed as [B][C_local][S] (S = 1 for a trailing class dimension); a "row" is one
+// (b, s) pair.  Each rank computes (max, sum exp, true-class logit if it owns the class) per row,
+// the partials are exchanged like the LayerNorm statistics, and every rank ends with
+//   lse = M + log sum_p s_p exp(m_p - M),   loss = lse - logit[target]   (0 for ignored rows).
+// Backward needs no communication: d logits = g_row (exp(x - lse) - onehot).
+// ------------------------------------------------------------------------------------------
+struct CeArgs {
+  const void* x; int x_bf16;
+  const long long* target;      // [R] global class index
+  long long ignore_index;
+  int B, C, S;                  // C = local classes
+  int class_lo;                 // first global class of this rank
+  float* loss;                  // [R]
+  float* lse;                   // [R]
+  const float* grow;            // backward: upstream gradient per row [R]
+  void* dx; int dx_bf16;        // backward: gradient of the logits
+  LnExchange ex;                // inbox slots are float4 here: [2][P][R][4]
+  int* status;
+};
+
+__device__ __forceinline__ float ce_load(const CeArgs& a, long long off) {
+  return a.x_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(a.x)[off]) : static_cast<const float*>(a.x)[off];
+}
+
+__device__ __forceinline__ void ce_row_partials(const CeArgs& a, long long r, int lane, int nl, float* m, float* s,
+                                                float* t) {
+  // nl = number of lanes cooperating on this row (1 or 32)
+  const long long b = r / a.S, sp = r % a.S;
+  const long long base = b * a.C * static_cast<long long>(a.S) + sp;
+  float mx = -INFINITY;
+  for (int c = lane; c < a.C; c += nl) mx = fmaxf(mx, ce_load(a, base + static_cast<long long>(c) * a.S));
+  if (nl == 32) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  float sum = 0.f;
+  for (int c = lane; c < a.C; c += nl) sum += __expf(ce_load(a, base + static_cast<long long>(c) * a.S) - mx);
+  if (nl == 32) sum = warp_sum(sum);
+  const long long tg = a.target[r] - a.class_lo;
+  float tv = 0.f;
+  if (a.target[r] != a.ignore_index && tg >= 0 && tg < a.C) tv = ce_load(a, base + tg * a.S);
+  *m = mx; *s = sum; *t = tv;
+}
+
+template <bool WARP_PER_ROW>
+__global__ void __launch_bounds__(LN_THREADS) ce_fwd_kernel(const CeArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = a.B * a.S;
+  int r0, r1;
+  ln_rows(R, &r0, &r1);
+  const LnExchange& ex = a.ex;
+  const int P = ex.parts;
+  const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
+  const size_t half = static_cast<size_t>(epoch & 1u) * P * R * 4;
+  const int first = WARP_PER_ROW ? warp : static_cast<int>(threadIdx.x);
+  const int step = WARP_PER_ROW ? LN_WARPS : LN_THREADS;
+  for (int r = r0 + first; r < r1; r += step) {
+    float m, s, t;
+    ce_row_partials(a, r, WARP_PER_ROW ? lane : 0, WARP_PER_ROW ? 32 : 1, &m, &s, &t);
+    if (P == 1) {
+      if (!WARP_PER_ROW || lane == 0) {
+        const float lse = m + __logf(s);
+        a.lse[r] = lse;
+        a.loss[r] = (a.target[r] != a.ignore_index) ? lse - t : 0.f;
+      }
+    } else {
+      const float4 v = make_float4(m, s, t, 0.f);
+      const size_t slot = half + (static_cast<size_t>(ex.me) * R + r) * 4;
+      if (WARP_PER_ROW) {
+        if (lane < P) {
+          float* dst = (lane == ex.me) ? ex.inbox_local : ex.inbox_peer[lane];
+          *reinterpret_cast<float4*>(dst + slot) = v;
+        }
+      } else {
+        for (int p = 0; p < P; ++p) {
+          float* dst = (p == ex.me) ? ex.inbox_local : ex.inbox_peer[p];
+          *reinterpret_cast<float4*>(dst + slot) = v;
+        }
+      }
+    }
+  }
+  if (P == 1) return;
+  ln_exchange(ex, epoch, a.status);
+  for (int r = r0 + static_cast<int>(threadIdx.x); r < r1; r += LN_THREADS) {
+    float M = -INFINITY;
+    for (int p = 0; p < P; ++p)
+      M = fmaxf(M, __ldcg(ex.inbox_local + half + (static_cast<size_t>(p) * R + r) * 4));
+    float S = 0.f, T = 0.f;
+    for (int p = 0; p < P; ++p) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(ex.inbox_local + half + (static_cast<size_t>(p) * R + r) * 4));
+      S += v.y * __expf(v.x - M);
+      T += v.z;
+    }
+    const float lse = M + __logf(S);
+    a.lse[r] = lse;
+    a.loss[r] = (a.target[r] != a.ignore_index) ? lse - T : 0.f;
+  }
+}
+
+// one thread per logit, in memory order
+__global__ void __launch_bounds__(256) ce_bwd_kernel(const CeArgs a) {
+  const long long total = static_cast<long long>(a.B) * a.C * a.S;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long sp = i % a.S;
+    const long long c = (i / a.S) % a.C;
+    const long long b = i / (static_cast<long long>(a.S) * a.C);
+    const long long r = b * a.S + sp;
+    const long long tg = a.target[r];
+    float g = 0.f;
+    if (tg != a.ignore_index) {
+      const float p = __expf(ce_load(a, i) - a.lse[r]);
+      g = a.grow[r] * (p - ((tg - a.class_lo) == c ? 1.f : 0.f));
+    }
+    if (a.dx_bf16) static_cast<__nv_bfloat16*>(a.dx)[i] = __float2bfloat16(g);
+    else static_cast<float*>(a.dx)[i] = g;
+  }
+}
+
 }  // namespace jb
 
 using namespace jb;
@@ -367,4 +489,50 @@ extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g
     if (cudaGetLastError() != cudaSuccess) return -4;
   }
   return 0;
+}
+
+// Per-row cross-entropy of logits [B][C][S] (C = local class shard starting at class_lo) against global
+// class indices target[B*S]; writes loss[R] and lse[R].  Exchange inbox slots are 4 floats per row.
+extern "C" int jb_cross_entropy_fwd(const void* x, int x_bf16, const long long* target, long long ignore_index, int B,
+                                    int C, int S, int class_lo, float* loss, float* lse, const JbLnExchange* ex,
+                                    int* status, int sm_count, void* stream) {
+  if (B <= 0 || C <= 0 || S <= 0) return -1;
+  CeArgs a{};
+  a.x = x; a.x_bf16 = x_bf16; a.target = target; a.ignore_index = ignore_index;
+  a.B = B; a.C = C; a.S = S; a.class_lo = class_lo; a.loss = loss; a.lse = lse; a.status = status;
+  LnArgs tmp{};
+  if (ln_fill(&tmp, ex) != 0) return -1;
+  a.ex = tmp.ex;
+  const int R = B * S;
+  const bool warp_rows = (S == 1 && C >= 64);
+  const int per_cta = warp_rows ? LN_WARPS : LN_THREADS;
+  int grid = (R + per_cta - 1) / per_cta;
+  if (grid > sm_count) grid = sm_count;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (warp_rows) ce_fwd_kernel<true><<<grid, LN_THREADS, 0, st>>>(a);
+  else ce_fwd_kernel<false><<<grid, LN_THREADS, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int jb_cross_entropy_grid(int B, int C, int S, int sm_count) {
+  const int R = B * S;
+  const int per_cta = (S == 1 && C >= 64) ? LN_WARPS : LN_THREADS;
+  const int grid = (R + per_cta - 1) / per_cta;
+  return grid > sm_count ? sm_count : grid;
+}
+
+// dx = grow[row] * (softmax - onehot) from the saved lse; rows with ignore_index get zero.
+extern "C" int jb_cross_entropy_bwd(const void* x, int x_bf16, const long long* target, long long ignore_index, int B,
+                                    int C, int S, int class_lo, const float* lse, const float* grow, void* dx,
+                                    int dx_bf16, int sm_count, void* stream) {
+  if (B <= 0 || C <= 0 || S <= 0) return -1;
+  CeArgs a{};
+  a.x = x; a.x_bf16 = x_bf16; a.target = target; a.ignore_index = ignore_index;
+  a.B = B; a.C = C; a.S = S; a.class_lo = class_lo; a.lse = const_cast<float*>(lse); a.grow = grow;
+  a.dx = dx; a.dx_bf16 = dx_bf16;
+  const long long total = static_cast<long long>(B) * C * S;
+  long long grid = (total + 255) / 256;
+  if (grid > static_cast<long long>(sm_count) * 16) grid = static_cast<long long>(sm_count) * 16;
+  ce_bwd_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -109,3 +109,78 @@ def maybe_fused_sq_diff_sum(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor | 
     if not _lib.available():
         raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
     return _SqDiffSum.apply(a, b)
+
+
+# ----------------------------------------------------------------------------- cross-entropy
+class _CrossEntropyRows(torch.autograd.Function):
+    """Per-row softmax cross-entropy of logits ``[B, C_local, S]`` whose class dimension is split
+    over ``group`` (``csrc/norm.cu``): one kernel computes the local (max, sum-exp, true-class logit),
+    exchanges them with the other class shards through peer memory and finishes the row."""
+
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, target: torch.Tensor, group: Any, ignore_index: int) -> torch.Tensor:
+        from .norm_fused import _Exchange
+        from . import symm
+
+        L, dev = _lib.lib(), x.device
+        B, C, S = x.shape
+        R = B * S
+        sm = _lib.sm_count(dev.index)
+        grid = L.jb_cross_entropy_grid(B, C, S, sm)
+        loss = torch.empty(R, dtype=torch.float32, device=dev)
+        lse = torch.empty(R, dtype=torch.float32, device=dev)
+        lo = 0 if group is None else group.rank() * C
+        ex = _Exchange(dev, group, R, grid, width=4, kind="cross_entropy")
+        rc = L.jb_cross_entropy_fwd(ctypes.c_void_p(x.data_ptr()), int(x.dtype == torch.bfloat16),
+                                    ctypes.c_void_p(target.data_ptr()), ignore_index, B, C, S, lo,
+                                    ctypes.c_void_p(loss.data_ptr()), ctypes.c_void_p(lse.data_ptr()), ctypes.byref(ex.desc),
+                                    ctypes.c_void_p(symm.arena(dev).status.data_ptr()), sm, _lib.stream_ptr())
+        ex.done()
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher cross_entropy_fwd failed with code {rc}")
+        _lib.count_launches(1)
+        ctx.save_for_backward(x, target, lse)
+        ctx.lo, ctx.ignore = lo, ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        x, target, lse = ctx.saved_tensors
+        L, dev = _lib.lib(), x.device
+        B, C, S = x.shape
+        dx = torch.empty_like(x)
+        grow = g.float().contiguous()
+        rc = L.jb_cross_entropy_bwd(ctypes.c_void_p(x.data_ptr()), int(x.dtype == torch.bfloat16),
+                                    ctypes.c_void_p(target.data_ptr()), ctx.ignore, B, C, S, ctx.lo,
+                                    ctypes.c_void_p(lse.data_ptr()), ctypes.c_void_p(grow.data_ptr()),
+                                    ctypes.c_void_p(dx.data_ptr()), int(dx.dtype == torch.bfloat16), _lib.sm_count(dev.index),
+                                    _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher cross_entropy_bwd failed with code {rc}")
+        _lib.count_launches(1)
+        return dx, None, None, None
+
+
+def maybe_fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, dim: int, channel_group: Any,
+                              ignore_index: int) -> torch.Tensor | None:
+    """Unreduced cross-entropy (shape of ``target``, fp32, zero where ignored) for index targets,
+    or ``None`` when the kernel does not apply."""
+    if not logits.is_cuda or logits.dtype not in _OK or target.dtype != torch.int64 or logits.numel() == 0:
+        return None
+    if logits.dim() < 2 or torch._C._functorch.is_batchedtensor(logits):
+        return None
+    parts = 1 if channel_group is None else channel_group.size()
+    if parts > 8 or logits.numel() >= 2 ** 31:
+        return None
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    shape = logits.shape
+    B = 1
+    for n in shape[:dim]:
+        B *= n
+    S = 1
+    for n in shape[dim + 1:]:
+        S *= n
+    x = logits.contiguous().view(B, shape[dim], S)
+    rows = _CrossEntropyRows.apply(x, target.contiguous().view(-1), channel_group if parts > 1 else None, int(ignore_index))
+    return rows.view(target.shape)

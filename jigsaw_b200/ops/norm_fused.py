@@ -37,19 +37,20 @@ class _Exchange:
     block (same offset on every rank); the block goes back to the arena right after the launch
     is queued (reuse is ordered by the stream, the inbox halves alternate with the epoch)."""
 
-    def __init__(self, device: torch.device, group: dist.ProcessGroup | None, rows: int, grid: int) -> None:
+    def __init__(self, device: torch.device, group: dist.ProcessGroup | None, rows: int, grid: int, width: int = 2,
+                 kind: str = "layer_norm") -> None:
         parts = 1 if group is None else group.size()
         self.desc = _lib.JbLnExchange()
         self.desc.parts, self.desc.me = parts, 0 if group is None else group.rank()
         self.block = None
         flag_bytes = (parts * grid * 4 + 255) // 256 * 256
-        inbox_bytes = 2 * parts * rows * 2 * 4
+        inbox_bytes = 2 * parts * rows * width * 4
         if parts == 1:
             self.local = torch.empty(inbox_bytes // 4, dtype=torch.float32, device=device)
             self.desc.inbox_local = self.local.data_ptr()
             return
         ar = symm.arena(device)
-        self.block = ar.alloc(flag_bytes + inbox_bytes, tag=("layer_norm", parts, rows, grid))
+        self.block = ar.alloc(flag_bytes + inbox_bytes, tag=(kind, parts, rows, grid))
         self.desc.flag_local = self.block.ptr
         self.desc.inbox_local = self.block.ptr + flag_bytes
         for i, r in enumerate(dist.get_process_group_ranks(group)):

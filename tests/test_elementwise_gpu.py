@@ -75,3 +75,26 @@ def test_fused_adam_matches_torch(adamw):
         opt_b.step()
     for p, q in zip(ours, theirs):
         torch.testing.assert_close(p, q, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("shape,dtype", [((8, 1000), torch.float32), ((2, 19, 30, 40), torch.bfloat16), ((300, 16), torch.float32)])
+@pytest.mark.parametrize("reduction", ["mean", "none"])
+def test_cross_entropy_kernel(shape, dtype, reduction):
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib
+
+    torch.manual_seed(3)
+    x = (torch.randn(*shape, device=DEV) * 3).to(dtype).requires_grad_(True)
+    tshape = (shape[0], *shape[2:])
+    t = torch.randint(0, shape[1], tshape, device=DEV)
+    t.view(-1)[::7] = -100
+    before = _lib.LAUNCHES
+    loss = jb.modules.functional.distributed_cross_entropy(x, t, reduction=reduction)
+    (loss.sum() * 1.5).backward()
+    assert _lib.LAUNCHES == before + 2
+    xr = x.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(xr, t, reduction=reduction)
+    (ref.sum() * 1.5).backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(loss.float(), ref, rtol=tol, atol=tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=tol, atol=tol * max(float(xr.grad.abs().max()), 1e-3))

@@ -179,3 +179,40 @@ def _worker_layer_norm(rank, world):
 @pytest.mark.multigpu(2)
 def test_fused_layer_norm_two_gpus():
     run_distributed(_worker_layer_norm, 2, backend="nccl", timeout=300)
+
+
+def _worker_cross_entropy(rank, world):
+    """Cross-entropy over classes cut over two GPUs (partials exchanged inside the kernel) against
+    the undivided torch op, for a trailing class dimension and for per-pixel classes."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": 1, "col": world})
+    col = mesh["col"]
+    torch.manual_seed(0)
+    for shape in ((16, 1000), (2, 20, 24, 40), (16, 1000)):
+        C = shape[1]
+        x = torch.randn(*shape, device=dev) * 3
+        t = torch.randint(0, C, (shape[0], *shape[2:]), device=dev)
+        t.view(-1)[::5] = -100
+        sl = slice(rank * C // world, (rank + 1) * C // world)
+        xl = x[:, sl].contiguous().requires_grad_(True)
+        before = _lib.LAUNCHES
+        loss = jb.modules.functional.distributed_cross_entropy(xl, t, channel_group=col)
+        loss.backward()
+        assert _lib.LAUNCHES == before + 2
+        symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(xr, t)
+        ref.backward()
+        assert_close(loss.detach(), ref.detach(), f"{shape}: loss", 1e-5, 1e-6)
+        assert_close(xl.grad, xr.grad[:, sl], f"{shape}: gradient", 1e-4, 1e-6)
+
+
+@pytest.mark.multigpu(2)
+def test_fused_cross_entropy_two_gpus():
+    run_distributed(_worker_cross_entropy, 2, backend="nccl", timeout=300)
