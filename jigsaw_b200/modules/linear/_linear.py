@@ -125,7 +125,6 @@ class DistributedLinear(torch.nn.Module):
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = parallel.sync_grad(self.weight, self.bias)
-        x_full = all_gather_cat(x, self.col_group, -1)                     # (.., M/R, K)
         w_rows = all_gather_cat(w, self.col_group, 1)                       # (N/Rw, K)
         j = self.col_group.rank()
         n = self.out_dim // self.col_split
@@ -134,6 +133,14 @@ class DistributedLinear(torch.nn.Module):
             w_j = w_all.narrow(0, j * n, n)
         else:
             w_j = w_rows.narrow(0, j * n, n)
+        if x.is_cuda and self.col_split > 1:
+            from ...ops import linear_fused
+
+            # all-gather of x fused into the GEMM: the kernel reads the peers' blocks itself
+            out = linear_fused.maybe_fused_gather_linear(x, w_j, b, self.col_group)
+            if out is not None:
+                return out
+        x_full = all_gather_cat(x, self.col_group, -1)                     # (.., M/R, K)
         return _local_linear(x_full, w_j, b)
 
     # ------------------------------------------------------------------ conversion

@@ -51,6 +51,13 @@ class JbLnExchange(ctypes.Structure):
     ]
 
 
+class JbGather(ctypes.Structure):
+    """A operand of a GEMM whose reduction dimension is split over GPUs (see ``jb_gemm_bf16_gather``)."""
+
+    _fields_ = [("a_part", c_void_p * 8), ("flag", c_void_p * 8), ("epoch", c_uint), ("stride", c_uint),
+                ("replay", c_void_p), ("parts", c_int), ("k_part", c_int), ("lda_part", c_longlong)]
+
+
 class JbStrided4(ctypes.Structure):
     """A tensor of up to four dimensions: base pointer, element type, element strides."""
 
@@ -107,6 +114,11 @@ def _declare(L: ctypes.CDLL) -> None:
         POINTER(JbHalo), c_void_p, c_int, c_void_p,
     ]
     L.jb_wgrad_thin.restype = c_int
+    L.jb_gemm_bf16_gather.argtypes = [POINTER(JbGather), c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong,
+                                      c_int, c_int, c_int, c_void_p, c_void_p]
+    L.jb_gemm_bf16_gather.restype = c_int
+    L.jb_publish.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]
+    L.jb_publish.restype = c_int
     L.jb_merge_chunks.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p]
     L.jb_merge_chunks.restype = c_int
     L.jb_mse_grid.argtypes = [c_longlong, c_int]

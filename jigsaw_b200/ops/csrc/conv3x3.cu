@@ -63,13 +63,6 @@ struct HaloWait {
   const uint32_t* replay;
 };
 
-// The launch arguments of a kernel inside a CUDA graph are frozen, but every replay must publish and
-// await a later epoch.  The graph bumps a device counter once per replay; the epoch of this launch is
-// its captured value plus (replays * productions of the slot per replay).
-__device__ __forceinline__ uint32_t live_epoch(uint32_t epoch, uint32_t stride, const uint32_t* replay) {
-  return replay == nullptr ? epoch : epoch + stride * __ldg(replay);
-}
-
 struct ConvArgs {
   int NB, H, W;            // local tile
   int tiles_w;             // ceil(W / 128)

@@ -33,6 +33,20 @@ struct GemmEpilogue {
   int accumulate;     // 1 -> C += result (fp32 output only)
 };
 
+// All-gather fused into the GEMM: the reduction dimension of A is split over `parts` GPUs, each part is
+// a [M, k_part] matrix in that GPU's memory (same symmetric offset everywhere).  The TMA producer reads
+// the k-blocks of part p straight from GPU p (plain TMA loads from peer memory, no cluster qualifier)
+// once p's epoch flag says its part is complete.
+constexpr int GEMM_MAX_PARTS = 8;
+struct GemmGather {
+  CUtensorMap map[GEMM_MAX_PARTS];
+  const uint32_t* flag[GEMM_MAX_PARTS];   // local flag words, one per source rank (null: no wait)
+  uint32_t epoch, stride;
+  const uint32_t* replay;
+  int parts;                               // <= 1: plain GEMM, `map` unused
+  int kblocks_per_part;
+};
+
 template <int BN>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * 128;
@@ -46,7 +60,7 @@ struct GemmSmem {
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 GemmEpilogue ep, int M, int N, int K, int* status) {
+                 const __grid_constant__ GemmGather gather, GemmEpilogue ep, int M, int N, int K, int* status) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,6 +108,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
+      int ready_parts = 0;     // parts [0, ready_parts) have been waited for
+      const uint32_t want = live_epoch(gather.epoch, gather.stride, gather.replay);
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         const int m0 = (t / tiles_n) * GEMM_BM;
         const int n0 = (t % tiles_n) * BN;
@@ -101,11 +117,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = 0; kb < kblocks && ok; ++kb) {
           ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, status);
           if (!ok) break;
+          const int k0 = kb * GEMM_BK;
+          int part = 0;
+          if (A_MN == 0 && gather.parts > 1) {
+            part = kb / gather.kblocks_per_part;
+            while (ready_parts <= part && ok) {          // first use of a part: its owner must have published it
+              const uint32_t* f = gather.flag[ready_parts];
+              if (f != nullptr) {
+                const uint64_t t0 = globaltimer_ns();
+                while (true) {
+                  uint32_t v;
+                  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                  if (static_cast<int32_t>(v - want) >= 0) break;
+                  if (*abort_flag || globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+                    *abort_flag = 1;      // every bounded wait of this CTA now returns at once
+                    if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+                    ok = false;
+                    break;
+                  }
+                  __nanosleep(64);
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");
+              }
+              ++ready_parts;
+            }
+            if (!ok) break;
+          }
           uint8_t* a_dst = smem + s * S::STAGE_BYTES;
           uint8_t* b_dst = a_dst + S::A_BYTES;
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
-          const int k0 = kb * GEMM_BK;
-          if (A_MN == 0) {
+          if (A_MN == 0 && gather.parts > 1) {
+            tma_load_2d(a_dst, &gather.map[part], &full[s], k0 - part * gather.kblocks_per_part * GEMM_BK, m0);
+          } else if (A_MN == 0) {
             tma_load_2d(a_dst, &tmA, &full[s], k0, m0);
           } else {
 #pragma unroll
@@ -238,9 +281,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+struct GatherSpec {                      // host-side description of a gathered A operand
+  const void* part[GEMM_MAX_PARTS];
+  const uint32_t* flag[GEMM_MAX_PARTS];
+  uint32_t epoch, stride;
+  const uint32_t* replay;
+  int parts, k_part;
+};
+
 template <int BN, int A_MN, int B_MN>
 static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int M, int N, int K, long long lda,
-                       long long ldb, int sm_count, int* status, cudaStream_t stream) {
+                       long long ldb, int sm_count, int* status, cudaStream_t stream,
+                       const GatherSpec* gs = nullptr) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   {
@@ -248,7 +300,8 @@ static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int
     uint64_t dims[2], strides[1];
     uint32_t box[2];
     if (A_MN == 0) {
-      dims[0] = K; dims[1] = M; box[0] = 64; box[1] = GEMM_BM;
+      // with a gathered A operand this map only describes part 0 (the kernel uses the per-part maps)
+      dims[0] = (gs != nullptr && gs->parts > 1) ? gs->k_part : K; dims[1] = M; box[0] = 64; box[1] = GEMM_BM;
     } else {
       dims[0] = M; dims[1] = K; box[0] = 64; box[1] = GEMM_BK;
     }
@@ -262,6 +315,20 @@ static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int
     strides[0] = static_cast<uint64_t>(ldb) * 2;
     if (make_tmap_bf16(&tmB, B, 2, dims, strides, box) != 0) return -2;
   }
+  GemmGather gather{};
+  if (gs != nullptr && gs->parts > 1) {
+    if (A_MN != 0 || gs->parts > GEMM_MAX_PARTS || gs->k_part % GEMM_BK != 0) return -1;
+    for (int p = 0; p < gs->parts; ++p) {
+      uint64_t dims[2] = {static_cast<uint64_t>(gs->k_part), static_cast<uint64_t>(M)};
+      uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+      uint32_t box[2] = {64, GEMM_BM};
+      if (make_tmap_bf16(&gather.map[p], gs->part[p], 2, dims, strides, box) != 0) return -2;
+      gather.flag[p] = gs->flag[p];
+    }
+    gather.epoch = gs->epoch; gather.stride = gs->stride; gather.replay = gs->replay;
+    gather.parts = gs->parts;
+    gather.kblocks_per_part = gs->k_part / GEMM_BK;
+  }
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -270,7 +337,7 @@ static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, ep, M, N, K, status);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, gather, ep, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -309,4 +376,63 @@ extern "C" int jb_gemm_bf16(const void* A, const void* B, void* C, const float* 
     JB_GEMM_DISPATCH(128)
   }
 #undef JB_GEMM_DISPATCH
+}
+
+// C = act(A * B^T + bias) where the reduction dimension of A is split over `parts` GPUs: part p is a
+// row-major [M, k_part] bf16 matrix (row stride lda_part) at a_part[p] (peer pointers allowed).  Before
+// the first k-block of part p is requested the kernel waits (bounded) until flag[p] (a local word, null
+// = ready) reaches epoch (+ stride * *replay inside a CUDA graph).  B is [N, parts * k_part] row-major.
+struct JbGather {
+  const void* a_part[8];
+  const void* flag[8];
+  unsigned int epoch, stride;
+  const unsigned int* replay;
+  int parts, k_part;
+  long long lda_part;
+};
+
+extern "C" int jb_gemm_bf16_gather(const JbGather* g, const void* B, void* C, const float* bias, int M, int N,
+                                   long long ldb, long long ldc, int act, int out_fp32, int sm_count, int* status,
+                                   void* stream) {
+  using namespace jb;
+  if (g == nullptr || g->parts < 2 || g->parts > GEMM_MAX_PARTS || (g->lda_part & 7) || (ldb & 7)) return -1;
+  GatherSpec gs{};
+  for (int p = 0; p < g->parts; ++p) {
+    if (reinterpret_cast<uintptr_t>(g->a_part[p]) & 15) return -1;
+    gs.part[p] = g->a_part[p];
+    gs.flag[p] = static_cast<const uint32_t*>(g->flag[p]);
+  }
+  gs.epoch = g->epoch; gs.stride = g->stride; gs.replay = g->replay; gs.parts = g->parts; gs.k_part = g->k_part;
+  const int K = g->parts * g->k_part;
+  GemmEpilogue ep{C, ldc, bias, act, out_fp32, 0};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool wide = (N >= 256) && (((M + 127) / 128) * ((N + 255) / 256) >= sm_count);
+  const bool narrow = (N <= 64) || ((((M + 127) / 128) * ((N + 127) / 128)) < sm_count / 2 && N % 64 == 0);
+  const void* A0 = g->a_part[0];
+  if (wide) return launch_gemm<256, 0, 0>(A0, B, ep, M, N, K, g->lda_part, ldb, sm_count, status, st, &gs);
+  if (narrow) return launch_gemm<64, 0, 0>(A0, B, ep, M, N, K, g->lda_part, ldb, sm_count, status, st, &gs);
+  return launch_gemm<128, 0, 0>(A0, B, ep, M, N, K, g->lda_part, ldb, sm_count, status, st, &gs);
+}
+
+namespace jb {
+__global__ void publish_kernel(uint32_t* f0, uint32_t* f1, uint32_t* f2, uint32_t* f3, uint32_t* f4, uint32_t* f5,
+                               uint32_t* f6, uint32_t* f7, uint32_t epoch, uint32_t stride, const uint32_t* replay) {
+  uint32_t* f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+  const uint32_t e = live_epoch(epoch, stride, replay);
+  __threadfence_system();
+  if (threadIdx.x < 8 && f[threadIdx.x] != nullptr)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f[threadIdx.x]), "r"(e) : "memory");
+}
+}  // namespace jb
+
+// Publish `epoch` into up to eight flag words (peer pointers allowed) once all earlier work of the stream
+// is complete: the hand-off from a producer of symmetric memory to kernels on other GPUs that read it.
+extern "C" int jb_publish(void* const* flags, int n, unsigned int epoch, unsigned int stride,
+                          const unsigned int* replay, void* stream) {
+  if (n < 0 || n > 8) return -1;
+  uint32_t* f[8] = {};
+  for (int i = 0; i < n; ++i) f[i] = static_cast<uint32_t*>(flags[i]);
+  jb::publish_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7],
+                                                                      epoch, stride, replay);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

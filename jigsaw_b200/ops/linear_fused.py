@@ -7,8 +7,16 @@ transposing anything: ``dX = dY @ W`` (B operand MN-major) and ``dW = dY.T @ X``
 MN-major, fp32 output).  Returns ``None`` when the kernel does not apply; the caller then uses
 ``torch.nn.functional.linear``.
 
+``maybe_fused_gather_linear(x_local, w, b, group)`` fuses the all-gather of the activations
+into that GEMM: every rank drops its ``[M, K / P]`` block (cast to bf16) into a symmetric buffer
+and publishes an epoch flag; the TMA producer of the GEMM then reads the k-blocks of part ``p``
+straight from GPU ``p`` over NVLink, so the gathered ``[M, K]`` matrix is never materialised
+and the transfer overlaps the tensor-core work tile by tile.  (The backward products use local
+GEMMs with an NCCL reduce-scatter / all-gather.)
+
 Reference parity: the ``torch.matmul`` / ``F.linear`` calls of
-jigsaw/modules/linear/_distributed_matmul.py:100-110,159-177 (cuBLAS there).
+jigsaw/modules/linear/_distributed_matmul.py:100-110,159-177 (cuBLAS there) and the masked
+all-to-alls that move ``x`` blocks before them (jigsaw/_core/comm.py:430-455).
 """
 
 from __future__ import annotations
@@ -17,6 +25,7 @@ import ctypes
 from typing import Any
 
 import torch
+import torch.distributed as dist
 
 from . import _lib, symm
 
@@ -99,3 +108,111 @@ def maybe_fused_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None)
     if not _lib.available():
         raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
     return _FusedLinear.apply(x, w, b)
+
+
+# ----------------------------------------------------------------------------- all-gather -> GEMM
+_HEADER = 256          # bytes of flag words in front of the staged block
+_rings: dict[tuple, list] = {}
+
+
+def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
+    """Two blocks per shape, used alternately: a rank can run at most one gathered layer ahead of
+    its peers (it needs their flag of the current layer, which they publish after their previous
+    GEMM), so the block it overwrites is never one that a peer may still be reading."""
+    ring = _rings.get(tag)
+    if ring is None:
+        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
+    blk = ring[0][ring[1] & 1]
+    ring[1] += 1
+    return blk
+
+
+class _GatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, group: Any) -> torch.Tensor:
+        L, dev = _lib.lib(), x.device
+        ar = symm.arena(dev)
+        P, me = group.size(), group.rank()
+        ranks = dist.get_process_group_ranks(group)
+        kp = x.shape[-1]
+        M = x.numel() // kp
+        N = w.shape[0]
+        blk = _staging_block(ar, ("gather_x", dev.index, M, kp, P), _HEADER + M * kp * 2)
+        staged = blk.tensor[_HEADER:].view(torch.bfloat16)[: M * kp].view(M, kp)
+        staged.copy_(x.reshape(M, kp))                                   # cast + copy in one kernel
+        epoch = ar.next_own_epoch(blk)
+        stride = ar.capture_stride or 0
+        replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+        st = _lib.stream_ptr()
+        flags = (ctypes.c_void_p * 8)()
+        n = 0
+        for i, r in enumerate(ranks):
+            if i != me:
+                flags[n] = blk.peer_ptr(r) + 4 * me
+                n += 1
+        rc = L.jb_publish(flags, n, epoch, stride, replay, st)
+        g = _lib.JbGather()
+        for i, r in enumerate(ranks):
+            g.a_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER
+            g.flag[i] = None if i == me else blk.ptr + 4 * i
+        g.epoch, g.stride, g.replay, g.parts, g.k_part, g.lda_part = epoch, stride, replay, P, kp, kp
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        wb = wb if wb.is_contiguous() else wb.contiguous()
+        bias = None if b is None else b.float().contiguous()
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        if rc == 0:
+            rc = L.jb_gemm_bf16_gather(ctypes.byref(g), _p(wb), _p(y), _p(bias), M, N, wb.stride(0), y.stride(0), 0, 0,
+                                       _lib.sm_count(dev.index), _p(ar.status), st)
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher gemm_bf16_gather failed with code {rc}")
+        _lib.count_launches(2)
+        ctx.save_for_backward(staged.clone() if ctx.needs_input_grad[1] else None, wb)
+        ctx.group, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = group, x.shape, x.dtype, w.dtype
+        ctx.b_dtype = None if b is None else b.dtype
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx: Any, gy: torch.Tensor) -> tuple:
+        xb, wb = ctx.saved_tensors
+        group = ctx.group
+        P = group.size()
+        N = wb.shape[0]
+        g = gy.reshape(-1, N)
+        g = g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)
+        g = g if g.is_contiguous() else g.contiguous()
+        M = g.shape[0]
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            full = gemm(g, wb, b_mn=True)                                   # [M, K]: every rank holds a partial sum
+            kp = full.shape[1] // P
+            parts = full.view(M, P, kp).permute(1, 0, 2).contiguous()
+            mine = torch.empty(M, kp, dtype=full.dtype, device=full.device)
+            dist.reduce_scatter_tensor(mine, parts, group=group)
+            dx = mine.view(ctx.x_shape).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            gathered = torch.empty(P, M, xb.shape[1], dtype=xb.dtype, device=xb.device)
+            dist.all_gather_into_tensor(gathered, xb, group=group)
+            x_full = gathered.permute(1, 0, 2).reshape(M, -1)
+            dw = gemm(g, x_full, a_mn=True, b_mn=True, out_dtype=torch.float32).to(ctx.w_dtype)
+        if ctx.b_dtype is not None and ctx.needs_input_grad[2]:
+            db = g.sum(dim=0, dtype=torch.float32).to(ctx.b_dtype)
+        return dx, dw, db, None
+
+
+def maybe_fused_gather_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, group: Any) -> torch.Tensor | None:
+    """``all_gather(x over group, last dim) @ w.T + b`` in one GEMM whose producer reads the other
+    ranks' blocks from their memory, or ``None`` when that does not apply.  ``w`` is ``[N, K]``
+    with ``K = group.size() * x.shape[-1]``."""
+    if group is None or group.size() < 2 or group.size() > 8 or not x.is_cuda or w.dim() != 2 or x.numel() == 0:
+        return None
+    bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    if not bf16 or x.dtype not in (torch.float32, torch.bfloat16) or w.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    kp = x.shape[-1]
+    N, K = w.shape
+    M = x.numel() // kp
+    if K != kp * group.size() or kp % 64 or N % 8 or M % 8 or N < 16 or torch._C._functorch.is_batchedtensor(x):
+        return None
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    return _GatherLinear.apply(x, w, b, group)

@@ -216,3 +216,58 @@ def _worker_cross_entropy(rank, world):
 @pytest.mark.multigpu(2)
 def test_fused_cross_entropy_two_gpus():
     run_distributed(_worker_cross_entropy, 2, backend="nccl", timeout=300)
+
+
+def _worker_gather_linear(rank, world, mesh_axes):
+    """DistributedLinear under bf16 autocast: the all-gather of the activations is fused into the
+    tcgen05 GEMM (TMA loads from the peers' memory); forward and all gradients against the
+    undivided fp32 layer, several layers in a row (the staging blocks alternate)."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh(mesh_axes)
+    row, col = mesh["row"], mesh["col"]
+    torch.manual_seed(0)
+    dims = [256, 512, 256, 256]
+    full = torch.nn.Sequential(*[torch.nn.Linear(dims[i], dims[i + 1], device=dev) for i in range(3)])
+    layers = torch.nn.Sequential(*[jb.modules.DistributedLinear.convert_to_jigsaw(l, mesh, dev) for l in full])
+    cuts = {0: row, 1: col}
+    from dist_utils import split
+
+    for it in range(2):
+        x = torch.randn(512, 256, device=dev)
+        g = torch.randn(512, 256, device=dev)
+        xl = split(x, cuts).requires_grad_(True)
+        before = _lib.LAUNCHES
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = layers(xl)
+        assert _lib.LAUNCHES - before == 6, "three gathered GEMMs (publish + GEMM each) expected"
+        y.backward(split(g, cuts).to(y.dtype))
+        symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        full.zero_grad()
+        yr = full(xr)
+        yr.backward(g)
+        scale = float(yr.abs().max())
+        assert_close(y.float(), split(yr.detach(), cuts), f"step {it}: output", 0.0, 3e-2 * scale)
+        assert_close(xl.grad, split(xr.grad, cuts), f"step {it}: input gradient", 0.0, 3e-2 * float(xr.grad.abs().max()))
+        for i, (a, b) in enumerate(zip(layers, full)):
+            wg = split(b.weight.grad, {0: row if a.row_split > 1 else None, 1: col})
+            assert_close(a.weight.grad, wg, f"step {it}: weight gradient {i}", 0.0, 3e-2 * float(b.weight.grad.abs().max()))
+            assert_close(a.bias.grad, split(b.bias.grad, {0: col}), f"step {it}: bias gradient {i}", 0.0,
+                         3e-2 * float(b.bias.grad.abs().max()))
+        layers.zero_grad()
+
+
+@pytest.mark.multigpu(2)
+def test_gather_linear_two_gpus():
+    run_distributed(_worker_gather_linear, 2, {"row": 1, "col": 2}, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_gather_linear_four_gpus():
+    run_distributed(_worker_gather_linear, 4, {"row": 2, "col": 2}, backend="nccl", timeout=300)
