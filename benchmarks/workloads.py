@@ -1,0 +1,226 @@
+"""Secondary benchmark workloads: the Vision Transformer and the 3-D encoder-decoder, for this
+framework and for the unmodified reference (``--impl reference``, from ``baseline/_ref``).
+
+Both arms build the *same* architecture from their own public layer API (the two APIs share
+signatures), run ``--warmup`` untimed and ``--steps`` timed training steps (forward, loss,
+backward, optimizer) on synthetic data under bf16 autocast, time on the device with CUDA events
+(max over ranks) and print one JSON line.
+
+    python benchmarks/workloads.py --config vit --gpus 1
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        --master-port 29600 benchmarks/workloads.py --config vit --gpus 2 [--impl reference]
+
+Configurations (``--scale small`` shrinks depth / width for quick runs):
+  vit     24 blocks, width 1024, 16 heads, MLP 4096, 1024x1024 image, patch 16 (4096 tokens), batch 8,
+          4 input channels, 1000-class cross-entropy; mesh row x col = {1: 1x1, 2: 1x2, 4: 2x2, 8: 4x2}
+  unet3d  channels 1-32-64-128, stride-2 Conv3d / ConvTranspose3d, GroupNorm(8) + GELU, BCE,
+          volume 128^3 (256^3 with --scale full); mesh sh x sw = {1: 1x1, 2: 2x1, 4: 2x2, 8: 4x2}
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+MESH2D = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (4, 2)}
+TILES = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}
+
+
+def load(impl: str):
+    if impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import jigsaw as lib
+    else:
+        import jigsaw_b200 as lib
+    return lib
+
+
+# ----------------------------------------------------------------------------- ViT (either API)
+class Block(nn.Module):
+    def __init__(self, lib, mesh, dev, dim, heads, hidden, ring):
+        super().__init__()
+        row, col, model = mesh["row"], mesh["col"], mesh["model"]
+        M = lib.modules
+        self.norm1 = M.DistributedLayerNorm(dim, model.rank(), dev, row, col)
+        self.norm2 = M.DistributedLayerNorm(dim, model.rank(), dev, row, col)
+        cfg = None
+        if ring:
+            from importlib import import_module
+
+            att = import_module(lib.__name__ + ".modules.attention")
+            cfg = M.RingAttentionConfig(device=dev, send_in_forward=att.SendForward.KV, save_for_backward=att.SaveBackward.KV)
+        self.attn = M.DistributedAttention(dim, dim, dim, heads, model.rank(), dev, spatial_group=row, channel_group=col,
+                                           ring=ring, config=cfg)
+        self.fc1 = M.DistributedLinear(dim, hidden, device=dev, model_group=model, row_group=row, col_group=col, bias=True)
+        self.fc2 = M.DistributedLinear(hidden, dim, device=dev, model_group=model, row_group=row, col_group=col, bias=True)
+
+    def forward(self, x):
+        x = x + self.attn(self.norm1(x))
+        return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.norm2(x))))
+
+
+class ViT(nn.Module):
+    def __init__(self, lib, mesh, dev, image, patch, chans, dim, heads, depth, hidden, classes):
+        super().__init__()
+        row, col, model = mesh["row"], mesh["col"], mesh["model"]
+        M = lib.modules
+        self.row, self.patch = row, patch
+        self.embed = M.DistributedConv2d(chans, dim, kernel_size=patch, stride=patch, device=dev, spatial_group=row,
+                                         channel_group=col)
+        self.blocks = nn.ModuleList(Block(lib, mesh, dev, dim, heads, hidden, row.size() > 1) for _ in range(depth))
+        self.norm = M.DistributedLayerNorm(dim, model.rank(), dev, row, col)
+        self.head = M.DistributedLinear(dim, classes, device=dev, model_group=col, row_group=row, col_group=col, bias=True)
+        hp, wp, e = image // patch, image // patch // row.size(), dim // col.size()
+        self.pos = nn.Parameter(torch.zeros(hp * wp, e, device=dev))
+        self.tokens = hp * wp * row.size()
+
+    def forward(self, x):
+        z = self.embed(x)
+        b, e, hp, wp = z.shape
+        z = z.permute(0, 2, 3, 1).reshape(b, hp * wp, e).contiguous() + self.pos.to(z.dtype)
+        for blk in self.blocks:
+            z = blk(z)
+        pooled = self.norm(z).sum(dim=1)
+        if self.row.size() > 1:
+            import torch.distributed.nn.functional as dfn
+
+            pooled = dfn.all_reduce(pooled, group=self.row)
+        return self.head(pooled / self.tokens)
+
+
+def build_vit(lib, n, dev, scale):
+    r, c = MESH2D[n]
+    mesh = lib.make_process_mesh({"row": r, "col": c})
+    small = scale == "small"
+    image, patch, chans = (256 if small else 1024), 16, 4
+    dim, heads, depth, hidden, classes, batch = (256, 4, 2, 1024, 1000, 8) if small else (1024, 16, 24, 4096, 1000, 8)
+    torch.manual_seed(mesh["model"].rank())
+    model = ViT(lib, mesh, dev, image, patch, chans, dim, heads, depth, hidden, classes)
+    loss_fn = lib.modules.DistributedCrossEntropyLoss(mesh["col"], (mesh["row"],))
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(batch, chans, image, image, generator=g)
+    x = x[:, mesh["col"].rank() * chans // c:(mesh["col"].rank() + 1) * chans // c]
+    w = image // r
+    x = x[..., mesh["row"].rank() * w:(mesh["row"].rank() + 1) * w].contiguous()
+    y = torch.randint(0, classes, (batch,), generator=g)
+    desc = {"model": f"ViT depth {depth} width {dim} heads {heads} mlp {hidden}, {image}x{image} patch {patch}",
+            "global_batch": batch, "seq_len": (image // patch) ** 2, "parallelism": f"row{r} x col{c}"}
+    return model, loss_fn, x, y, desc, batch
+
+
+def build_unet3d(lib, n, dev, scale):
+    sh, sw = TILES[n]
+    mesh = lib.make_process_mesh({"sh": sh, "sw": sw, "col": 1})
+    M = lib.modules
+    size = {"small": 64, "default": 128, "full": 256}[scale]
+    widths = (32, 64, 128)
+    spatial = (None, mesh["sh"], mesh["sw"])
+    kw = dict(device=dev, spatial_group=spatial, channel_group=mesh["col"])
+    torch.manual_seed(0)
+
+    def norm(ch):
+        return M.DistributedGroupNorm(8, ch, dev, channel_group=mesh["col"], spatial_group=spatial)
+
+    chans = (1, *widths)
+    layers = []
+    for i in range(3):
+        layers += [M.DistributedConv3d(chans[i], chans[i + 1], 3, stride=2, padding=1, **kw), norm(chans[i + 1]), nn.GELU()]
+    ups = (64, 32, 1)
+    ins = (128, 64, 32)
+    for i in range(3):
+        layers.append(M.DistributedConvTranspose3d(ins[i], ups[i], 4, stride=2, padding=1, **kw))
+        if i < 2:
+            layers += [norm(ups[i]), nn.GELU()]
+    model = nn.Sequential(*layers)
+    loss_fn = M.DistributedBCEWithLogitsLoss(reduce_groups=(mesh["sh"], mesh["sw"]))
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1, 1, size, size, size, generator=g)
+    y = (torch.rand(1, 1, size, size, size, generator=g) > 0.5).float()
+    h, w = size // sh, size // sw
+
+    def tile(t):
+        return t[..., mesh["sh"].rank() * h:(mesh["sh"].rank() + 1) * h, mesh["sw"].rank() * w:(mesh["sw"].rank() + 1) * w].contiguous()
+
+    desc = {"model": f"3-D enc-dec 1-32-64-128, {size}^3", "global_batch": 1, "seq_len": None, "parallelism": f"sh{sh} x sw{sw}"}
+    return model, loss_fn, tile(x), tile(y), desc, 1
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", choices=("vit", "unet3d"), default="vit")
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--scale", default="default")
+    args = ap.parse_args()
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "jigsaw")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    lib = load(args.impl)
+    model, loss_fn, x, y, desc, batch = (build_vit if args.config == "vit" else build_unet3d)(lib, args.gpus, dev, args.scale)
+    x, y = x.to(dev), y.to(dev)
+    if args.impl == "ours":
+        from jigsaw_b200.optim import FusedAdam
+
+        opt = FusedAdam(model.parameters(), lr=1e-4, decoupled_weight_decay=True)
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.0, fused=True)
+
+    def step():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = model(x)
+        loss = loss_fn(out.float(), y)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(args.warmup):
+        loss = step()
+    launches0 = 0
+    if args.impl == "ours":
+        from jigsaw_b200.ops import _lib
+
+        launches0 = _lib.LAUNCHES
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = (_lib.LAUNCHES - launches0) if args.impl == "ours" else 0
+    if args.impl == "ours":
+        from jigsaw_b200.ops import symm
+
+        symm.arena(dev).check_status()
+    if rank == 0:
+        print(json.dumps({"metric": f"{args.config} samples/sec (fwd+bwd+AdamW)", "value": batch * 1000.0 / float(ms), "unit": "samples/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(ms), "impl": args.impl,
+                          "dtype": "bf16", "data": "synthetic", "config": desc, "gpu_launches": launches,
+                          "loss": float(loss)}), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
