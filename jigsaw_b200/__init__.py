@@ -10,7 +10,7 @@ peer memory over NVLink; on CPU (gloo) the same layers run on ``torch.distribute
 Reference parity: jigsaw/__init__.py:3-17.
 """
 
-from . import checkpoint, convert, data, debug, gather, init, launch, log, models, modules, parallel
+from . import checkpoint, convert, data, debug, gather, init, launch, log, models, modules, optim, parallel, utils
 from ._core.public import set_module
 from .mesh import ProcessMesh, make_process_mesh
 
@@ -27,7 +27,9 @@ __all__ = [
     "log",
     "models",
     "modules",
+    "optim",
     "parallel",
+    "utils",
 ]
 
 set_module(globals(), __all__)

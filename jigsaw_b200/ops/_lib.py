@@ -58,6 +58,14 @@ class JbGather(ctypes.Structure):
                 ("replay", c_void_p), ("parts", c_int), ("k_part", c_int), ("lda_part", c_longlong)]
 
 
+class JbRoll(ctypes.Structure):
+    """Arguments of the fused distributed roll (see ``csrc/roll.cu``)."""
+
+    _fields_ = [("x", c_void_p), ("A", c_longlong), ("M", c_longlong), ("I16", c_longlong), ("H", c_int), ("W", c_int),
+                ("rem_h", c_int), ("rem_w", c_int), ("out", c_void_p * 4), ("flag_out", c_void_p * 4),
+                ("flag_in", c_void_p * 4), ("epoch", c_uint), ("stride", c_uint), ("replay", c_void_p)]
+
+
 class JbStrided4(ctypes.Structure):
     """A tensor of up to four dimensions: base pointer, element type, element strides."""
 
@@ -119,6 +127,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_gemm_bf16_gather.restype = c_int
     L.jb_publish.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]
     L.jb_publish.restype = c_int
+    L.jb_roll.argtypes = [POINTER(JbRoll), c_void_p, c_void_p, c_int, c_void_p]
+    L.jb_roll.restype = c_int
     L.jb_merge_chunks.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p]
     L.jb_merge_chunks.restype = c_int
     L.jb_mse_grid.argtypes = [c_longlong, c_int]

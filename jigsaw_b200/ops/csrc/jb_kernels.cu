@@ -7,5 +7,6 @@
 #include "wgrad_noalloc.cu"
 #include "norm.cu"
 #include "elementwise.cu"
+#include "roll.cu"
 
 extern "C" int jb_abi_version() { return 1; }

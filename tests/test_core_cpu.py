@@ -13,7 +13,7 @@ import torch
 from dist_utils import assert_close, run_distributed, split
 
 EXPECTED = {
-    "jigsaw_b200": {"ProcessMesh", "make_process_mesh", "checkpoint", "convert", "data", "models", "debug", "gather", "init", "launch", "log", "modules",
+    "jigsaw_b200": {"ProcessMesh", "make_process_mesh", "checkpoint", "convert", "data", "models", "optim", "utils", "debug", "gather", "init", "launch", "log", "modules",
                     "parallel"},
     "jigsaw_b200.parallel": {"JointCommHookState", "broadcast_replicas", "check_ddp", "clip_grad_norm_", "joint_comm_hook",
                              "mark_replicated", "register_joint_comm_hook", "replica_groups", "sync_grad", "synced_call",

@@ -271,3 +271,45 @@ def test_gather_linear_two_gpus():
 @pytest.mark.multigpu(4)
 def test_gather_linear_four_gpus():
     run_distributed(_worker_gather_linear, 4, {"row": 2, "col": 2}, backend="nccl", timeout=300)
+
+
+def _worker_roll(rank, world, axes):
+    """DistributedRoll on the fused kernel (elements stored straight into the neighbours' outputs)
+    against torch.roll of the undivided tensor: several shifts (negative, larger than a tile),
+    forward and backward, bf16 and fp32."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import merge, split
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh(axes)
+    sh, sw = mesh["sh"], mesh["sw"]
+    cuts = {1: sh, 2: sw}
+    torch.manual_seed(0)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(2, 16, 12, 8, device=dev).to(dtype)
+        for shifts in ((3, -2), (-5, 4), (9, 0), (16, -7)):
+            layer = jb.modules.DistributedRoll(shifts, (1, 2), (1, 2), (sh, sw), dev, dtype=dtype)
+            xl = split(x, cuts).requires_grad_(True)
+            before = _lib.LAUNCHES
+            y = layer(xl)
+            assert _lib.LAUNCHES == before + 1
+            ref = torch.roll(x, shifts, (1, 2))
+            assert torch.equal(y.detach(), split(ref, cuts)), (dtype, shifts)
+            g = torch.randn_like(x)
+            y.backward(split(g, cuts))
+            assert torch.equal(xl.grad, split(torch.roll(g, tuple(-s for s in shifts), (1, 2)), cuts)), (dtype, shifts)
+    symm.arena(dev).check_status()
+
+
+@pytest.mark.multigpu(2)
+def test_fused_roll_two_gpus():
+    run_distributed(_worker_roll, 2, {"sh": 2, "sw": 1, "col": 1}, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_fused_roll_four_gpus():
+    run_distributed(_worker_roll, 4, {"sh": 2, "sw": 2, "col": 1}, backend="nccl", timeout=300)
