@@ -82,6 +82,12 @@ class DistributedGroupNorm(torch.nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = parallel.sync_grad(self.weight, self.bias)
+        if x.is_cuda:
+            from ...ops import norm_fused
+
+            out = norm_fused.maybe_fused_group_norm(x, self.local_groups, w, b, list(self._sync_groups), self.eps)
+            if out is not None:
+                return out
         if not self._sync_groups:
             return F.group_norm(x, self.local_groups, w, b, self.eps)
         return distributed_group_norm(x, self.local_groups, w, b, self._sync_groups, self.eps)

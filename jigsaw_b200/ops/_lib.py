@@ -156,6 +156,15 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_cross_entropy_bwd.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                        c_void_p, c_int, c_int, c_void_p]
     L.jb_cross_entropy_bwd.restype = c_int
+    L.jb_group_norm_splits.argtypes = [c_int, c_int]
+    L.jb_group_norm_splits.restype = c_int
+    L.jb_group_norm_fwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_longlong, c_float, POINTER(JbLnExchange), c_void_p, c_int, c_void_p]
+    L.jb_group_norm_fwd.restype = c_int
+    L.jb_group_norm_bwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, POINTER(JbLnExchange), c_void_p, c_int,
+                                    c_void_p]
+    L.jb_group_norm_bwd.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [

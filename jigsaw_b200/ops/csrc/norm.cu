@@ -405,6 +405,291 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(const CeArgs a) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// GroupNorm whose spatial extent is tiled over GPUs.  x is [N][C][S] (S = local voxels); a
+// normalisation group (n, g) is a contiguous run of L = cg * S elements.  Every group is split over
+// `splits` CTAs (grid = groups * splits <= number of SMs, all CTAs co-resident):
+//   phase 1  each CTA: (count, mean, M2) of its chunk                       -> partials in global memory
+//   barrier  grid-wide (atomic counter, bounded spin)
+//   leaders  the first CTA of a group merges the chunk partials, exchanges the group's partial with
+//            the other tile ranks through peer memory (as the LayerNorm rows above) and writes
+//            (mean, rstd) of the group
+//   barrier  grid-wide
+//   phase 2  each CTA normalises its chunk (per-channel affine).
+// Backward has the same shape with (sum g w, sum g w xhat) as the exchanged pair; the per-channel
+// sums for dw / db are accumulated per CTA in shared memory and written as partials.
+// ------------------------------------------------------------------------------------------
+constexpr int GN_MAX_CG = 256;   // channels per group
+
+struct GnArgs {
+  const void* x; int x_bf16;
+  const void* g; int g_bf16;        // backward
+  void* out; int out_bf16;
+  const float* w; const float* b;   // [C] local, may be null
+  float* stats;                     // [groups][2] mean, rstd (forward writes, backward reads)
+  float* partial;                   // [grid][4]
+  float* dw_part; float* db_part;   // backward: [grid][cg]
+  unsigned int* counters;           // 3 zeroed words (left zero)
+  int groups;                       // N * local groups
+  int groups_per_sample;            // local groups
+  int splits;
+  int cg;                           // channels per group
+  long long S;                      // local voxels per channel
+  float eps;
+  LnExchange ex;                    // inbox [2][P][groups][4]; flags [P][groups]
+  int* status;
+};
+
+__device__ __forceinline__ bool gn_grid_barrier(unsigned int* counter, unsigned int target, int* status) {
+  __shared__ int ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok = 1;
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const uint64_t t0 = globaltimer_ns();
+    while (atomicAdd(counter, 0u) < target) {
+      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+        if (status) atomicCAS(status, JB_OK, JB_ERR_MBAR_TIMEOUT);
+        ok = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+__device__ __forceinline__ float gn_block_sum(float v) {
+  __shared__ float red[LN_WARPS];
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_WARPS; ++i) t += red[i];
+  return t;
+}
+
+// Leader of a group: push (a, b, c) to the peers' inboxes, wait for theirs.  One warp.
+__device__ __forceinline__ void gn_exchange(const LnExchange& ex, uint32_t epoch, int gi, int groups, float4 mine,
+                                            int* status) {
+  const int lane = threadIdx.x & 31;
+  const size_t half = static_cast<size_t>(epoch & 1u) * ex.parts * groups * 4;
+  if (lane < ex.parts) {
+    float* dst = (lane == ex.me) ? ex.inbox_local : ex.inbox_peer[lane];
+    *reinterpret_cast<float4*>(dst + half + (static_cast<size_t>(ex.me) * groups + gi) * 4) = mine;
+    __threadfence_system();
+    if (lane != ex.me) {
+      uint32_t* out = ex.flag_peer[lane] + static_cast<size_t>(ex.me) * groups + gi;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(out), "r"(epoch) : "memory");
+      const uint32_t* in = ex.flag_local + static_cast<size_t>(lane) * groups + gi;
+      const uint64_t t0 = globaltimer_ns();
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(in) : "memory");
+        if (static_cast<int32_t>(v - epoch) >= 0) break;
+        if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+          if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+  }
+  __syncwarp();
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(LN_THREADS) gn_kernel(const GnArgs a) {
+  extern __shared__ float ch_acc[];   // backward: [2][cg]
+  const int gi = blockIdx.x / a.splits, j = blockIdx.x % a.splits;
+  const long long L = static_cast<long long>(a.cg) * a.S;
+  long long Lc = (L + a.splits - 1) / a.splits;
+  Lc = (Lc + 3) & ~3ll;
+  const long long e0 = min(L, j * Lc), e1 = min(L, e0 + Lc);
+  const long long base = static_cast<long long>(gi) * L;
+  const int c0 = (gi % a.groups_per_sample) * a.cg;     // first local channel of the group
+  const LnExchange& ex = a.ex;
+  const int P = ex.parts;
+  const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
+  float mean_g = 0.f, rstd_g = 0.f;
+  if (BWD) {
+    mean_g = a.stats[gi * 2];
+    rstd_g = a.stats[gi * 2 + 1];
+    for (int i = threadIdx.x; i < 2 * a.cg; i += LN_THREADS) ch_acc[i] = 0.f;
+    __syncthreads();
+  }
+  // ---- phase 1
+  float p0 = 0.f, p1 = 0.f;
+  if (!BWD) {
+    float s = 0.f;
+    for (long long e = e0 + threadIdx.x * 4; e < e1; e += LN_THREADS * 4) {
+      const float4 v = ln_load4(a.x, a.x_bf16, base + e);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    const float cnt = static_cast<float>(e1 - e0);
+    const float mean_c = cnt > 0.f ? gn_block_sum(s) / cnt : 0.f;
+    float q = 0.f;
+    for (long long e = e0 + threadIdx.x * 4; e < e1; e += LN_THREADS * 4) {
+      const float4 v = ln_load4(a.x, a.x_bf16, base + e);
+      const float d0 = v.x - mean_c, d1 = v.y - mean_c, d2 = v.z - mean_c, d3 = v.w - mean_c;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+    p0 = mean_c;
+    p1 = gn_block_sum(q);
+    if (threadIdx.x == 0)
+      *reinterpret_cast<float4*>(a.partial + static_cast<size_t>(blockIdx.x) * 4) = make_float4(cnt, p0, p1, 0.f);
+  } else {
+    float s1 = 0.f, s2 = 0.f;
+    int cur = -1;                 // channel whose sums are held in registers
+    float cgh = 0.f, cgs = 0.f;
+    for (long long e = e0 + threadIdx.x * 4; e < e1; e += LN_THREADS * 4) {
+      const float4 x = ln_load4(a.x, a.x_bf16, base + e);
+      const float4 g = ln_load4(a.g, a.g_bf16, base + e);
+      const int c = static_cast<int>(e / a.S);
+      if (c != cur) {
+        if (cur >= 0) {
+          atomicAdd(ch_acc + cur, cgh);
+          atomicAdd(ch_acc + a.cg + cur, cgs);
+        }
+        cur = c;
+        cgh = cgs = 0.f;
+      }
+      const float w = a.w != nullptr ? a.w[c0 + c] : 1.f;
+      const float h0 = (x.x - mean_g) * rstd_g, h1 = (x.y - mean_g) * rstd_g, h2 = (x.z - mean_g) * rstd_g,
+                  h3 = (x.w - mean_g) * rstd_g;
+      const float gh = (g.x * h0 + g.y * h1) + (g.z * h2 + g.w * h3);
+      const float gs = (g.x + g.y) + (g.z + g.w);
+      s1 += w * gs;
+      s2 += w * gh;
+      cgh += gh;
+      cgs += gs;
+    }
+    if (cur >= 0) {
+      atomicAdd(ch_acc + cur, cgh);
+      atomicAdd(ch_acc + a.cg + cur, cgs);
+    }
+    p0 = gn_block_sum(s1);
+    p1 = gn_block_sum(s2);
+    if (threadIdx.x == 0)
+      *reinterpret_cast<float4*>(a.partial + static_cast<size_t>(blockIdx.x) * 4) = make_float4(p0, p1, 0.f, 0.f);
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.cg; i += LN_THREADS) {
+      a.dw_part[static_cast<size_t>(blockIdx.x) * a.cg + i] = ch_acc[i];
+      a.db_part[static_cast<size_t>(blockIdx.x) * a.cg + i] = ch_acc[a.cg + i];
+    }
+  }
+  gn_grid_barrier(a.counters + 0, gridDim.x, a.status);
+  // ---- leaders: merge chunks, exchange across tile ranks
+  if (j == 0 && threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float4 mine;
+    if (!BWD) {
+      // merge (count, mean, M2) of the chunks: sequential Chan updates in lane 0 (splits is small)
+      float n = 0.f, mu = 0.f, m2 = 0.f;
+      if (lane == 0) {
+        for (int k = 0; k < a.splits; ++k) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(a.partial + static_cast<size_t>(gi * a.splits + k) * 4));
+          if (v.x <= 0.f) continue;
+          const float tot = n + v.x, d = v.y - mu;
+          mu += d * v.x / tot;
+          m2 += v.z + d * d * n * v.x / tot;
+          n = tot;
+        }
+      }
+      mine = make_float4(n, mu, m2, 0.f);
+    } else {
+      float s1 = 0.f, s2 = 0.f;
+      if (lane == 0) {
+        for (int k = 0; k < a.splits; ++k) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(a.partial + static_cast<size_t>(gi * a.splits + k) * 4));
+          s1 += v.x;
+          s2 += v.y;
+        }
+      }
+      mine = make_float4(s1, s2, 0.f, 0.f);
+    }
+    mine.x = __shfl_sync(0xffffffffu, mine.x, 0);
+    mine.y = __shfl_sync(0xffffffffu, mine.y, 0);
+    mine.z = __shfl_sync(0xffffffffu, mine.z, 0);
+    if (P > 1) {
+      gn_exchange(ex, epoch, gi, a.groups, mine, a.status);
+      if (lane == 0) {
+        const size_t half = static_cast<size_t>(epoch & 1u) * P * a.groups * 4;
+        float n = 0.f, mu = 0.f, m2 = 0.f, s1 = 0.f, s2 = 0.f;
+        for (int p = 0; p < P; ++p) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(ex.inbox_local + half + (static_cast<size_t>(p) * a.groups + gi) * 4));
+          if (!BWD) {
+            if (v.x <= 0.f) continue;
+            const float tot = n + v.x, d = v.y - mu;
+            mu += d * v.x / tot;
+            m2 += v.z + d * d * n * v.x / tot;
+            n = tot;
+          } else {
+            s1 += v.x;
+            s2 += v.y;
+          }
+        }
+        mine = BWD ? make_float4(s1, s2, 0.f, 0.f) : make_float4(n, mu, m2, 0.f);
+      }
+    }
+    if (lane == 0) {
+      if (!BWD) {
+        a.stats[gi * 2] = mine.y;
+        a.stats[gi * 2 + 1] = rsqrtf(mine.z / mine.x + a.eps);
+      } else {
+        const float inv = 1.f / (static_cast<float>(L) * static_cast<float>(P));
+        a.partial[static_cast<size_t>(gi * a.splits) * 4 + 2] = mine.x * inv;    // S1 / N
+        a.partial[static_cast<size_t>(gi * a.splits) * 4 + 3] = mine.y * inv;    // S2 / N
+      }
+      __threadfence();
+    }
+  }
+  gn_grid_barrier(a.counters + 1, gridDim.x, a.status);
+  // ---- phase 2
+  if (!BWD) {
+    const float mean = __ldcg(a.stats + gi * 2), rstd = __ldcg(a.stats + gi * 2 + 1);
+    for (long long e = e0 + threadIdx.x * 4; e < e1; e += LN_THREADS * 4) {
+      float4 v = ln_load4(a.x, a.x_bf16, base + e);
+      const int c = c0 + static_cast<int>(e / a.S);
+      const float w = (a.w != nullptr ? a.w[c] : 1.f) * rstd;
+      const float b = a.b != nullptr ? a.b[c] : 0.f;
+      v.x = (v.x - mean) * w + b; v.y = (v.y - mean) * w + b; v.z = (v.z - mean) * w + b; v.w = (v.w - mean) * w + b;
+      ln_store4(a.out, a.out_bf16, base + e, v);
+    }
+  } else {
+    const float S1 = __ldcg(a.partial + static_cast<size_t>(gi * a.splits) * 4 + 2);
+    const float S2 = __ldcg(a.partial + static_cast<size_t>(gi * a.splits) * 4 + 3);
+    for (long long e = e0 + threadIdx.x * 4; e < e1; e += LN_THREADS * 4) {
+      const float4 x = ln_load4(a.x, a.x_bf16, base + e);
+      const float4 g = ln_load4(a.g, a.g_bf16, base + e);
+      const int c = c0 + static_cast<int>(e / a.S);
+      const float w = a.w != nullptr ? a.w[c] : 1.f;
+      float4 d;
+      d.x = rstd_g * (g.x * w - S1 - (x.x - mean_g) * rstd_g * S2);
+      d.y = rstd_g * (g.y * w - S1 - (x.y - mean_g) * rstd_g * S2);
+      d.z = rstd_g * (g.z * w - S1 - (x.z - mean_g) * rstd_g * S2);
+      d.w = rstd_g * (g.w * w - S1 - (x.w - mean_g) * rstd_g * S2);
+      ln_store4(a.out, a.out_bf16, base + e, d);
+    }
+  }
+  // ---- leave the counters zero for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(a.counters + 2, 1u) == gridDim.x - 1) {
+      a.counters[0] = 0u;
+      a.counters[1] = 0u;
+      a.counters[2] = 0u;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace jb
 
 using namespace jb;
@@ -534,5 +819,48 @@ extern "C" int jb_cross_entropy_bwd(const void* x, int x_bf16, const long long* 
   long long grid = (total + 255) / 256;
   if (grid > static_cast<long long>(sm_count) * 16) grid = static_cast<long long>(sm_count) * 16;
   ce_bwd_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Number of CTAs per normalisation group so that groups * splits fits the SMs (0: too many groups).
+extern "C" int jb_group_norm_splits(int groups, int sm_count) { return groups > sm_count ? 0 : sm_count / groups; }
+
+static int gn_fill(GnArgs* a, const JbLnExchange* ex, int groups, int groups_per_sample, int cg, long long S,
+                   int sm_count) {
+  if (groups <= 0 || cg <= 0 || cg > GN_MAX_CG || S <= 0 || (S & 3)) return -1;
+  a->groups = groups; a->groups_per_sample = groups_per_sample; a->cg = cg; a->S = S;
+  a->splits = jb_group_norm_splits(groups, sm_count);
+  if (a->splits <= 0) return -1;
+  LnArgs tmp{};
+  if (ln_fill(&tmp, ex) != 0) return -1;
+  a->ex = tmp.ex;
+  return 0;
+}
+
+// y = GroupNorm(x) for x [N][C][S] with `groups_per_sample` local groups of cg channels; stats [groups][2]
+// receives (mean, rstd).  partial: 4 * groups * splits floats; counters: 3 zeroed words (left zero).
+extern "C" int jb_group_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16, const float* w, const float* b,
+                                 float* stats, float* partial, unsigned int* counters, int groups,
+                                 int groups_per_sample, int cg, long long S, float eps, const JbLnExchange* ex,
+                                 int* status, int sm_count, void* stream) {
+  GnArgs a{};
+  if (gn_fill(&a, ex, groups, groups_per_sample, cg, S, sm_count) != 0) return -1;
+  a.x = x; a.x_bf16 = x_bf16; a.out = y; a.out_bf16 = y_bf16; a.w = w; a.b = b; a.stats = stats;
+  a.partial = partial; a.counters = counters; a.eps = eps; a.status = status;
+  gn_kernel<false><<<groups * a.splits, LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// dx and per-CTA channel partials dw_part / db_part ([groups * splits][cg]) of the same.
+extern "C" int jb_group_norm_bwd(const void* x, int x_bf16, const void* g, int g_bf16, void* dx, int dx_bf16,
+                                 const float* w, const float* stats, float* partial, float* dw_part, float* db_part,
+                                 unsigned int* counters, int groups, int groups_per_sample, int cg, long long S,
+                                 const JbLnExchange* ex, int* status, int sm_count, void* stream) {
+  GnArgs a{};
+  if (gn_fill(&a, ex, groups, groups_per_sample, cg, S, sm_count) != 0) return -1;
+  a.x = x; a.x_bf16 = x_bf16; a.g = g; a.g_bf16 = g_bf16; a.out = dx; a.out_bf16 = dx_bf16; a.w = w;
+  a.stats = const_cast<float*>(stats); a.partial = partial; a.dw_part = dw_part; a.db_part = db_part;
+  a.counters = counters; a.status = status;
+  gn_kernel<true><<<groups * a.splits, LN_THREADS, 2 * cg * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

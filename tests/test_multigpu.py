@@ -313,3 +313,53 @@ def test_fused_roll_two_gpus():
 @pytest.mark.multigpu(4)
 def test_fused_roll_four_gpus():
     run_distributed(_worker_roll, 4, {"sh": 2, "sw": 2, "col": 1}, backend="nccl", timeout=300)
+
+
+def _worker_group_norm(rank, world, axes):
+    """GroupNorm of a volume tiled over GPUs on the fused kernels (grid barrier + in-kernel exchange
+    between the tile ranks) against the undivided torch op."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import split
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh(axes)
+    sh, sw = mesh["sh"], mesh["sw"]
+    torch.manual_seed(0)
+    full = torch.nn.GroupNorm(4, 16, device=dev)
+    with torch.no_grad():
+        full.weight.uniform_(0.5, 1.5)
+        full.bias.normal_()
+    gn = jb.modules.DistributedGroupNorm.convert_to_jigsaw(full, mesh, dev, row_kw="sh", spatial_group=(None, sh, sw))
+    cuts = {3: sh, 4: sw}
+    for it in range(3):
+        x = torch.randn(2, 16, 6, 16, 8, device=dev) * 2 + it
+        g = torch.randn(2, 16, 6, 16, 8, device=dev)
+        xl = split(x, cuts).requires_grad_(True)
+        before = _lib.LAUNCHES
+        y = gn(xl)
+        y.backward(split(g, cuts))
+        assert _lib.LAUNCHES == before + 2
+        symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        full.zero_grad()
+        yr = full(xr)
+        yr.backward(g)
+        assert_close(y.detach(), split(yr.detach(), cuts), f"call {it}: output", 1e-4, 1e-4)
+        assert_close(xl.grad, split(xr.grad, cuts), f"call {it}: input gradient", 1e-4, 1e-4)
+        assert_close(gn.weight.grad, full.weight.grad, f"call {it}: weight gradient", 1e-4, 1e-3)
+        assert_close(gn.bias.grad, full.bias.grad, f"call {it}: bias gradient", 1e-4, 1e-3)
+        gn.zero_grad()
+
+
+@pytest.mark.multigpu(2)
+def test_fused_group_norm_two_gpus():
+    run_distributed(_worker_group_norm, 2, {"sh": 2, "sw": 1, "col": 1}, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_fused_group_norm_four_gpus():
+    run_distributed(_worker_group_norm, 4, {"sh": 2, "sw": 2, "col": 1}, backend="nccl", timeout=300)
