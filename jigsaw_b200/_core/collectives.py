@@ -57,34 +57,57 @@ def _scatter_sum(x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> torch.T
     return out
 
 
+def _batched_dim(x: torch.Tensor, bdim: int | None, dim: int) -> tuple[torch.Tensor, int]:
+    """vmap helper: batch dimension to the front, ``dim`` (non-negative, of the unbatched tensor)
+    shifted behind it."""
+    if bdim is None:
+        return x, dim
+    return x.movedim(bdim, 0), dim + 1
+
+
 class _AllGatherCat(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> torch.Tensor:
-        ctx.group, ctx.dim = group, dim
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> torch.Tensor:
         return _gather_cat(x, group, dim)
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, ctx.group, ctx.dim = inputs
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        return _scatter_sum(g, ctx.group, ctx.dim), None, None
+        return _ReduceScatterSum.apply(g, ctx.group, ctx.dim), None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> tuple:
+        xb, d = _batched_dim(x, in_dims[0], dim)
+        return _AllGatherCat.apply(xb, group, d), 0
 
 
 class _ReduceScatterSum(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> torch.Tensor:
-        ctx.group, ctx.dim = group, dim
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> torch.Tensor:
         return _scatter_sum(x, group, dim)
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, ctx.group, ctx.dim = inputs
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        return _gather_cat(g, ctx.group, ctx.dim), None, None
+        return _AllGatherCat.apply(g, ctx.group, ctx.dim), None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: dist.ProcessGroup, dim: int) -> tuple:
+        xb, d = _batched_dim(x, in_dims[0], dim)
+        return _ReduceScatterSum.apply(xb, group, d), 0
 
 
 class _AllReduce(torch.autograd.Function):
     """mode: 'both' (sum fwd, sum bwd), 'fwd' (sum fwd, identity bwd), 'bwd' (identity fwd, sum bwd)."""
 
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, groups: tuple, mode: str) -> torch.Tensor:
-        ctx.groups, ctx.mode = groups, mode
+    def forward(x: torch.Tensor, groups: tuple, mode: str) -> torch.Tensor:
         if mode == "bwd":
             return x.view_as(x)
         y = x.contiguous().clone()
@@ -93,13 +116,15 @@ class _AllReduce(torch.autograd.Function):
         return y
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, ctx.groups, ctx.mode = inputs
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
         if ctx.mode == "fwd":
             return g, None, None
-        y = g.contiguous().clone()
-        for grp in ctx.groups:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=grp)
-        return y, None, None
+        # the gradient of a sum over ranks is again a sum over ranks (and differentiable in turn)
+        return _AllReduce.apply(g, ctx.groups, "both"), None, None
 
     @staticmethod
     def vmap(info: Any, in_dims: tuple, x: torch.Tensor, groups: tuple, mode: str) -> tuple:
@@ -108,15 +133,21 @@ class _AllReduce(torch.autograd.Function):
 
 class _RingPass(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, group: dist.ProcessGroup, direction: int, comm: CommOp) -> torch.Tensor:
-        ctx.group, ctx.direction, ctx.comm = group, direction, comm
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, direction: int, comm: CommOp) -> torch.Tensor:
         out, _ = ring_shift(x.contiguous(), None, direction, group, comm)
         return out
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, ctx.group, ctx.direction, ctx.comm = inputs
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        out, _ = ring_shift(g.contiguous(), None, -ctx.direction, ctx.group, ctx.comm)
-        return out, None, None, None
+        return _RingPass.apply(g, ctx.group, -ctx.direction, ctx.comm), None, None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: dist.ProcessGroup, direction: int, comm: CommOp) -> tuple:
+        return _RingPass.apply(x, group, direction, comm), in_dims[0]      # whole tensors travel: any layout
 
 
 def _a2a(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor:
@@ -134,13 +165,55 @@ def _a2a(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int
 
 class _AllToAllDims(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor:
-        ctx.group, ctx.split_dim, ctx.cat_dim = group, split_dim, cat_dim
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor:
         return _a2a(x, group, split_dim, cat_dim)
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, ctx.group, ctx.split_dim, ctx.cat_dim = inputs
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        return _a2a(g, ctx.group, ctx.cat_dim, ctx.split_dim), None, None, None
+        return _AllToAllDims.apply(g, ctx.group, ctx.cat_dim, ctx.split_dim), None, None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> tuple:
+        if in_dims[0] is None:
+            return _AllToAllDims.apply(x, group, split_dim, cat_dim), None
+        return _AllToAllDims.apply(x.movedim(in_dims[0], 0), group, split_dim + 1, cat_dim + 1), 0
+
+
+class _ReduceNoGrad(torch.autograd.Function):
+    """Element-wise MAX / MIN all-reduce of a detached tensor (no gradient flows); elementwise in
+    every dimension, so ``vmap`` passes the batch dimension straight through."""
+
+    @staticmethod
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, op: Any) -> torch.Tensor:
+        y = x.detach().contiguous().clone()
+        dist.all_reduce(y, op=op, group=group)
+        return y
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        ctx.mark_non_differentiable(output)
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        return None, None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: dist.ProcessGroup, op: Any) -> tuple:
+        return _ReduceNoGrad.apply(x, group, op), in_dims[0]
+
+
+def all_reduce_max(x: torch.Tensor, group: dist.ProcessGroup | None) -> torch.Tensor:
+    """Element-wise maximum over the group (detached)."""
+    return _ReduceNoGrad.apply(x, group, dist.ReduceOp.MAX) if _live(group) else x.detach()
+
+
+def all_reduce_min(x: torch.Tensor, group: dist.ProcessGroup | None) -> torch.Tensor:
+    """Element-wise minimum over the group (detached)."""
+    return _ReduceNoGrad.apply(x, group, dist.ReduceOp.MIN) if _live(group) else x.detach()
 
 
 def _norm_groups(groups: Any) -> tuple:

@@ -15,7 +15,7 @@ import torch
 import torch.distributed as dist
 
 from ..._core.autocast import promote_to_fp32_under_autocast
-from ..._core.collectives import all_reduce_sum
+from ..._core.collectives import all_reduce_max, all_reduce_min, all_reduce_sum
 
 
 def _live(group: dist.ProcessGroup | None) -> bool:
@@ -23,10 +23,7 @@ def _live(group: dist.ProcessGroup | None) -> bool:
 
 
 def _global_max(x: torch.Tensor, dim: int, group: dist.ProcessGroup | None) -> torch.Tensor:
-    m = x.detach().amax(dim=dim, keepdim=True)
-    if _live(group):
-        m = m.contiguous()
-        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+    m = all_reduce_max(x.detach().amax(dim=dim, keepdim=True), group)
     # rows that are entirely -inf would give inf - inf
     return torch.where(torch.isfinite(m), m, torch.zeros_like(m))
 
@@ -65,10 +62,8 @@ def distributed_argmax(x: torch.Tensor, dim: int, group: dist.ProcessGroup | Non
     is_max = x == local_val.unsqueeze(dim)
     ar = torch.arange(x.shape[dim], device=x.device).view([-1 if i == dim % x.dim() else 1 for i in range(x.dim())])
     local_idx = torch.where(is_max, ar, torch.full_like(ar, x.shape[dim])).amin(dim=dim)
-    best = local_val.clone().contiguous()
-    dist.all_reduce(best, op=dist.ReduceOp.MAX, group=group)
+    best = all_reduce_max(local_val, group)
     offset = group.rank() * x.shape[dim]
     sentinel = group.size() * x.shape[dim]
-    cand = torch.where(local_val == best, local_idx + offset, torch.full_like(local_idx, sentinel)).contiguous()
-    dist.all_reduce(cand, op=dist.ReduceOp.MIN, group=group)
-    return cand
+    cand = torch.where(local_val == best, local_idx + offset, torch.full_like(local_idx, sentinel))
+    return all_reduce_min(cand, group)

@@ -157,24 +157,43 @@ def _reduce(y: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
 
 class _SpanGather(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
-        ctx.plan = plan
+    def forward(x: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
         return _gather(x, plan)
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        ctx.plan = inputs[1]
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        return _reduce(g, ctx.plan), None
+        return _SpanReduce.apply(g, ctx.plan), None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, plan: AxisPlan) -> tuple:
+        # the plan addresses its axis from the end, so a leading batch dimension does not disturb it
+        if in_dims[0] is None:
+            return _SpanGather.apply(x, plan), None
+        return _SpanGather.apply(x.movedim(in_dims[0], 0), plan), 0
 
 
 class _SpanReduce(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, y: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
-        ctx.plan = plan
+    def forward(y: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
         return _reduce(y, plan)
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        ctx.plan = inputs[1]
+
+    @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        return _gather(g, ctx.plan), None
+        return _SpanGather.apply(g, ctx.plan), None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, y: torch.Tensor, plan: AxisPlan) -> tuple:
+        if in_dims[0] is None:
+            return _SpanReduce.apply(y, plan), None
+        return _SpanReduce.apply(y.movedim(in_dims[0], 0), plan), 0
 
 
 def span_gather(x: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
