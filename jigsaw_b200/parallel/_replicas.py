@@ -75,11 +75,14 @@ def mark_replicated(
             "parameter is already marked replicated; a second mark would sum its gradient twice. "
             "Pass extend=True to add groups to the mark."
         )
+    wanted = _real_groups(groups)
+    if not wanted:                       # nothing to add (also: a single process without a process group)
+        return
     me = dist.get_rank()
     known = {tuple(dist.get_process_group_ranks(g)) for g in current}
     covered = {r for ranks in known for r in ranks}
     merged = list(current)
-    for g in _real_groups(groups):
+    for g in wanted:
         ranks = tuple(dist.get_process_group_ranks(g))
         if ranks in known:
             continue
