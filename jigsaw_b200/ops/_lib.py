@@ -125,6 +125,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_gemm_bf16_gather.argtypes = [POINTER(JbGather), c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong,
                                       c_int, c_int, c_int, c_void_p, c_void_p]
     L.jb_gemm_bf16_gather.restype = c_int
+    L.jb_gemm_bf16_scatter.argtypes = [c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                                       c_int, c_int, c_int, c_void_p, c_void_p]
+    L.jb_gemm_bf16_scatter.restype = c_int
+    L.jb_sum_slabs.argtypes = [c_void_p, c_longlong, c_int, POINTER(c_void_p), c_uint, c_uint, c_void_p, c_void_p, c_int,
+                               c_void_p, c_int, c_void_p]
+    L.jb_sum_slabs.restype = c_int
     L.jb_publish.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]
     L.jb_publish.restype = c_int
     L.jb_roll.argtypes = [POINTER(JbRoll), c_void_p, c_void_p, c_int, c_void_p]

@@ -31,6 +31,11 @@ struct GemmEpilogue {
   int act;            // 0 none, 1 GELU(erf)
   int out_fp32;       // 0 -> bf16 output, 1 -> fp32 output
   int accumulate;     // 1 -> C += result (fp32 output only)
+  // Reduce-scatter fused into the epilogue: the N dimension is cut into parts of `part_cols` columns,
+  // part p belongs to GPU p, and a tile of part p is stored into c_part[p] (row stride part_cols) --
+  // this GPU's slab in GPU p's inbox (a peer pointer) -- instead of into c.  part_cols = 0: off.
+  void* c_part[8];
+  int part_cols;
 };
 
 // All-gather fused into the GEMM: the reduction dimension of A is split over `parts` GPUs, each part is
@@ -219,6 +224,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(as * BN);
+      // destination of this tile: the plain output, or the slab of the GPU that owns these columns
+      void* c_base = ep.c;
+      long long ldc = ep.ldc;
+      int col_shift = 0;
+      if (ep.part_cols > 0) {
+        const int part = n0 / ep.part_cols;
+        c_base = ep.c_part[part];
+        ldc = ep.part_cols;
+        col_shift = part * ep.part_cols;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -235,8 +250,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             v[j] = x;
           }
           if (ep.out_fp32) {
-            float* dst = reinterpret_cast<float*>(ep.c) + static_cast<long long>(row) * ep.ldc + col0;
-            if (col0 + 32 <= N && (ep.ldc & 3) == 0) {
+            float* dst = reinterpret_cast<float*>(c_base) + static_cast<long long>(row) * ldc + (col0 - col_shift);
+            if (col0 + 32 <= N && (ldc & 3) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -250,8 +265,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = ep.accumulate ? dst[j] + v[j] : v[j];
             }
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.c) + static_cast<long long>(row) * ep.ldc + col0;
-            if (col0 + 32 <= N && (ep.ldc & 7) == 0) {
+            __nv_bfloat16* dst =
+                reinterpret_cast<__nv_bfloat16*>(c_base) + static_cast<long long>(row) * ldc + (col0 - col_shift);
+            if (col0 + 32 <= N && (ldc & 7) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 o;
@@ -434,5 +450,115 @@ extern "C" int jb_publish(void* const* flags, int n, unsigned int epoch, unsigne
   for (int i = 0; i < n; ++i) f[i] = static_cast<uint32_t*>(flags[i]);
   jb::publish_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7],
                                                                       epoch, stride, replay);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// C = A * B with the reduce-scatter of C's column parts fused into the epilogue: column part p
+// (part_cols columns, part_cols a multiple of 64) of this GPU's partial product is stored as a bf16
+// [M, part_cols] slab at c_part[p] (for p != this GPU a pointer into GPU p's inbox).  The caller
+// publishes a flag afterwards (jb_publish) and the owners sum their slabs (jb_sum_slabs).
+extern "C" int jb_gemm_bf16_scatter(const void* A, const void* B, void* const* c_part, int parts, int part_cols, int M,
+                                    int K, long long lda, long long ldb, int a_mn, int b_mn, int sm_count, int* status,
+                                    void* stream) {
+  using namespace jb;
+  if (parts < 2 || parts > 8 || part_cols % 64 != 0 || (lda & 7) || (ldb & 7)) return -1;
+  const int N = parts * part_cols;
+  GemmEpilogue ep{};
+  ep.out_fp32 = 0;
+  ep.part_cols = part_cols;
+  for (int p = 0; p < parts; ++p) ep.c_part[p] = c_part[p];
+  ep.c = c_part[0];
+  ep.ldc = part_cols;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  // tiles must not straddle two parts: the tile width divides part_cols
+  const int bn = (part_cols % 256 == 0 && ((M + 127) / 128) * (N / 256) >= sm_count) ? 256 : (part_cols % 128 == 0 ? 128 : 64);
+#define JB_GEMM_SC(BN)                                                                              \
+  switch (key) {                                                                                     \
+    case 0: return launch_gemm<BN, 0, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);        \
+    case 1: return launch_gemm<BN, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);        \
+    case 2: return launch_gemm<BN, 1, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);        \
+    default: return launch_gemm<BN, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);       \
+  }
+  if (bn == 256) { JB_GEMM_SC(256) } else if (bn == 128) { JB_GEMM_SC(128) } else { JB_GEMM_SC(64) }
+#undef JB_GEMM_SC
+}
+
+namespace jb {
+// out = sum over the slabs [parts][n] (bf16) of this GPU's inbox, after every source rank's flag has
+// reached the epoch (bounded wait by one thread per CTA; null flag = this GPU's own slab).
+struct SumSlabArgs {
+  const __nv_bfloat16* slabs;
+  long long n;                 // elements per slab
+  int parts;
+  const uint32_t* flag[8];
+  uint32_t epoch, stride;
+  const uint32_t* replay;
+  void* out; int out_bf16;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) sum_slabs_kernel(const SumSlabArgs a) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    ok = 1;
+    const uint32_t want = live_epoch(a.epoch, a.stride, a.replay);
+    const uint64_t t0 = globaltimer_ns();
+    for (int p = 0; p < a.parts && ok; ++p) {
+      const uint32_t* f = a.flag[p];
+      if (f == nullptr) continue;
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if (static_cast<int32_t>(v - want) >= 0) break;
+        if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+          if (a.status) atomicCAS(a.status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+  }
+  __syncthreads();
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < a.n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < a.parts; ++p) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(a.slabs + static_cast<long long>(p) * a.n + i));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __low2float(h[j]);
+        acc[2 * j + 1] += __high2float(h[j]);
+      }
+    }
+    if (a.out_bf16) {
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + i) = o;
+    } else {
+      float* o = static_cast<float*>(a.out) + i;
+      *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+}  // namespace jb
+
+// out[n] = sum_p slabs[p][n] (bf16 slabs, n a multiple of 8) once flag[p] >= epoch for every p.
+extern "C" int jb_sum_slabs(const void* slabs, long long n, int parts, const void* const* flags, unsigned int epoch,
+                            unsigned int stride, const unsigned int* replay, void* out, int out_bf16, int* status,
+                            int sm_count, void* stream) {
+  using namespace jb;
+  if (n <= 0 || (n & 7) || parts < 1 || parts > 8) return -1;
+  SumSlabArgs a{};
+  a.slabs = static_cast<const __nv_bfloat16*>(slabs); a.n = n; a.parts = parts;
+  for (int p = 0; p < parts; ++p) a.flag[p] = static_cast<const uint32_t*>(flags[p]);
+  a.epoch = epoch; a.stride = stride; a.replay = replay; a.out = out; a.out_bf16 = out_bf16; a.status = status;
+  long long grid = (n / 8 + 255) / 256;
+  if (grid > static_cast<long long>(sm_count) * 4) grid = static_cast<long long>(sm_count) * 4;
+  sum_slabs_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

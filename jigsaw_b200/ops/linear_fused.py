@@ -11,8 +11,10 @@ MN-major, fp32 output).  Returns ``None`` when the kernel does not apply; the ca
 into that GEMM: every rank drops its ``[M, K / P]`` block (cast to bf16) into a symmetric buffer
 and publishes an epoch flag; the TMA producer of the GEMM then reads the k-blocks of part ``p``
 straight from GPU ``p`` over NVLink, so the gathered ``[M, K]`` matrix is never materialised
-and the transfer overlaps the tensor-core work tile by tile.  (The backward products use local
-GEMMs with an NCCL reduce-scatter / all-gather.)
+and the transfer overlaps the tensor-core work tile by tile.  The input gradient is the mirror
+image, GEMM -> reduce-scatter in one pass: the epilogue of ``dY @ W`` stores each tile into the
+inbox of the rank that owns those columns, and every rank sums the slabs it received.  (The
+weight gradient re-gathers ``x`` with NCCL and uses a local GEMM.)
 
 Reference parity: the ``torch.matmul`` / ``F.linear`` calls of
 jigsaw/modules/linear/_distributed_matmul.py:100-110,159-177 (cuBLAS there) and the masked
@@ -127,6 +129,49 @@ def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block
     return blk
 
 
+def _scatter_gemm(g: torch.Tensor, wb: torch.Tensor, group: Any) -> torch.Tensor:
+    """``reduce_scatter(g @ wb, last dim over group)`` with the scatter fused into the GEMM: the
+    epilogue stores every tile of column part ``p`` straight into rank ``p``'s inbox (this rank's
+    slab), a flag follows, and each rank sums the ``P`` slabs of its inbox."""
+    L, dev = _lib.lib(), g.device
+    ar = symm.arena(dev)
+    P, me = group.size(), group.rank()
+    ranks = dist.get_process_group_ranks(group)
+    M, N = g.shape
+    K = wb.shape[1]
+    kp = K // P
+    slab = M * kp * 2
+    blk = _staging_block(ar, ("scatter_dx", dev.index, M, kp, P), _HEADER + P * slab)
+    epoch = ar.next_own_epoch(blk)
+    stride = ar.capture_stride or 0
+    replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+    st = _lib.stream_ptr()
+    c_part = (ctypes.c_void_p * 8)()
+    for i, r in enumerate(ranks):
+        c_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER + me * slab
+    rc = L.jb_gemm_bf16_scatter(_p(g), _p(wb), c_part, P, kp, M, N, g.stride(0), wb.stride(0), 0, 1,
+                                _lib.sm_count(dev.index), _p(ar.status), st)
+    flags = (ctypes.c_void_p * 8)()
+    n = 0
+    for i, r in enumerate(ranks):
+        if i != me:
+            flags[n] = blk.peer_ptr(r) + 4 * me
+            n += 1
+    if rc == 0:
+        rc = L.jb_publish(flags, n, epoch, stride, replay, st)
+    waits = (ctypes.c_void_p * 8)()
+    for i in range(P):
+        waits[i] = None if i == me else blk.ptr + 4 * i
+    out = torch.empty(M, kp, dtype=torch.bfloat16, device=dev)
+    if rc == 0:
+        rc = L.jb_sum_slabs(ctypes.c_void_p(blk.ptr + _HEADER), M * kp, P, waits, epoch, stride, replay, _p(out), 1,
+                            _p(ar.status), _lib.sm_count(dev.index), st)
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launcher gemm_bf16_scatter failed with code {rc}")
+    _lib.count_launches(3)
+    return out
+
+
 class _GatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, group: Any) -> torch.Tensor:
@@ -183,12 +228,7 @@ class _GatherLinear(torch.autograd.Function):
         M = g.shape[0]
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            full = gemm(g, wb, b_mn=True)                                   # [M, K]: every rank holds a partial sum
-            kp = full.shape[1] // P
-            parts = full.view(M, P, kp).permute(1, 0, 2).contiguous()
-            mine = torch.empty(M, kp, dtype=full.dtype, device=full.device)
-            dist.reduce_scatter_tensor(mine, parts, group=group)
-            dx = mine.view(ctx.x_shape).to(ctx.x_dtype)
+            dx = _scatter_gemm(g, wb, group).view(ctx.x_shape).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
             gathered = torch.empty(P, M, xb.shape[1], dtype=xb.dtype, device=xb.device)
             dist.all_gather_into_tensor(gathered, xb, group=group)
