@@ -124,9 +124,10 @@ def main() -> None:
         f = lambda: torch.autograd.grad(rows, [xc], g, retain_graph=True)
         return timed(f, args.warmup, args.reps), xc.numel() * 2 * 2 + tc.numel() * 16, None
 
-    xm = torch.randn(1, 64, 2048 // scale, 2048, device=dev).bfloat16().permute(0, 2, 3, 1).contiguous().permute(0, 3, 1, 2)
+    # the shape of the CNN benchmark's loss: a 3-channel bf16 channels-last prediction against an fp32 NCHW target
+    xm = torch.randn(1, 3, 4096 // scale, 4096, device=dev).bfloat16().permute(0, 2, 3, 1).contiguous().permute(0, 3, 1, 2)
     xm.requires_grad_(True)
-    ym = torch.randn(1, 64, 2048 // scale, 2048, device=dev)
+    ym = torch.randn(1, 3, 4096 // scale, 4096, device=dev)
 
     @case("mse_fwd")
     def _():

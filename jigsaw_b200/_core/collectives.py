@@ -151,6 +151,12 @@ class _RingPass(torch.autograd.Function):
 
 
 def _a2a(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor:
+    if x.is_cuda:
+        from ..ops import exchange_fused
+
+        out = exchange_fused.maybe_fused_all_to_all(x, group, split_dim, cat_dim)     # one kernel over peer memory
+        if out is not None:
+            return out
     n = group.size()
     ins = [c.contiguous() for c in x.chunk(n, dim=split_dim)]
     outs = [torch.empty_like(ins[0]) for _ in range(n)]

@@ -66,6 +66,14 @@ class JbRoll(ctypes.Structure):
                 ("flag_in", c_void_p * 4), ("epoch", c_uint), ("stride", c_uint), ("replay", c_void_p)]
 
 
+class JbA2a(ctypes.Structure):
+    """Arguments of the fused re-sharding all-to-all (see ``csrc/alltoall.cu``)."""
+
+    _fields_ = [("x", c_void_p), ("dim", c_longlong * 5), ("split", c_int), ("cat", c_int), ("parts", c_int), ("me", c_int),
+                ("out", c_void_p * 8), ("flag_out", c_void_p * 8), ("flag_in", c_void_p * 8), ("epoch", c_uint),
+                ("stride", c_uint), ("replay", c_void_p)]
+
+
 class JbStrided4(ctypes.Structure):
     """A tensor of up to four dimensions: base pointer, element type, element strides."""
 
@@ -133,6 +141,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_sum_slabs.restype = c_int
     L.jb_publish.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]
     L.jb_publish.restype = c_int
+    L.jb_all_to_all.argtypes = [POINTER(JbA2a), c_void_p, c_void_p, c_int, c_void_p]
+    L.jb_all_to_all.restype = c_int
     L.jb_roll.argtypes = [POINTER(JbRoll), c_void_p, c_void_p, c_int, c_void_p]
     L.jb_roll.restype = c_int
     L.jb_merge_chunks.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p]
@@ -173,6 +183,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_group_norm_bwd.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
+    L.jb_layer_norm_grid2.argtypes = [c_int, c_int, c_int]
+    L.jb_layer_norm_grid2.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,  # x x_bf16 y y_bf16 w b
         c_void_p, c_void_p, c_int, c_int, c_float,  # mean rstd R n eps

@@ -1,0 +1,119 @@
+// All-to-all that re-shards a tensor (split one dimension over the ranks, concatenate what arrives
+// along another) as ONE kernel over peer memory: every 16-byte vector is stored straight at its final
+// position in the destination rank's output (plain stores over NVLink), the last CTA publishes an epoch
+// flag to every peer and waits (bounded) for theirs.  This is the sequence <-> head exchange of Ulysses
+// attention.
+//
+// The tensor is viewed as [D0][D1][D2][D3][V] (V = 16-byte vectors of the contiguous tail); dimension
+// `split` is cut into P chunks, chunk p goes to rank p and lands at block `me` of dimension `cat`.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace jb {
+
+struct A2aArgs {
+  const uint4* x;
+  long long dim[5];            // input extents, dim[4] in vectors
+  int split, cat;              // dimensions 0..3
+  int parts, me;
+  uint4* out[8];               // output base on every rank
+  uint32_t* flag_out[8];       // flag word on rank p for source `me` (null for p == me)
+  const uint32_t* flag_in[8];  // local flag words, one per source (null for me)
+  uint32_t epoch, stride;
+  const uint32_t* replay;
+  unsigned int* done_counter;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) a2a_kernel(const A2aArgs a) {
+  const long long total = a.dim[0] * a.dim[1] * a.dim[2] * a.dim[3] * a.dim[4];
+  const long long chunk = a.dim[a.split] / a.parts;
+  long long od[5];             // output extents
+  for (int i = 0; i < 5; ++i) od[i] = a.dim[i];
+  od[a.split] = chunk;
+  od[a.cat] = a.dim[a.cat] * a.parts;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    long long r = idx, ix[5];
+    for (int i = 4; i >= 0; --i) {
+      ix[i] = r % a.dim[i];
+      r /= a.dim[i];
+    }
+    const int dest = static_cast<int>(ix[a.split] / chunk);
+    ix[a.split] -= dest * chunk;
+    ix[a.cat] += static_cast<long long>(a.me) * a.dim[a.cat];
+    const long long o = (((ix[0] * od[1] + ix[1]) * od[2] + ix[2]) * od[3] + ix[3]) * od[4] + ix[4];
+    a.out[dest][o] = a.x[idx];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence();
+  if (atomicAdd(a.done_counter, 1u) != gridDim.x - 1) return;
+  *a.done_counter = 0u;
+  __threadfence_system();
+  const uint32_t epoch = live_epoch(a.epoch, a.stride, a.replay);
+  for (int p = 0; p < a.parts; ++p)
+    if (a.flag_out[p] != nullptr)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flag_out[p]), "r"(epoch) : "memory");
+  const uint64_t t0 = globaltimer_ns();
+  for (int p = 0; p < a.parts; ++p) {
+    const uint32_t* f = a.flag_in[p];
+    if (f == nullptr) continue;
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+        if (a.status) atomicCAS(a.status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+        return;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+}  // namespace jb
+
+struct JbA2a {
+  const void* x;
+  long long dim[5];
+  int split, cat, parts, me;
+  void* out[8];
+  void* flag_out[8];
+  const void* flag_in[8];
+  unsigned int epoch, stride;
+  const unsigned int* replay;
+};
+
+extern "C" int jb_all_to_all(const JbA2a* r, unsigned int* done_counter, int* status, int sm_count, void* stream) {
+  using namespace jb;
+  if (r->parts < 2 || r->parts > 8 || r->split < 0 || r->split > 3 || r->cat < 0 || r->cat > 3 || r->split == r->cat)
+    return -1;
+  A2aArgs a{};
+  a.x = static_cast<const uint4*>(r->x);
+  long long total = 1;
+  for (int i = 0; i < 5; ++i) {
+    if (r->dim[i] <= 0) return -1;
+    a.dim[i] = r->dim[i];
+    total *= r->dim[i];
+  }
+  if (a.dim[r->split] % r->parts != 0) return -1;
+  a.split = r->split; a.cat = r->cat; a.parts = r->parts; a.me = r->me;
+  for (int p = 0; p < r->parts; ++p) {
+    a.out[p] = static_cast<uint4*>(r->out[p]);
+    a.flag_out[p] = static_cast<uint32_t*>(r->flag_out[p]);
+    a.flag_in[p] = static_cast<const uint32_t*>(r->flag_in[p]);
+    if (a.out[p] == nullptr) return -1;
+  }
+  a.epoch = r->epoch; a.stride = r->stride; a.replay = r->replay;
+  a.done_counter = done_counter; a.status = status;
+  long long grid = (total + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count) * 8;
+  if (grid > cap) grid = cap;
+  a2a_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -17,26 +17,61 @@ namespace jb {
 __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o1, float* __restrict__ l1,
                                                     const void* __restrict__ o2, int o2_bf16,
                                                     const float* __restrict__ l2, long long rows, int d) {
+  // one thread per four consecutive features (d % 4 == 0); the thread of a row's first vector also
+  // updates the row's log-sum-exp.  Every thread of a row reads l1 before any of them writes it: the
+  // write happens after a warp-level barrier and rows never straddle... a row may span several warps
+  // only when d > 128, which the launcher routes to the scalar variant below.
+  const int vec_per_row = d >> 2;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = idx / vec_per_row;
+  const int v = static_cast<int>(idx % vec_per_row);
+  float a = 0.f, b = 0.f;
+  const bool live = row < rows;
+  if (live) {
+    a = l1[row];
+    b = l2[row];
+  }
+  __syncwarp();
+  if (!live) return;
+  // a = -inf (nothing merged yet) gives w = 1; b = -inf keeps the state
+  const float diff = b - a;
+  const float w = (b == -INFINITY) ? 0.f : 1.f / (1.f + __expf(-diff));
+  float4* po = reinterpret_cast<float4*>(o1 + row * d) + v;
+  float4 cur = *po;
+  float4 nw;
+  if (o2_bf16) {
+    const uint2 raw = *(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(o2) + row * d) + v);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    nw = make_float4(__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1));
+  } else {
+    nw = *(reinterpret_cast<const float4*>(static_cast<const float*>(o2) + row * d) + v);
+  }
+  cur.x += w * (nw.x - cur.x); cur.y += w * (nw.y - cur.y); cur.z += w * (nw.z - cur.z); cur.w += w * (nw.w - cur.w);
+  *po = cur;
+  if (v == 0) {
+    const float m = fmaxf(a, b);
+    l1[row] = (m == -INFINITY) ? m : m + log1pf(__expf(-fabsf(diff)));
+  }
+}
+
+// scalar variant: one warp per row, any d
+__global__ void __launch_bounds__(256) merge_rows_kernel(float* __restrict__ o1, float* __restrict__ l1,
+                                                         const void* __restrict__ o2, int o2_bf16,
+                                                         const float* __restrict__ l2, long long rows, int d) {
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const float a = l1[row], b = l2[row];
-  // a = -inf (nothing merged yet) gives w = 1; both -inf keeps the state
+  __syncwarp();
   const float diff = b - a;
   const float w = (b == -INFINITY) ? 0.f : 1.f / (1.f + __expf(-diff));
   float* po = o1 + row * d;
-  if (o2_bf16) {
-    const __nv_bfloat16* pn = static_cast<const __nv_bfloat16*>(o2) + row * d;
-    for (int i = lane; i < d; i += 32) {
-      const float cur = po[i];
-      po[i] = cur + w * (__bfloat162float(pn[i]) - cur);
-    }
-  } else {
-    const float* pn = static_cast<const float*>(o2) + row * d;
-    for (int i = lane; i < d; i += 32) {
-      const float cur = po[i];
-      po[i] = cur + w * (pn[i] - cur);
-    }
+  for (int i = lane; i < d; i += 32) {
+    const float nw = o2_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(o2)[row * d + i])
+                             : static_cast<const float*>(o2)[row * d + i];
+    const float cur = po[i];
+    po[i] = cur + w * (nw - cur);
   }
   if (lane == 0) {
     const float m = fmaxf(a, b);
@@ -238,9 +273,18 @@ using namespace jb;
 extern "C" int jb_merge_chunks(float* o1, float* l1, const void* o2, int o2_bf16, const float* l2, long long rows,
                                int d, void* stream) {
   if (rows <= 0 || d <= 0) return -1;
-  const long long threads = rows * 32;
-  const unsigned int grid = static_cast<unsigned int>((threads + 255) / 256);
-  merge_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(o1, l1, o2, o2_bf16, l2, rows, d);
+  // vector variant: rows must not straddle warps (32 % (d / 4) == 0), so that all readers of a row's
+  // log-sum-exp pass the warp barrier before its writer stores the new value
+  const bool vec = (d % 4 == 0) && (d / 4 <= 32) && (32 % (d / 4) == 0);
+  if (vec) {
+    const long long threads = rows * (d / 4);
+    const unsigned int grid = static_cast<unsigned int>((threads + 255) / 256);
+    merge_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(o1, l1, o2, o2_bf16, l2, rows, d);
+  } else {
+    const long long threads = rows * 32;
+    const unsigned int grid = static_cast<unsigned int>((threads + 255) / 256);
+    merge_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(o1, l1, o2, o2_bf16, l2, rows, d);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -8,5 +8,6 @@
 #include "norm.cu"
 #include "elementwise.cu"
 #include "roll.cu"
+#include "alltoall.cu"
 
 extern "C" int jb_abi_version() { return 1; }

@@ -25,6 +25,7 @@ namespace jb {
 constexpr int LN_THREADS = 256;
 constexpr int LN_WARPS = LN_THREADS / 32;
 constexpr int LN_MAX_PARTS = 8;
+constexpr int LN_REG_CHUNKS = 8;     // columns per lane kept in registers by the backward kernel (n <= 1024)
 
 struct LnExchange {
   float* inbox_local;               // [2][P][R][2] this rank's inbox (parity, source rank, row, value)
@@ -203,13 +204,20 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
   if (want_dw)
     for (int i = threadIdx.x; i < 2 * a.n; i += LN_THREADS) acc[i] = 0.f;
   __syncthreads();
+  float4 rdw[LN_REG_CHUNKS], rdb[LN_REG_CHUNKS];
+#pragma unroll
+  for (int k = 0; k < LN_REG_CHUNKS; ++k) rdw[k] = rdb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float inv_N = 1.f / (static_cast<float>(a.n) * static_cast<float>(P));
   // ---- phase 1: S1 = sum g w, S2 = sum g w xhat per row (local part); dw / db partials
   for (int r = r0 + warp; r < r1; r += LN_WARPS) {
     const long long base = static_cast<long long>(r) * a.n;
     const float mean = a.mean[r], rstd = a.rstd[r];
     float s1 = 0.f, s2 = 0.f;
-    for (int i = lane * 4; i < a.n; i += 128) {
+    const int chunks = (a.n + 127) / 128;
+#pragma unroll LN_REG_CHUNKS
+    for (int k = 0; k < chunks; ++k) {
+      const int i = lane * 4 + k * 128;
+      if (i >= a.n) break;
       const float4 x = ln_load4(a.x, a.x_bf16, base + i);
       const float4 g = ln_load4(a.g, a.g_bf16, base + i);
       float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -219,10 +227,15 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
       s1 += (gw0 + gw1) + (gw2 + gw3);
       s2 += (gw0 * h0 + gw1 * h1) + (gw2 * h2 + gw3 * h3);
       if (want_dw) {
-        atomicAdd(acc + i + 0, g.x * h0); atomicAdd(acc + i + 1, g.y * h1);
-        atomicAdd(acc + i + 2, g.z * h2); atomicAdd(acc + i + 3, g.w * h3);
-        atomicAdd(acc + a.n + i + 0, g.x); atomicAdd(acc + a.n + i + 1, g.y);
-        atomicAdd(acc + a.n + i + 2, g.z); atomicAdd(acc + a.n + i + 3, g.w);
+        if (k < LN_REG_CHUNKS) {       // a lane owns the same columns in every row: keep their sums in registers
+          rdw[k].x += g.x * h0; rdw[k].y += g.y * h1; rdw[k].z += g.z * h2; rdw[k].w += g.w * h3;
+          rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
+        } else {
+          atomicAdd(acc + i + 0, g.x * h0); atomicAdd(acc + i + 1, g.y * h1);
+          atomicAdd(acc + i + 2, g.z * h2); atomicAdd(acc + i + 3, g.w * h3);
+          atomicAdd(acc + a.n + i + 0, g.x); atomicAdd(acc + a.n + i + 1, g.y);
+          atomicAdd(acc + a.n + i + 2, g.z); atomicAdd(acc + a.n + i + 3, g.w);
+        }
       }
     }
     s1 = warp_sum(s1);
@@ -261,6 +274,16 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
     }
   }
   if (want_dw) {
+#pragma unroll
+    for (int k = 0; k < LN_REG_CHUNKS; ++k) {        // one shared-memory add per warp and column
+      const int i = lane * 4 + k * 128;
+      if (i < a.n) {
+        atomicAdd(acc + i + 0, rdw[k].x); atomicAdd(acc + i + 1, rdw[k].y);
+        atomicAdd(acc + i + 2, rdw[k].z); atomicAdd(acc + i + 3, rdw[k].w);
+        atomicAdd(acc + a.n + i + 0, rdb[k].x); atomicAdd(acc + a.n + i + 1, rdb[k].y);
+        atomicAdd(acc + a.n + i + 2, rdb[k].z); atomicAdd(acc + a.n + i + 3, rdb[k].w);
+      }
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < a.n; i += LN_THREADS) {
       a.dw_part[static_cast<size_t>(blockIdx.x) * a.n + i] = acc[i];
@@ -726,11 +749,25 @@ static int ln_fill(LnArgs* a, const JbLnExchange* ex) {
   return 0;
 }
 
-// Number of CTAs a LayerNorm launch uses for R rows (the caller sizes flags and partials with it).
-extern "C" int jb_layer_norm_grid(int R, int sm_count) {
-  const int want = (R + LN_WARPS - 1) / LN_WARPS;
-  return want < sm_count ? (want < 1 ? 1 : want) : sm_count;
+// CTAs of `kernel` that can be resident at once (the kernels here wait on one another across GPUs or
+// across the grid, so a grid never exceeds this).
+template <typename K>
+static int resident_ctas(K kernel, int threads, size_t smem, int sm_count) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+  return per_sm * sm_count;
 }
+
+// Number of CTAs a LayerNorm launch uses for R rows of n features (the caller sizes flags and partials
+// with it; forward and backward use the same number so that their CTAs own the same rows).
+extern "C" int jb_layer_norm_grid2(int R, int n, int sm_count) {
+  const int want = (R + LN_WARPS - 1) / LN_WARPS;
+  const int a = resident_ctas(ln_fwd_kernel, LN_THREADS, 0, sm_count);
+  const int b = resident_ctas(ln_bwd_kernel, LN_THREADS, 2 * static_cast<size_t>(n) * sizeof(float), sm_count);
+  const int cap = a < b ? a : b;
+  return want < cap ? (want < 1 ? 1 : want) : cap;
+}
+extern "C" int jb_layer_norm_grid(int R, int sm_count) { return jb_layer_norm_grid2(R, 1024, sm_count); }
 
 // y = LayerNorm(x) over the last dimension of x [R][n] (n = local slice, n % 4 == 0); saves mean / rstd.
 extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16, const float* w, const float* b,
@@ -741,7 +778,7 @@ extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16,
   a.x = x; a.x_bf16 = x_bf16; a.out = y; a.out_bf16 = y_bf16; a.w = w; a.b = b;
   a.mean = mean; a.rstd = rstd; a.R = R; a.n = n; a.eps = eps; a.status = status;
   if (ln_fill(&a, ex) != 0) return -1;
-  const int grid = jb_layer_norm_grid(R, sm_count);
+  const int grid = jb_layer_norm_grid2(R, n, sm_count);
   ln_fwd_kernel<<<grid, LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -756,7 +793,7 @@ extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g
   a.x = x; a.x_bf16 = x_bf16; a.g = g; a.g_bf16 = g_bf16; a.out = dx; a.out_bf16 = dx_bf16; a.w = w;
   a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd); a.R = R; a.n = n; a.status = status;
   if (ln_fill(&a, ex) != 0) return -1;
-  const int grid = jb_layer_norm_grid(R, sm_count);
+  const int grid = jb_layer_norm_grid2(R, n, sm_count);
   const bool want = dw != nullptr || db != nullptr;
   if (want) {
     a.dw_part = scratch;
@@ -776,6 +813,8 @@ extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g
   return 0;
 }
 
+extern "C" int jb_cross_entropy_grid(int B, int C, int S, int sm_count);
+
 // Per-row cross-entropy of logits [B][C][S] (C = local class shard starting at class_lo) against global
 // class indices target[B*S]; writes loss[R] and lse[R].  Exchange inbox slots are 4 floats per row.
 extern "C" int jb_cross_entropy_fwd(const void* x, int x_bf16, const long long* target, long long ignore_index, int B,
@@ -790,9 +829,7 @@ extern "C" int jb_cross_entropy_fwd(const void* x, int x_bf16, const long long* 
   a.ex = tmp.ex;
   const int R = B * S;
   const bool warp_rows = (S == 1 && C >= 64);
-  const int per_cta = warp_rows ? LN_WARPS : LN_THREADS;
-  int grid = (R + per_cta - 1) / per_cta;
-  if (grid > sm_count) grid = sm_count;
+  const int grid = jb_cross_entropy_grid(B, C, S, sm_count);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (warp_rows) ce_fwd_kernel<true><<<grid, LN_THREADS, 0, st>>>(a);
   else ce_fwd_kernel<false><<<grid, LN_THREADS, 0, st>>>(a);
@@ -801,9 +838,12 @@ extern "C" int jb_cross_entropy_fwd(const void* x, int x_bf16, const long long* 
 
 extern "C" int jb_cross_entropy_grid(int B, int C, int S, int sm_count) {
   const int R = B * S;
-  const int per_cta = (S == 1 && C >= 64) ? LN_WARPS : LN_THREADS;
+  const bool warp_rows = (S == 1 && C >= 64);
+  const int per_cta = warp_rows ? LN_WARPS : LN_THREADS;
   const int grid = (R + per_cta - 1) / per_cta;
-  return grid > sm_count ? sm_count : grid;
+  const int cap = warp_rows ? resident_ctas(ce_fwd_kernel<true>, LN_THREADS, 0, sm_count)
+                            : resident_ctas(ce_fwd_kernel<false>, LN_THREADS, 0, sm_count);
+  return grid > cap ? cap : grid;
 }
 
 // dx = grow[row] * (softmax - onehot) from the saved lse; rows with ignore_index get zero.
@@ -823,7 +863,12 @@ extern "C" int jb_cross_entropy_bwd(const void* x, int x_bf16, const long long* 
 }
 
 // Number of CTAs per normalisation group so that groups * splits fits the SMs (0: too many groups).
-extern "C" int jb_group_norm_splits(int groups, int sm_count) { return groups > sm_count ? 0 : sm_count / groups; }
+extern "C" int jb_group_norm_splits(int groups, int sm_count) {
+  const int a = resident_ctas(gn_kernel<false>, LN_THREADS, 0, sm_count);
+  const int b = resident_ctas(gn_kernel<true>, LN_THREADS, 2 * GN_MAX_CG * sizeof(float), sm_count);
+  const int cap = a < b ? a : b;
+  return groups > cap ? 0 : cap / groups;
+}
 
 static int gn_fill(GnArgs* a, const JbLnExchange* ex, int groups, int groups_per_sample, int cg, long long S,
                    int sm_count) {

@@ -1,0 +1,86 @@
+"""Re-sharding all-to-all over peer memory (``csrc/alltoall.cu``): split one dimension over the
+ranks of a group and concatenate what arrives along another, in one kernel that stores every
+vector at its final place in the destination rank's output.  This is the sequence <-> head
+exchange of Ulysses attention (and its inverse, which is also its backward).
+
+Reference parity: ``all_to_all_single`` in
+jigsaw/modules/attention/_functional/ulysses.py:40,63 (NCCL there, plus the permutes around it).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, symm
+
+_HEADER = 256
+_rings: dict[tuple, list] = {}
+
+
+def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
+    ring = _rings.get(tag)
+    if ring is None:
+        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
+    blk = ring[0][ring[1] & 1]
+    ring[1] += 1
+    return blk
+
+
+def maybe_fused_all_to_all(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor | None:
+    """``cat(all_to_all(chunks of x along split_dim), dim=cat_dim)`` or ``None`` when the kernel
+    does not apply (needs a contiguous CUDA tensor whose trailing dimensions behind both
+    ``split_dim`` and ``cat_dim`` make up a multiple of 16 bytes)."""
+    nd = x.dim()
+    s, c = split_dim % nd, cat_dim % nd
+    P = group.size()
+    if not x.is_cuda or P < 2 or P > 8 or s == c or x.numel() == 0 or x.shape[s] % P:
+        return None
+    last = max(s, c)
+    tail = 1
+    for n in x.shape[last + 1:]:
+        tail *= n
+    if (tail * x.element_size()) % 16 or torch._C._functorch.is_batchedtensor(x) or not _lib.available():
+        return None
+    # collapse to [D0][D1][D2][D3][V]: before first, first, between, second, tail
+    first, second = min(s, c), last
+    d0 = 1
+    for n in x.shape[:first]:
+        d0 *= n
+    mid = 1
+    for n in x.shape[first + 1:second]:
+        mid *= n
+    dims = [d0, x.shape[first], mid, x.shape[second], tail * x.element_size() // 16]
+    split, cat = (1, 3) if s < c else (3, 1)
+    x = x.contiguous()
+    dev = x.device
+    ar = symm.arena(dev)
+    L = _lib.lib()
+    me = group.rank()
+    ranks = dist.get_process_group_ranks(group)
+    nbytes = x.numel() * x.element_size()
+    blk = _ring_block(ar, ("a2a", dev.index, nbytes, P), _HEADER + nbytes)
+    epoch = ar.next_own_epoch(blk)
+    a = _lib.JbA2a()
+    a.x = x.data_ptr()
+    for i, n in enumerate(dims):
+        a.dim[i] = n
+    a.split, a.cat, a.parts, a.me = split, cat, P, me
+    for i, r in enumerate(ranks):
+        a.out[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER
+        a.flag_out[i] = None if i == me else blk.peer_ptr(r) + 4 * me
+        a.flag_in[i] = None if i == me else blk.ptr + 4 * i
+    a.epoch = epoch
+    if ar.capture_stride is not None:
+        a.stride, a.replay = ar.capture_stride, ar.replay.data_ptr()
+    rc = L.jb_all_to_all(ctypes.byref(a), ctypes.c_void_p(ar.done_counter.data_ptr()), ctypes.c_void_p(ar.status.data_ptr()),
+                         _lib.sm_count(dev.index), _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launcher all_to_all failed with code {rc}")
+    _lib.count_launches(1)
+    shape = list(x.shape)
+    shape[s] //= P
+    shape[c] *= P
+    return blk.tensor[_HEADER:_HEADER + nbytes].view(x.dtype).view(shape).clone()

@@ -363,3 +363,47 @@ def test_fused_group_norm_two_gpus():
 @pytest.mark.multigpu(4)
 def test_fused_group_norm_four_gpus():
     run_distributed(_worker_group_norm, 4, {"sh": 2, "sw": 2, "col": 1}, backend="nccl", timeout=300)
+
+
+def _worker_all_to_all(rank, world):
+    """The re-sharding all-to-all on the peer-memory kernel (Ulysses' sequence <-> head exchange):
+    against a reference assembled from an all-gather, its inverse, and through autograd."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+
+    import jigsaw_b200 as jb
+    from jigsaw_b200._core.collectives import all_to_all_dims
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": world, "col": 1})
+    group = mesh["row"]
+    torch.manual_seed(rank)
+    for dtype in (torch.bfloat16, torch.float32):
+        x = torch.randn(3, 2, 6, 4 * world, 16, device=dev).to(dtype)            # (3, b, s/P, h, d)
+        everyone = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(everyone, x, group=group)
+        h = x.shape[-2] // world
+        expect = torch.cat([e[..., rank * h:(rank + 1) * h, :] for e in everyone], dim=-3)   # (3, b, s, h/P, d)
+        before = _lib.LAUNCHES
+        xg = x.clone().requires_grad_(True)
+        y = all_to_all_dims(xg, group, split_dim=-2, cat_dim=-3)
+        assert _lib.LAUNCHES == before + 1
+        assert torch.equal(y.detach(), expect)
+        back = all_to_all_dims(y, group, split_dim=-3, cat_dim=-2)
+        assert torch.equal(back.detach(), x)
+        back.backward(torch.ones_like(back))
+        assert torch.equal(xg.grad, torch.ones_like(x))
+    symm.arena(dev).check_status()
+
+
+@pytest.mark.multigpu(2)
+def test_fused_all_to_all_two_gpus():
+    run_distributed(_worker_all_to_all, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_fused_all_to_all_four_gpus():
+    run_distributed(_worker_all_to_all, 4, backend="nccl", timeout=300)
