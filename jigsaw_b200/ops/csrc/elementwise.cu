@@ -100,6 +100,7 @@ struct MseArgs {
   const float* scale;   // backward: upstream gradient (device scalar)
   void* ga;             // backward: gradient of a (strides of a)
   int ga_bf16;
+  int a_dense;          // a's offset equals the linear index in the given dimension order
 };
 
 __device__ __forceinline__ float load_strided(const Strided4& t, long long off) {
@@ -107,16 +108,26 @@ __device__ __forceinline__ float load_strided(const Strided4& t, long long off) 
                    : static_cast<const float*>(t.ptr)[off];
 }
 
-// Elements are visited in the memory order of `a` when `order_a`, so that its accesses coalesce.
+// The caller orders the dimensions so that `a` is walked in memory order (its offset is then the linear
+// index when it is dense); only `b` needs its index taken apart, in 32-bit arithmetic when it fits.
 __device__ __forceinline__ void mse_offsets(const MseArgs& p, long long i, long long* oa, long long* ob) {
   const int s3 = p.size[3], s2 = p.size[2], s1 = p.size[1];
-  const int i3 = static_cast<int>(i % s3);
-  long long r = i / s3;
-  const int i2 = static_cast<int>(r % s2);
-  r /= s2;
-  const int i1 = static_cast<int>(r % s1);
-  const long long i0 = r / s1;
-  *oa = i0 * p.a.stride[0] + i1 * p.a.stride[1] + i2 * p.a.stride[2] + i3 * p.a.stride[3];
+  long long i0;
+  int i1, i2, i3;
+  if (p.numel < 0x7fffffffll) {
+    unsigned int r = static_cast<unsigned int>(i);
+    i3 = r % s3; r /= s3;
+    i2 = r % s2; r /= s2;
+    i1 = r % s1;
+    i0 = r / s1;
+  } else {
+    long long r = i;
+    i3 = static_cast<int>(r % s3); r /= s3;
+    i2 = static_cast<int>(r % s2); r /= s2;
+    i1 = static_cast<int>(r % s1);
+    i0 = r / s1;
+  }
+  *oa = p.a_dense ? i : i0 * p.a.stride[0] + i1 * p.a.stride[1] + i2 * p.a.stride[2] + i3 * p.a.stride[3];
   *ob = i0 * p.b.stride[0] + i1 * p.b.stride[1] + i2 * p.b.stride[2] + i3 * p.b.stride[3];
 }
 
@@ -303,6 +314,12 @@ static void mse_fill(MseArgs* p, const JbStrided4* a, const JbStrided4* b, const
     p->b.stride[i] = b->stride[i];
     p->size[i] = size[i];
     p->numel *= size[i];
+  }
+  long long expect = 1;
+  p->a_dense = 1;
+  for (int i = 3; i >= 0; --i) {
+    if (size[i] != 1 && a->stride[i] != expect) p->a_dense = 0;
+    expect *= size[i];
   }
 }
 

@@ -124,6 +124,54 @@ __global__ void __launch_bounds__(LN_THREADS) ln_fwd_kernel(const LnArgs a) {
   const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
   const size_t half = static_cast<size_t>(epoch & 1u) * P * a.R * 2;
   const float inv_n = 1.f / static_cast<float>(a.n);
+  if (P == 1 && a.n <= LN_REG_CHUNKS * 128) {
+    // unsplit feature dimension: the row stays in registers between the statistics and the normalisation
+    const int chunks = (a.n + 127) / 128;
+    for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+      const long long base = static_cast<long long>(r) * a.n;
+      float4 v[LN_REG_CHUNKS];
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < LN_REG_CHUNKS; ++k) {
+        const int i = lane * 4 + k * 128;
+        v[k] = (k < chunks && i < a.n) ? ln_load4(a.x, a.x_bf16, base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+      }
+      const float mean = warp_sum(s) * inv_n;
+      float q = 0.f;
+#pragma unroll
+      for (int k = 0; k < LN_REG_CHUNKS; ++k) {
+        const int i = lane * 4 + k * 128;
+        if (k < chunks && i < a.n) {
+          const float d0 = v[k].x - mean, d1 = v[k].y - mean, d2 = v[k].z - mean, d3 = v[k].w - mean;
+          q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
+      }
+      const float rstd = rsqrtf(warp_sum(q) * inv_n + a.eps);
+      if (lane == 0) {
+        a.mean[r] = mean;
+        a.rstd[r] = rstd;
+      }
+#pragma unroll
+      for (int k = 0; k < LN_REG_CHUNKS; ++k) {
+        const int i = lane * 4 + k * 128;
+        if (k < chunks && i < a.n) {
+          float4 o = v[k];
+          o.x = (o.x - mean) * rstd; o.y = (o.y - mean) * rstd; o.z = (o.z - mean) * rstd; o.w = (o.w - mean) * rstd;
+          if (a.w != nullptr) {
+            const float4 w = *reinterpret_cast<const float4*>(a.w + i);
+            o.x *= w.x; o.y *= w.y; o.z *= w.z; o.w *= w.w;
+          }
+          if (a.b != nullptr) {
+            const float4 b = *reinterpret_cast<const float4*>(a.b + i);
+            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+          }
+          ln_store4(a.out, a.out_bf16, base + i, o);
+        }
+      }
+    }
+    return;
+  }
   // ---- phase 1: local mean and centred second moment of every row
   for (int r = r0 + warp; r < r1; r += LN_WARPS) {
     const long long base = static_cast<long long>(r) * a.n;
@@ -338,15 +386,24 @@ __device__ __forceinline__ void ce_row_partials(const CeArgs& a, long long r, in
   // nl = number of lanes cooperating on this row (1 or 32)
   const long long b = r / a.S, sp = r % a.S;
   const long long base = b * a.C * static_cast<long long>(a.S) + sp;
-  float mx = -INFINITY;
-  for (int c = lane; c < a.C; c += nl) mx = fmaxf(mx, ce_load(a, base + static_cast<long long>(c) * a.S));
-  if (nl == 32) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  // one pass: running maximum with the sum rescaled whenever the maximum moves
+  float mx = -INFINITY, sum = 0.f;
+  for (int c = lane; c < a.C; c += nl) {
+    const float v = ce_load(a, base + static_cast<long long>(c) * a.S);
+    if (v > mx) {
+      sum = sum * __expf(mx - v) + 1.f;
+      mx = v;
+    } else if (mx != -INFINITY) {      // (both -inf: nothing to add, and -inf - -inf is not a number)
+      sum += __expf(v - mx);
+    }
   }
-  float sum = 0.f;
-  for (int c = lane; c < a.C; c += nl) sum += __expf(ce_load(a, base + static_cast<long long>(c) * a.S) - mx);
-  if (nl == 32) sum = warp_sum(sum);
+  if (nl == 32) {
+    float all = mx;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) all = fmaxf(all, __shfl_xor_sync(0xffffffffu, all, o));
+    sum = warp_sum(mx == -INFINITY ? 0.f : sum * __expf(mx - all));
+    mx = all;
+  }
   const long long tg = a.target[r] - a.class_lo;
   float tv = 0.f;
   if (a.target[r] != a.ignore_index && tg >= 0 && tg < a.C) tv = ce_load(a, base + tg * a.S);
@@ -408,26 +465,34 @@ __global__ void __launch_bounds__(LN_THREADS) ce_fwd_kernel(const CeArgs a) {
   }
 }
 
-// one thread per logit, in memory order
+// One thread per row walks the classes (no index arithmetic per element; with a strided class
+// dimension the threads of a warp touch consecutive addresses); a trailing class dimension takes one
+// warp per row.
+template <bool WARP_PER_ROW>
 __global__ void __launch_bounds__(256) ce_bwd_kernel(const CeArgs a) {
-  const long long total = static_cast<long long>(a.B) * a.C * a.S;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long sp = i % a.S;
-    const long long c = (i / a.S) % a.C;
-    const long long b = i / (static_cast<long long>(a.S) * a.C);
-    const long long r = b * a.S + sp;
+  const long long R = static_cast<long long>(a.B) * a.S;
+  const int lane = WARP_PER_ROW ? (threadIdx.x & 31) : 0;
+  const int nl = WARP_PER_ROW ? 32 : 1;
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long first = WARP_PER_ROW ? (t >> 5) : t;
+  const long long step = (static_cast<long long>(gridDim.x) * blockDim.x) / nl;
+  for (long long r = first; r < R; r += step) {
+    const long long b = r / a.S, sp = r % a.S;
+    const long long base = b * a.C * static_cast<long long>(a.S) + sp;
     const long long tg = a.target[r];
-    float g = 0.f;
-    if (tg != a.ignore_index) {
-      const float p = __expf(ce_load(a, i) - a.lse[r]);
-      g = a.grow[r] * (p - ((tg - a.class_lo) == c ? 1.f : 0.f));
+    const bool live = tg != a.ignore_index;
+    const float lse = a.lse[r];
+    const float gr = live ? a.grow[r] : 0.f;
+    const long long hot = tg - a.class_lo;
+    for (int c = lane; c < a.C; c += nl) {
+      const long long off = base + static_cast<long long>(c) * a.S;
+      float g = 0.f;
+      if (live) g = gr * (__expf(ce_load(a, off) - lse) - (hot == c ? 1.f : 0.f));
+      if (a.dx_bf16) static_cast<__nv_bfloat16*>(a.dx)[off] = __float2bfloat16(g);
+      else static_cast<float*>(a.dx)[off] = g;
     }
-    if (a.dx_bf16) static_cast<__nv_bfloat16*>(a.dx)[i] = __float2bfloat16(g);
-    else static_cast<float*>(a.dx)[i] = g;
   }
 }
-
 
 // ------------------------------------------------------------------------------------------
 // GroupNorm whose spatial extent is tiled over GPUs.  x is [N][C][S] (S = local voxels); a
@@ -855,10 +920,12 @@ extern "C" int jb_cross_entropy_bwd(const void* x, int x_bf16, const long long* 
   a.x = x; a.x_bf16 = x_bf16; a.target = target; a.ignore_index = ignore_index;
   a.B = B; a.C = C; a.S = S; a.class_lo = class_lo; a.lse = const_cast<float*>(lse); a.grow = grow;
   a.dx = dx; a.dx_bf16 = dx_bf16;
-  const long long total = static_cast<long long>(B) * C * S;
-  long long grid = (total + 255) / 256;
-  if (grid > static_cast<long long>(sm_count) * 16) grid = static_cast<long long>(sm_count) * 16;
-  ce_bwd_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  const bool warp_rows = (S == 1 && C >= 64);
+  const long long threads = static_cast<long long>(B) * S * (warp_rows ? 32 : 1);
+  long long grid = (threads + 255) / 256;
+  if (grid > static_cast<long long>(sm_count) * 32) grid = static_cast<long long>(sm_count) * 32;
+  if (warp_rows) ce_bwd_kernel<true><<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  else ce_bwd_kernel<false><<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -25,18 +25,24 @@ def __getattr__(name: str):
     raise AttributeError(name)
 
 
-def _desc(t: torch.Tensor) -> "_lib.JbStrided4":
+def _order(a: torch.Tensor) -> list[int]:
+    """Dimension order that walks ``a`` in memory order (largest stride first), so that the kernel's
+    innermost loop index is contiguous in ``a``."""
+    return sorted(range(a.dim()), key=lambda i: (-a.stride(i), i))
+
+
+def _desc(t: torch.Tensor, order: list[int]) -> "_lib.JbStrided4":
     d = _lib.JbStrided4()
     d.ptr, d.is_bf16 = t.data_ptr(), int(t.dtype == torch.bfloat16)
     pad = 4 - t.dim()
     for i in range(4):
-        d.stride[i] = 0 if i < pad else t.stride(i - pad)
+        d.stride[i] = 0 if i < pad else t.stride(order[i - pad])
     return d
 
 
-def _sizes(t: torch.Tensor):
+def _sizes(t: torch.Tensor, order: list[int]):
     pad = 4 - t.dim()
-    return (ctypes.c_int * 4)(*([1] * pad + list(t.shape)))
+    return (ctypes.c_int * 4)(*([1] * pad + [t.shape[i] for i in order]))
 
 
 _scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
@@ -66,8 +72,9 @@ class _SqDiffSum(torch.autograd.Function):
         L, dev = _lib.lib(), a.device
         partial, counter = _scratch_for(dev)
         out = torch.empty((), dtype=torch.float32, device=dev)
-        da, db = _desc(a), _desc(b)
-        rc = L.jb_mse_sum(ctypes.byref(da), ctypes.byref(db), _sizes(a), ctypes.c_void_p(partial.data_ptr()),
+        order = _order(a)
+        da, db = _desc(a, order), _desc(b, order)
+        rc = L.jb_mse_sum(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), ctypes.c_void_p(partial.data_ptr()),
                           ctypes.c_void_p(counter.data_ptr()), ctypes.c_void_p(out.data_ptr()), _lib.sm_count(dev.index),
                           _lib.stream_ptr())
         if rc != 0:
@@ -84,8 +91,9 @@ class _SqDiffSum(torch.autograd.Function):
         scale = g.float().contiguous()
         if ctx.needs_input_grad[0]:
             ga = torch.empty_strided(a.shape, a.stride(), dtype=a.dtype, device=dev)
-            da, db = _desc(a), _desc(b)
-            rc = L.jb_mse_grad(ctypes.byref(da), ctypes.byref(db), _sizes(a), ctypes.c_void_p(scale.data_ptr()),
+            order = _order(a)
+            da, db = _desc(a, order), _desc(b, order)
+            rc = L.jb_mse_grad(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), ctypes.c_void_p(scale.data_ptr()),
                                ctypes.c_void_p(ga.data_ptr()), int(ga.dtype == torch.bfloat16), _lib.sm_count(dev.index),
                                _lib.stream_ptr())
             if rc != 0:
