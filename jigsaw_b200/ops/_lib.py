@@ -183,7 +183,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_group_norm_bwd.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
-    L.jb_layer_norm_grid2.argtypes = [c_int, c_int, c_int]
+    L.jb_layer_norm_grid2.argtypes = [c_int, c_int, c_int, c_int]
     L.jb_layer_norm_grid2.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,  # x x_bf16 y y_bf16 w b

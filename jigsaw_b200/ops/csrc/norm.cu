@@ -256,6 +256,48 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
 #pragma unroll
   for (int k = 0; k < LN_REG_CHUNKS; ++k) rdw[k] = rdb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float inv_N = 1.f / (static_cast<float>(a.n) * static_cast<float>(P));
+  if (P == 1 && a.n <= LN_REG_CHUNKS * 128) {
+    // unsplit feature dimension: x and g of a row stay in registers between the two reductions and dx
+    const int chunks = (a.n + 127) / 128;
+    for (int r = r0 + warp; r < r1; r += LN_WARPS) {
+      const long long base = static_cast<long long>(r) * a.n;
+      const float mean = a.mean[r], rstd = a.rstd[r];
+      float4 hx[LN_REG_CHUNKS], gw[LN_REG_CHUNKS];
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < LN_REG_CHUNKS; ++k) {
+        const int i = lane * 4 + k * 128;
+        hx[k] = gw[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < chunks && i < a.n) {
+          const float4 x = ln_load4(a.x, a.x_bf16, base + i);
+          const float4 g = ln_load4(a.g, a.g_bf16, base + i);
+          float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (a.w != nullptr) w = *reinterpret_cast<const float4*>(a.w + i);
+          hx[k] = make_float4((x.x - mean) * rstd, (x.y - mean) * rstd, (x.z - mean) * rstd, (x.w - mean) * rstd);
+          if (want_dw) {
+            rdw[k].x += g.x * hx[k].x; rdw[k].y += g.y * hx[k].y; rdw[k].z += g.z * hx[k].z; rdw[k].w += g.w * hx[k].w;
+            rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
+          }
+          gw[k] = make_float4(g.x * w.x, g.y * w.y, g.z * w.z, g.w * w.w);
+          s1 += (gw[k].x + gw[k].y) + (gw[k].z + gw[k].w);
+          s2 += (gw[k].x * hx[k].x + gw[k].y * hx[k].y) + (gw[k].z * hx[k].z + gw[k].w * hx[k].w);
+        }
+      }
+      const float S1 = warp_sum(s1) * inv_N, S2 = warp_sum(s2) * inv_N;
+#pragma unroll
+      for (int k = 0; k < LN_REG_CHUNKS; ++k) {
+        const int i = lane * 4 + k * 128;
+        if (k < chunks && i < a.n) {
+          float4 d;
+          d.x = rstd * (gw[k].x - S1 - hx[k].x * S2);
+          d.y = rstd * (gw[k].y - S1 - hx[k].y * S2);
+          d.z = rstd * (gw[k].z - S1 - hx[k].z * S2);
+          d.w = rstd * (gw[k].w - S1 - hx[k].w * S2);
+          ln_store4(a.out, a.out_bf16, base + i, d);
+        }
+      }
+    }
+  } else {
   // ---- phase 1: S1 = sum g w, S2 = sum g w xhat per row (local part); dw / db partials
   for (int r = r0 + warp; r < r1; r += LN_WARPS) {
     const long long base = static_cast<long long>(r) * a.n;
@@ -321,6 +363,7 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
       ln_store4(a.out, a.out_bf16, base + i, d);
     }
   }
+  }   // split feature dimension
   if (want_dw) {
 #pragma unroll
     for (int k = 0; k < LN_REG_CHUNKS; ++k) {        // one shared-memory add per warp and column
@@ -824,15 +867,14 @@ static int resident_ctas(K kernel, int threads, size_t smem, int sm_count) {
 }
 
 // Number of CTAs a LayerNorm launch uses for R rows of n features (the caller sizes flags and partials
-// with it; forward and backward use the same number so that their CTAs own the same rows).
-extern "C" int jb_layer_norm_grid2(int R, int n, int sm_count) {
+// with it); `backward` selects the kernel whose residency bounds the grid.
+extern "C" int jb_layer_norm_grid2(int R, int n, int backward, int sm_count) {
   const int want = (R + LN_WARPS - 1) / LN_WARPS;
-  const int a = resident_ctas(ln_fwd_kernel, LN_THREADS, 0, sm_count);
-  const int b = resident_ctas(ln_bwd_kernel, LN_THREADS, 2 * static_cast<size_t>(n) * sizeof(float), sm_count);
-  const int cap = a < b ? a : b;
+  const int cap = backward ? resident_ctas(ln_bwd_kernel, LN_THREADS, 2 * static_cast<size_t>(n) * sizeof(float), sm_count)
+                           : resident_ctas(ln_fwd_kernel, LN_THREADS, 0, sm_count);
   return want < cap ? (want < 1 ? 1 : want) : cap;
 }
-extern "C" int jb_layer_norm_grid(int R, int sm_count) { return jb_layer_norm_grid2(R, 1024, sm_count); }
+extern "C" int jb_layer_norm_grid(int R, int sm_count) { return jb_layer_norm_grid2(R, 1024, 1, sm_count); }
 
 // y = LayerNorm(x) over the last dimension of x [R][n] (n = local slice, n % 4 == 0); saves mean / rstd.
 extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16, const float* w, const float* b,
@@ -843,7 +885,7 @@ extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16,
   a.x = x; a.x_bf16 = x_bf16; a.out = y; a.out_bf16 = y_bf16; a.w = w; a.b = b;
   a.mean = mean; a.rstd = rstd; a.R = R; a.n = n; a.eps = eps; a.status = status;
   if (ln_fill(&a, ex) != 0) return -1;
-  const int grid = jb_layer_norm_grid2(R, n, sm_count);
+  const int grid = jb_layer_norm_grid2(R, n, 0, sm_count);
   ln_fwd_kernel<<<grid, LN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -858,7 +900,7 @@ extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g
   a.x = x; a.x_bf16 = x_bf16; a.g = g; a.g_bf16 = g_bf16; a.out = dx; a.out_bf16 = dx_bf16; a.w = w;
   a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd); a.R = R; a.n = n; a.status = status;
   if (ln_fill(&a, ex) != 0) return -1;
-  const int grid = jb_layer_norm_grid2(R, n, sm_count);
+  const int grid = jb_layer_norm_grid2(R, n, 1, sm_count);
   const bool want = dw != nullptr || db != nullptr;
   if (want) {
     a.dw_part = scratch;

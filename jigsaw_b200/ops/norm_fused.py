@@ -85,7 +85,7 @@ class _FusedLayerNorm(torch.autograd.Function):
         x2 = x.reshape(-1, n)
         R = x2.shape[0]
         sm = _lib.sm_count(dev.index)
-        grid = L.jb_layer_norm_grid2(R, n, sm)
+        grid = L.jb_layer_norm_grid2(R, n, 0, sm)
         y = torch.empty(x.shape, dtype=out_dtype, device=dev)
         mean = torch.empty(R, dtype=torch.float32, device=dev)
         rstd = torch.empty(R, dtype=torch.float32, device=dev)
@@ -110,7 +110,7 @@ class _FusedLayerNorm(torch.autograd.Function):
             g = g.float()
         g2 = g.reshape(R, n).contiguous()
         sm = _lib.sm_count(dev.index)
-        grid = L.jb_layer_norm_grid2(R, n, sm)
+        grid = L.jb_layer_norm_grid2(R, n, 1, sm)
         dx = torch.empty_like(x2)
         want_w = w is not None and ctx.needs_input_grad[1]
         want_b = ctx.has_b and ctx.needs_input_grad[2]
