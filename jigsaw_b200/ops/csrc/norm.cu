@@ -303,11 +303,27 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
     const long long base = static_cast<long long>(r) * a.n;
     const float mean = a.mean[r], rstd = a.rstd[r];
     float s1 = 0.f, s2 = 0.f;
-    const int chunks = (a.n + 127) / 128;
-#pragma unroll LN_REG_CHUNKS
-    for (int k = 0; k < chunks; ++k) {
+    // columns [0, LN_REG_CHUNKS * 128): sums for dw / db in registers (constant trip count, so the
+    // accumulators are never indexed dynamically); columns beyond: shared-memory adds
+#pragma unroll
+    for (int k = 0; k < LN_REG_CHUNKS; ++k) {
       const int i = lane * 4 + k * 128;
-      if (i >= a.n) break;
+      if (i < a.n) {
+        const float4 x = ln_load4(a.x, a.x_bf16, base + i);
+        const float4 g = ln_load4(a.g, a.g_bf16, base + i);
+        float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (a.w != nullptr) w = *reinterpret_cast<const float4*>(a.w + i);
+        const float h0 = (x.x - mean) * rstd, h1 = (x.y - mean) * rstd, h2 = (x.z - mean) * rstd, h3 = (x.w - mean) * rstd;
+        const float gw0 = g.x * w.x, gw1 = g.y * w.y, gw2 = g.z * w.z, gw3 = g.w * w.w;
+        s1 += (gw0 + gw1) + (gw2 + gw3);
+        s2 += (gw0 * h0 + gw1 * h1) + (gw2 * h2 + gw3 * h3);
+        if (want_dw) {
+          rdw[k].x += g.x * h0; rdw[k].y += g.y * h1; rdw[k].z += g.z * h2; rdw[k].w += g.w * h3;
+          rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
+        }
+      }
+    }
+    for (int i = lane * 4 + LN_REG_CHUNKS * 128; i < a.n; i += 128) {
       const float4 x = ln_load4(a.x, a.x_bf16, base + i);
       const float4 g = ln_load4(a.g, a.g_bf16, base + i);
       float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -317,15 +333,10 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
       s1 += (gw0 + gw1) + (gw2 + gw3);
       s2 += (gw0 * h0 + gw1 * h1) + (gw2 * h2 + gw3 * h3);
       if (want_dw) {
-        if (k < LN_REG_CHUNKS) {       // a lane owns the same columns in every row: keep their sums in registers
-          rdw[k].x += g.x * h0; rdw[k].y += g.y * h1; rdw[k].z += g.z * h2; rdw[k].w += g.w * h3;
-          rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
-        } else {
-          atomicAdd(acc + i + 0, g.x * h0); atomicAdd(acc + i + 1, g.y * h1);
-          atomicAdd(acc + i + 2, g.z * h2); atomicAdd(acc + i + 3, g.w * h3);
-          atomicAdd(acc + a.n + i + 0, g.x); atomicAdd(acc + a.n + i + 1, g.y);
-          atomicAdd(acc + a.n + i + 2, g.z); atomicAdd(acc + a.n + i + 3, g.w);
-        }
+        atomicAdd(acc + i + 0, g.x * h0); atomicAdd(acc + i + 1, g.y * h1);
+        atomicAdd(acc + i + 2, g.z * h2); atomicAdd(acc + i + 3, g.w * h3);
+        atomicAdd(acc + a.n + i + 0, g.x); atomicAdd(acc + a.n + i + 1, g.y);
+        atomicAdd(acc + a.n + i + 2, g.z); atomicAdd(acc + a.n + i + 3, g.w);
       }
     }
     s1 = warp_sum(s1);
@@ -429,24 +440,16 @@ __device__ __forceinline__ void ce_row_partials(const CeArgs& a, long long r, in
   // nl = number of lanes cooperating on this row (1 or 32)
   const long long b = r / a.S, sp = r % a.S;
   const long long base = b * a.C * static_cast<long long>(a.S) + sp;
-  // one pass: running maximum with the sum rescaled whenever the maximum moves
-  float mx = -INFINITY, sum = 0.f;
-  for (int c = lane; c < a.C; c += nl) {
-    const float v = ce_load(a, base + static_cast<long long>(c) * a.S);
-    if (v > mx) {
-      sum = sum * __expf(mx - v) + 1.f;
-      mx = v;
-    } else if (mx != -INFINITY) {      // (both -inf: nothing to add, and -inf - -inf is not a number)
-      sum += __expf(v - mx);
-    }
-  }
+  float mx = -INFINITY;
+  for (int c = lane; c < a.C; c += nl) mx = fmaxf(mx, ce_load(a, base + static_cast<long long>(c) * a.S));
   if (nl == 32) {
-    float all = mx;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) all = fmaxf(all, __shfl_xor_sync(0xffffffffu, all, o));
-    sum = warp_sum(mx == -INFINITY ? 0.f : sum * __expf(mx - all));
-    mx = all;
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   }
+  float sum = 0.f;
+  if (mx != -INFINITY)
+    for (int c = lane; c < a.C; c += nl) sum += __expf(ce_load(a, base + static_cast<long long>(c) * a.S) - mx);
+  if (nl == 32) sum = warp_sum(sum);
   const long long tg = a.target[r] - a.class_lo;
   float tv = 0.f;
   if (a.target[r] != a.ignore_index && tg >= 0 && tg < a.C) tv = ce_load(a, base + tg * a.S);
