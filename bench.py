@@ -174,6 +174,8 @@ def main() -> None:
 
         run = GraphedStep(step, (x_dev, y_dev), warmup=max(args.warmup, 3))
 
+    sizes = {"loss": 4}
+
     def timed(n_steps: int, e2e: bool) -> tuple[float, float]:
         dist.barrier()
         torch.cuda.synchronize()
@@ -184,11 +186,15 @@ def main() -> None:
             if e2e and run is not None:
                 x_dev.copy_(x_host, non_blocking=True)
                 y_dev.copy_(y_host, non_blocking=True)
-                last = float(run.replay().item())
+                out = run.replay()
+                sizes["loss"] = out.element_size()
+                last = float(out.item())
             elif e2e:
                 x = x_host.to(dev, non_blocking=True)
                 y = y_host.to(dev, non_blocking=True)
-                last = float(step(x, y).item())
+                out = step(x, y)
+                sizes["loss"] = out.element_size()
+                last = float(out.item())
             elif run is not None:
                 loss = run.replay()
             else:
@@ -225,6 +231,7 @@ def main() -> None:
         symm.arena(dev).check_status()
     if rank == 0:
         h2d = (x_host.numel() + y_host.numel()) * 4
+        loss_bytes = sizes["loss"]
         line = {
             "metric": "CNN images/sec (domain-parallel 8x Conv2d(64ch,k3)+GELU, 1x3x4096x4096, fwd+bwd+Adam)",
             "value": 1000.0 / ms_dev,
@@ -250,7 +257,7 @@ def main() -> None:
             },
             "clocks": clocks,
             "e2e": {"value": 1000.0 / ms_e2e, "unit": "images/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": loss_bytes},
             "gpu_launches": launches,
             "loss": loss_val,
         }
