@@ -183,6 +183,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_group_norm_bwd.restype = c_int
     L.jb_layer_norm_grid.argtypes = [c_int, c_int]
     L.jb_layer_norm_grid.restype = c_int
+    L.jb_layer_norm_scratch_floats.argtypes = [c_int, c_int]
+    L.jb_layer_norm_scratch_floats.restype = c_longlong
     L.jb_layer_norm_grid2.argtypes = [c_int, c_int, c_int, c_int]
     L.jb_layer_norm_grid2.restype = c_int
     L.jb_layer_norm_fwd.argtypes = [

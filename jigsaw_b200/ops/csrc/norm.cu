@@ -239,7 +239,8 @@ __global__ void __launch_bounds__(LN_THREADS) ln_fwd_kernel(const LnArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
+template <bool WANT_DW>
+__global__ void __launch_bounds__(LN_THREADS, WANT_DW ? 1 : 3) ln_bwd_kernel(const LnArgs a) {
   extern __shared__ float acc[];   // [2][n]: dw, db partials of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int r0, r1;
@@ -248,13 +249,13 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
   const int P = ex.parts;
   const uint32_t epoch = live_epoch(ex.epoch, ex.stride, ex.replay);
   const size_t half = static_cast<size_t>(epoch & 1u) * P * a.R * 2;
-  const bool want_dw = a.dw_part != nullptr;
+  constexpr bool want_dw = WANT_DW;
   if (want_dw)
     for (int i = threadIdx.x; i < 2 * a.n; i += LN_THREADS) acc[i] = 0.f;
   __syncthreads();
-  float4 rdw[LN_REG_CHUNKS], rdb[LN_REG_CHUNKS];
+  float4 rdw[WANT_DW ? LN_REG_CHUNKS : 1], rdb[WANT_DW ? LN_REG_CHUNKS : 1];
 #pragma unroll
-  for (int k = 0; k < LN_REG_CHUNKS; ++k) rdw[k] = rdb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < (WANT_DW ? LN_REG_CHUNKS : 1); ++k) rdw[k] = rdb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float inv_N = 1.f / (static_cast<float>(a.n) * static_cast<float>(P));
   if (P == 1 && a.n <= LN_REG_CHUNKS * 128) {
     // unsplit feature dimension: x and g of a row stay in registers between the two reductions and dx
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
           float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
           if (a.w != nullptr) w = *reinterpret_cast<const float4*>(a.w + i);
           hx[k] = make_float4((x.x - mean) * rstd, (x.y - mean) * rstd, (x.z - mean) * rstd, (x.w - mean) * rstd);
-          if (want_dw) {
+          if constexpr (WANT_DW) {
             rdw[k].x += g.x * hx[k].x; rdw[k].y += g.y * hx[k].y; rdw[k].z += g.z * hx[k].z; rdw[k].w += g.w * hx[k].w;
             rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
           }
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
         const float gw0 = g.x * w.x, gw1 = g.y * w.y, gw2 = g.z * w.z, gw3 = g.w * w.w;
         s1 += (gw0 + gw1) + (gw2 + gw3);
         s2 += (gw0 * h0 + gw1 * h1) + (gw2 * h2 + gw3 * h3);
-        if (want_dw) {
+        if constexpr (WANT_DW) {
           rdw[k].x += g.x * h0; rdw[k].y += g.y * h1; rdw[k].z += g.z * h2; rdw[k].w += g.w * h3;
           rdb[k].x += g.x; rdb[k].y += g.y; rdb[k].z += g.z; rdb[k].w += g.w;
         }
@@ -375,7 +376,7 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
     }
   }
   }   // split feature dimension
-  if (want_dw) {
+  if constexpr (WANT_DW) {
 #pragma unroll
     for (int k = 0; k < LN_REG_CHUNKS; ++k) {        // one shared-memory add per warp and column
       const int i = lane * 4 + k * 128;
@@ -391,6 +392,44 @@ __global__ void __launch_bounds__(LN_THREADS) ln_bwd_kernel(const LnArgs a) {
       a.dw_part[static_cast<size_t>(blockIdx.x) * a.n + i] = acc[i];
       a.db_part[static_cast<size_t>(blockIdx.x) * a.n + i] = acc[a.n + i];
     }
+  }
+}
+
+// dw / db partial sums of LayerNorm: a CTA owns 128 columns and a slab of rows; 32 column lanes (four
+// columns each, so a warp reads 256 or 512 consecutive bytes of a row) times 8 row lanes.
+constexpr int LN_COL_ROWS = 512;   // rows per slab
+__global__ void __launch_bounds__(256) ln_dwdb_kernel(const LnArgs a) {
+  __shared__ float4 red[2][8][32];
+  const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int i = blockIdx.x * 128 + cl * 4;
+  const int r0 = blockIdx.y * LN_COL_ROWS;
+  const int r1 = min(a.R, r0 + LN_COL_ROWS);
+  float4 dw = make_float4(0.f, 0.f, 0.f, 0.f), db = dw;
+  if (i < a.n) {
+#pragma unroll 4
+    for (int r = r0 + rl; r < r1; r += 8) {
+      const long long base = static_cast<long long>(r) * a.n + i;
+      const float4 x = ln_load4(a.x, a.x_bf16, base);
+      const float4 g = ln_load4(a.g, a.g_bf16, base);
+      const float mean = __ldg(a.mean + r), rstd = __ldg(a.rstd + r);
+      dw.x += g.x * (x.x - mean) * rstd; dw.y += g.y * (x.y - mean) * rstd;
+      dw.z += g.z * (x.z - mean) * rstd; dw.w += g.w * (x.w - mean) * rstd;
+      db.x += g.x; db.y += g.y; db.z += g.z; db.w += g.w;
+    }
+  }
+  red[0][rl][cl] = dw;
+  red[1][rl][cl] = db;
+  __syncthreads();
+  if (rl == 0 && i < a.n) {
+    float4 sw = red[0][0][cl], sb = red[1][0][cl];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      const float4 u = red[0][k][cl], v = red[1][k][cl];
+      sw.x += u.x; sw.y += u.y; sw.z += u.z; sw.w += u.w;
+      sb.x += v.x; sb.y += v.y; sb.z += v.z; sb.w += v.w;
+    }
+    *reinterpret_cast<float4*>(a.dw_part + static_cast<size_t>(blockIdx.y) * a.n + i) = sw;
+    *reinterpret_cast<float4*>(a.db_part + static_cast<size_t>(blockIdx.y) * a.n + i) = sb;
   }
 }
 
@@ -873,9 +912,12 @@ static int resident_ctas(K kernel, int threads, size_t smem, int sm_count) {
 // with it); `backward` selects the kernel whose residency bounds the grid.
 extern "C" int jb_layer_norm_grid2(int R, int n, int backward, int sm_count) {
   const int want = (R + LN_WARPS - 1) / LN_WARPS;
-  const int cap = backward ? resident_ctas(ln_bwd_kernel, LN_THREADS, 2 * static_cast<size_t>(n) * sizeof(float), sm_count)
+  const int cap = backward ? resident_ctas(ln_bwd_kernel<false>, LN_THREADS, 0, sm_count)
                            : resident_ctas(ln_fwd_kernel, LN_THREADS, 0, sm_count);
   return want < cap ? (want < 1 ? 1 : want) : cap;
+}
+extern "C" long long jb_layer_norm_scratch_floats(int R, int n) {
+  return 2ll * ((R + LN_COL_ROWS - 1) / LN_COL_ROWS) * n;
 }
 extern "C" int jb_layer_norm_grid(int R, int sm_count) { return jb_layer_norm_grid2(R, 1024, 1, sm_count); }
 
@@ -893,7 +935,7 @@ extern "C" int jb_layer_norm_fwd(const void* x, int x_bf16, void* y, int y_bf16,
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-// dx, dw, db of the same.  scratch: 2 * grid * n floats.  The exchange needs an inbox even with one part.
+// dx, dw, db of the same.  scratch: 2 * ceil(R / 512) * n floats (jb_layer_norm_scratch_floats).  The exchange needs an inbox even with one part.
 extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g_bf16, void* dx, int dx_bf16,
                                  const float* w, const float* mean, const float* rstd, float* dw, float* db,
                                  float* scratch, int R, int n, const JbLnExchange* ex, int* status, int sm_count,
@@ -905,19 +947,19 @@ extern "C" int jb_layer_norm_bwd(const void* x, int x_bf16, const void* g, int g
   if (ln_fill(&a, ex) != 0) return -1;
   const int grid = jb_layer_norm_grid2(R, n, 1, sm_count);
   const bool want = dw != nullptr || db != nullptr;
+  const int slabs = (R + LN_COL_ROWS - 1) / LN_COL_ROWS;
   if (want) {
     a.dw_part = scratch;
-    a.db_part = scratch + static_cast<size_t>(grid) * n;
+    a.db_part = scratch + static_cast<size_t>(slabs) * n;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int smem = want ? 2 * n * static_cast<int>(sizeof(float)) : 0;
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(ln_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return -3;
-  ln_bwd_kernel<<<grid, LN_THREADS, smem, st>>>(a);
+  ln_bwd_kernel<false><<<grid, LN_THREADS, 0, st>>>(a);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (want) {
-    ln_colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(a.dw_part, a.db_part, grid, n, dw, db);
+    // the row statistics are already final (forward): the column sums need no exchange
+    ln_dwdb_kernel<<<dim3((n + 127) / 128, slabs), 256, 0, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return -4;
+    ln_colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(a.dw_part, a.db_part, slabs, n, dw, db);
     if (cudaGetLastError() != cudaSuccess) return -4;
   }
   return 0;

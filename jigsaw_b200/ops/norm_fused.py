@@ -116,14 +116,15 @@ class _FusedLayerNorm(torch.autograd.Function):
         want_b = ctx.has_b and ctx.needs_input_grad[2]
         dw = torch.empty(n, dtype=torch.float32, device=dev) if want_w else None
         db = torch.empty(n, dtype=torch.float32, device=dev) if want_b else None
-        scratch = torch.empty(2 * grid * n, dtype=torch.float32, device=dev) if (want_w or want_b) else None
+        scratch = (torch.empty(L.jb_layer_norm_scratch_floats(R, n), dtype=torch.float32, device=dev)
+                   if (want_w or want_b) else None)
         ex = _Exchange(dev, ctx.group, R, grid)
         status = symm.arena(dev).status
         _check(L.jb_layer_norm_bwd(_p(x2), int(x2.dtype == torch.bfloat16), _p(g2), int(g2.dtype == torch.bfloat16), _p(dx),
                                    int(dx.dtype == torch.bfloat16), _p(w), _p(mean), _p(rstd), _p(dw), _p(db), _p(scratch),
                                    R, n, ctypes.byref(ex.desc), _p(status), sm, _lib.stream_ptr()), "layer_norm_bwd")
         ex.done()
-        _lib.count_launches(2 if scratch is not None else 1)
+        _lib.count_launches(3 if scratch is not None else 1)
         return dx.view(ctx.shape), dw, db, None, None, None
 
 
