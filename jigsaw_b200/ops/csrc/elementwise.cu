@@ -167,6 +167,63 @@ __global__ void __launch_bounds__(256) mse_fwd_kernel(const MseArgs p) {
   }
 }
 
+// Few innermost entries (the channels of a channels-last prediction): one thread per pixel.  The
+// prediction is read and its gradient written as one short run per thread, consecutive threads take
+// consecutive pixels, so each of the target's channel planes is read coalesced; the index is taken
+// apart once per pixel.
+template <bool BWD>
+__global__ void __launch_bounds__(256) mse_pix_kernel(const MseArgs p) {
+  const int C = p.size[3];
+  const unsigned int s2 = p.size[2], s1 = p.size[1];
+  const long long pixels = p.numel / C;
+  const float k = BWD ? 2.f * __ldg(p.scale) : 0.f;
+  float s = 0.f;
+  for (long long j = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; j < pixels;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    long long r = j;
+    const long long i2 = r % s2; r /= s2;
+    const long long i1 = r % s1;
+    const long long i0 = r / s1;
+    const long long ob = i0 * p.b.stride[0] + i1 * p.b.stride[1] + i2 * p.b.stride[2];
+    const long long oa = j * C;
+    for (int c = 0; c < C; ++c) {
+      const float d = load_strided(p.a, oa + c) - load_strided(p.b, ob + c * p.b.stride[3]);
+      if (BWD) {
+        if (p.ga_bf16) static_cast<__nv_bfloat16*>(p.ga)[oa + c] = __float2bfloat16(k * d);
+        else static_cast<float*>(p.ga)[oa + c] = k * d;
+      } else {
+        s += d * d;
+      }
+    }
+  }
+  if (BWD) return;
+  __shared__ float red[8];
+  __shared__ bool last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    p.partial[blockIdx.x] = t;
+    __threadfence();
+    last = atomicAdd(p.counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (last && threadIdx.x < 32) {
+    __threadfence();
+    float t = 0.f;
+    for (unsigned int g = threadIdx.x; g < gridDim.x; g += 32) t += __ldcg(p.partial + g);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) {
+      *p.out = t;
+      *p.counter = 0u;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) mse_bwd_kernel(const MseArgs p) {
   const float k = 2.f * __ldg(p.scale);
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel;
@@ -336,7 +393,10 @@ extern "C" int jb_mse_sum(const JbStrided4* a, const JbStrided4* b, const int* s
   mse_fill(&p, a, b, size);
   if (p.numel <= 0) return -1;
   p.partial = partial; p.counter = counter; p.out = out;
-  mse_fwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (p.a_dense && p.size[3] <= 4)
+    mse_pix_kernel<false><<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    mse_fwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -347,7 +407,10 @@ extern "C" int jb_mse_grad(const JbStrided4* a, const JbStrided4* b, const int* 
   mse_fill(&p, a, b, size);
   if (p.numel <= 0) return -1;
   p.scale = scale; p.ga = ga; p.ga_bf16 = ga_bf16;
-  mse_bwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  if (p.a_dense && p.size[3] <= 4)
+    mse_pix_kernel<true><<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    mse_bwd_kernel<<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
