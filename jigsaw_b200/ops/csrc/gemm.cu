@@ -10,7 +10,7 @@
 // run from the stored tensors without a transpose pass.  A CTA is persistent over
 // 128 x BN output tiles; warp 0 issues TMA loads into a multi-stage shared-memory
 // ring, warp 1 issues tcgen05.mma into a double-buffered TMEM accumulator, warps
-// 2..5 drain finished accumulators (tcgen05.ld), apply bias / GELU and store.
+// 2..9 drain finished accumulators (tcgen05.ld), apply bias / GELU and store.
 //
 // Capability parity: replaces the cuBLAS `torch.matmul` calls of the reference
 // (jigsaw/modules/linear/_distributed_matmul.py:100-110, 159-177).
@@ -22,7 +22,8 @@ namespace jb {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;   // 64 bf16 = one 128-byte swizzle row
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 8;     // two per TMEM lane quadrant, each draining half of the columns
+constexpr int GEMM_THREADS = 32 * (2 + GEMM_EPI_WARPS);
 
 struct GemmEpilogue {
   void* c;            // output, row-major [M, ldc]
@@ -92,7 +93,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], 4);
+      mbar_init(&acc_empty[s], GEMM_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -212,8 +213,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps)
-    const int quad = warp & 3;
+    // ------------------------------------------------------------ epilogue (8 warps)
+    const int quad = warp & 3;                 // TMEM lanes 32 * quad .. + 31 are the ones this warp may read
+    const int chalf = (warp - 2) >> 2;         // which half of the tile's columns
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       const int as = it & 1;
@@ -235,7 +237,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         col_shift = part * ep.part_cols;
       }
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
