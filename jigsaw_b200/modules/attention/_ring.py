@@ -63,8 +63,25 @@ class _Fetcher:
     def owner(self, p: int, s: int) -> int:
         return chunk_owner(self.cfg.send_op, p, s, self.P, self.cfg.intra_size)
 
+    def _peer(self):
+        """Peer-memory transport (CUDA): the payload is published once in symmetric memory and every
+        chunk is pulled from its owner by a copy kernel on a side stream."""
+        if getattr(self, "_peer_chunks", None) is None:
+            self._peer_chunks = False
+            if self.payload.is_cuda:
+                from ...ops import exchange_fused
+
+                if exchange_fused.PeerChunks.usable(self.payload, self.group):
+                    self._peer_chunks = exchange_fused.PeerChunks(self.payload, self.group)
+        return self._peer_chunks
+
     def _start(self, s: int) -> None:
         o = self.owner(self.me, s)
+        peer = self._peer()
+        if peer:
+            buf, ready = peer.start(o)
+            self._pending[s] = (buf, ready)
+            return
         sends = {p: self.payload for p in range(self.P) if p != self.me and self.owner(p, s) == self.me}
         if o == self.me:
             buf, recvs = self.payload, {}
@@ -81,7 +98,10 @@ class _Fetcher:
             self._start(s + 1)
         buf, work = self._pending.pop(s)
         if work is not None:
-            work.wait()
+            if isinstance(work, torch.cuda.Event):
+                torch.cuda.current_stream(buf.device).wait_event(work)
+            else:
+                work.wait()
         return buf
 
 

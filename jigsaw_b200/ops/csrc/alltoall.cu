@@ -117,3 +117,58 @@ extern "C" int jb_all_to_all(const JbA2a* r, unsigned int* done_counter, int* st
   a2a_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ------------------------------------------------------------------------------------------
+// Fetch a contiguous block from another GPU's memory with plain 16-byte loads over NVLink, after
+// its owner's epoch flag says the block is complete (bounded wait).  Ring attention uses this to
+// pull the key / value chunk of a step straight from the chunk's owner while the previous chunk
+// is being attended to on another stream.
+// ------------------------------------------------------------------------------------------
+namespace jb {
+__global__ void __launch_bounds__(256) peer_fetch_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                         long long n16, const uint32_t* flag, uint32_t epoch,
+                                                         uint32_t stride, const uint32_t* replay, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    ok = 1;
+    if (flag != nullptr) {
+      const uint32_t want = live_epoch(epoch, stride, replay);
+      const uint64_t t0 = globaltimer_ns();
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (static_cast<int32_t>(v - want) >= 0) break;
+        if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+          if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+          ok = 0;
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 v;
+    asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+    dst[i] = v;
+  }
+}
+}  // namespace jb
+
+// dst[0 .. nbytes) = src[0 .. nbytes) where src may be a peer pointer; waits for *flag >= epoch first
+// (flag is a local word, null = no wait).  nbytes must be a multiple of 16.
+extern "C" int jb_peer_fetch(const void* src, void* dst, long long nbytes, const void* flag, unsigned int epoch,
+                             unsigned int stride, const unsigned int* replay, int* status, int ctas, void* stream) {
+  if (nbytes <= 0 || (nbytes & 15)) return -1;
+  const long long n16 = nbytes / 16;
+  long long grid = (n16 + 255) / 256;
+  if (grid > ctas) grid = ctas;
+  jb::peer_fetch_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), n16, static_cast<const uint32_t*>(flag), epoch, stride,
+      replay, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

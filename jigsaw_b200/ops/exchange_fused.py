@@ -18,6 +18,7 @@ from . import _lib, symm
 
 _HEADER = 256
 _rings: dict[tuple, list] = {}
+_side_streams: dict[int, "torch.cuda.Stream"] = {}
 
 
 def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
@@ -84,3 +85,72 @@ def maybe_fused_all_to_all(x: torch.Tensor, group: dist.ProcessGroup, split_dim:
     shape[s] //= P
     shape[c] *= P
     return blk.tensor[_HEADER:_HEADER + nbytes].view(x.dtype).view(shape).clone()
+
+
+class PeerChunks:
+    """A tensor that every rank of ``group`` publishes once in symmetric memory and whose copies the
+    others fetch on demand, straight from the owner's memory (ring attention's key / value chunks).
+
+    ``PeerChunks(payload, group)`` stages the local payload and publishes its epoch flag to the
+    peers; ``fetch(owner)`` returns a local copy of ``owner``'s payload, pulled by a kernel that
+    waits (bounded) for the owner's flag and then reads over NVLink.  Fetches run on a side stream,
+    so the next chunk can travel while the current one is being used; the returned tensor is safe
+    to use on the current stream."""
+
+    def __init__(self, payload: torch.Tensor, group: dist.ProcessGroup) -> None:
+        self.payload = payload.contiguous()
+        self.group = group
+        dev = payload.device
+        self.ar = symm.arena(dev)
+        self.me = group.rank()
+        self.ranks = dist.get_process_group_ranks(group)
+        self.nbytes = self.payload.numel() * self.payload.element_size()
+        blk = _ring_block(self.ar, ("chunks", dev.index, self.nbytes, group.size()), _HEADER + self.nbytes)
+        self.blk = blk
+        staged = blk.tensor[_HEADER:_HEADER + self.nbytes].view(self.payload.dtype).view(self.payload.shape)
+        staged.copy_(self.payload)
+        self.epoch = self.ar.next_own_epoch(blk)
+        self.stride = self.ar.capture_stride or 0
+        self.replay = self.ar.replay.data_ptr() if self.ar.capture_stride is not None else None
+        flags = (ctypes.c_void_p * 8)()
+        n = 0
+        for i, r in enumerate(self.ranks):
+            if i != self.me:
+                flags[n] = blk.peer_ptr(r) + 4 * self.me
+                n += 1
+        rc = _lib.lib().jb_publish(flags, n, self.epoch, self.stride, self.replay, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher publish failed with code {rc}")
+        _lib.count_launches(1)
+        if dev.index not in _side_streams:
+            _side_streams[dev.index] = torch.cuda.Stream(dev)
+        self._side = _side_streams[dev.index]
+        self._staged_event = torch.cuda.Event()
+        self._staged_event.record()
+
+    @staticmethod
+    def usable(payload: torch.Tensor, group: dist.ProcessGroup) -> bool:
+        nbytes = payload.numel() * payload.element_size()
+        return (payload.is_cuda and 2 <= group.size() <= 8 and nbytes % 16 == 0 and nbytes > 0
+                and not torch._C._functorch.is_batchedtensor(payload) and _lib.available())
+
+    def start(self, owner: int) -> tuple[torch.Tensor, "torch.cuda.Event | None"]:
+        """Begin fetching ``owner``'s payload (group rank); returns ``(buffer, ready event)``."""
+        if owner == self.me:
+            return self.payload, None
+        dev = self.payload.device
+        buf = torch.empty_like(self.payload)
+        self._side.wait_event(self._staged_event)
+        with torch.cuda.stream(self._side):
+            src = self.blk.peer_ptr(self.ranks[owner]) + _HEADER
+            rc = _lib.lib().jb_peer_fetch(ctypes.c_void_p(src), ctypes.c_void_p(buf.data_ptr()), self.nbytes,
+                                          ctypes.c_void_p(self.blk.ptr + 4 * owner), self.epoch, self.stride, self.replay,
+                                          ctypes.c_void_p(self.ar.status.data_ptr()), 4 * _lib.sm_count(dev.index),
+                                          _lib.stream_ptr())
+            if rc != 0:
+                raise RuntimeError(f"jigsaw_b200 kernel launcher peer_fetch failed with code {rc}")
+            ready = torch.cuda.Event()
+            ready.record()
+        buf.record_stream(self._side)
+        _lib.count_launches(1)
+        return buf, ready

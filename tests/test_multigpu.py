@@ -407,3 +407,50 @@ def test_fused_all_to_all_two_gpus():
 @pytest.mark.multigpu(4)
 def test_fused_all_to_all_four_gpus():
     run_distributed(_worker_all_to_all, 4, backend="nccl", timeout=300)
+
+
+def _worker_ring_attention(rank, world):
+    """Ring attention whose key / value chunks are pulled from their owners' memory by the peer-fetch
+    kernel (side stream, next chunk in flight while the current one is attended to) against the
+    undivided attention layer: output and every gradient."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import split
+    from jigsaw_b200.modules.attention import Attention
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": world, "col": 1})
+    torch.manual_seed(0)
+    serial = Attention(64, 64, 64, 4, dev, attn_backend="math")
+    ring = jb.modules.DistributedAttention.convert_to_jigsaw(serial, mesh, dev, ring=True, attn_backend="math")
+    for it in range(2):
+        x = torch.randn(2, 32 * world, 64, device=dev)
+        g = torch.randn(2, 32 * world, 64, device=dev)
+        xl = split(x, {1: mesh["row"]}).requires_grad_(True)
+        before = _lib.LAUNCHES
+        y = ring(xl)
+        assert _lib.LAUNCHES > before, "the peer-fetch kernels did not run"
+        y.backward(split(g, {1: mesh["row"]}))
+        symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        serial.zero_grad()
+        yr = serial(xr)
+        yr.backward(g)
+        assert_close(y.detach(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 1e-4, 1e-5)
+        assert_close(xl.grad, split(xr.grad, {1: mesh["row"]}), f"call {it}: input gradient", 1e-3, 1e-5)
+        for (n, p), q in zip(ring.named_parameters(), serial.parameters()):
+            assert_close(p.grad, q.grad, f"call {it}: gradient of {n}", 1e-3, 1e-5)
+        ring.zero_grad()
+
+
+@pytest.mark.multigpu(2)
+def test_ring_attention_peer_fetch_two_gpus():
+    run_distributed(_worker_ring_attention, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_ring_attention_peer_fetch_four_gpus():
+    run_distributed(_worker_ring_attention, 4, backend="nccl", timeout=300)
