@@ -1,4 +1,4 @@
-"""Secondary benchmark workloads: the Vision Transformer and the 3-D encoder-decoder, for this
+"""Secondary benchmark workloads: the Vision Transformer, Swin and the 3-D encoder-decoder, for this
 framework and for the unmodified reference (``--impl reference``, from ``baseline/_ref``).
 
 Both arms build the *same* architecture from their own public layer API (the two APIs share
@@ -13,6 +13,9 @@ backward, optimizer) on synthetic data under bf16 autocast, time on the device w
 Configurations (``--scale small`` shrinks depth / width for quick runs):
   vit     24 blocks, width 1024, 16 heads, MLP 4096, 1024x1024 image, patch 16 (4096 tokens), batch 8,
           4 input channels, 1000-class cross-entropy; mesh row x col = {1: 1x1, 2: 1x2, 4: 2x2, 8: 4x2}
+  swin    1536^2 image, patch 4 (384^2 tokens), widths 128-256-512-1024, depths 2-2-18-2, heads 4-8-16-32,
+          window 16 (the largest window that divides a stage's tile), 19-class map at 1/4 resolution, batch 2;
+          replicated weights, tiles sh x sw = {1: 1x1, 2: 2x1, 4: 2x2, 8: 4x2}
   unet3d  channels 1-32-64-128, stride-2 Conv3d / ConvTranspose3d, GroupNorm(8) + GELU, BCE,
           volume 128^3 (256^3 with --scale full); mesh sh x sw = {1: 1x1, 2: 2x1, 4: 2x2, 8: 4x2}
 """
@@ -116,6 +119,133 @@ def build_vit(lib, n, dev, scale):
     return model, loss_fn, x, y, desc, batch
 
 
+# ----------------------------------------------------------------------------- Swin (either API)
+def _windows(x, ws):
+    b, h, w, c = x.shape
+    return x.view(b, h // ws, ws, w // ws, ws, c).permute(0, 1, 3, 2, 4, 5).reshape(b, (h // ws) * (w // ws), ws * ws, c)
+
+
+def _unwindows(x, ws, h, w):
+    b, _, _, c = x.shape
+    return x.view(b, h // ws, w // ws, ws, ws, c).permute(0, 1, 3, 2, 4, 5).reshape(b, h, w, c)
+
+
+def _shift_mask(h, w, ws, shift, sh, sw):
+    def region(local, group):
+        g = group.rank() * local + torch.arange(local)
+        total = group.size() * local
+        return (g >= total - ws).long() + (g >= total - shift).long()
+
+    label = region(h, sh)[:, None] * 3 + region(w, sw)[None, :]
+    win = _windows(label[None, :, :, None].float(), ws)[0, :, :, 0]
+    return torch.zeros(win.shape[0], ws * ws, ws * ws).masked_fill(win[:, :, None] != win[:, None, :], -100.0)
+
+
+class SwinBlock(nn.Module):
+    def __init__(self, lib, mesh, dev, dim, heads, tile, ws, shift):
+        super().__init__()
+        sh, sw = mesh["sh"], mesh["sw"]
+        self.tile, self.ws, self.heads, self.shift = tile, ws, heads, shift
+        self.norm1, self.norm2 = nn.LayerNorm(dim, device=dev), nn.LayerNorm(dim, device=dev)
+        self.qkv, self.proj = nn.Linear(dim, 3 * dim, device=dev), nn.Linear(dim, dim, device=dev)
+        self.fc1, self.fc2 = nn.Linear(dim, 4 * dim, device=dev), nn.Linear(4 * dim, dim, device=dev)
+        self.bias = nn.Parameter(torch.zeros(heads, ws * ws, ws * ws, device=dev))
+        mask = _shift_mask(tile[0], tile[1], ws, shift, sh, sw) if shift else torch.zeros(1, ws * ws, ws * ws)
+        self.register_buffer("mask", mask.to(dev), persistent=False)
+        if shift:
+            M = lib.modules
+            self.roll_in = M.DistributedRoll((-shift, -shift), (1, 2), (1, 2), (sh, sw), dev)
+            self.roll_out = M.DistributedRoll((shift, shift), (1, 2), (1, 2), (sh, sw), dev)
+
+    def forward(self, x):
+        h, w = self.tile
+        y = self.norm1(x)
+        if self.shift:
+            y = self.roll_in(y.contiguous())
+        win = _windows(y, self.ws)
+        b, nw, n, c = win.shape
+        qkv = self.qkv(win).view(b, nw, n, 3, self.heads, c // self.heads).permute(3, 0, 1, 4, 2, 5)
+        bias = (self.bias[None] + self.mask[:, None]).to(qkv.dtype)
+        att = torch.nn.functional.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2], attn_mask=bias)
+        y = _unwindows(self.proj(att.transpose(2, 3).reshape(b, nw, n, c)), self.ws, h, w)
+        if self.shift:
+            y = self.roll_out(y.contiguous())
+        x = x + y
+        return x + self.fc2(torch.nn.functional.gelu(self.fc1(self.norm2(x))))
+
+
+class Merge(nn.Module):
+    def __init__(self, dev, dim, out):
+        super().__init__()
+        self.norm, self.reduce = nn.LayerNorm(4 * dim, device=dev), nn.Linear(4 * dim, out, bias=False, device=dev)
+
+    def forward(self, x):
+        return self.reduce(self.norm(torch.cat([x[:, i::2, j::2] for i in (0, 1) for j in (0, 1)], dim=-1)))
+
+
+class Swin(nn.Module):
+    """Tiled Swin with replicated weights: plain torch layers whose parameters are marked replicated over
+    the tile groups and synchronised through the library (the pattern of the reference's Swin tutorial)."""
+
+    def __init__(self, lib, mesh, dev, image, patch, chans, dims, heads, depths, window, classes):
+        super().__init__()
+        self.lib = lib
+        sh, sw = mesh["sh"], mesh["sw"]
+        M = lib.modules
+        kw = dict(device=dev, spatial_group=(sh, sw), channel_group=mesh["col"])
+        self.embed = M.DistributedConv2d(chans, dims[0], kernel_size=patch, stride=patch, **kw)
+        tile = (image // patch // sh.size(), image // patch // sw.size())
+        layers = []
+        for i, (dim, hd, depth) in enumerate(zip(dims, heads, depths)):
+            ws = max(d for d in range(1, window + 1) if tile[0] % d == 0 and tile[1] % d == 0)
+            for j in range(depth):
+                layers.append(SwinBlock(lib, mesh, dev, dim, hd, tile, ws, 0 if j % 2 == 0 else ws // 2))
+            if i + 1 < len(dims):
+                layers.append(Merge(dev, dim, dims[i + 1]))
+                tile = (tile[0] // 2, tile[1] // 2)
+        self.layers = nn.Sequential(*layers)
+        self.norm = nn.LayerNorm(dims[-1], device=dev)
+        up = 2 ** (len(dims) - 1)
+        self.decode = M.DistributedConvTranspose2d(dims[-1], classes, kernel_size=up, stride=up, **kw)
+        live = [g for g in (sh, sw) if g.size() > 1]
+        if live:
+            for mod in [self.layers, self.norm]:
+                for p in mod.parameters():
+                    lib.parallel.mark_replicated(p, live)
+            lib.parallel.broadcast_replicas(self)
+
+    def forward(self, x):
+        synced = self.lib.parallel.synced_parameters(self)
+        if synced:
+            return torch.func.functional_call(self, synced, (x,))
+        z = self.embed(x).permute(0, 2, 3, 1).contiguous()
+        z = self.norm(self.layers(z)).permute(0, 3, 1, 2).contiguous()
+        return self.decode(z)
+
+
+def build_swin(lib, n, dev, scale):
+    sh, sw = TILES[n]
+    mesh = lib.make_process_mesh({"sh": sh, "sw": sw, "col": 1})
+    small = scale == "small"
+    image, patch, chans, classes, batch = (256 if small else 1536), 4, 3, 19, 2
+    dims, heads, depths, window = ((32, 64), (2, 4), (2, 2), 8) if small else ((128, 256, 512, 1024), (4, 8, 16, 32), (2, 2, 18, 2), 16)
+    torch.manual_seed(0)
+    model = Swin(lib, mesh, dev, image, patch, chans, dims, heads, depths, window, classes)
+    loss_fn = lib.modules.DistributedCrossEntropyLoss(None, (mesh["sh"], mesh["sw"]))
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(batch, chans, image, image, generator=g)
+    y = torch.randint(0, classes, (batch, image // patch, image // patch), generator=g)
+    h, w = image // sh, image // sw
+
+    def tile(t, f=1):
+        return t[..., mesh["sh"].rank() * h // f:(mesh["sh"].rank() + 1) * h // f,
+                 mesh["sw"].rank() * w // f:(mesh["sw"].rank() + 1) * w // f].contiguous()
+
+    desc = {"model": f"Swin {image}^2 patch {patch} dims {dims} depths {depths} window {window}, {classes}-class map at 1/{patch}",
+            "global_batch": batch, "seq_len": (image // patch) ** 2, "parallelism": f"sh{sh} x sw{sw}"}
+    return model, loss_fn, tile(x), tile(y, patch), desc, batch
+
+
 def build_unet3d(lib, n, dev, scale):
     sh, sw = TILES[n]
     mesh = lib.make_process_mesh({"sh": sh, "sw": sw, "col": 1})
@@ -155,7 +285,7 @@ def build_unet3d(lib, n, dev, scale):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", choices=("vit", "unet3d"), default="vit")
+    ap.add_argument("--config", choices=("vit", "swin", "unet3d"), default="vit")
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -174,7 +304,8 @@ def main() -> None:
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     lib = load(args.impl)
-    model, loss_fn, x, y, desc, batch = (build_vit if args.config == "vit" else build_unet3d)(lib, args.gpus, dev, args.scale)
+    builders = {"vit": build_vit, "swin": build_swin, "unet3d": build_unet3d}
+    model, loss_fn, x, y, desc, batch = builders[args.config](lib, args.gpus, dev, args.scale)
     x, y = x.to(dev), y.to(dev)
     if args.impl == "ours":
         from jigsaw_b200.optim import FusedAdam
