@@ -425,7 +425,7 @@ def _worker_ring_attention(rank, world):
     mesh = jb.make_process_mesh({"row": world, "col": 1})
     torch.manual_seed(0)
     serial = Attention(64, 64, 64, 4, dev, attn_backend="math")
-    ring = jb.modules.DistributedAttention.convert_to_jigsaw(serial, mesh, dev, ring=True, attn_backend="math")
+    ring = Attention.convert_to_jigsaw(serial, mesh, dev, ring=True, attn_backend="math")
     for it in range(2):
         x = torch.randn(2, 32 * world, 64, device=dev)
         g = torch.randn(2, 32 * world, 64, device=dev)
