@@ -182,14 +182,30 @@ def main() -> None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         last = 0.0
         e0.record()
-        for _ in range(n_steps):
-            if e2e and run is not None:
-                x_dev.copy_(x_host, non_blocking=True)
-                y_dev.copy_(y_host, non_blocking=True)
+        if e2e and run is not None:
+            # The framework's input pipeline: every step's inputs travel from pinned host memory on a side
+            # stream while the previous step computes (DevicePrefetcher), land in the graph's static inputs,
+            # and every step's loss is read back to the host, one step behind the launch so that the read
+            # does not stall the next launch.
+            from jigsaw_b200.data import DevicePrefetcher
+
+            host_loss = [torch.empty((), dtype=run.outputs.dtype).pin_memory() for _ in range(2)]
+            done = [torch.cuda.Event(), torch.cuda.Event()]
+            sizes["loss"] = run.outputs.element_size()
+            batches = ((x_host, y_host) for _ in range(n_steps))
+            for i, (xb, yb) in enumerate(DevicePrefetcher(batches, dev, depth=2)):
+                x_dev.copy_(xb)
+                y_dev.copy_(yb)
                 out = run.replay()
-                sizes["loss"] = out.element_size()
-                last = float(out.item())
-            elif e2e:
+                host_loss[i & 1].copy_(out, non_blocking=True)
+                done[i & 1].record()
+                if i > 0:
+                    done[(i - 1) & 1].synchronize()
+                    last = float(host_loss[(i - 1) & 1].item())
+            done[(n_steps - 1) & 1].synchronize()
+            last = float(host_loss[(n_steps - 1) & 1].item())
+        for _ in range(0 if (e2e and run is not None) else n_steps):
+            if e2e:
                 x = x_host.to(dev, non_blocking=True)
                 y = y_host.to(dev, non_blocking=True)
                 out = step(x, y)

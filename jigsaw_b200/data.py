@@ -88,6 +88,12 @@ class DevicePrefetcher:
                 if not torch.is_tensor(t):
                     out.append(t)
                     continue
+                if t.is_pinned():                      # already page-locked: copy straight from it
+                    while len(stage) <= j:
+                        stage.append(t)
+                    out.append(t.to(self.device, non_blocking=True))
+                    self.bytes_copied += t.numel() * t.element_size()
+                    continue
                 if j >= len(stage) or stage[j].shape != t.shape or stage[j].dtype != t.dtype:
                     buf = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                     stage[j:j + 1] = [buf]
