@@ -12,15 +12,14 @@ namespace jb {
 // ------------------------------------------------------------------------------------------
 // Merge the result (o2, l2) of a new key/value chunk into the running state (o1 fp32, l1):
 //   w = sigmoid(l2 - l1);  o1 += w (o2 - o1);  l1 = max(l1, l2) + log1p(exp(-|l1 - l2|))
-// One warp per row (a query of one head); rows = b * h * s.
+// rows = b * h * s (a query of one head).
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) merge_kernel(float* __restrict__ o1, float* __restrict__ l1,
                                                     const void* __restrict__ o2, int o2_bf16,
                                                     const float* __restrict__ l2, long long rows, int d) {
-  // one thread per four consecutive features (d % 4 == 0); the thread of a row's first vector also
-  // updates the row's log-sum-exp.  Every thread of a row reads l1 before any of them writes it: the
-  // write happens after a warp-level barrier and rows never straddle... a row may span several warps
-  // only when d > 128, which the launcher routes to the scalar variant below.
+  // One thread per four consecutive features; the thread of a row's first vector also updates the
+  // row's log-sum-exp.  All threads of a row sit in one warp (the launcher only picks this variant when
+  // d / 4 divides 32), so every reader of l1[row] has passed the warp barrier before the writer stores.
   const int vec_per_row = d >> 2;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long row = idx / vec_per_row;
