@@ -10,7 +10,9 @@ from collections.abc import Sequence
 import torch.distributed as dist
 
 
-def _n(g: "dist.ProcessGroup | None") -> int:
+def _n(g: "dist.ProcessGroup | int | None") -> int:
+    if isinstance(g, int):
+        return g
     return 1 if g is None else g.size()
 
 

@@ -1,0 +1,69 @@
+"""Small runtime utilities on CPU: buffer cache, activation offloader (pass-through without CUDA),
+autocast policy helpers, config checks, shard descriptions."""
+
+import pytest
+import torch
+
+
+def test_preallocated_buffers_are_cached_per_call_site():
+    from jigsaw_b200._core import buffers
+
+    buffers.clear_preallocated_buffers()
+
+    def site(shape, **kw):
+        return buffers.preallocated_buffer(shape, torch.float32, "cpu", depth=1, **kw)
+
+    a = site((4, 8))
+    a.fill_(3.0)
+    b = site((4, 8))
+    assert a.data_ptr() == b.data_ptr() and float(b.sum()) == 96.0         # same line -> same storage, contents kept
+    c = site((2, 8), zero=True)
+    assert c.data_ptr() == a.data_ptr() and float(c.sum()) == 0.0
+    big = site((16, 16))
+    assert big.numel() == 256                                               # grows when needed
+    other = buffers.preallocated_buffer((4, 8), torch.float32, "cpu", index=1)
+    assert other.data_ptr() != big.data_ptr()
+    buffers.clear_preallocated_buffers()
+    assert not buffers._cache
+
+
+def test_offloader_is_transparent_on_cpu():
+    from jigsaw_b200._core.offload import ActivationOffloader
+
+    off = ActivationOffloader("cpu")
+    t = torch.randn(5)
+    assert off.offload(t) is t
+    off.wait_offloads()
+    dev, ev = off.prefetch(t)
+    assert dev is t and ev is None and off.consume(dev, ev) is t
+
+
+def test_autocast_helpers():
+    from jigsaw_b200._core import autocast as A
+
+    x, w = torch.randn(3, dtype=torch.bfloat16), torch.randn(3)
+    assert A.autocast_dtype("cpu") is None
+    assert A.cast_to_autocast_dtype(x, None, w) == (x, None, w)
+    assert A.promote_to_fp32_under_autocast(x)[0].dtype == torch.bfloat16
+    assert A.resolve_matmul_dtype(torch.device("cpu"), x, w) == torch.float32
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        assert A.autocast_dtype("cpu") == torch.bfloat16
+        cx, none, cw = A.cast_to_autocast_dtype(x, None, w)
+        assert cx.dtype == cw.dtype == torch.bfloat16 and none is None
+        px, pd = A.promote_to_fp32_under_autocast(x, torch.randn(2, dtype=torch.float64))
+        assert px.dtype == torch.float32 and pd.dtype == torch.float64
+        assert A.resolve_matmul_dtype(torch.device("cpu"), w, w) == torch.bfloat16
+
+
+def test_config_check_and_shard_repr():
+    from jigsaw_b200._core.config import check_config
+    from jigsaw_b200._core.shard_repr import shard_repr
+
+    class Cfg:
+        _layer_key = {"kernel_size": (3, 3), "bias": True}
+
+    check_config(Cfg(), {"kernel_size": (3, 3), "bias": True})
+    with pytest.raises(ValueError, match="different layer"):
+        check_config(Cfg(), {"kernel_size": (5, 5)})
+    assert shard_repr(row=None, col=4) == "row=1, col=4"
+    assert shard_repr(spatial=(None, 2)) == "spatial=(1, 2)"
