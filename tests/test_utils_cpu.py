@@ -67,3 +67,30 @@ def test_config_check_and_shard_repr():
         check_config(Cfg(), {"kernel_size": (5, 5)})
     assert shard_repr(row=None, col=4) == "row=1, col=4"
     assert shard_repr(spatial=(None, 2)) == "spatial=(1, 2)"
+
+
+def test_ring_attention_config_validation():
+    from jigsaw_b200.modules.attention import Offload, RingAttentionConfig, SaveScope, SendOp
+
+    cfg = RingAttentionConfig(device="cpu", send_op="hybrid", intra_size=2, save_scope="local")
+    assert cfg.send_op is SendOp.HYBRID and cfg.save_scope is SaveScope.LOCAL
+    with pytest.raises(ValueError, match="must be one of"):
+        RingAttentionConfig(device="cpu", send_op="zigzag")
+    with pytest.raises(ValueError, match="save_scope=GLOBAL"):
+        RingAttentionConfig(device="cuda", offload=Offload.CPU, save_scope="local")
+    with pytest.raises(ValueError, match="CUDA"):
+        RingAttentionConfig(device="cpu", offload="cpu")
+    with pytest.raises(ValueError, match="intra_size"):
+        RingAttentionConfig(device="cpu", send_op="hybrid", intra_size=0)
+
+
+def test_chunk_owner_schedules_visit_every_chunk_once():
+    from jigsaw_b200.modules.attention import SendOp
+    from jigsaw_b200.modules.attention._ring import chunk_owner
+
+    for op, P, A in ((SendOp.RING, 6, 1), (SendOp.BROADCAST, 5, 1), (SendOp.HYBRID, 8, 4), (SendOp.HYBRID, 6, 2)):
+        for p in range(P):
+            owners = [chunk_owner(op, p, s, P, A) for s in range(P)]
+            assert sorted(owners) == list(range(P)), (op, P, A, p, owners)
+    with pytest.raises(ValueError):
+        chunk_owner(SendOp.HYBRID, 0, 0, 6, 4)
