@@ -275,6 +275,19 @@ class DistributedAttention(torch.nn.Module):
         if attn_mask is not None and (self.ring or self.ulysses):
             raise NotImplementedError("attn_mask is supported only without ring / ulysses sequence parallelism")
         core = attn_core_dtype(x)
+        p = self.dropout_p if self.training else 0.0
+        if self.ulysses and not self.ulysses_intra_size and not self.qk_norm and x.is_cuda and type(self.qkv) is torch.nn.Linear:
+            from ...ops import ulysses_fused
+            from ._ulysses import heads_to_seq
+
+            # projection with the sequence -> head exchange inside its epilogue: (3, b, s, h / P, d)
+            full = ulysses_fused.maybe_fused_ulysses_qkv(x, self.qkv.weight, self.spatial_group, self.heads, self.head_dim)
+            if full is not None:
+                q, k, v = (t.transpose(-3, -2) for t in full.to(core).unbind(0))
+                out = _dense_attention(q, k, v, self.scale, p, self.attn_backend, None, True).transpose(-3, -2)
+                out = heads_to_seq(out.contiguous(), self.spatial_group)
+                out = out.reshape(*x.shape[:-1], self.heads * self.head_dim).to(x.dtype)
+                return self.head_concat(out)
         qkv = _split_heads(self.qkv(x), self.heads, bshd=self.ulysses)
         if self.qk_norm:
             q, k, v = qkv.unbind(0)
@@ -282,7 +295,6 @@ class DistributedAttention(torch.nn.Module):
             qkv = torch.stack((q, k, v))
         else:
             qkv = qkv.to(core)
-        p = self.dropout_p if self.training else 0.0
         if self.ring:
             q, k, v = (t.contiguous() for t in qkv.unbind(0))
             send_x = self.config.send_in_forward is SendForward.X and isinstance(self.qkv, torch.nn.Linear)

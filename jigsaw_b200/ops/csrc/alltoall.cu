@@ -172,3 +172,37 @@ extern "C" int jb_peer_fetch(const void* src, void* dst, long long nbytes, const
       replay, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// Wait (bounded) until every given local flag word has reached the epoch: the consumer side of a push
+// whose data is then read by ordinary kernels of the same stream.
+namespace jb {
+__global__ void wait_flags_kernel(const uint32_t* f0, const uint32_t* f1, const uint32_t* f2, const uint32_t* f3,
+                                  const uint32_t* f4, const uint32_t* f5, const uint32_t* f6, const uint32_t* f7,
+                                  uint32_t epoch, uint32_t stride, const uint32_t* replay, int* status) {
+  const uint32_t* f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+  const uint32_t* mine = f[threadIdx.x & 7];
+  if (threadIdx.x >= 8 || mine == nullptr) return;
+  const uint32_t want = live_epoch(epoch, stride, replay);
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(v - want) >= 0) break;
+    if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+      if (status) atomicCAS(status, JB_OK, JB_ERR_FLAG_TIMEOUT);
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+}  // namespace jb
+
+extern "C" int jb_wait_flags(const void* const* flags, int n, unsigned int epoch, unsigned int stride,
+                             const unsigned int* replay, int* status, void* stream) {
+  if (n < 0 || n > 8) return -1;
+  const uint32_t* f[8] = {};
+  for (int i = 0; i < n; ++i) f[i] = static_cast<const uint32_t*>(flags[i]);
+  jb::wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7],
+                                                                         epoch, stride, replay, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

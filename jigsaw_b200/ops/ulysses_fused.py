@@ -1,0 +1,134 @@
+"""Ulysses attention: the sequence -> head exchange fused into the QKV projection.
+
+The projection ``x @ W_qkv.T`` of a sequence shard produces, for every head group ``p``, the
+columns that rank ``p`` needs.  With the rows of ``W_qkv`` ordered (head group, q|k|v, head, d)
+those columns are one contiguous part, and the scatter epilogue of the tcgen05 GEMM
+(``csrc/gemm.cu``) stores each output tile straight into rank ``p``'s inbox as it is produced: the
+all-to-all rides inside the GEMM, tile by tile, and the projected ``(b, s / P, 3 h d)`` tensor is
+never written locally.  The receiver waits for the senders' flags and views its inbox as
+``(3, b, s, h / P, d)``.  The backward pass sends the gradient back with the peer-memory
+all-to-all kernel and runs the two remaining products on the same GEMM kernel.
+
+Reference parity: the projection followed by ``all_to_all_single`` in
+jigsaw/modules/attention/_functional/ulysses.py:19-63.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, symm
+from .linear_fused import _HEADER, _staging_block, gemm
+
+
+def head_group_major(w: torch.Tensor, parts: int, heads: int, head_dim: int) -> torch.Tensor:
+    """Rows of a qkv weight ``(3 h d, in)`` reordered from (q|k|v, head, d) to
+    (head group, q|k|v, head in group, d)."""
+    k = w.shape[1]
+    return w.view(3, parts, heads // parts, head_dim, k).permute(1, 0, 2, 3, 4).reshape(3 * heads * head_dim, k)
+
+
+def inbox_to_qkv(inbox: torch.Tensor, parts: int, b: int, sl: int, hl: int, d: int) -> torch.Tensor:
+    """``inbox`` holds one slab per source rank, each ``(b * sl, 3 * hl * d)``; returns the gathered
+    ``(3, b, parts * sl, hl, d)`` (source rank ``r`` owns sequence block ``r``)."""
+    t = inbox.view(parts, b, sl, 3, hl, d).permute(3, 1, 0, 2, 4, 5)
+    return t.reshape(3, b, parts * sl, hl, d)
+
+
+class _UlyssesQKV(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, group: Any, heads: int, head_dim: int) -> torch.Tensor:
+        L, dev = _lib.lib(), x.device
+        ar = symm.arena(dev)
+        P, me = group.size(), group.rank()
+        ranks = dist.get_process_group_ranks(group)
+        K = x.shape[-1]
+        b, sl = x.shape[0], x.shape[1]
+        M = b * sl
+        hl = heads // P
+        cols = 3 * hl * head_dim
+        xb = x.reshape(M, K)
+        xb = xb if xb.dtype == torch.bfloat16 else xb.to(torch.bfloat16)
+        xb = xb if xb.is_contiguous() else xb.contiguous()
+        wp = head_group_major(w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16), P, heads, head_dim).contiguous()
+        slab = M * cols * 2
+        blk = _staging_block(ar, ("ulysses_qkv", dev.index, M, cols, P), _HEADER + P * slab)
+        epoch = ar.next_own_epoch(blk)
+        stride = ar.capture_stride or 0
+        replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+        st = _lib.stream_ptr()
+        c_part = (ctypes.c_void_p * 8)()
+        for i, r in enumerate(ranks):
+            c_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER + me * slab
+        rc = L.jb_gemm_bf16_scatter(ctypes.c_void_p(xb.data_ptr()), ctypes.c_void_p(wp.data_ptr()), c_part, P, cols, M, K,
+                                    xb.stride(0), wp.stride(0), 0, 0, _lib.sm_count(dev.index),
+                                    ctypes.c_void_p(ar.status.data_ptr()), st)
+        flags = (ctypes.c_void_p * 8)()
+        waits = (ctypes.c_void_p * 8)()
+        n = 0
+        for i, r in enumerate(ranks):
+            if i != me:
+                flags[n] = blk.peer_ptr(r) + 4 * me
+                waits[n] = blk.ptr + 4 * i
+                n += 1
+        if rc == 0:
+            rc = L.jb_publish(flags, n, epoch, stride, replay, st)
+        if rc == 0:
+            rc = L.jb_wait_flags(waits, n, epoch, stride, replay, ctypes.c_void_p(ar.status.data_ptr()), st)
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher ulysses_qkv failed with code {rc}")
+        _lib.count_launches(3)
+        inbox = blk.tensor[_HEADER:_HEADER + P * slab].view(torch.bfloat16)
+        out = inbox_to_qkv(inbox, P, b, sl, hl, head_dim).contiguous()      # copy out: the block is reused two calls later
+        ctx.save_for_backward(xb, wp)
+        ctx.meta = (group, heads, head_dim, x.shape, x.dtype, w.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        from .._core.collectives import all_to_all_dims
+
+        xb, wp = ctx.saved_tensors
+        group, heads, d, x_shape, x_dtype, w_dtype = ctx.meta
+        P = group.size()
+        b, sl = x_shape[0], x_shape[1]
+        g = g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)
+        # (3, b, s, h / P, d) -> (3, b, s / P, h, d): the inverse exchange (one peer-memory kernel)
+        back = all_to_all_dims(g.contiguous(), group, split_dim=-3, cat_dim=-2)
+        hl = heads // P
+        # columns in the order of wp: (head group, q|k|v, head in group, d)
+        g2 = back.view(3, b, sl, P, hl, d).permute(1, 2, 3, 0, 4, 5).reshape(b * sl, 3 * heads * d).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(g2, wp, b_mn=True).view(x_shape).to(x_dtype)
+        if ctx.needs_input_grad[1]:
+            dwp = gemm(g2, xb, a_mn=True, b_mn=True, out_dtype=torch.float32)          # rows ordered like wp
+            K = dwp.shape[1]
+            dw = dwp.view(P, 3, hl, d, K).permute(1, 0, 2, 3, 4).reshape(3 * heads * d, K).to(w_dtype)
+        return dx, dw, None, None, None
+
+
+def maybe_fused_ulysses_qkv(x: torch.Tensor, w: torch.Tensor, group: Any, heads: int, head_dim: int) -> torch.Tensor | None:
+    """``seq_to_heads(split_heads(x @ w.T))`` as ``(3, b, s, heads / P, head_dim)`` in bf16 with the
+    exchange fused into the GEMM epilogue, or ``None`` when that does not apply.  ``x`` is
+    ``(b, s / P, in)``, ``w`` is ``(3 * heads * head_dim, in)``."""
+    if group is None or not x.is_cuda or x.dim() != 3 or w.dim() != 2 or x.numel() == 0:
+        return None
+    P = group.size()
+    bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    if not bf16 or P < 2 or P > 8 or heads % P or w.shape[0] != 3 * heads * head_dim:
+        return None
+    K = x.shape[-1]
+    cols = 3 * (heads // P) * head_dim
+    M = x.shape[0] * x.shape[1]
+    if K % 64 or cols % 64 or M % 8 or torch._C._functorch.is_batchedtensor(x):
+        return None
+    if x.dtype not in (torch.float32, torch.bfloat16) or w.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    return _UlyssesQKV.apply(x, w, group, heads, head_dim)

@@ -441,7 +441,7 @@ def _worker_ring_attention(rank, world):
         yr.backward(g)
         # on CUDA the attention core computes in half precision even for fp32 inputs: compare at that level
         tol = 2e-2
-        assert_close(y.detach(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 0.0, tol * float(yr.abs().max()))
+        assert_close(y.detach(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 0.0, tol * float(yr.detach().abs().max()))
         assert_close(xl.grad, split(xr.grad, {1: mesh["row"]}), f"call {it}: input gradient", 0.0, tol * float(xr.grad.abs().max()))
         for (n, p), q in zip(ring.named_parameters(), serial.parameters()):
             assert_close(p.grad, q.grad, f"call {it}: gradient of {n}", 0.0, tol * float(q.grad.abs().max()))
@@ -456,3 +456,54 @@ def test_ring_attention_peer_fetch_two_gpus():
 @pytest.mark.multigpu(4)
 def test_ring_attention_peer_fetch_four_gpus():
     run_distributed(_worker_ring_attention, 4, backend="nccl", timeout=300)
+
+
+def _worker_ulysses_qkv(rank, world):
+    """Ulysses attention under bf16 autocast: the sequence -> head exchange rides in the epilogue of the
+    QKV projection GEMM (tiles stored into the destination ranks' inboxes), against the undivided
+    attention layer: output and every gradient."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import split
+    from jigsaw_b200.modules.attention import Attention
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank) if torch.cuda.is_available() else torch.device("cpu")
+    mesh = jb.make_process_mesh({"row": world, "col": 1})
+    torch.manual_seed(0)
+    serial = Attention(128, 256, 128, 4, dev, attn_backend="math")
+    uly = Attention.convert_to_jigsaw(serial, mesh, dev, ring=False, ulysses=True, attn_backend="math")
+    for it in range(3):
+        x = torch.randn(2, 96 * world, 128, device=dev)
+        g = torch.randn(2, 96 * world, 128, device=dev)
+        xl = split(x, {1: mesh["row"]}).requires_grad_(True)
+        before = _lib.LAUNCHES
+        with torch.autocast(dev.type, dtype=torch.bfloat16):
+            y = uly(xl)
+        if dev.type == "cuda":
+            assert _lib.LAUNCHES >= before + 3, "the fused projection + exchange did not run"
+        y.float().backward(split(g, {1: mesh["row"]}))
+        if dev.type == "cuda":
+            symm.arena(dev).check_status()
+        xr = x.clone().requires_grad_(True)
+        serial.zero_grad()
+        yr = serial(xr)
+        yr.backward(g)
+        tol = 3e-2
+        assert_close(y.detach().float(), split(yr.detach(), {1: mesh["row"]}), f"call {it}: output", 0.0, tol * float(yr.detach().abs().max()))
+        assert_close(xl.grad, split(xr.grad, {1: mesh["row"]}), f"call {it}: input gradient", 0.0, tol * float(xr.grad.abs().max()))
+        for (n, p), q in zip(uly.named_parameters(), serial.parameters()):
+            assert_close(p.grad, q.grad, f"call {it}: gradient of {n}", 0.0, tol * float(q.grad.abs().max()))
+        uly.zero_grad()
+
+
+@pytest.mark.multigpu(2)
+def test_ulysses_fused_projection_two_gpus():
+    run_distributed(_worker_ulysses_qkv, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_ulysses_fused_projection_four_gpus():
+    run_distributed(_worker_ulysses_qkv, 4, backend="nccl", timeout=300)
