@@ -39,6 +39,18 @@ def inbox_to_qkv(inbox: torch.Tensor, parts: int, b: int, sl: int, hl: int, d: i
     return t.reshape(3, b, parts * sl, hl, d)
 
 
+def from_head_group_major(wp: torch.Tensor, parts: int, heads: int, head_dim: int) -> torch.Tensor:
+    """Inverse of :func:`head_group_major` (used for the weight gradient)."""
+    k = wp.shape[1]
+    return wp.view(parts, 3, heads // parts, head_dim, k).permute(1, 0, 2, 3, 4).reshape(3 * heads * head_dim, k)
+
+
+def grad_columns(back: torch.Tensor, parts: int, b: int, sl: int, hl: int, d: int) -> torch.Tensor:
+    """Gradient of the local projection ``(3, b, sl, h, d)`` as a matrix ``(b * sl, 3 h d)`` whose
+    columns follow the row order of :func:`head_group_major`."""
+    return back.view(3, b, sl, parts, hl, d).permute(1, 2, 3, 0, 4, 5).reshape(b * sl, 3 * parts * hl * d)
+
+
 class _UlyssesQKV(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, x: torch.Tensor, w: torch.Tensor, group: Any, heads: int, head_dim: int) -> torch.Tensor:
@@ -100,15 +112,13 @@ class _UlyssesQKV(torch.autograd.Function):
         # (3, b, s, h / P, d) -> (3, b, s / P, h, d): the inverse exchange (one peer-memory kernel)
         back = all_to_all_dims(g.contiguous(), group, split_dim=-3, cat_dim=-2)
         hl = heads // P
-        # columns in the order of wp: (head group, q|k|v, head in group, d)
-        g2 = back.view(3, b, sl, P, hl, d).permute(1, 2, 3, 0, 4, 5).reshape(b * sl, 3 * heads * d).contiguous()
+        g2 = grad_columns(back, P, b, sl, hl, d).contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gemm(g2, wp, b_mn=True).view(x_shape).to(x_dtype)
         if ctx.needs_input_grad[1]:
             dwp = gemm(g2, xb, a_mn=True, b_mn=True, out_dtype=torch.float32)          # rows ordered like wp
-            K = dwp.shape[1]
-            dw = dwp.view(P, 3, hl, d, K).permute(1, 0, 2, 3, 4).reshape(3 * heads * d, K).to(w_dtype)
+            dw = from_head_group_major(dwp, P, heads, d).to(w_dtype)
         return dx, dw, None, None, None
 
 

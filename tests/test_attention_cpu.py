@@ -139,3 +139,39 @@ def test_ulysses_and_hierarchical():
 
 def test_head_parallel_and_window_attention():
     run_distributed(_worker_heads, 4)
+
+
+@pytest.mark.parametrize("parts", [2, 4])
+def test_fused_ulysses_projection_layouts(parts):
+    """Layout algebra of the projection with the exchange in its epilogue, with the ranks emulated by a
+    loop: column part ``p`` of ``x_r @ head_group_major(w).T`` is what rank ``r`` stores into rank ``p``'s
+    inbox; the inbox must read as the head shard of the gathered q, k, v, and the helpers of the
+    backward pass must reproduce autograd's gradients of the unfused formulation."""
+    from jigsaw_b200.ops.ulysses_fused import from_head_group_major, grad_columns, head_group_major, inbox_to_qkv
+
+    torch.manual_seed(0)
+    b, sl, heads, d, K = 2, 3, 8, 4, 5
+    hl, cols = heads // parts, 3 * (heads // parts) * d
+    w = torch.randn(3 * heads * d, K, dtype=torch.float64, requires_grad=True)
+    xs = [torch.randn(b, sl, K, dtype=torch.float64, requires_grad=True) for _ in range(parts)]
+    # unfused formulation: project, split heads, gather the sequence, keep this rank's heads
+    full = torch.cat([(x @ w.T).view(b, sl, 3, heads, d).permute(2, 0, 1, 3, 4) for x in xs], dim=2)
+    wp = head_group_major(w.detach(), parts, heads, d)
+    assert torch.equal(from_head_group_major(wp, parts, heads, d), w.detach())
+    slabs = [(x.detach().reshape(b * sl, K) @ wp.T) for x in xs]              # what each source rank's GEMM produces
+    gs = []
+    for p in range(parts):
+        inbox = torch.stack([s[:, p * cols:(p + 1) * cols] for s in slabs]).contiguous()
+        out = inbox_to_qkv(inbox, parts, b, sl, hl, d)
+        ref = full[..., p * hl:(p + 1) * hl, :]
+        assert torch.allclose(out, ref.detach(), atol=1e-12), f"forward layout of rank {p}"
+        gs.append(torch.randn_like(out))
+    g_full = torch.cat(gs, dim=3)                                             # (3, b, s, heads, d)
+    grads = torch.autograd.grad(full, [w, *xs], g_full)
+    dw = torch.zeros_like(wp)
+    for r, x in enumerate(xs):
+        back = g_full[:, :, r * sl:(r + 1) * sl].contiguous()                 # what the inverse exchange returns to rank r
+        g2 = grad_columns(back, parts, b, sl, hl, d)
+        assert torch.allclose((g2 @ wp).view(b, sl, K), grads[1 + r], atol=1e-12), f"input gradient of rank {r}"
+        dw += g2.T @ x.detach().reshape(b * sl, K)
+    assert torch.allclose(from_head_group_major(dw, parts, heads, d), grads[0], atol=1e-12), "weight gradient"
