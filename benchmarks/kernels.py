@@ -51,8 +51,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--small", action="store_true", help="a few hundred MB per case (profiler captures)")
     args = ap.parse_args()
-    import jigsaw_b200 as jb
-    from jigsaw_b200.ops import _lib, conv_fused, linear_fused, loss_fused, norm_fused, symm
+    import jigsaw_b200  # noqa: F401  (package import registers the kernel library path)
+    from jigsaw_b200.ops import _lib, linear_fused, loss_fused, norm_fused, symm
     from jigsaw_b200.optim import FusedAdam
 
     dev = torch.device("cuda", 0)

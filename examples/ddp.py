@@ -23,7 +23,7 @@ import tempfile
 import torch
 import torch.distributed as dist
 
-from _common import denoising_batch, setup, shard, steps_flag
+from _common import setup, shard, steps_flag
 from vit import CFG, build
 
 import jigsaw_b200 as jb

@@ -285,6 +285,11 @@ class DistributedAttention(torch.nn.Module):
             if full is not None:
                 q, k, v = (t.transpose(-3, -2) for t in full.to(core).unbind(0))
                 out = _dense_attention(q, k, v, self.scale, p, self.attn_backend, None, True).transpose(-3, -2)
+                if type(self.head_concat) is torch.nn.Linear:
+                    # output projection whose operand loads do the head -> sequence exchange
+                    y = ulysses_fused.maybe_fused_ulysses_out(out, self.head_concat.weight, self.head_concat.bias, self.spatial_group)
+                    if y is not None:
+                        return y
                 out = heads_to_seq(out.contiguous(), self.spatial_group)
                 out = out.reshape(*x.shape[:-1], self.heads * self.head_dim).to(x.dtype)
                 return self.head_concat(out)

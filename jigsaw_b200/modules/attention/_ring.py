@@ -29,7 +29,7 @@ from typing import Any
 import torch
 import torch.distributed as dist
 
-from ..._core.comm import CommOp, sparse_exchange
+from ..._core.comm import sparse_exchange
 from ._config import Offload, RingAttentionConfig, SaveScope, SendBackward, SendForward, SendOp
 from ._cores import chunk_seed, merge_chunks, select_core
 

@@ -175,3 +175,32 @@ def test_fused_ulysses_projection_layouts(parts):
         assert torch.allclose((g2 @ wp).view(b, sl, K), grads[1 + r], atol=1e-12), f"input gradient of rank {r}"
         dw += g2.T @ x.detach().reshape(b * sl, K)
     assert torch.allclose(from_head_group_major(dw, parts, heads, d), grads[0], atol=1e-12), "weight gradient"
+
+
+@pytest.mark.parametrize("parts", [2, 4])
+def test_fused_ulysses_output_projection_layouts(parts):
+    """Layout algebra of the output projection whose operand loads do the head -> sequence exchange,
+    ranks emulated by a loop: k-block part ``p`` of rank ``r``'s A operand is entry ``r`` of rank ``p``'s
+    staging block; in the backward pass column part ``p`` of ``gy_r @ W`` is slab ``r`` of rank ``p``'s inbox."""
+    from jigsaw_b200.ops.ulysses_fused import stage_for_owners
+
+    torch.manual_seed(0)
+    b, sl, hl, d, N = 2, 3, 2, 4, 6
+    s, kp = parts * sl, hl * d
+    w = torch.randn(N, parts * kp, dtype=torch.float64)
+    os_ = [torch.randn(b, hl, s, d, dtype=torch.float64).transpose(1, 2).requires_grad_(True) for _ in range(parts)]   # (b, s, hl, d) views
+    ys = []
+    for r in range(parts):                                                    # unfused formulation on rank r
+        mine = torch.cat([o[:, r * sl:(r + 1) * sl] for o in os_], dim=2)     # heads_to_seq: (b, sl, h, d)
+        ys.append(mine.reshape(b * sl, parts * kp) @ w.T)
+    staged = [stage_for_owners(o.detach(), parts).contiguous() for o in os_]
+    for r in range(parts):
+        a = torch.cat([staged[p][r].reshape(b * sl, kp) for p in range(parts)], dim=1)
+        assert torch.allclose(a @ w.T, ys[r].detach(), atol=1e-12), f"forward operand of rank {r}"
+    gys = [torch.randn_like(y) for y in ys]
+    grads = torch.autograd.grad(ys, os_, gys)
+    full = [g @ w for g in gys]                                               # (M, P * kp) on every source rank
+    for p in range(parts):
+        inbox = torch.stack([f[:, p * kp:(p + 1) * kp] for f in full]).contiguous()
+        do = inbox.view(parts, b, sl, hl, d).permute(1, 0, 2, 3, 4).reshape(b, s, hl, d)
+        assert torch.allclose(do, grads[p], atol=1e-12), f"gradient of rank {p}'s heads"

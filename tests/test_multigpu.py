@@ -468,8 +468,9 @@ def _worker_ulysses_qkv(rank, world):
     import jigsaw_b200 as jb
     from dist_utils import split
     from jigsaw_b200.modules.attention import Attention
-    from jigsaw_b200.ops import _lib, symm
+    from jigsaw_b200.ops import _lib, symm, ulysses_fused
 
+    ulysses_fused.FUSE_OUTPUT_PROJECTION = True
     dev = torch.device("cuda", rank) if torch.cuda.is_available() else torch.device("cpu")
     mesh = jb.make_process_mesh({"row": world, "col": 1})
     torch.manual_seed(0)
@@ -483,7 +484,7 @@ def _worker_ulysses_qkv(rank, world):
         with torch.autocast(dev.type, dtype=torch.bfloat16):
             y = uly(xl)
         if dev.type == "cuda":
-            assert _lib.LAUNCHES >= before + 3, "the fused projection + exchange did not run"
+            assert _lib.LAUNCHES >= before + 5, "the fused projections did not run"
         y.float().backward(split(g, {1: mesh["row"]}))
         if dev.type == "cuda":
             symm.arena(dev).check_status()
