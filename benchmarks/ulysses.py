@@ -1,9 +1,15 @@
-"""Ulysses QKV projection + sequence -> head exchange on P GPUs, three ways, device-timed (max over ranks):
+"""Ulysses projections with their exchanges on P GPUs, device-timed (max over ranks).
+
+QKV projection + sequence -> head exchange, three ways:
 
 * ``fused``    - one tcgen05 GEMM whose epilogue stores every tile into the destination rank's inbox
                  (``jigsaw_b200.ops.ulysses_fused``), flag publish, bounded wait, layout copy;
 * ``unfused``  - the same GEMM kernel into local memory, then the peer-memory all-to-all kernel;
 * ``library``  - cuBLAS (``F.linear``) followed by NCCL ``all_to_all_single``.
+
+Head -> sequence exchange + output projection (``out_*`` keys): ``fused`` is one GEMM that loads the heads
+of rank ``p`` by TMA from rank ``p``'s staging block, ``unfused`` the all-to-all kernel followed by the GEMM
+kernel, ``library`` NCCL followed by cuBLAS.
 
     torchrun --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/ulysses.py [--out result.json]
 
@@ -59,9 +65,10 @@ def main() -> None:
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
     import jigsaw_b200 as jb
-    from jigsaw_b200.modules.attention._ulysses import seq_to_heads
+    from jigsaw_b200.modules.attention._ulysses import heads_to_seq, seq_to_heads
     from jigsaw_b200.ops import linear_fused, symm, ulysses_fused
 
+    ulysses_fused.FUSE_QKV_PROJECTION = ulysses_fused.FUSE_OUTPUT_PROJECTION = True      # measure them, whatever the defaults
     mesh = jb.make_process_mesh({"row": world, "col": 1})
     group = mesh["row"]
     P, b, h = world, args.batch, args.heads
@@ -93,6 +100,31 @@ def main() -> None:
     res = {"world": P, "batch": b, "seq": args.seq, "dim": args.dim, "heads": h, "fused_equals_unfused": bool(same),
            "max_abs_diff_vs_library": err}
     for name, fn in (("fused", fused), ("unfused", unfused), ("library", library)):
+        res[name + "_ms"] = round(timed(fn, args.warmup, args.reps), 4)
+    # ---- head -> sequence exchange + output projection
+    o = torch.randn(b, hl, P * sl, d, device=dev).bfloat16().transpose(1, 2)          # (b, s, hl, d) as the core returns it
+    wo = (torch.randn(args.dim, h * d, device=dev) * 0.03).bfloat16()
+    bo = torch.randn(args.dim, device=dev)
+
+    def out_fused():
+        return ulysses_fused.maybe_fused_ulysses_out(o, wo, bo, group)
+
+    def out_unfused():
+        mine = heads_to_seq(o.contiguous(), group)
+        return linear_fused.gemm(mine.view(b * sl, h * d), wo, bias=bo).view(b, sl, -1)
+
+    def out_library():
+        send = o.unflatten(1, (P, sl)).permute(1, 0, 2, 3, 4).contiguous()              # (P, b, sl, hl, d)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        mine = recv.permute(1, 2, 0, 3, 4).reshape(b * sl, h * d)
+        return F.linear(mine, wo, bo.bfloat16()).view(b, sl, -1)
+
+    ya, yc = out_fused(), out_unfused()
+    assert ya is not None, "the fused output projection did not apply"
+    res["out_fused_equals_unfused"] = bool(torch.equal(ya, yc))
+    res["out_max_abs_diff_vs_library"] = float((ya.float() - out_library().float()).abs().max())
+    for name, fn in (("out_fused", out_fused), ("out_unfused", out_unfused), ("out_library", out_library)):
         res[name + "_ms"] = round(timed(fn, args.warmup, args.reps), 4)
     symm.arena(dev).check_status()
     flops = 2.0 * b * sl * args.dim * 3 * h * d

@@ -32,7 +32,7 @@ from ..linear import DistributedLinear
 from ._config import AttnBackend, JIGSAW_TE_AVAILABLE, Offload, RingAttentionConfig, SaveBackward, SaveScope, SendForward, coerce_enum
 from ._cores import MathCore
 from ._ring import hybrid_subgroups, ring_attention
-from ._ulysses import hierarchical_ulysses_attention, ulysses_attention
+from ._ulysses import heads_to_seq, hierarchical_ulysses_attention, seq_to_heads
 
 
 def attn_core_dtype(x: torch.Tensor) -> torch.dtype:
@@ -278,21 +278,11 @@ class DistributedAttention(torch.nn.Module):
         p = self.dropout_p if self.training else 0.0
         if self.ulysses and not self.ulysses_intra_size and not self.qk_norm and x.is_cuda and type(self.qkv) is torch.nn.Linear:
             from ...ops import ulysses_fused
-            from ._ulysses import heads_to_seq
 
             # projection with the sequence -> head exchange inside its epilogue: (3, b, s, h / P, d)
             full = ulysses_fused.maybe_fused_ulysses_qkv(x, self.qkv.weight, self.spatial_group, self.heads, self.head_dim)
             if full is not None:
-                q, k, v = (t.transpose(-3, -2) for t in full.to(core).unbind(0))
-                out = _dense_attention(q, k, v, self.scale, p, self.attn_backend, None, True).transpose(-3, -2)
-                if type(self.head_concat) is torch.nn.Linear:
-                    # output projection whose operand loads do the head -> sequence exchange
-                    y = ulysses_fused.maybe_fused_ulysses_out(out, self.head_concat.weight, self.head_concat.bias, self.spatial_group)
-                    if y is not None:
-                        return y
-                out = heads_to_seq(out.contiguous(), self.spatial_group)
-                out = out.reshape(*x.shape[:-1], self.heads * self.head_dim).to(x.dtype)
-                return self.head_concat(out)
+                return self._ulysses_core(full.to(core), x, p)
         qkv = _split_heads(self.qkv(x), self.heads, bshd=self.ulysses)
         if self.qk_norm:
             q, k, v = qkv.unbind(0)
@@ -310,13 +300,27 @@ class DistributedAttention(torch.nn.Module):
         elif self.ulysses and self.ulysses_intra_size:
             out = hierarchical_ulysses_attention(qkv, self._intra, self._inter, self.scale, self._inter_cfg, p)
         elif self.ulysses:
-            dense = lambda q, k, v: _dense_attention(q, k, v, self.scale, p, self.attn_backend, None, True)  # noqa: E731
-            out = ulysses_attention(qkv, self.spatial_group, dense)
+            return self._ulysses_core(seq_to_heads(qkv, self.spatial_group), x, p)
         else:
             q, k, v = qkv.unbind(0)
             if attn_mask is not None and attn_mask.dtype != torch.bool:
                 attn_mask = attn_mask.to(core)
             out = _dense_attention(q, k, v, self.scale, p, self.attn_backend, attn_mask, True).transpose(-3, -2)
+        out = out.reshape(*x.shape[:-1], self.heads * self.head_dim).to(x.dtype)
+        return self.head_concat(out)
+
+    def _ulysses_core(self, full: torch.Tensor, x: torch.Tensor, p: float) -> torch.Tensor:
+        """Dense attention on the head shard ``full`` ``(3, ..., s, h / P, d)``, the head -> sequence
+        exchange and the output projection (one GEMM whose operand loads do the exchange, when that applies)."""
+        q, k, v = (t.transpose(-3, -2) for t in full.unbind(0))
+        out = _dense_attention(q, k, v, self.scale, p, self.attn_backend, None, True).transpose(-3, -2)
+        if out.is_cuda and type(self.head_concat) is torch.nn.Linear:
+            from ...ops import ulysses_fused
+
+            y = ulysses_fused.maybe_fused_ulysses_out(out, self.head_concat.weight, self.head_concat.bias, self.spatial_group)
+            if y is not None:
+                return y
+        out = heads_to_seq(out.contiguous(), self.spatial_group)
         out = out.reshape(*x.shape[:-1], self.heads * self.head_dim).to(x.dtype)
         return self.head_concat(out)
 

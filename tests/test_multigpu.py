@@ -470,7 +470,7 @@ def _worker_ulysses_qkv(rank, world):
     from jigsaw_b200.modules.attention import Attention
     from jigsaw_b200.ops import _lib, symm, ulysses_fused
 
-    ulysses_fused.FUSE_OUTPUT_PROJECTION = True
+    ulysses_fused.FUSE_QKV_PROJECTION = ulysses_fused.FUSE_OUTPUT_PROJECTION = True
     dev = torch.device("cuda", rank) if torch.cuda.is_available() else torch.device("cpu")
     mesh = jb.make_process_mesh({"row": world, "col": 1})
     torch.manual_seed(0)
