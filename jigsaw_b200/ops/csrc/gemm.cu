@@ -61,9 +61,15 @@ struct GemmSmem {
   static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int BAR_BYTES = 256;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  // staged epilogue: 32 rows x 128 bytes per epilogue warp behind the barriers
+  static constexpr int EPI_STAGE_BYTES = 32 * 128;
+  static constexpr int TOTAL_STAGED = TOTAL + GEMM_EPI_WARPS * EPI_STAGE_BYTES;
 };
 
-template <int BN, int A_MN, int B_MN>
+// STAGED = 1: bf16 tiles leave through a per-warp shared-memory buffer so that eight lanes write 128
+// contiguous bytes of one output row (a full line per request, which is what stores into a peer's memory
+// across NVLink need); STAGED = 0: every thread stores its own row, 16 bytes per instruction.
+template <int BN, int A_MN, int B_MN, int STAGED = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ GemmGather gather, GemmEpilogue ep, int M, int N, int K, int* status) {
@@ -236,8 +242,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ldc = ep.part_cols;
         col_shift = part * ep.part_cols;
       }
+      bool staged_done = false;
+      if constexpr (STAGED != 0 && BN >= 128) {
+        if (!ep.out_fp32 && n0 + BN <= N && (ldc & 7) == 0) {
+          uint8_t* stage = smem + S::STAGES * S::STAGE_BYTES + S::BAR_BYTES + (warp - 2) * S::EPI_STAGE_BYTES;
+          __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(c_base);
 #pragma unroll 1
-      for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
+          for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 64) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + c0 + 32 * h, r);
+              tmem_ld_wait();
+              const int col0 = n0 + c0 + 32 * h;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  float x = __uint_as_float(r[j + e]);
+                  if (ep.bias != nullptr) x += __ldg(ep.bias + col0 + j + e);
+                  if (ep.act == 1) x = gelu_erf(x);
+                  v[e] = x;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                const int chunk = h * 4 + (j >> 3);                  // 16-byte chunk of the 128-byte staged row
+                *reinterpret_cast<uint4*>(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = o;
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {                            // four rows per instruction, 128 bytes each
+              const int rl = i * 4 + (lane >> 3);
+              const int chunk = lane & 7;
+              const int grow = m0 + quad * 32 + rl;
+              const uint4 o = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
+              if (grow < M)
+                *reinterpret_cast<uint4*>(cb + static_cast<long long>(grow) * ldc + (n0 + c0 - col_shift) + chunk * 8) = o;
+            }
+            __syncwarp();
+          }
+          staged_done = true;
+        }
+      }
+#pragma unroll 1
+      for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2) && !staged_done; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
@@ -307,7 +360,7 @@ struct GatherSpec {                      // host-side description of a gathered 
   int parts, k_part;
 };
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int STAGED = 0>
 static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int M, int N, int K, long long lda,
                        long long ldb, int sm_count, int* status, cudaStream_t stream,
                        const GatherSpec* gs = nullptr) {
@@ -347,15 +400,17 @@ static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int
     gather.parts = gs->parts;
     gather.kblocks_per_part = gs->k_part / GEMM_BK;
   }
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, STAGED>;
+  constexpr int smem_bytes = STAGED != 0 ? S::TOTAL_STAGED : S::TOTAL;
+  static_assert(smem_bytes <= 227 * 1024, "shared memory of one CTA");
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;
     attr_set = true;
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, gather, ep, M, N, K, status);
+  kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(tmA, tmB, gather, ep, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -459,9 +514,9 @@ extern "C" int jb_publish(void* const* flags, int n, unsigned int epoch, unsigne
 // (part_cols columns, part_cols a multiple of 64) of this GPU's partial product is stored as a bf16
 // [M, part_cols] slab at c_part[p] (for p != this GPU a pointer into GPU p's inbox).  The caller
 // publishes a flag afterwards (jb_publish) and the owners sum their slabs (jb_sum_slabs).
-extern "C" int jb_gemm_bf16_scatter(const void* A, const void* B, void* const* c_part, int parts, int part_cols, int M,
-                                    int K, long long lda, long long ldb, int a_mn, int b_mn, int sm_count, int* status,
-                                    void* stream) {
+static int gemm_scatter(const void* A, const void* B, void* const* c_part, int parts, int part_cols, int M, int K,
+                        long long lda, long long ldb, int a_mn, int b_mn, int staged, int sm_count, int* status,
+                        void* stream) {
   using namespace jb;
   if (parts < 2 || parts > 8 || part_cols % 64 != 0 || (lda & 7) || (ldb & 7)) return -1;
   const int N = parts * part_cols;
@@ -482,8 +537,31 @@ extern "C" int jb_gemm_bf16_scatter(const void* A, const void* B, void* const* c
     case 2: return launch_gemm<BN, 1, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);        \
     default: return launch_gemm<BN, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);       \
   }
+#define JB_GEMM_SC_STAGED(BN)                                                                       \
+  switch (key) {                                                                                     \
+    case 0: return launch_gemm<BN, 0, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);     \
+    case 1: return launch_gemm<BN, 0, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);     \
+    case 2: return launch_gemm<BN, 1, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);     \
+    default: return launch_gemm<BN, 1, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);    \
+  }
+  if (staged != 0 && bn == 256) { JB_GEMM_SC_STAGED(256) }
+  if (staged != 0 && bn == 128) { JB_GEMM_SC_STAGED(128) }
   if (bn == 256) { JB_GEMM_SC(256) } else if (bn == 128) { JB_GEMM_SC(128) } else { JB_GEMM_SC(64) }
 #undef JB_GEMM_SC
+#undef JB_GEMM_SC_STAGED
+}
+
+extern "C" int jb_gemm_bf16_scatter(const void* A, const void* B, void* const* c_part, int parts, int part_cols, int M,
+                                    int K, long long lda, long long ldb, int a_mn, int b_mn, int sm_count, int* status,
+                                    void* stream) {
+  return gemm_scatter(A, B, c_part, parts, part_cols, M, K, lda, ldb, a_mn, b_mn, 0, sm_count, status, stream);
+}
+
+// The same product with the staged epilogue (tiles leave through shared memory as 128-byte row pieces).
+extern "C" int jb_gemm_bf16_scatter_staged(const void* A, const void* B, void* const* c_part, int parts, int part_cols,
+                                           int M, int K, long long lda, long long ldb, int a_mn, int b_mn, int sm_count,
+                                           int* status, void* stream) {
+  return gemm_scatter(A, B, c_part, parts, part_cols, M, K, lda, ldb, a_mn, b_mn, 1, sm_count, status, stream);
 }
 
 namespace jb {

@@ -24,6 +24,7 @@ all-to-alls that move ``x`` blocks before them (jigsaw/_core/comm.py:430-455).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any
 
 import torch
@@ -129,6 +130,16 @@ def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block
     return blk
 
 
+# Epilogue of the scatter GEMM: off = every thread stores its own accumulator row (16 bytes per
+# instruction), on = tiles leave through shared memory as 128-byte row pieces, which suits stores into a
+# peer's memory.  The staged form has not run on hardware yet; JIGSAW_STAGED_EPILOGUE=1 selects it.
+STAGED_SCATTER_EPILOGUE = os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") == "1"
+
+
+def scatter_gemm_launcher(L: Any) -> Any:
+    return L.jb_gemm_bf16_scatter_staged if STAGED_SCATTER_EPILOGUE else L.jb_gemm_bf16_scatter
+
+
 def _scatter_gemm(g: torch.Tensor, wb: torch.Tensor, group: Any) -> torch.Tensor:
     """``reduce_scatter(g @ wb, last dim over group)`` with the scatter fused into the GEMM: the
     epilogue stores every tile of column part ``p`` straight into rank ``p``'s inbox (this rank's
@@ -149,7 +160,7 @@ def _scatter_gemm(g: torch.Tensor, wb: torch.Tensor, group: Any) -> torch.Tensor
     c_part = (ctypes.c_void_p * 8)()
     for i, r in enumerate(ranks):
         c_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER + me * slab
-    rc = L.jb_gemm_bf16_scatter(_p(g), _p(wb), c_part, P, kp, M, N, g.stride(0), wb.stride(0), 0, 1,
+    rc = scatter_gemm_launcher(L)(_p(g), _p(wb), c_part, P, kp, M, N, g.stride(0), wb.stride(0), 0, 1,
                                 _lib.sm_count(dev.index), _p(ar.status), st)
     flags = (ctypes.c_void_p * 8)()
     n = 0

@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, symm
-from .linear_fused import _HEADER, _staging_block, gemm
+from .linear_fused import _HEADER, _staging_block, gemm, scatter_gemm_launcher
 
 
 def head_group_major(w: torch.Tensor, parts: int, heads: int, head_dim: int) -> torch.Tensor:
@@ -71,7 +71,7 @@ def _scatter_exchange(a: torch.Tensor, bmat: torch.Tensor, b_mn: bool, cols: int
     c_part = (ctypes.c_void_p * 8)()
     for i, r in enumerate(ranks):
         c_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER + me * slab
-    rc = L.jb_gemm_bf16_scatter(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(bmat.data_ptr()), c_part, P, cols, M, K,
+    rc = scatter_gemm_launcher(L)(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(bmat.data_ptr()), c_part, P, cols, M, K,
                                 a.stride(0), bmat.stride(0), 0, 1 if b_mn else 0, _lib.sm_count(dev.index), status, st)
     flags = (ctypes.c_void_p * 8)()
     waits = (ctypes.c_void_p * 8)()
