@@ -164,6 +164,25 @@ def main() -> None:
         f = lambda: attention_fused.maybe_fused_merge(o1, l1, o2, l2)
         return timed(f, args.warmup, args.reps), o1.numel() * (4 + 4 + 2), None
 
+    # ---- tcgen05 attention forward (only on request: JIGSAW_FLASH_ATTENTION=1), against SDPA for reference
+    if os.environ.get("JIGSAW_FLASH_ATTENTION", "0") == "1":
+        qa = torch.randn(8, 16, 4096 // scale, 64, device=dev).bfloat16()
+        ka, va = torch.randn_like(qa), torch.randn_like(qa)
+        fa_flops = 4.0 * qa.shape[0] * qa.shape[1] * qa.shape[2] * qa.shape[2] * 64
+
+        @case("flash_attn_fwd")
+        def _():
+            from jigsaw_b200.ops import attention_fused
+
+            f = lambda: attention_fused.flash_attention_forward(qa, ka, va, 0.125)
+            return timed(f, args.warmup, args.reps), None, fa_flops
+
+        @case("sdpa_fwd_library")
+        def _():
+            with torch.no_grad():
+                f = lambda: torch.nn.functional.scaled_dot_product_attention(qa, ka, va, scale=0.125)
+                return timed(f, args.warmup, args.reps), None, fa_flops
+
     # ---- GEMM
     for (M, N, K) in ((8192, 8192, 8192), (8192, 4096, 1024), (8192, 1024, 4096)):
         if args.small and M * N * K > 2 ** 36:

@@ -42,3 +42,42 @@ def maybe_fused_merge(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor,
         raise RuntimeError(f"jigsaw_b200 kernel launcher merge_chunks failed with code {rc}")
     _lib.count_launches(1)
     return out, lse
+
+
+def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """``softmax(scale * q k^T) v`` and the row-wise log-sum-exp on the tcgen05 kernel of
+    ``csrc/flash_attn.cu``.  ``q`` is ``(..., sq, 64)``, ``k`` and ``v`` are ``(..., sk, 64)``, all bf16 on
+    one CUDA device with equal leading dimensions; returns ``(out bf16 (..., sq, 64), lse fp32 (..., sq))``.
+    Forward only (no autograd): the cores of ``jigsaw_b200.modules.attention`` do not call it yet, because
+    the kernel has not run on hardware; ``tests/test_elementwise_gpu.py`` holds its numerics test, which
+    runs when ``JIGSAW_FLASH_ATTENTION=1`` is set.
+
+    Reference parity: the role of the SDPA flash core, jigsaw/modules/attention/_functional/cores/sdpa.py:17-165.
+    """
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("flash_attention_forward needs bf16 inputs")
+    if q.shape[-1] != 64 or k.shape[-1] != 64 or v.shape[-1] != 64 or k.shape != v.shape or q.shape[:-2] != k.shape[:-2]:
+        raise ValueError("flash_attention_forward needs head dimension 64 and matching leading dimensions")
+    if not _lib.available():
+        raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
+    lead = q.shape[:-2]
+    sq, sk = q.shape[-2], k.shape[-2]
+    q3, k3, v3 = (t.reshape(-1, t.shape[-2], 64).contiguous() for t in (q, k, v))
+    bh = q3.shape[0]
+    out = torch.empty_like(q3)
+    lse = torch.empty(bh, sq, dtype=torch.float32, device=q.device)
+    status = None
+    if bh > 0 and sq > 0:
+        from . import symm
+
+        ar = symm.arena(q.device)
+        status = ar.status
+        rc = _lib.lib().jb_flash_attn_fwd(
+            ctypes.c_void_p(q3.data_ptr()), ctypes.c_void_p(k3.data_ptr()), ctypes.c_void_p(v3.data_ptr()),
+            ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(lse.data_ptr()), bh, sq, sk,
+            q3.stride(1), q3.stride(0), k3.stride(1), k3.stride(0), v3.stride(1), v3.stride(0), out.stride(1), out.stride(0),
+            float(scale), ctypes.c_void_p(status.data_ptr()), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_fwd failed with code {rc}")
+        _lib.count_launches(1)
+    return out.view(*lead, sq, 64), lse.view(*lead, sq)

@@ -9,5 +9,6 @@
 #include "elementwise.cu"
 #include "roll.cu"
 #include "alltoall.cu"
+#include "flash_attn.cu"
 
 extern "C" int jb_abi_version() { return 1; }

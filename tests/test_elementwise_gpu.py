@@ -98,3 +98,31 @@ def test_cross_entropy_kernel(shape, dtype, reduction):
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
     torch.testing.assert_close(loss.float(), ref, rtol=tol, atol=tol)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=tol, atol=tol * max(float(xr.grad.abs().max()), 1e-3))
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 128, 128), (1, 2, 300, 520), (2, 4, 1024, 2048)])
+def test_flash_attention_forward(shape):
+    """tcgen05 attention forward (head dimension 64) against fp32 attention of the same bf16 inputs:
+    output and log-sum-exp.  The kernel has not run on hardware yet, so the test runs only when
+    JIGSAW_FLASH_ATTENTION=1 is set."""
+    import os
+
+    if os.environ.get("JIGSAW_FLASH_ATTENTION", "0") != "1":
+        pytest.skip("set JIGSAW_FLASH_ATTENTION=1 to run the tcgen05 attention forward")
+    from jigsaw_b200.ops import attention_fused, symm
+
+    b, h, sq, sk = shape
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    q = torch.randn(b, h, sq, 64, device=dev).bfloat16()
+    k = torch.randn(b, h, sk, 64, device=dev).bfloat16()
+    v = torch.randn(b, h, sk, 64, device=dev).bfloat16()
+    scale = 0.125
+    out, lse = attention_fused.flash_attention_forward(q, k, v, scale)
+    torch.cuda.synchronize()
+    symm.arena(dev).check_status()
+    t = scale * (q.float() @ k.float().transpose(-1, -2))
+    ref_lse = torch.logsumexp(t, dim=-1)
+    ref = torch.softmax(t, dim=-1) @ v.float()
+    assert float((lse - ref_lse).abs().max()) < 2e-2
+    assert float((out.float() - ref).abs().max()) < 3e-2 * float(ref.abs().max())
