@@ -138,6 +138,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_gemm_bf16_scatter.restype = c_int
     L.jb_gemm_bf16_scatter_staged.argtypes = L.jb_gemm_bf16_scatter.argtypes
     L.jb_gemm_bf16_scatter_staged.restype = c_int
+    L.jb_set_staged_epilogue.argtypes = [c_int]
+    L.jb_set_staged_epilogue.restype = None
+    L.jb_set_staged_epilogue(1 if os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") == "1" else 0)
     L.jb_sum_slabs.argtypes = [c_void_p, c_longlong, c_int, POINTER(c_void_p), c_uint, c_uint, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_void_p]
     L.jb_sum_slabs.restype = c_int

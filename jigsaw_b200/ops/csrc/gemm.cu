@@ -416,6 +416,11 @@ static int launch_gemm(const void* A, const void* B, const GemmEpilogue& ep, int
 
 }  // namespace jb
 
+// Process-wide switch: bf16 outputs of jb_gemm_bf16 leave through the staged epilogue (128-byte row
+// pieces written by eight lanes) instead of one row per thread.  Off unless the host turns it on.
+static int g_staged_epilogue = 0;
+extern "C" void jb_set_staged_epilogue(int on) { g_staged_epilogue = on; }
+
 // C ABI.  a_mn / b_mn select the stored layout of each operand:
 //   a_mn = 0: A is [M, K] row-major (lda = row stride);  a_mn = 1: A is [K, M] row-major.
 //   b_mn = 0: B is [N, K] row-major (ldb = row stride);  b_mn = 1: B is [K, N] row-major.
@@ -441,14 +446,25 @@ extern "C" int jb_gemm_bf16(const void* A, const void* B, void* C, const float* 
     case 2: return launch_gemm<BN, 1, 0>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                    \
     default: return launch_gemm<BN, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                   \
   }
+#define JB_GEMM_DISPATCH_STAGED(BN)                                                                            \
+  switch (key) {                                                                                                \
+    case 0: return launch_gemm<BN, 0, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                 \
+    case 1: return launch_gemm<BN, 0, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                 \
+    case 2: return launch_gemm<BN, 1, 0, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                 \
+    default: return launch_gemm<BN, 1, 1, 1>(A, B, ep, M, N, K, lda, ldb, sm_count, status, st);                \
+  }
+  const bool staged = g_staged_epilogue != 0 && out_fp32 == 0 && !narrow;
   if (wide) {
+    if (staged) { JB_GEMM_DISPATCH_STAGED(256) }
     JB_GEMM_DISPATCH(256)
   } else if (narrow) {
     JB_GEMM_DISPATCH(64)
   } else {
+    if (staged) { JB_GEMM_DISPATCH_STAGED(128) }
     JB_GEMM_DISPATCH(128)
   }
 #undef JB_GEMM_DISPATCH
+#undef JB_GEMM_DISPATCH_STAGED
 }
 
 // C = act(A * B^T + bias) where the reduction dimension of A is split over `parts` GPUs: part p is a
