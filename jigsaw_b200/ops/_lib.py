@@ -153,6 +153,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_flash_attn_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int] + [c_longlong] * 8 + [
         c_float, c_void_p, c_void_p]
     L.jb_flash_attn_fwd.restype = c_int
+    L.jb_flash_attn_bwd.argtypes = [c_void_p] * 10 + [c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+    L.jb_flash_attn_bwd.restype = c_int
     L.jb_peer_fetch.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_uint, c_uint, c_void_p, c_void_p, c_int, c_void_p]
     L.jb_peer_fetch.restype = c_int
     L.jb_roll.argtypes = [POINTER(JbRoll), c_void_p, c_void_p, c_int, c_void_p]

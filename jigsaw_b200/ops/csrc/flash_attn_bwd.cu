@@ -1,0 +1,337 @@
+// Attention backward for head dimension 64 on tcgen05, companion of flash_attn.cu.  Three kernels:
+//   fa_delta_kernel     D[row] = sum_d dO[row][d] * O[row][d]                       (memory-bound)
+//   fa_bwd_kernel<0>    one CTA per block of 128 keys, loop over query blocks:
+//                         S = Q K^T, dP = dO V^T, P = exp(scale S - LSE), dS = scale P (dP - D),
+//                         dV += P^T dO, dK += dS^T Q      (accumulators stay in TMEM over the loop)
+//   fa_bwd_kernel<1>    one CTA per block of 128 queries, loop over key blocks:
+//                         S, dP, dS as above, dQ += dS K
+// S and dP are recomputed in both kernels so that no gradient needs atomics.  Roles as in the forward
+// kernel: warp 0 TMA producer, warp 1 UMMA issuer, warps 2-5 one query row per thread.  P and dS go to
+// the tensor cores through shared memory as [query][key] tiles in the 128-byte swizzled layout; the
+// same bytes serve as a K-major operand (dS K) and, transposed, as an MN-major operand (P^T dO, dS^T Q).
+// Every mbarrier wait is bounded.  All tensors are contiguous [bh][s][64] bf16 (LSE, D: [bh][sq] fp32).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace jb {
+
+constexpr int FB_D = 64;
+constexpr int FB_B = 128;                       // rows of a query block and of a key block
+constexpr int FB_THREADS = 32 * 6;
+constexpr int FB_TILE = 128 * 128;              // bytes of a [128 x 64] bf16 tile
+constexpr int FB_PT = 2 * FB_TILE;              // bytes of a [128 x 128] bf16 tile (two 64-wide blocks)
+constexpr int FB_STAGES = 2;
+// resident pair (K, V or Q, dO) + ring of streamed pairs + P + dS + barriers + alignment slack
+constexpr int FB_SMEM = 2 * FB_TILE + FB_STAGES * 2 * FB_TILE + 2 * FB_PT + 256 + 1024;
+static_assert(FB_SMEM <= 227 * 1024, "shared memory of one CTA");
+
+__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                float* __restrict__ delta, long long rows) {
+  // eight lanes per row of 64 values (16 bytes each)
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const int part = threadIdx.x & 7;
+  float s = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * FB_D + part * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * FB_D + part * 8);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(pa[i]);
+      const float2 y = __bfloat1622float2(pb[i]);
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  if (row < rows && part == 0) delta[row] = s;
+}
+
+// One thread's row of 128 values as bf16 into a [128 x 128] tile made of two [128 rows x 128 bytes]
+// blocks with the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7).
+__device__ __forceinline__ void store_row_chunk(uint8_t* tile, int row, int c0, const float (&p)[32]) {
+  uint8_t* blk = tile + (c0 >> 6) * FB_TILE + row * 128;
+#pragma unroll
+  for (int e = 0; e < 32; e += 8) {
+    uint4 v;
+    v.x = pack_bf16x2(p[e], p[e + 1]);
+    v.y = pack_bf16x2(p[e + 2], p[e + 3]);
+    v.z = pack_bf16x2(p[e + 4], p[e + 5]);
+    v.w = pack_bf16x2(p[e + 6], p[e + 7]);
+    const int chunk = ((c0 & 63) + e) >> 3;
+    *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = v;
+  }
+}
+
+// MODE 0: dK / dV (the CTA's block is a key block, the loop runs over query blocks).
+// MODE 1: dQ      (the CTA's block is a query block, the loop runs over key blocks).
+// tmA / tmB: the resident pair (MODE 0: K, V; MODE 1: Q, dO); tmC / tmD: the streamed pair
+// (MODE 0: Q, dO; MODE 1: K, V).
+template <int MODE>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+              const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ out0,
+              __nv_bfloat16* __restrict__ out1, int sq, int sk, float scale, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* res_s = smem;                                         // resident pair: [0] and [1]
+  uint8_t* ring_s = smem + 2 * FB_TILE;                          // stage s: first at 2 s, second at 2 s + 1
+  uint8_t* p_s = ring_s + FB_STAGES * 2 * FB_TILE;               // P   [query][key]
+  uint8_t* ds_s = p_s + FB_PT;                                   // dS  [query][key]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + FB_PT);
+  uint64_t* res_full = bars;                     // [1]
+  uint64_t* ring_full = bars + 1;                // [STAGES]
+  uint64_t* ring_empty = ring_full + FB_STAGES;  // [STAGES]
+  uint64_t* s_full = ring_empty + FB_STAGES;     // S and dP are in TMEM
+  uint64_t* s_free = s_full + 1;                 // the four row warps have read S and dP
+  uint64_t* p_full = s_free + 1;                 // P is in shared memory
+  uint64_t* ds_full = p_full + 1;                // dS is in shared memory
+  uint64_t* pds_free = ds_full + 1;              // the UMMAs that read P and dS are done
+  uint64_t* acc_full = pds_free + 1;             // the last accumulation is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int own0 = blockIdx.x * FB_B;            // first row of this CTA's block
+  const int bh = blockIdx.y;
+  const int n_loop = ((MODE == 0 ? sq : sk) + FB_B - 1) / FB_B;
+  constexpr uint32_t TMEM_COLS = 512;            // S 0..127, dP 128..255, accumulators 256.. (64 columns each)
+
+  if (threadIdx.x == 0) {
+    mbar_init(res_full, 1);
+    for (int s = 0; s < FB_STAGES; ++s) {
+      mbar_init(&ring_full[s], 1);
+      mbar_init(&ring_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 4);
+    mbar_init(p_full, 4);
+    mbar_init(ds_full, 4);
+    mbar_init(pds_free, 1);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+    tma_prefetch_desc(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(res_full, 2 * FB_TILE);
+      tma_load_3d(res_s, &tmA, res_full, 0, own0, bh);
+      tma_load_3d(res_s + FB_TILE, &tmB, res_full, 0, own0, bh);
+      for (int i = 0; i < n_loop; ++i) {
+        const int st = i % FB_STAGES;
+        mbar_wait(&ring_empty[st], (static_cast<uint32_t>(i / FB_STAGES) & 1u) ^ 1u, abort_flag, status, 1);
+        mbar_expect_tx(&ring_full[st], 2 * FB_TILE);
+        tma_load_3d(ring_s + (2 * st) * FB_TILE, &tmC, &ring_full[st], 0, i * FB_B, bh);
+        tma_load_3d(ring_s + (2 * st + 1) * FB_TILE, &tmD, &ring_full[st], 0, i * FB_B, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    constexpr uint32_t idesc_s = make_idesc_bf16(FB_B, FB_B, 0, 0);        // [128 x 64] x [128 x 64]^T
+    constexpr uint32_t idesc_t = make_idesc_bf16(FB_B, FB_D, 1, 1);        // transposed tile x streamed rows
+    constexpr uint32_t idesc_q = make_idesc_bf16(FB_B, FB_D, 0, 1);        // dS (K-major) x K rows
+    const uint32_t res_a = smem_u32(res_s);
+    const uint32_t ring_a = smem_u32(ring_s);
+    mbar_wait(res_full, 0, abort_flag, status, 2);
+    for (int i = 0; i < n_loop; ++i) {
+      const int st = i % FB_STAGES;
+      const uint32_t ph = static_cast<uint32_t>(i) & 1u;
+      mbar_wait(&ring_full[st], static_cast<uint32_t>(i / FB_STAGES) & 1u, abort_flag, status, 3);
+      mbar_wait(s_free, ph ^ 1u, abort_flag, status, 4);
+      tc_fence_after_sync();
+      // query-side tiles (Q, dO) and key-side tiles (K, V) of this iteration
+      const uint32_t q_a = MODE == 0 ? ring_a + (2 * st) * FB_TILE : res_a;
+      const uint32_t do_a = q_a + FB_TILE;
+      const uint32_t k_a = MODE == 0 ? res_a : ring_a + (2 * st) * FB_TILE;
+      const uint32_t v_a = k_a + FB_TILE;
+      const uint64_t qd = make_smem_desc_sw128(q_a, 16, 1024), kd = make_smem_desc_sw128(k_a, 16, 1024);
+      const uint64_t dod = make_smem_desc_sw128(do_a, 16, 1024), vd = make_smem_desc_sw128(v_a, 16, 1024);
+#pragma unroll
+      for (int k = 0; k < FB_D / 16; ++k)                                   // S = Q K^T
+        umma_f16_elect(tmem_base, desc_advance(qd, k * 32), desc_advance(kd, k * 32), idesc_s, k != 0 ? 1u : 0u);
+#pragma unroll
+      for (int k = 0; k < FB_D / 16; ++k)                                   // dP = dO V^T
+        umma_f16_elect(tmem_base + 128u, desc_advance(dod, k * 32), desc_advance(vd, k * 32), idesc_s, k != 0 ? 1u : 0u);
+      umma_commit_elect(s_full);
+      if (MODE == 0) {
+        // dV += P^T dO and dK += dS^T Q: A is the [query][key] tile read transposed (rows = reduction index,
+        // two 64-key blocks one tile apart), B the streamed [query][64] tile (rows = reduction index)
+        const uint64_t pt = make_smem_desc_sw128(smem_u32(p_s), FB_TILE, 1024);
+        const uint64_t dst = make_smem_desc_sw128(smem_u32(ds_s), FB_TILE, 1024);
+        const uint64_t dob = make_smem_desc_sw128(do_a, 8192, 1024), qb = make_smem_desc_sw128(q_a, 8192, 1024);
+        mbar_wait(p_full, ph, abort_flag, status, 5);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < FB_B / 16; ++k)
+          umma_f16_elect(tmem_base + 256u, desc_advance(pt, k * 2048), desc_advance(dob, k * 2048), idesc_t,
+                         (i | k) != 0 ? 1u : 0u);
+        mbar_wait(ds_full, ph, abort_flag, status, 6);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < FB_B / 16; ++k)
+          umma_f16_elect(tmem_base + 320u, desc_advance(dst, k * 2048), desc_advance(qb, k * 2048), idesc_t,
+                         (i | k) != 0 ? 1u : 0u);
+      } else {
+        // dQ += dS K: A = dS K-major (two blocks of 64 keys), B = K rows (rows = reduction index)
+        const uint64_t dsk = make_smem_desc_sw128(smem_u32(ds_s), 16, 1024);
+        const uint64_t kb = make_smem_desc_sw128(k_a, 8192, 1024);
+        mbar_wait(ds_full, ph, abort_flag, status, 6);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < FB_B / 16; ++k)
+          umma_f16_elect(tmem_base + 256u, desc_advance(dsk, static_cast<uint32_t>((k >> 2) * FB_TILE + (k & 3) * 32)),
+                         desc_advance(kb, k * 2048), idesc_q, (i | k) != 0 ? 1u : 0u);
+      }
+      umma_commit_elect(&ring_empty[st]);
+      umma_commit_elect(pds_free);
+    }
+    umma_commit_elect(acc_full);
+  } else {
+    // ------------------------------------------------------------ row warps (thread = query row of the tile)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    for (int i = 0; i < n_loop; ++i) {
+      const uint32_t ph = static_cast<uint32_t>(i) & 1u;
+      const int qrow = (MODE == 0 ? i * FB_B : own0) + row;      // global query row of this thread
+      // rows past the end get P = 0 (LSE = +inf) and D = 0
+      const float l2 = qrow < sq ? lse[static_cast<long long>(bh) * sq + qrow] * 1.4426950408889634f : INFINITY;
+      const float dl = qrow < sq ? delta[static_cast<long long>(bh) * sq + qrow] : 0.f;
+      mbar_wait(s_full, ph, abort_flag, status, 7);
+      mbar_wait(pds_free, ph ^ 1u, abort_flag, status, 8);
+      tc_fence_after_sync();
+      if (MODE == 0) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < FB_B; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(lane_addr + c0, r);
+          tmem_ld_wait();
+          float p[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) p[e] = ex2_approx(fmaf(__uint_as_float(r[e]), scale_log2, -l2));
+          store_row_chunk(p_s, row, c0, p);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < FB_B; c0 += 32) {
+        uint32_t r[32], g[32];
+        tmem_ld_32x32(lane_addr + c0, r);
+        tmem_ld_32x32(lane_addr + 128u + c0, g);
+        tmem_ld_wait();
+        float d[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float p = ex2_approx(fmaf(__uint_as_float(r[e]), scale_log2, -l2));
+          d[e] = p * (__uint_as_float(g[e]) - dl) * scale;
+        }
+        store_row_chunk(ds_s, row, c0, d);
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(ds_full);
+        mbar_arrive(s_free);
+      }
+    }
+    // ---- accumulators -> global (thread = row of this CTA's block)
+    mbar_wait(acc_full, 0, abort_flag, status, 9);
+    tc_fence_after_sync();
+    const int limit = MODE == 0 ? sk : sq;
+    const long long base = (static_cast<long long>(bh) * limit + own0 + row) * FB_D;
+#pragma unroll 1
+    for (int a = 0; a < (MODE == 0 ? 2 : 1); ++a) {
+      // MODE 0: accumulator 0 = dV (out1), accumulator 1 = dK (out0); MODE 1: dQ (out0)
+      __nv_bfloat16* dst = (MODE == 0 && a == 0) ? out1 : out0;
+#pragma unroll
+      for (int c0 = 0; c0 < FB_D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(lane_addr + 256u + static_cast<uint32_t>(a * 64 + c0), r);
+        tmem_ld_wait();
+        if (own0 + row < limit) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+            *reinterpret_cast<uint4*>(dst + base + c0 + e) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace jb
+
+// C ABI.  q, o, d_o, dq: [bh][sq][64]; k, v, dk, dv: [bh][sk][64]; all bf16, contiguous, 16-byte aligned.
+// lse: [bh][sq] fp32 as returned by jb_flash_attn_fwd (natural logarithm, of the scaled scores);
+// delta: [bh][sq] fp32 scratch.  Returns 0 on success, a negative code if a launch could not be set up.
+extern "C" int jb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int bh, int sq, int sk,
+                                 float scale, int* status, void* stream) {
+  using namespace jb;
+  if (bh < 1 || bh > 65535 || sq < 1 || sk < 1) return -1;
+  const void* ptrs[] = {q, k, v, o, d_o, dq, dk, dv};
+  for (const void* p : ptrs)
+    if (reinterpret_cast<uintptr_t>(p) & 15) return -1;
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  const uint32_t box[3] = {FB_D, FB_B, 1};
+  auto make = [&](CUtensorMap* m, const void* base, int rows) {
+    const uint64_t dims[3] = {FB_D, static_cast<uint64_t>(rows), static_cast<uint64_t>(bh)};
+    const uint64_t st[2] = {FB_D * 2, static_cast<uint64_t>(rows) * FB_D * 2};
+    return make_tmap_bf16(m, base, 3, dims, st, box);
+  };
+  if (make(&tmQ, q, sq) != 0 || make(&tmDO, d_o, sq) != 0 || make(&tmK, k, sk) != 0 || make(&tmV, v, sk) != 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(fa_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(fa_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long rows = static_cast<long long>(bh) * sq;
+  fa_delta_kernel<<<static_cast<unsigned>((rows * 8 + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, rows);
+  fa_bwd_kernel<0><<<dim3((sk + FB_B - 1) / FB_B, bh), FB_THREADS, FB_SMEM, st>>>(
+      tmK, tmV, tmQ, tmDO, lse, delta, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), sq, sk, scale, status);
+  fa_bwd_kernel<1><<<dim3((sq + FB_B - 1) / FB_B, bh), FB_THREADS, FB_SMEM, st>>>(
+      tmQ, tmDO, tmK, tmV, lse, delta, static_cast<__nv_bfloat16*>(dq), nullptr, sq, sk, scale, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

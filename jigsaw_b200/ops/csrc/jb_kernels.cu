@@ -10,5 +10,6 @@
 #include "roll.cu"
 #include "alltoall.cu"
 #include "flash_attn.cu"
+#include "flash_attn_bwd.cu"
 
 extern "C" int jb_abi_version() { return 1; }

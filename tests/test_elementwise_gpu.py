@@ -101,9 +101,9 @@ def test_cross_entropy_kernel(shape, dtype, reduction):
 
 
 @pytest.mark.parametrize("shape", [(2, 3, 128, 128), (1, 2, 300, 520), (2, 4, 1024, 2048)])
-def test_flash_attention_forward(shape):
-    """tcgen05 attention forward (head dimension 64) against fp32 attention of the same bf16 inputs:
-    output and log-sum-exp.  The kernel has not run on hardware yet, so the test runs only when
+def test_flash_attention_forward_backward(shape):
+    """tcgen05 attention (head dimension 64) against fp32 attention of the same bf16 inputs: output,
+    log-sum-exp and the three gradients.  The kernel has not run on hardware yet, so the test runs only when
     JIGSAW_FLASH_ATTENTION=1 is set."""
     import os
 
@@ -126,3 +126,13 @@ def test_flash_attention_forward(shape):
     ref = torch.softmax(t, dim=-1) @ v.float()
     assert float((lse - ref_lse).abs().max()) < 2e-2
     assert float((out.float() - ref).abs().max()) < 3e-2 * float(ref.abs().max())
+    # backward kernels against autograd of the fp32 formulation
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    g = torch.randn(b, h, sq, 64, device=dev).bfloat16()
+    (torch.softmax(scale * (qf @ kf.transpose(-1, -2)), dim=-1) @ vf).backward(g.float())
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    attention_fused.FlashAttention.apply(qg, kg, vg, scale).backward(g)
+    torch.cuda.synchronize()
+    symm.arena(dev).check_status()
+    for name, mine, ref_g in (("dq", qg.grad, qf.grad), ("dk", kg.grad, kf.grad), ("dv", vg.grad, vf.grad)):
+        assert float((mine.float() - ref_g).abs().max()) < 4e-2 * float(ref_g.abs().max()), name
