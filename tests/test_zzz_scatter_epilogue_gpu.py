@@ -1,0 +1,50 @@
+"""Scatter epilogue of the tcgen05 GEMM on one GPU: column part ``p`` of the product goes to slab ``p``.
+Sorted last among the test files on purpose: it covers tile shapes that no other single-GPU test reaches."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("staged", [False, True])
+@pytest.mark.parametrize("M,K,part_cols,b_mn", [(300, 256, 256, False), (9516, 128, 256, True), (520, 192, 64, False)])
+def test_scatter_epilogue_into_local_slabs(M, K, part_cols, b_mn, staged):
+    """The GEMM whose epilogue stores column part ``p`` of the product into slab ``p``; here both slabs
+    are buffers of this GPU, so that the epilogue's addressing is checked without peers.  The staged
+    form (tiles leave through shared memory as 128-byte row pieces) runs only when
+    JIGSAW_STAGED_EPILOGUE=1 is set: it has not been measured on hardware yet."""
+    import ctypes
+    import os
+
+    from jigsaw_b200.ops import _lib, symm
+
+    if staged and os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") != "1":
+        pytest.skip("set JIGSAW_STAGED_EPILOGUE=1 to run the staged epilogue")
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    parts = 2
+    N = parts * part_cols
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16()
+    b = B.t().contiguous() if b_mn else B
+    slabs = [torch.full((M, part_cols), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(parts)]
+    c_part = (ctypes.c_void_p * 8)()
+    for i, t in enumerate(slabs):
+        c_part[i] = t.data_ptr()
+    L = _lib.lib()
+    ar = symm.arena(dev)
+    fn = L.jb_gemm_bf16_scatter_staged if staged else L.jb_gemm_bf16_scatter
+    rc = fn(ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(b.data_ptr()), c_part, parts, part_cols, M, K, A.stride(0),
+            b.stride(0), 0, 1 if b_mn else 0, _lib.sm_count(0), ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    ar.check_status()
+    ref = A.float() @ B.float().t()
+    for i, t in enumerate(slabs):
+        assert not torch.isnan(t).any(), f"slab {i} has rows the epilogue did not write"
+        assert _rel(t, ref[:, i * part_cols:(i + 1) * part_cols]) < 1e-2
