@@ -291,6 +291,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", default="default")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay the whole step as one CUDA graph (this framework only; GraphedStep)")
     args = ap.parse_args()
     if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "jigsaw")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
@@ -323,8 +325,15 @@ def main() -> None:
         opt.step()
         return loss
 
-    for _ in range(args.warmup):
-        loss = step()
+    run = step
+    graphed = None
+    if args.graph and args.impl == "ours":
+        from jigsaw_b200.utils import GraphedStep
+
+        graphed = GraphedStep(lambda a, b: step(), (x, y), warmup=max(args.warmup, 3))
+        run = graphed.replay
+    for _ in range(0 if graphed is not None else args.warmup):
+        loss = run()
     launches0 = 0
     if args.impl == "ours":
         from jigsaw_b200.ops import _lib
@@ -335,12 +344,14 @@ def main() -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        loss = step()
+        loss = run()
     e1.record()
     torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     launches = (_lib.LAUNCHES - launches0) if args.impl == "ours" else 0
+    if graphed is not None:
+        launches = graphed.launches_per_step * args.steps
     if args.impl == "ours":
         from jigsaw_b200.ops import symm
 
@@ -349,7 +360,9 @@ def main() -> None:
         print(json.dumps({"metric": f"{args.config} samples/sec (fwd+bwd+AdamW)", "value": batch * 1000.0 / float(ms), "unit": "samples/s",
                           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(ms), "impl": args.impl,
                           "dtype": "bf16", "data": "synthetic", "config": desc, "gpu_launches": launches,
-                          "loss": float(loss)}), flush=True)
+                          "graph": graphed is not None, "loss": float(loss)}), flush=True)
+    if graphed is not None:
+        graphed.close()                      # a live graph that holds collectives blocks the teardown
     dist.destroy_process_group()
 
 
