@@ -12,7 +12,7 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("staged", [False, True])
-@pytest.mark.parametrize("M,K,part_cols,b_mn", [(300, 256, 256, False), (9516, 128, 256, True), (520, 192, 64, False)])
+@pytest.mark.parametrize("M,K,part_cols,b_mn", [(300, 256, 256, False), (9516, 128, 256, True), (520, 192, 64, False), (520, 192, 64, True), (1000, 128, 128, True)])
 def test_scatter_epilogue_into_local_slabs(M, K, part_cols, b_mn, staged):
     """The GEMM whose epilogue stores column part ``p`` of the product into slab ``p``; here both slabs
     are buffers of this GPU, so that the epilogue's addressing is checked without peers.  The staged
