@@ -16,6 +16,7 @@ cores/sdpa.py:17-165, forward.py:23-61 and _merge_kernel.py:37-172 (merge).
 
 from __future__ import annotations
 
+import os
 from typing import Any
 
 import torch
@@ -104,9 +105,41 @@ class SdpaCore:
         return dq.reshape(q.shape), dk.reshape(k.shape), dv.reshape(v.shape)
 
 
+class Tcgen05Core:
+    """Own attention kernels for head dimension 64 (``ops/attention_fused.py``); anything they do not
+    cover (other head sizes, dropout, non-bf16 data, CPU) goes to :class:`SdpaCore`.  Selected instead of
+    ``SdpaCore`` only when ``JIGSAW_FLASH_ATTENTION=1`` is set."""
+
+    name = "tcgen05"
+
+    @staticmethod
+    def _usable(q: torch.Tensor, k: torch.Tensor, dropout_p: float) -> bool:
+        return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 64 and dropout_p == 0.0
+                and q.shape[:-2] == k.shape[:-2] and not torch._C._functorch.is_batchedtensor(q))
+
+    @staticmethod
+    def forward(q, k, v, scale: float, dropout_p: float = 0.0, seed: int = 0):
+        if not Tcgen05Core._usable(q, k, dropout_p):
+            return SdpaCore.forward(q, k, v, scale, dropout_p, seed)
+        from ...ops import attention_fused
+
+        out, lse = attention_fused.flash_attention_forward(q, k, v, scale)
+        return out, lse, "tcgen05"
+
+    @staticmethod
+    def backward(dout, q, k, v, out, lse, scale: float, dropout_p: float = 0.0, rng_state: Any = None):
+        if rng_state != "tcgen05":
+            return SdpaCore.backward(dout, q, k, v, out, lse, scale, dropout_p, rng_state)
+        from ...ops import attention_fused
+
+        return attention_fused.flash_attention_backward(dout, q, k, v, out, lse, scale)
+
+
 def select_core(backend: Any) -> Any:
     name = getattr(backend, "value", backend)
-    return MathCore if name == "math" else SdpaCore
+    if name == "math":
+        return MathCore
+    return Tcgen05Core if os.environ.get("JIGSAW_FLASH_ATTENTION", "0") == "1" else SdpaCore
 
 
 def merge_chunks(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor, lse_j: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:

@@ -83,10 +83,32 @@ def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     return out.view(*lead, sq, 64), lse.view(*lead, sq)
 
 
+def flash_attention_backward(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                             lse: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of :func:`flash_attention_forward` (``csrc/flash_attn_bwd.cu``): ``lse`` is the forward's
+    log-sum-exp, ``out`` its output; returns ``(dq, dk, dv)`` in bf16 with the shapes of ``q``, ``k``, ``v``."""
+    from . import symm
+
+    sq, sk = q.shape[-2], k.shape[-2]
+    q3, k3, v3, o3, g3 = (t.to(torch.bfloat16).reshape(-1, t.shape[-2], 64).contiguous() for t in (q, k, v, out, dout))
+    bh = q3.shape[0]
+    lse2 = lse.float().reshape(bh, sq).contiguous()
+    delta = torch.empty_like(lse2)
+    dq, dk, dv = torch.empty_like(q3), torch.empty_like(k3), torch.empty_like(v3)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    rc = _lib.lib().jb_flash_attn_bwd(P(q3), P(k3), P(v3), P(o3), P(g3), P(lse2), P(delta), P(dq), P(dk), P(dv),
+                                      bh, sq, sk, float(scale), P(symm.arena(q.device).status), _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_bwd failed with code {rc}")
+    _lib.count_launches(3)
+    return dq.view(q.shape), dk.view(k.shape), dv.view(v.shape)
+
+
 class FlashAttention(torch.autograd.Function):
     """``softmax(scale * q k^T) v`` with forward and backward on the tcgen05 kernels
     (``csrc/flash_attn.cu``, ``csrc/flash_attn_bwd.cu``); same shapes as :func:`flash_attention_forward`.
-    Not called by the attention cores yet (the kernels have not run on hardware)."""
+    Not called by the attention layers unless ``JIGSAW_FLASH_ATTENTION=1`` (the kernels have not run on
+    hardware)."""
 
     @staticmethod
     def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
@@ -97,19 +119,5 @@ class FlashAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g: torch.Tensor) -> tuple:
-        from . import symm
-
         q, k, v, out, lse = ctx.saved_tensors
-        sq, sk = q.shape[-2], k.shape[-2]
-        q3, k3, v3, o3, g3 = (t.reshape(-1, t.shape[-2], 64).contiguous() for t in (q, k, v, out, g.to(torch.bfloat16)))
-        bh = q3.shape[0]
-        lse2 = lse.reshape(bh, sq).contiguous()
-        delta = torch.empty_like(lse2)
-        dq, dk, dv = torch.empty_like(q3), torch.empty_like(k3), torch.empty_like(v3)
-        P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
-        rc = _lib.lib().jb_flash_attn_bwd(P(q3), P(k3), P(v3), P(o3), P(g3), P(lse2), P(delta), P(dq), P(dk), P(dv),
-                                          bh, sq, sk, ctx.scale, P(symm.arena(q.device).status), _lib.stream_ptr())
-        if rc != 0:
-            raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_bwd failed with code {rc}")
-        _lib.count_launches(3)
-        return dq.view(q.shape), dk.view(k.shape), dv.view(v.shape), None
+        return (*flash_attention_backward(g, q, k, v, out, lse, ctx.scale), None)
