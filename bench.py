@@ -244,7 +244,7 @@ def main() -> None:
     if args.impl == "ours":
         from jigsaw_b200.ops import symm
 
-        symm.arena(dev).check_status()
+        symm.arena(dev).check_status(collective=True)      # every rank raises if any rank saw a kernel error
     if rank == 0:
         h2d = (x_host.numel() + y_host.numel()) * 4
         loss_bytes = sizes["loss"]

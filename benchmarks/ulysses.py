@@ -126,7 +126,7 @@ def main() -> None:
     res["out_max_abs_diff_vs_library"] = float((ya.float() - out_library().float()).abs().max())
     for name, fn in (("out_fused", out_fused), ("out_unfused", out_unfused), ("out_library", out_library)):
         res[name + "_ms"] = round(timed(fn, args.warmup, args.reps), 4)
-    symm.arena(dev).check_status()
+    symm.arena(dev).check_status(collective=True)
     flops = 2.0 * b * sl * args.dim * 3 * h * d
     sent = b * sl * 3 * h * d * 2 * (P - 1) / P
     peaks = {}

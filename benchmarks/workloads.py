@@ -355,7 +355,7 @@ def main() -> None:
     if args.impl == "ours":
         from jigsaw_b200.ops import symm
 
-        symm.arena(dev).check_status()
+        symm.arena(dev).check_status(collective=True)      # every rank raises if any rank saw a kernel error
     if rank == 0:
         print(json.dumps({"metric": f"{args.config} samples/sec (fwd+bwd+AdamW)", "value": batch * 1000.0 / float(ms), "unit": "samples/s",
                           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(ms), "impl": args.impl,

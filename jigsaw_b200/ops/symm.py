@@ -199,13 +199,31 @@ class PeerArena:
     def flag_ptr(self, world_rank: int, slot: int, direction: int) -> int:
         return self._flags["ptrs"][world_rank] + (slot * _FLAG_WORDS + direction) * 4
 
-    def check_status(self) -> None:
-        """Raise if any kernel recorded a bounded-wait timeout (synchronises the device)."""
-        code = int(self.status[0].item())
+    def check_status(self, group: dist.ProcessGroup | None = None, collective: bool = False) -> None:
+        """Raise if any kernel recorded a bounded-wait timeout (synchronises the device).  With
+        ``collective=True`` (or a ``group``) the code is MAX-reduced first, so that every rank of the
+        group raises when any of them saw an error: a rank whose peer never arrived and the peer that
+        was late fail together instead of one of them waiting in the next collective."""
+        if collective or group is not None:
+            code = agree_on_status(self.status[:1], group)
+        else:
+            code = int(self.status[0].item())
         if code != 0:
             self.status.zero_()
-            names = {1: "an mbarrier wait timed out", 2: "a cross-GPU flag wait timed out", 3: "bad argument"}
-            raise RuntimeError(f"jigsaw_b200 kernel error {code}: {names.get(code, 'unknown')}")
+            raise RuntimeError(f"jigsaw_b200 kernel error {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+STATUS_NAMES = {1: "an mbarrier wait timed out", 2: "a cross-GPU flag wait timed out", 3: "bad argument"}
+
+
+def agree_on_status(status: torch.Tensor, group: dist.ProcessGroup | None = None) -> int:
+    """Largest status code over the ranks of ``group`` (the world when ``None``); ``status`` is a
+    one-element integer tensor on the device of the group's backend.  Without a process group it is
+    just this rank's code."""
+    t = status.detach().clone()
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return int(t.item())
 
 
 _arenas: dict[int, PeerArena] = {}

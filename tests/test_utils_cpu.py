@@ -94,3 +94,21 @@ def test_chunk_owner_schedules_visit_every_chunk_once():
             assert sorted(owners) == list(range(P)), (op, P, A, p, owners)
     with pytest.raises(ValueError):
         chunk_owner(SendOp.HYBRID, 0, 0, 6, 4)
+
+
+def _worker_status_agreement(rank, world):
+    """A kernel error code seen by one rank reaches every rank (host-side part of the bounded waits:
+    the device tensor is replaced by a CPU tensor, the reduction is the same)."""
+    import torch
+    from jigsaw_b200.ops import symm
+
+    mine = torch.tensor([2 if rank == 1 else 0], dtype=torch.int32)
+    assert symm.agree_on_status(mine) == 2
+    assert int(mine) == (2 if rank == 1 else 0), "the local status word is left as it was"
+    assert symm.agree_on_status(torch.zeros(1, dtype=torch.int32)) == 0
+
+
+def test_kernel_status_is_agreed_over_ranks():
+    from dist_utils import run_distributed
+
+    run_distributed(_worker_status_agreement, 3, backend="gloo", timeout=120)
