@@ -257,3 +257,27 @@ LAUNCHES = 0
 def count_launches(n: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += n
+
+
+def traced(name: str):
+    """Decorator: an NVTX range named ``name`` around every call when ``JIGSAW_NVTX=1`` is set (for
+    Nsight timelines); otherwise the function is returned unchanged and costs nothing."""
+    if os.environ.get("JIGSAW_NVTX", "0") != "1":
+        return lambda fn: fn
+
+    def wrap(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            if not torch.cuda.is_available():
+                return fn(*args, **kwargs)
+            torch.cuda.nvtx.range_push(name)
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+
+        return inner
+
+    return wrap

@@ -20,6 +20,7 @@ def __getattr__(name: str):
     raise AttributeError(name)
 
 
+@_lib.traced("jb.maybe_fused_merge")
 def maybe_fused_merge(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor, lse_j: torch.Tensor):
     """In place: ``out += sigmoid(lse_j - lse) (out_j - out)``, ``lse = logaddexp(lse, lse_j)``;
     returns ``(out, lse)``, or ``None`` when the kernel does not apply (the state must be
@@ -44,6 +45,7 @@ def maybe_fused_merge(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor,
     return out, lse
 
 
+@_lib.traced("jb.flash_attention_forward")
 def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
     """``softmax(scale * q k^T) v`` and the row-wise log-sum-exp on the tcgen05 kernel of
     ``csrc/flash_attn.cu``.  ``q`` is ``(..., sq, 64)``, ``k`` and ``v`` are ``(..., sk, 64)``, all bf16 on
@@ -83,6 +85,7 @@ def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     return out.view(*lead, sq, 64), lse.view(*lead, sq)
 
 
+@_lib.traced("jb.flash_attention_backward")
 def flash_attention_backward(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                              lse: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients of :func:`flash_attention_forward` (``csrc/flash_attn_bwd.cu``): ``lse`` is the forward's

@@ -244,6 +244,7 @@ class _ConvChain(torch.autograd.Function):
         return (gx, None, None, None, *grads)
 
 
+@_lib.traced("jb.conv_chain")
 def conv_chain(x: torch.Tensor, geom: Geometry, kinds: list[str], acts: list[bool], weights: list, biases: list) -> torch.Tensor:
     """Run an eligible chain on the fused kernels.  ``x``: ``(N, C, H, W)`` local tile (any
     strides, fp32 or bf16).  Returns the output tile as a bf16 ``(N, C_out, H, W)`` tensor in
@@ -280,6 +281,7 @@ def layer_is_eligible(layer: Any, x: torch.Tensor) -> bool:
     return _lib.available()
 
 
+@_lib.traced("jb.maybe_fused_conv2d")
 def maybe_fused_conv2d(layer: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     """Single-layer entry point used by ``DistributedConv2d.forward``."""
     if not layer_is_eligible(layer, x):

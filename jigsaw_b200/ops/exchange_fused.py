@@ -30,6 +30,7 @@ def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
     return blk
 
 
+@_lib.traced("jb.maybe_fused_all_to_all")
 def maybe_fused_all_to_all(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor | None:
     """``cat(all_to_all(chunks of x along split_dim), dim=cat_dim)`` or ``None`` when the kernel
     does not apply (needs a contiguous CUDA tensor whose trailing dimensions behind both

@@ -98,6 +98,7 @@ class _FusedLinear(torch.autograd.Function):
         return dx, dw, db
 
 
+@_lib.traced("jb.maybe_fused_linear")
 def maybe_fused_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     if not x.is_cuda or w.dim() != 2 or x.numel() == 0:
         return None
@@ -250,6 +251,7 @@ class _GatherLinear(torch.autograd.Function):
         return dx, dw, db, None
 
 
+@_lib.traced("jb.maybe_fused_gather_linear")
 def maybe_fused_gather_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, group: Any) -> torch.Tensor | None:
     """``all_gather(x over group, last dim) @ w.T + b`` in one GEMM whose producer reads the other
     ranks' blocks from their memory, or ``None`` when that does not apply.  ``w`` is ``[N, K]``

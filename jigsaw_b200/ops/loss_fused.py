@@ -104,6 +104,7 @@ class _SqDiffSum(torch.autograd.Function):
         return ga, gb
 
 
+@_lib.traced("jb.maybe_fused_sq_diff_sum")
 def maybe_fused_sq_diff_sum(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor | None:
     """``sum((a - b)^2)`` as an fp32 scalar (differentiable in ``a``), or ``None`` when the
     kernel does not apply."""
@@ -169,6 +170,7 @@ class _CrossEntropyRows(torch.autograd.Function):
         return dx, None, None, None
 
 
+@_lib.traced("jb.maybe_fused_cross_entropy")
 def maybe_fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, dim: int, channel_group: Any,
                               ignore_index: int) -> torch.Tensor | None:
     """Unreduced cross-entropy (shape of ``target``, fp32, zero where ignored) for index targets,

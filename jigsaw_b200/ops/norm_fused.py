@@ -128,6 +128,7 @@ class _FusedLayerNorm(torch.autograd.Function):
         return dx.view(ctx.shape), dw, db, None, None, None
 
 
+@_lib.traced("jb.maybe_fused_layer_norm")
 def maybe_fused_layer_norm(x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None,
                            col_group: dist.ProcessGroup | None, eps: float) -> torch.Tensor | None:
     """LayerNorm of the last dimension of ``x`` (split over ``col_group``) with the fused
@@ -229,6 +230,7 @@ class _FusedGroupNorm(torch.autograd.Function):
         return dx, dw, db, None, None, None, None
 
 
+@_lib.traced("jb.maybe_fused_group_norm")
 def maybe_fused_group_norm(x: torch.Tensor, groups_local: int, w: torch.Tensor | None, b: torch.Tensor | None,
                            spatial_groups: list, eps: float) -> torch.Tensor | None:
     """GroupNorm with statistics over the tiles of ``spatial_groups`` on the fused kernels, or

@@ -117,6 +117,7 @@ def _launch(x: torch.Tensor, shifts: tuple, dims: tuple, groups: tuple) -> torch
     return blk.tensor[_HEADER:_HEADER + nbytes].view(x.dtype).view(shape).clone()
 
 
+@_lib.traced("jb.maybe_fused_roll")
 def maybe_fused_roll(x: torch.Tensor, shifts: tuple, dims: tuple, where: dict) -> torch.Tensor | None:
     """Roll ``x`` by ``shifts`` along ``dims``; ``where`` maps a dimension to the group that tiles
     it.  ``None`` when the kernel does not apply."""

@@ -218,6 +218,7 @@ class _UlyssesOut(torch.autograd.Function):
         return do, dw, db, None
 
 
+@_lib.traced("jb.maybe_fused_ulysses_out")
 def maybe_fused_ulysses_out(o: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, group: Any) -> torch.Tensor | None:
     """``heads_to_seq(o).flatten(-2) @ w.T + bias`` as ``(b, s / P, N)`` in bf16 with the exchange fused
     into the GEMM's operand loads, or ``None`` when that does not apply.  ``o`` is ``(b, s, heads / P,
@@ -241,6 +242,7 @@ def maybe_fused_ulysses_out(o: torch.Tensor, w: torch.Tensor, bias: torch.Tensor
     return _UlyssesOut.apply(o, w, bias, group)
 
 
+@_lib.traced("jb.maybe_fused_ulysses_qkv")
 def maybe_fused_ulysses_qkv(x: torch.Tensor, w: torch.Tensor, group: Any, heads: int, head_dim: int) -> torch.Tensor | None:
     """``seq_to_heads(split_heads(x @ w.T))`` as ``(3, b, s, heads / P, head_dim)`` in bf16 with the
     exchange fused into the GEMM epilogue, or ``None`` when that does not apply.  ``x`` is
