@@ -81,3 +81,22 @@ def test_torchrun_launch():
         env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     assert "step   0" in out.stderr + out.stdout
+
+
+def test_cpu_gloo_cnn_workload_matches_undivided_model():
+    """The CPU / gloo workload of the benchmarks (four ranks, fp32, two convolutions, Adam): ten steps must
+    follow the undivided PyTorch model to rounding."""
+    import json
+
+    env = {k: v for k, v in os.environ.items() if not k.startswith("SLURM_")}
+    env["CUDA_VISIBLE_DEVICES"] = ""
+    script = os.path.join(os.path.dirname(EXAMPLES), "benchmarks", "cpu_cnn.py")
+    out = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
+         "--master-port", "29633", script, "--steps", "2", "--image", "128"],
+        env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = [ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1]
+    res = json.loads(line)
+    assert res["impl"] == "ours" and res["world"] == 4
+    assert res["max_loss_diff_vs_undivided"] < 1e-5 and res["max_param_diff_vs_undivided"] < 1e-5
