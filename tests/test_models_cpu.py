@@ -173,3 +173,39 @@ def _worker_checkpoint(rank, world, tmp):
 
 def test_sharded_checkpoint_across_meshes(tmp_path):
     run_distributed(_worker_checkpoint, 4, str(tmp_path))
+
+
+def _worker_reshard_hops(rank, world):
+    """A ViT (patch convolution, layer norms, attention, block linears) carried 2x2 -> 1x4 -> 4x1 -> 2x2 with
+    ``reshard_parameters``: after every hop the gathered state equals the original, and back on the first
+    mesh the model computes what it computed before."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import ViT, ViTConfig
+
+    meshes = [jb.make_process_mesh({"row": 2, "col": 2}), jb.make_process_mesh({"row": 1, "col": 4}),
+              jb.make_process_mesh({"row": 4, "col": 1})]
+    cfg = ViTConfig(image_size=(16, 32), depth=1, heads=4, num_classes=None, sequence_parallel="ulysses", attn_backend="math")
+    jb.launch.set_all_seeds(7 + meshes[0]["model"].rank())
+    model = ViT(meshes[0], "cpu", cfg)
+    torch.manual_seed(3)
+    x = torch.randn(2, 4, 16, 32)
+    xl = split(x, {1: meshes[0]["col"], 3: meshes[0]["row"]})
+    with torch.no_grad():
+        y0 = model(xl)
+    state0 = {k: v.clone() for k, v in checkpoint.full_state_dict(model).items()}
+    hops = [(0, 1), (1, 2), (2, 0)]
+    for a, b in hops:
+        for layer in model.modules():
+            if hasattr(layer, "reshard_parameters"):
+                layer.reshard_parameters(meshes[a], meshes[b])
+        state = checkpoint.full_state_dict(model)
+        assert state.keys() == state0.keys()
+        for k in state0:
+            assert_close(state[k], state0[k], f"hop {a}->{b}: {k}", 0, 0)
+    with torch.no_grad():
+        assert_close(model(xl), y0, "output after the round trip", 0, 1e-6)
+
+
+def test_reshard_multi_hop_round_trip():
+    run_distributed(_worker_reshard_hops, 4)

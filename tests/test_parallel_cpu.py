@@ -63,7 +63,7 @@ def _worker_marks_and_sync(rank, world):
     assert jb.debug.count_parameters(model, mesh) == serial
     assert jb.debug.count_parameters(model) == serial
     # clipping equals torch on the unsharded model
-    for norm in (2.0, 1.0, float("inf")):
+    for norm in (2.0, 1.0, 3.0, float("inf")):
         model.zero_grad()
         x = torch.randn(1, 2, 4, 4)
         model(x).square().sum().backward()
