@@ -15,7 +15,8 @@ Every distributed layer describes its own cut with ``shard_spec()`` (parameter n
     a replicated weight - do not write) plus ``manifest.json`` with the mesh axis sizes and,
     per tensor, the global shape and which dimension is cut over which axis.  Loading works on
     any mesh whose cuts divide the global shapes: every rank reads just the blocks that
-    overlap its own shard.
+    overlap its own shard.  With ``optimizer=`` the optimizer's state travels too (moments cut
+    like their parameters, counters and hyper-parameters in the manifest): resume on any mesh.
 
 Reference parity: the reference has no checkpoint module; its documented recipe is "ranks with
 dp rank 0 save one ``state_dict`` per model rank" (examples/ddp.py:20-22) and
@@ -141,21 +142,14 @@ def _mesh_groups(mesh: Any) -> dict[str, dist.ProcessGroup]:
     return {n: mesh[n] for n in names}
 
 
-def _shard_file(coord: Mapping[str, int]) -> str:
-    return "shard" + "".join(f"-{a}{i}" for a, i in sorted(coord.items())) + ".pt"
+def _shard_file(coord: Mapping[str, int], stem: str = "shard") -> str:
+    return stem + "".join(f"-{a}{i}" for a, i in sorted(coord.items())) + ".pt"
 
 
-def save_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike, extra: dict | None = None) -> None:
-    """Write this model's shards and the manifest into ``directory`` (collective).
-
-    ``extra`` (JSON-serialisable: step counter, hyper-parameters ...) goes into the manifest.
-    """
-    groups = _mesh_groups(mesh)
-    layout = parameter_layout(model)
-    state = model.state_dict()
+def _describe(state: Mapping[str, torch.Tensor], layout: Layout, orders: dict, groups: dict) -> tuple[dict, set]:
+    """Manifest entries of ``state`` and the mesh axes that cut any of its tensors."""
     cut_axes: set[str] = set()
     entries: dict[str, dict] = {}
-    orders = row_orders(model)
     for key, value in state.items():
         cuts = [(d, _axis_of(g, groups)) for d, g in layout[key]]
         shape = list(value.shape)
@@ -165,6 +159,60 @@ def save_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike
         entries[key] = {"shape": shape, "dtype": str(value.dtype).removeprefix("torch."), "cuts": cuts}
         if key in orders:
             entries[key]["rows"] = orders[key][0]
+    return entries, cut_axes
+
+
+def _optimizer_tensors(model: torch.nn.Module, optimizer: torch.optim.Optimizer) -> tuple[dict[str, dict], dict[str, dict]]:
+    """Optimizer state by parameter name: ``{state name: {parameter key: tensor}}`` for the entries
+    shaped like their parameter (moments, momentum buffers), which are cut like the parameter, and
+    ``{parameter key: {state name: number}}`` for the scalar entries (step counters)."""
+    names = {id(p): key for key, p in model.named_parameters()}
+    shaped: dict[str, dict] = {}
+    scalars: dict[str, dict] = {}
+    for p, st in optimizer.state.items():
+        key = names.get(id(p))
+        if key is None:
+            continue
+        for name, val in st.items():
+            if torch.is_tensor(val) and val.dim() > 0 and val.shape == p.shape:
+                shaped.setdefault(name, {})[key] = val
+            elif torch.is_tensor(val) and val.numel() == 1:
+                scalars.setdefault(key, {})[name] = float(val)
+            elif isinstance(val, (int, float)):
+                scalars.setdefault(key, {})[name] = val
+    return shaped, scalars
+
+
+def _group_settings(optimizer: torch.optim.Optimizer) -> list[dict]:
+    """JSON-able hyper-parameters of every parameter group, and the device-side step counter that
+    :class:`jigsaw_b200.optim.FusedAdam` keeps per group (``fused_step``)."""
+    out = []
+    for group in optimizer.param_groups:
+        entry: dict[str, Any] = {}
+        for k, v in group.items():
+            if isinstance(k, str) and k != "params" and isinstance(v, (int, float, bool, str, list, tuple, type(None))):
+                entry[k] = list(v) if isinstance(v, tuple) else v
+            elif isinstance(k, tuple) and k and k[0] == "step" and torch.is_tensor(v):
+                entry["fused_step"] = max(float(v), entry.get("fused_step", 0.0))
+        out.append(entry)
+    return out
+
+
+def save_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike, extra: dict | None = None,
+                 optimizer: torch.optim.Optimizer | None = None) -> None:
+    """Write this model's shards and the manifest into ``directory`` (collective).
+
+    ``extra`` (JSON-serialisable: step counter, hyper-parameters ...) goes into the manifest.  With
+    ``optimizer`` its state is written too: entries shaped like their parameter (Adam moments, momentum
+    buffers) as shards cut like the parameter, scalar entries and the groups' hyper-parameters in the
+    manifest, so that training resumes on any mesh (:func:`load_sharded` with the new optimizer).
+    """
+    groups = _mesh_groups(mesh)
+    layout = parameter_layout(model)
+    state = model.state_dict()
+    orders = row_orders(model)
+    entries, cut_axes = _describe(state, layout, orders, groups)
+    shaped, scalars = _optimizer_tensors(model, optimizer) if optimizer is not None else ({}, {})
     directory = Path(directory)
     rank = dist.get_rank()
     if rank == 0:
@@ -173,9 +221,11 @@ def save_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike
     axes = sorted(cut_axes)
     # a rank writes iff it is the first copy: coordinate 0 on every axis that cuts nothing
     writer = all(g.rank() == 0 for a, g in groups.items() if a not in cut_axes)
+    coord = {a: groups[a].rank() for a in axes}
     if writer:
-        coord = {a: groups[a].rank() for a in axes}
         torch.save({k: v.detach().cpu() for k, v in state.items()}, directory / _shard_file(coord))
+        for name, tensors in shaped.items():
+            torch.save({k: v.detach().cpu() for k, v in tensors.items()}, directory / _shard_file(coord, f"optim-{name}"))
     if rank == 0:
         manifest = {
             "format": FORMAT,
@@ -184,36 +234,97 @@ def save_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike
             "tensors": entries,
             "extra": extra or {},
         }
+        if optimizer is not None:
+            manifest["optimizer"] = {
+                "class": type(optimizer).__name__,
+                "states": {name: _describe(tensors, layout, orders, groups)[0] for name, tensors in shaped.items()},
+                "scalars": scalars,
+                "groups": _group_settings(optimizer),
+            }
         (directory / MANIFEST).write_text(json.dumps(manifest, indent=1))
     dist.barrier()
 
 
-def load_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike, strict: bool = True) -> dict:
+def load_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike, strict: bool = True,
+                 optimizer: torch.optim.Optimizer | None = None) -> dict:
     """Fill ``model`` (sharded over ``mesh``) from a checkpoint written on any mesh; returns the
-    manifest's ``extra``.  Each rank reads only the files whose blocks overlap its shards."""
+    manifest's ``extra``.  Each rank reads only the files whose blocks overlap its shards.
+
+    With ``optimizer`` (built over ``model.parameters()``) its state is restored from a checkpoint
+    that was saved with one: moments are cut for this mesh like the parameters, step counters and the
+    groups' hyper-parameters (learning rate included) come from the manifest."""
     directory = Path(directory)
     manifest = json.loads((directory / MANIFEST).read_text())
     if manifest.get("format") != FORMAT:
         raise ValueError(f"unknown checkpoint format {manifest.get('format')!r}")
-    groups = _mesh_groups(mesh)
     layout = parameter_layout(model)
     own = model.state_dict()
-    src_sizes: dict[str, int] = manifest["axes"]
-    src_axes: list[str] = manifest["shard_axes"]
     tensors: dict[str, dict] = manifest["tensors"]
     missing = [k for k in own if k not in tensors]
     unexpected = [k for k in tensors if k not in own]
     if strict and (missing or unexpected):
         raise KeyError(f"checkpoint mismatch: missing {missing}, unexpected {unexpected}")
+    orders = row_orders(model)
+    _fill(own, tensors, layout, orders, manifest, directory, "shard")
+    if optimizer is not None:
+        saved = manifest.get("optimizer")
+        if saved is None:
+            raise KeyError("the checkpoint holds no optimizer state")
+        _restore_optimizer(model, optimizer, saved, layout, orders, manifest, directory)
+    return manifest.get("extra", {})
+
+
+def _restore_optimizer(model: torch.nn.Module, optimizer: torch.optim.Optimizer, saved: dict, layout: Layout, orders: dict,
+                       manifest: dict, directory: Path) -> None:
+    params = dict(model.named_parameters())
+    for name, entries in saved["states"].items():
+        own = {}
+        for key in entries:
+            if key not in params:
+                raise KeyError(f"optimizer state for unknown parameter {key}")
+            st = optimizer.state[params[key]]
+            if name not in st or not torch.is_tensor(st[name]) or st[name].shape != params[key].shape:
+                st[name] = torch.zeros_like(params[key], memory_format=torch.preserve_format)
+            own[key] = st[name]
+        _fill(own, entries, layout, orders, manifest, directory, f"optim-{name}")
+    fused = type(optimizer).__name__ == "FusedAdam"
+    for key, values in saved["scalars"].items():
+        if key not in params:
+            continue
+        st = optimizer.state[params[key]]
+        for name, val in values.items():
+            if torch.is_tensor(st.get(name)):
+                st[name].fill_(val)
+            elif fused or name != "step":
+                st[name] = val
+            else:                                   # PyTorch's optimizers keep their step counters as fp32 scalars
+                st[name] = torch.tensor(float(val), dtype=torch.float32)
+    for group, settings in zip(optimizer.param_groups, saved["groups"]):
+        step = settings.get("fused_step")
+        for k, v in settings.items():
+            if k != "fused_step" and k in group:
+                group[k] = tuple(v) if isinstance(group[k], tuple) and isinstance(v, list) else v
+        if step is not None:
+            for p in group["params"]:
+                if p.is_cuda:
+                    group[("step", p.device)] = torch.full((), float(step), dtype=torch.float32, device=p.device)
+                elif "exp_avg" in optimizer.state[p]:
+                    optimizer.state[p].setdefault("step", int(step))
+
+
+def _fill(own: Mapping[str, torch.Tensor], tensors: Mapping[str, dict], layout: Layout, orders: dict, manifest: dict,
+          directory: Path, stem: str) -> None:
+    """Copy into every tensor of ``own`` (this rank's blocks, cut as ``layout`` says) its part of the
+    global tensors that the files ``<stem>-<coordinates>.pt`` hold in the source mesh's blocks."""
+    src_sizes: dict[str, int] = manifest["axes"]
+    src_axes: list[str] = manifest["shard_axes"]
     files: dict[str, dict] = {}
 
     def read(coord: dict[str, int]) -> dict:
-        name = _shard_file(coord)
+        name = _shard_file(coord, stem)
         if name not in files:
             files[name] = torch.load(directory / name, map_location="cpu", weights_only=True)
         return files[name]
-
-    orders = row_orders(model)
 
     def assemble(key: str, entry: dict) -> torch.Tensor:
         """The whole global tensor from every source block (used when rows must be reordered)."""
@@ -280,4 +391,3 @@ def load_sharded(model: torch.nn.Module, mesh: Any, directory: str | os.PathLike
                     if d not in src_cut.values() and (lo[d], hi[d]) != (0, shape[d]):
                         src = src.narrow(d, lo[d], hi[d] - lo[d])
                 dst.copy_(src.to(device=target.device, dtype=target.dtype))
-    return manifest.get("extra", {})

@@ -209,3 +209,56 @@ def _worker_reshard_hops(rank, world):
 
 def test_reshard_multi_hop_round_trip():
     run_distributed(_worker_reshard_hops, 4)
+
+
+def _worker_resume(rank, world, tmp, which):
+    """Two steps on a 2 x 2 mesh, checkpoint with the optimizer, two more steps on a 1 x 4 mesh from the
+    checkpoint: the result equals four uninterrupted steps."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import ViT, ViTConfig
+    from jigsaw_b200.optim import FusedAdam
+
+    cfg = ViTConfig(image_size=(16, 32), depth=1, heads=4, attn_backend="math")
+    make_opt = (lambda ps: FusedAdam(ps, lr=1e-2)) if which == "fused" else (lambda ps: torch.optim.Adam(ps, lr=1e-2))
+    torch.manual_seed(0)
+    xs = [torch.randn(2, 4, 16, 32) for _ in range(4)]
+
+    def train(model, opt, mesh, batches):
+        cuts = {1: mesh["col"], 3: mesh["row"]}
+        loss_fn = jb.modules.DistributedMSELoss(reduce_groups=(mesh["row"], mesh["col"]))
+        for x in batches:
+            loss = loss_fn(model(split(x, cuts)), split(torch.zeros_like(x), cuts))
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+
+    mesh_a = jb.make_process_mesh({"row": 2, "col": 2})
+    mesh_b = jb.make_process_mesh({"row": 1, "col": 4})
+    jb.launch.set_all_seeds(11 + mesh_a["model"].rank())
+    straight = ViT(mesh_a, "cpu", cfg)
+    start = checkpoint.full_state_dict(straight)
+    opt = make_opt(straight.parameters())
+    train(straight, opt, mesh_a, xs)
+    want = checkpoint.full_state_dict(straight)
+
+    first = ViT(mesh_a, "cpu", cfg)
+    checkpoint.load_full_state_dict(first, start)
+    opt1 = make_opt(first.parameters())
+    train(first, opt1, mesh_a, xs[:2])
+    checkpoint.save_sharded(first, mesh_a, tmp, extra={"step": 2}, optimizer=opt1)
+    second = ViT(mesh_b, "cpu", cfg)
+    opt2 = make_opt(second.parameters())
+    for g in opt2.param_groups:
+        g["lr"] = 123.0                                    # must be replaced by the saved value
+    assert checkpoint.load_sharded(second, mesh_b, tmp, optimizer=opt2) == {"step": 2}
+    assert opt2.param_groups[0]["lr"] == 1e-2
+    train(second, opt2, mesh_b, xs[2:])
+    got = checkpoint.full_state_dict(second)
+    for k in want:
+        assert_close(got[k], want[k], f"{which}: {k} after resuming on another mesh", 1e-4, 1e-6)
+
+
+@pytest.mark.parametrize("which", ["fused", "torch"])
+def test_resume_with_optimizer_on_another_mesh(tmp_path, which):
+    run_distributed(_worker_resume, 4, str(tmp_path), which)
