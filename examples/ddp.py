@@ -9,7 +9,7 @@
 * A **replica check** (``assert_replica_consistency``) every few steps raises on every rank if a
   replicated weight has drifted apart, the symptom of a gradient that is not summed over its copies.
 * **Checkpoint**: ``jigsaw_b200.checkpoint.save_sharded`` writes one file per model shard (copies do not
-  write) and a manifest that any other mesh can load.
+  write), the optimizer's moments cut the same way, and a manifest that any other mesh can load.
 
     torchrun --nproc-per-node 8 examples/ddp.py        # 4 ranks also run: a single copy
 
@@ -70,7 +70,7 @@ def main(steps: int = 100, joint_hook: bool = True) -> list[float]:
             jb.log.info("step %3d  loss %.4f", step, losses[-1])
     holder = [tempfile.mkdtemp() if rank == 0 else None]
     dist.broadcast_object_list(holder, src=0)
-    jb.checkpoint.save_sharded(ddp.module, mesh, holder[0], extra={"steps": steps})
+    jb.checkpoint.save_sharded(ddp.module, mesh, holder[0], extra={"steps": steps}, optimizer=opt)
     jb.log.info("checkpoint with one file per model shard in %s", holder[0])
     return losses
 
