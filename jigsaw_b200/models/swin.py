@@ -29,6 +29,7 @@ from collections.abc import Mapping
 from dataclasses import dataclass
 
 import torch
+import torch.utils.checkpoint
 import torch.distributed as dist
 import torch.nn.functional as F
 from torch import nn
@@ -52,6 +53,7 @@ class SwinConfig:
     mlp_ratio: int = 4
     num_classes: int | None = None
     dtype: torch.dtype = torch.float32
+    recompute_blocks: bool = False      # activation checkpointing: keep only each layer's input, recompute in backward
 
 
 def window_partition(x: torch.Tensor, ws: int) -> torch.Tensor:
@@ -215,6 +217,11 @@ class Swin(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         z = self.embed(x).permute(0, 2, 3, 1).contiguous()           # (B, h, w, C / col)
-        z = self.norm(self.layers(z)).permute(0, 3, 1, 2).contiguous()
+        if self.cfg.recompute_blocks and torch.is_grad_enabled() and z.requires_grad:
+            for layer in self.layers:                                 # same order on every rank: collectives stay matched
+                z = torch.utils.checkpoint.checkpoint(layer, z, use_reentrant=False)
+        else:
+            z = self.layers(z)
+        z = self.norm(z).permute(0, 3, 1, 2).contiguous()
         out = self.decode(z)
         return out if self.cfg.num_classes is not None else x + out

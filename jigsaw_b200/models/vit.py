@@ -26,6 +26,7 @@ from collections.abc import Mapping
 from dataclasses import dataclass
 
 import torch
+import torch.utils.checkpoint
 import torch.distributed as dist
 from torch import nn
 
@@ -56,6 +57,7 @@ class ViTConfig:
     sequence_parallel: str = "ring"     # "ring" | "ulysses"
     attn_backend: str = "sdpa"
     dtype: torch.dtype = torch.float32
+    recompute_blocks: bool = False      # activation checkpointing: keep only each block's input, recompute in backward
 
 
 def sincos_position(dim: int, h_idx: torch.Tensor, w_idx: torch.Tensor) -> torch.Tensor:
@@ -141,7 +143,12 @@ class ViT(nn.Module):
         b, e, hp, wp = z.shape
         z = (z.permute(0, 2, 3, 1) + self.pos_embed.to(z.dtype)).reshape(b, hp * wp, e).contiguous()
         for blk in self.blocks:
-            z = blk(z)
+            if self.cfg.recompute_blocks and torch.is_grad_enabled() and z.requires_grad:
+                # every rank recomputes the same block at the same point of its backward pass, so the
+                # collectives inside the block stay matched
+                z = torch.utils.checkpoint.checkpoint(blk, z, use_reentrant=False)
+            else:
+                z = blk(z)
         return self.norm(z)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

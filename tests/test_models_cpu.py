@@ -262,3 +262,62 @@ def _worker_resume(rank, world, tmp, which):
 @pytest.mark.parametrize("which", ["fused", "torch"])
 def test_resume_with_optimizer_on_another_mesh(tmp_path, which):
     run_distributed(_worker_resume, 4, str(tmp_path), which)
+
+
+def _worker_recompute(rank, world):
+    """Activation checkpointing of the transformer blocks (ring and Ulysses attention inside) leaves the
+    loss and every gradient unchanged."""
+    import dataclasses
+
+    import jigsaw_b200 as jb
+    from jigsaw_b200.models import ViT, ViTConfig
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    torch.manual_seed(2)
+    x = torch.randn(2, 4, 16, 32)
+    cuts = {1: mesh["col"], 3: mesh["row"]}
+    for seq in ("ring", "ulysses"):
+        cfg = ViTConfig(image_size=(16, 32), depth=2, heads=4, sequence_parallel=seq, attn_backend="math")
+        jb.launch.set_all_seeds(5 + mesh["model"].rank())
+        plain = ViT(mesh, "cpu", cfg)
+        saving = ViT(mesh, "cpu", dataclasses.replace(cfg, recompute_blocks=True))
+        saving.load_state_dict(plain.state_dict())
+        loss_fn = jb.modules.DistributedMSELoss(reduce_groups=(mesh["row"], mesh["col"]))
+        outs = []
+        for model in (plain, saving):
+            loss = loss_fn(model(split(x, cuts)), split(torch.zeros_like(x), cuts))
+            loss.backward()
+            outs.append(loss.detach())
+        assert_close(outs[1], outs[0], f"{seq}: loss with recomputation", 0, 1e-7)
+        for (n, p), q in zip(plain.named_parameters(), saving.parameters()):
+            assert_close(q.grad, p.grad, f"{seq}: gradient of {n} with recomputation", 1e-5, 1e-7)
+
+
+def test_vit_block_recomputation_keeps_gradients():
+    run_distributed(_worker_recompute, 4)
+
+
+def _worker_recompute_swin(rank, world):
+    """The same for the Swin layers (rolls, window attention, patch merging inside the recomputed part)."""
+    import dataclasses
+
+    import jigsaw_b200 as jb
+    from jigsaw_b200.models import Swin, SwinConfig
+
+    mesh = jb.make_process_mesh({"sh": 2, "sw": 1, "col": 2})
+    cfg = SwinConfig(image_size=(32, 32), in_channels=2, patch=2, dims=(8, 16), heads=(2, 4), depths=(2, 2), window=4)
+    jb.launch.set_all_seeds(7 + mesh["col"].rank())
+    plain = Swin(mesh, "cpu", cfg)
+    saving = Swin(mesh, "cpu", dataclasses.replace(cfg, recompute_blocks=True))
+    saving.load_state_dict(plain.state_dict())
+    torch.manual_seed(3)
+    x = torch.randn(2, 2, 32, 32)
+    cuts = {1: mesh["col"], 2: mesh["sh"], 3: mesh["sw"]}
+    for model in (plain, saving):
+        model(split(x, cuts)).square().sum().backward()
+    for (n, p), q in zip(plain.named_parameters(), saving.parameters()):
+        assert_close(q.grad, p.grad, f"swin: gradient of {n} with recomputation", 1e-5, 1e-7)
+
+
+def test_swin_layer_recomputation_keeps_gradients():
+    run_distributed(_worker_recompute_swin, 4)
