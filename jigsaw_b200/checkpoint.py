@@ -192,6 +192,8 @@ def _group_settings(optimizer: torch.optim.Optimizer) -> list[dict]:
         for k, v in group.items():
             if isinstance(k, str) and k != "params" and isinstance(v, (int, float, bool, str, list, tuple, type(None))):
                 entry[k] = list(v) if isinstance(v, tuple) else v
+            elif isinstance(k, str) and torch.is_tensor(v) and v.numel() == 1:
+                entry[k] = float(v)                     # a device-side hyper-parameter (learning rate as a tensor)
             elif isinstance(k, tuple) and k and k[0] == "step" and torch.is_tensor(v):
                 entry["fused_step"] = max(float(v), entry.get("fused_step", 0.0))
         out.append(entry)
@@ -303,7 +305,10 @@ def _restore_optimizer(model: torch.nn.Module, optimizer: torch.optim.Optimizer,
         step = settings.get("fused_step")
         for k, v in settings.items():
             if k != "fused_step" and k in group:
-                group[k] = tuple(v) if isinstance(group[k], tuple) and isinstance(v, list) else v
+                if torch.is_tensor(group[k]):
+                    group[k].fill_(v)
+                else:
+                    group[k] = tuple(v) if isinstance(group[k], tuple) and isinstance(v, list) else v
         if step is not None:
             for p in group["params"]:
                 if p.is_cuda:

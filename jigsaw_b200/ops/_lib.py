@@ -174,6 +174,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_adam_multi.argtypes = [POINTER(JbAdamTensors), c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p,
                                 c_void_p, c_void_p]
     L.jb_adam_multi.restype = c_int
+    L.jb_adam_multi_lr.argtypes = [POINTER(JbAdamTensors), c_void_p, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p,
+                                   c_void_p, c_void_p]
+    L.jb_adam_multi_lr.restype = c_int
     L.jb_sumsq_multi.argtypes = [POINTER(JbAdamTensors), c_void_p, c_void_p, c_void_p, c_void_p]
     L.jb_sumsq_multi.restype = c_int
     L.jb_chunks.argtypes = [c_longlong]

@@ -261,7 +261,7 @@ struct AdamHyper {
   const float* grad_scale;  // optional device scalar multiplied into every gradient (clipping), may be null
 };
 
-__global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamTable t, const AdamHyper h) {
+__device__ __forceinline__ void adam_update(const AdamTable& t, const AdamHyper& h, const float lr) {
   // which tensor does this block's chunk belong to (few tensors: linear scan)
   int ti = 0;
   while (ti + 1 < t.count && static_cast<int>(blockIdx.x) >= t.first_chunk[ti + 1]) ++ti;
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamT
   const float step = __ldg(h.step);
   const float c1 = 1.f - __powf(h.beta1, step);
   const float c2 = 1.f - __powf(h.beta2, step);
-  const float step_size = h.lr / c1;
+  const float step_size = lr / c1;
   const float inv_sqrt_c2 = rsqrtf(c2);
   const float gs = h.grad_scale != nullptr ? __ldg(h.grad_scale) : 1.f;
   float* p = t.p[ti];
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamT
     if (h.maximize) grad = -grad;
     float w = p[i];
     if (h.weight_decay != 0.f) {
-      if (h.decoupled) w *= 1.f - h.lr * h.weight_decay;
+      if (h.decoupled) w *= 1.f - lr * h.weight_decay;
       else grad += h.weight_decay * w;
     }
     const float mi = h.beta1 * m[i] + (1.f - h.beta1) * grad;
@@ -291,6 +291,17 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamT
     v[i] = vi;
     p[i] = w - step_size * mi / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
   }
+}
+
+__global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ AdamTable t, const AdamHyper h) {
+  adam_update(t, h, h.lr);
+}
+
+// The same update with the learning rate read from device memory, so that a schedule can change it between
+// replays of a CUDA graph that captured the launch.
+__global__ void __launch_bounds__(256) adam_lr_kernel(const __grid_constant__ AdamTable t, const AdamHyper h,
+                                                      const float* __restrict__ lr) {
+  adam_update(t, h, __ldg(lr));
 }
 
 // Sum of squares of up to ADAM_MAX_TENSORS tensors (gradient norm): per-block partials, then the
@@ -453,6 +464,18 @@ extern "C" int jb_adam_multi(const JbAdamTensors* tensors, float lr, float beta1
   if (chunks <= 0) return -1;
   AdamHyper h{lr, beta1, beta2, eps, weight_decay, decoupled, maximize, step, grad_scale};
   adam_kernel<<<chunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(t, h);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// The same step with the learning rate in device memory (`lr`: one float).
+extern "C" int jb_adam_multi_lr(const JbAdamTensors* tensors, const float* lr, float beta1, float beta2, float eps,
+                                float weight_decay, int decoupled, int maximize, const float* step,
+                                const float* grad_scale, void* stream) {
+  AdamTable t{};
+  const int chunks = adam_table(&t, tensors);
+  if (chunks <= 0 || lr == nullptr) return -1;
+  AdamHyper h{0.f, beta1, beta2, eps, weight_decay, decoupled, maximize, step, grad_scale};
+  adam_lr_kernel<<<chunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(t, h, lr);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

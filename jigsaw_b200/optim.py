@@ -38,11 +38,15 @@ def _table(params, grads, ms, vs) -> "_lib.JbAdamTensors":
 
 
 class FusedAdam(torch.optim.Optimizer):
-    """Adam (``decoupled_weight_decay=False``) or AdamW (``True``) with bias correction."""
+    """Adam (``decoupled_weight_decay=False``) or AdamW (``True``) with bias correction.
+
+    ``lr`` may be a one-element fp32 tensor on the parameters' device: the kernel then reads it from
+    memory at every step, so a schedule can change it (``group["lr"].fill_(x)``) between replays of a
+    CUDA graph that captured the step."""
 
     def __init__(self, params: Iterable, lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, decoupled_weight_decay: bool = False, maximize: bool = False) -> None:
-        if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
+        if float(lr) < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("invalid Adam hyper-parameter")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                       decoupled_weight_decay=decoupled_weight_decay, maximize=maximize))
@@ -86,10 +90,17 @@ class FusedAdam(torch.optim.Optimizer):
                         chunk = ps[i:i + _MAX]
                         tab = _table(chunk, [p.grad for p in chunk], [self.state[p]["exp_avg"] for p in chunk],
                                      [self.state[p]["exp_avg_sq"] for p in chunk])
-                        rc = L.jb_adam_multi(ctypes.byref(tab), group["lr"], b1, b2, group["eps"], group["weight_decay"],
-                                             int(group["decoupled_weight_decay"]), int(group["maximize"]),
-                                             ctypes.c_void_p(step.data_ptr()),
-                                             None if grad_scale is None else ctypes.c_void_p(grad_scale.data_ptr()), st_ptr)
+                        tail = (b1, b2, group["eps"], group["weight_decay"], int(group["decoupled_weight_decay"]),
+                                int(group["maximize"]), ctypes.c_void_p(step.data_ptr()),
+                                None if grad_scale is None else ctypes.c_void_p(grad_scale.data_ptr()), st_ptr)
+                        lr = group["lr"]
+                        if torch.is_tensor(lr):
+                            # a device scalar: a schedule may overwrite it between replays of a captured step
+                            if lr.device != dev or lr.dtype != torch.float32 or lr.numel() != 1:
+                                raise ValueError("a tensor learning rate must be one fp32 value on the parameters' device")
+                            rc = L.jb_adam_multi_lr(ctypes.byref(tab), ctypes.c_void_p(lr.data_ptr()), *tail)
+                        else:
+                            rc = L.jb_adam_multi(ctypes.byref(tab), lr, *tail)
                         if rc != 0:
                             raise RuntimeError(f"jigsaw_b200 kernel launcher adam_multi failed with code {rc}")
                     _lib.count_launches(1 + (len(ps) + _MAX - 1) // _MAX)
@@ -100,13 +111,13 @@ class FusedAdam(torch.optim.Optimizer):
                 g = -g if group["maximize"] else g
                 if group["weight_decay"]:
                     if group["decoupled_weight_decay"]:
-                        p.mul_(1 - group["lr"] * group["weight_decay"])
+                        p.mul_(1 - float(group["lr"]) * group["weight_decay"])
                     else:
                         g = g.add(p, alpha=group["weight_decay"])
                 st["exp_avg"].mul_(b1).add_(g, alpha=1 - b1)
                 st["exp_avg_sq"].mul_(b2).addcmul_(g, g, value=1 - b2)
                 c1, c2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
-                p.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / c2).sqrt_().add_(group["eps"]), value=-group["lr"] / c1)
+                p.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / c2).sqrt_().add_(group["eps"]), value=-float(group["lr"]) / c1)
         return loss
 
 

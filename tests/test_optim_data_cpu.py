@@ -63,3 +63,25 @@ def _worker_data(rank, world, tmp):
 
 def test_tile_dataset_and_sampler(tmp_path):
     run_distributed(_worker_data, 4, str(tmp_path))
+
+
+def test_fused_adam_with_tensor_learning_rate_on_cpu():
+    """A learning rate given as a one-element tensor (the form that a CUDA graph can read at replay time)
+    gives the same updates as the float, and changing it in place changes the next step."""
+    from jigsaw_b200.optim import FusedAdam
+
+    torch.manual_seed(0)
+    a = torch.nn.Parameter(torch.randn(7))
+    b = torch.nn.Parameter(a.detach().clone())
+    lr = torch.tensor(1e-2)
+    oa = FusedAdam([a], lr=1e-2, weight_decay=0.1, decoupled_weight_decay=True)
+    ob = FusedAdam([b], lr=lr, weight_decay=0.1, decoupled_weight_decay=True)
+    for i in range(4):
+        if i == 2:                                   # a schedule: the float is replaced, the tensor overwritten
+            oa.param_groups[0]["lr"] = 5e-3
+            lr.fill_(5e-3)
+        g = torch.randn(7)
+        a.grad, b.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    assert torch.allclose(a, b, atol=1e-7)

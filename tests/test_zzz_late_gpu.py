@@ -1,5 +1,6 @@
-"""Scatter epilogue of the tcgen05 GEMM on one GPU: column part ``p`` of the product goes to slab ``p``.
-Sorted last among the test files on purpose: it covers tile shapes that no other single-GPU test reaches."""
+"""Single-GPU checks that are sorted last on purpose, because they reach kernel variants that no other test
+reaches: the scatter epilogue of the tcgen05 GEMM with both slabs on this GPU (column part ``p`` of the product
+goes to slab ``p``), and the Adam kernel that reads its learning rate from device memory."""
 
 import pytest
 import torch
@@ -48,3 +49,29 @@ def test_scatter_epilogue_into_local_slabs(M, K, part_cols, b_mn, staged):
     for i, t in enumerate(slabs):
         assert not torch.isnan(t).any(), f"slab {i} has rows the epilogue did not write"
         assert _rel(t, ref[:, i * part_cols:(i + 1) * part_cols]) < 1e-2
+
+
+def test_fused_adam_learning_rate_from_device_memory():
+    """The Adam kernel that reads its learning rate from device memory against the one that takes it by
+    value, including a change of the rate between steps."""
+    from jigsaw_b200.optim import FusedAdam
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter(torch.randn(n, device=dev)) for n in (1000, 70000, 33)]
+    qs = [torch.nn.Parameter(p.detach().clone()) for p in ps]
+    lr = torch.full((), 1e-2, device=dev)
+    oa = FusedAdam(ps, lr=1e-2, weight_decay=0.05, decoupled_weight_decay=True)
+    ob = FusedAdam(qs, lr=lr, weight_decay=0.05, decoupled_weight_decay=True)
+    for i in range(4):
+        if i == 2:
+            oa.param_groups[0]["lr"] = 3e-3
+            lr.fill_(3e-3)
+        for p, q in zip(ps, qs):
+            p.grad = torch.randn_like(p)
+            q.grad = p.grad.clone()
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    for p, q in zip(ps, qs):
+        assert torch.allclose(p, q, atol=1e-7, rtol=1e-6)
