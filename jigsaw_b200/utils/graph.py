@@ -13,8 +13,10 @@ as one graph removes that.  Two things make a captured step different from an ea
   bookkeeping advances by the same stride per replay, so eager launches may follow replays
   (up to ``EPOCH_STRIDE`` productions of one buffer slot between two replays).
 
-The optimizer must be capturable (``torch.optim.Adam(..., capturable=True)``; ``fused=True``
-is fine).  NCCL collectives inside the step are captured by PyTorch's process group.
+The optimizer must be capturable (``jigsaw_b200.optim.FusedAdam``, or ``torch.optim.Adam(...,
+capturable=True)``; ``fused=True`` is fine).  A learning rate given as a float is frozen into the
+graph; for a schedule give the optimizer a one-element device tensor and overwrite it in place
+between replays.  NCCL collectives inside the step are captured by PyTorch's process group.
 
 Reference parity: none - the reference has no graph capture.
 """
