@@ -1,6 +1,7 @@
 """Replica marks, gradient synchronisation, DDP composition and gradient clipping.
 
-Reference parity: jigsaw/parallel/__init__.py:24-37 (the twelve public names).
+Reference parity: jigsaw/parallel/__init__.py:24-37 (the twelve public names); ``no_grad_sync`` and
+``reduce_replica_grads`` (gradient accumulation in the in-graph mode) have no counterpart there.
 """
 
 from .._core.public import set_module
@@ -8,7 +9,7 @@ from ._clip import clip_grad_norm_
 from ._ddp import check_ddp, wrap_ddp
 from ._joint import JointCommHookState, joint_comm_hook, register_joint_comm_hook
 from ._replicas import broadcast_replicas, mark_replicated, replica_groups
-from ._sync import sync_grad, synced_call, synced_parameters
+from ._sync import no_grad_sync, reduce_replica_grads, sync_grad, synced_call, synced_parameters
 
 __all__ = [
     "JointCommHookState",
@@ -17,6 +18,8 @@ __all__ = [
     "clip_grad_norm_",
     "joint_comm_hook",
     "mark_replicated",
+    "no_grad_sync",
+    "reduce_replica_grads",
     "register_joint_comm_hook",
     "replica_groups",
     "sync_grad",

@@ -15,7 +15,9 @@ Reference parity: jigsaw/parallel/_sync.py:13-16 (switch), :19-53 (_SyncGrad), :
 
 from __future__ import annotations
 
+import contextlib
 import os
+from collections.abc import Iterable, Iterator
 from typing import Any
 
 import torch
@@ -26,6 +28,7 @@ from ._joint import JointCommHookState, active_joint_state, joint_state_of
 from ._replicas import Groups, merged_group, replica_groups
 
 _SYNC_DISABLED = os.environ.get("JIGSAW_DISABLE_GRAD_SYNC", "") == "1"
+_deferred = 0          # nesting depth of no_grad_sync()
 
 
 def _reduce_flat(flat: torch.Tensor, groups: Groups) -> None:
@@ -111,12 +114,58 @@ def sync_grad(*tensors: torch.Tensor | None) -> tuple[torch.Tensor | None, ...]:
     for (groups, _, state), idx in buckets.items():
         members = [tensors[i] for i in idx]
         if state is None:
+            if _deferred:
+                continue                     # gradient accumulation: reduce_replica_grads() sums once at the end
             routed = _SumGradOverGroups.apply(groups, *members)
         else:
             routed = _ScaleGrad.apply(state.factor(groups), *members)
         for i, r in zip(idx, routed):
             result[i] = r
     return tuple(result)
+
+
+@contextlib.contextmanager
+def no_grad_sync() -> Iterator[None]:
+    """Gradient accumulation without a reduction per micro-batch: inside the block :func:`sync_grad`
+    leaves the gradients of replicated parameters local (every rank accumulates its own contribution
+    in ``.grad``); call :func:`reduce_replica_grads` once after the last micro-batch.  The counterpart
+    of DDP's ``no_sync`` for the in-graph mode; under the joint DDP hook, where DDP reduces, it changes
+    nothing.
+
+        with jb.parallel.no_grad_sync():
+            for micro in batches:
+                loss_fn(model(micro.x), micro.y).backward()
+        jb.parallel.reduce_replica_grads(model)
+        optimizer.step()
+    """
+    global _deferred
+    _deferred += 1
+    try:
+        yield
+    finally:
+        _deferred -= 1
+
+
+def reduce_replica_grads(module_or_parameters: torch.nn.Module | Iterable[torch.Tensor]) -> None:
+    """SUM all-reduce the accumulated ``.grad`` of every marked parameter over its replica groups:
+    one flattened all-reduce per (groups, dtype) bucket (collective; the same call on every rank)."""
+    if not dist.is_initialized() or _SYNC_DISABLED:
+        return
+    params = module_or_parameters.parameters() if isinstance(module_or_parameters, torch.nn.Module) else module_or_parameters
+    buckets: dict[tuple[Groups, torch.dtype], list[torch.Tensor]] = {}
+    for p in params:
+        groups = replica_groups(p)
+        if p.grad is None or not groups:
+            continue
+        buckets.setdefault((groups, p.grad.dtype), []).append(p.grad)
+    with torch.no_grad():
+        for (groups, _), grads in buckets.items():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            _reduce_flat(flat, groups)
+            offset = 0
+            for g in grads:
+                g.copy_(flat[offset: offset + g.numel()].view_as(g))
+                offset += g.numel()
 
 
 def synced_parameters(module: torch.nn.Module) -> dict[str, torch.Tensor]:

@@ -182,3 +182,49 @@ def test_ddp_guards():
 
 def test_disabling_grad_sync_is_detected():
     run_distributed(_worker_mutation, 2)
+
+
+def _worker_accumulate(rank, world):
+    """Gradient accumulation over three micro-batches: with ``no_grad_sync`` + one ``reduce_replica_grads``
+    the gradients equal those of three synchronised backward passes, with a third of the all-reduces."""
+    import torch.distributed as dist
+
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh({"sh": 2, "sw": 2, "col": 1})
+    loss_fn = jb.modules.DistributedMSELoss(reduce_groups=(mesh["sh"], mesh["sw"]))
+    spec = {2: mesh["sh"], 3: mesh["sw"]}
+    torch.manual_seed(5)
+    batches = [(torch.randn(2, 2, 8, 8), torch.randn(2, 2, 8, 8)) for _ in range(3)]
+    calls = {"n": 0}
+    plain = dist.all_reduce
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return plain(*a, **k)
+
+    grads = []
+    for deferred in (False, True):
+        model = _tiny_model(mesh)
+        dist.all_reduce = counting
+        calls["n"] = 0
+        try:
+            if deferred:
+                with jb.parallel.no_grad_sync():
+                    for x, y in batches:
+                        loss_fn(model(split(x, spec)), split(y, spec)).backward()
+                jb.parallel.reduce_replica_grads(model)
+            else:
+                for x, y in batches:
+                    loss_fn(model(split(x, spec)), split(y, spec)).backward()
+        finally:
+            dist.all_reduce = plain
+        grads.append(([p.grad.clone() for p in model.parameters()], calls["n"]))
+    (g_sync, n_sync), (g_acc, n_acc) = grads
+    for a, b in zip(g_sync, g_acc):
+        assert_close(b, a, "accumulated gradient", 1e-6, 1e-7)
+    assert n_acc < n_sync, (n_acc, n_sync)
+
+
+def test_gradient_accumulation_with_one_reduction():
+    run_distributed(_worker_accumulate, 4)
