@@ -49,7 +49,8 @@ def _worker_selfcheck(rank, world, name, kwargs):
     _load(name).main(**kwargs)
 
 
-@pytest.mark.parametrize("name,kwargs", [("autoconvert", {}), ("reshard", {"steps": 30}), ("dataloader", {"num_workers": 0})])
+@pytest.mark.parametrize("name,kwargs", [("autoconvert", {}), ("reshard", {"steps": 30}), ("dataloader", {"num_workers": 0}),
+                                         ("resume", {"steps": 8})])
 def test_self_checking_examples(name, kwargs):
     run_distributed(_worker_selfcheck, 4, name, kwargs)
 
