@@ -1,4 +1,6 @@
-"""Ulysses attention: the sequence -> head exchange fused into the QKV projection.
+"""Ulysses attention: both exchanges fused into the projections next to them (opt-in, see the switches below).
+
+QKV projection (sequence -> head exchange in the epilogue):
 
 The projection ``x @ W_qkv.T`` of a sequence shard produces, for every head group ``p``, the
 columns that rank ``p`` needs.  With the rows of ``W_qkv`` ordered (head group, q|k|v, head, d)
@@ -8,6 +10,15 @@ all-to-all rides inside the GEMM, tile by tile, and the projected ``(b, s / P, 3
 never written locally.  The receiver waits for the senders' flags and views its inbox as
 ``(3, b, s, h / P, d)``.  The backward pass sends the gradient back with the peer-memory
 all-to-all kernel and runs the two remaining products on the same GEMM kernel.
+
+Output projection (head -> sequence exchange in the operand loads): every rank stages its heads ordered
+by destination; the GEMM of rank ``r`` loads k-block part ``p`` (the heads of rank ``p``) by TMA from
+rank ``p``'s staging block, so the exchanged tensor is never materialised.  Its input gradient is again
+a scatter-epilogue GEMM.
+
+Both forms give the results of the unfused path on 2 GPUs; neither measured faster there (the
+epilogue's 64-byte row stores use NVLink poorly), so the attention layer uses them only when the
+switches ``FUSE_QKV_PROJECTION`` / ``FUSE_OUTPUT_PROJECTION`` are set.
 
 Reference parity: the projection followed by ``all_to_all_single`` in
 jigsaw/modules/attention/_functional/ulysses.py:19-63.
