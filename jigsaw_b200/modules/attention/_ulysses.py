@@ -5,9 +5,9 @@ Tensors are ``bshd``.  The all-to-all is the differentiable ``all_to_all_dims`` 
 is the inverse exchange), so no hand-written backward is needed.  The hierarchical variant
 runs Ulysses inside intra groups and a K/V ring across them.
 
-On CUDA the exchange is fused into the producing / consuming kernels by
-``jigsaw_b200.ops.ulysses_fused`` when available (head blocks are stored straight into the
-destination rank's buffer).
+On CUDA each exchange is one peer-memory all-to-all kernel (``jigsaw_b200.ops.exchange_fused``);
+``jigsaw_b200.ops.ulysses_fused`` holds opt-in forms that fuse the exchanges into the projections
+next to them.
 
 Reference parity: jigsaw/modules/attention/_functional/ulysses.py:19-63 (all-to-alls),
 :66-144 (ulysses_attention), :147-180 (hierarchical).
