@@ -177,6 +177,15 @@ def main() -> None:
             f = lambda: attention_fused.flash_attention_forward(qa, ka, va, 0.125)
             return timed(f, args.warmup, args.reps), None, fa_flops
 
+        @case("flash_attn_bwd")
+        def _():
+            from jigsaw_b200.ops import attention_fused
+
+            out, lse = attention_fused.flash_attention_forward(qa, ka, va, 0.125)
+            go = torch.randn_like(out)
+            f = lambda: attention_fused.flash_attention_backward(go, qa, ka, va, out, lse, 0.125)
+            return timed(f, args.warmup, args.reps), None, 2.5 * fa_flops      # five products, two of them recomputed twice: 3.5x issued
+
         @case("sdpa_fwd_library")
         def _():
             with torch.no_grad():
