@@ -27,6 +27,7 @@ jigsaw/modules/attention/_functional/ulysses.py:19-63.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any
 
 import torch
@@ -146,8 +147,8 @@ class _UlyssesQKV(torch.autograd.Function):
 # Switches of the two fused projections.  The QKV projection with the exchange in its epilogue is off by
 # default: on 2 GPUs it measured 0.55 ms against 0.41 ms for the GEMM followed by the all-to-all kernel
 # (batch 8, 4096 tokens, width 1024), because the epilogue's 64-byte row stores use NVLink poorly.
-FUSE_QKV_PROJECTION = False
-FUSE_OUTPUT_PROJECTION = False
+FUSE_QKV_PROJECTION = os.environ.get("JIGSAW_FUSE_ULYSSES_QKV", "0") == "1"
+FUSE_OUTPUT_PROJECTION = os.environ.get("JIGSAW_FUSE_ULYSSES_OUT", "0") == "1"
 
 
 def stage_for_owners(o: torch.Tensor, parts: int) -> torch.Tensor:
