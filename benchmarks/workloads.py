@@ -34,6 +34,7 @@ from torch import nn
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 MESH2D = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (4, 2)}
+SEQUENCE_PARALLEL = "ring"          # how attention sees the whole sequence when rows split it: "ring" | "ulysses" (--seq)
 TILES = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}
 
 
@@ -60,8 +61,9 @@ class Block(nn.Module):
 
             att = import_module(lib.__name__ + ".modules.attention")
             cfg = M.RingAttentionConfig(device=dev, send_in_forward=att.SendForward.KV, save_for_backward=att.SaveBackward.KV)
+        ulysses = ring and SEQUENCE_PARALLEL == "ulysses"
         self.attn = M.DistributedAttention(dim, dim, dim, heads, model.rank(), dev, spatial_group=row, channel_group=col,
-                                           ring=ring, config=cfg)
+                                           ring=ring and not ulysses, ulysses=ulysses, config=None if ulysses else cfg)
         self.fc1 = M.DistributedLinear(dim, hidden, device=dev, model_group=model, row_group=row, col_group=col, bias=True)
         self.fc2 = M.DistributedLinear(hidden, dim, device=dev, model_group=model, row_group=row, col_group=col, bias=True)
 
@@ -115,7 +117,7 @@ def build_vit(lib, n, dev, scale):
     x = x[..., mesh["row"].rank() * w:(mesh["row"].rank() + 1) * w].contiguous()
     y = torch.randint(0, classes, (batch,), generator=g)
     desc = {"model": f"ViT depth {depth} width {dim} heads {heads} mlp {hidden}, {image}x{image} patch {patch}",
-            "global_batch": batch, "seq_len": (image // patch) ** 2, "parallelism": f"row{r} x col{c}"}
+            "global_batch": batch, "seq_len": (image // patch) ** 2, "parallelism": f"row{r} x col{c}" + (f", {SEQUENCE_PARALLEL} attention" if r > 1 else "")}
     return model, loss_fn, x, y, desc, batch
 
 
@@ -291,6 +293,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", default="default")
+    ap.add_argument("--seq", choices=("ring", "ulysses"), default="ring", help="sequence parallelism of the ViT's attention")
     ap.add_argument("--graph", action="store_true",
                     help="replay the whole step as one CUDA graph (this framework only; GraphedStep)")
     args = ap.parse_args()
@@ -306,6 +309,8 @@ def main() -> None:
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     lib = load(args.impl)
+    global SEQUENCE_PARALLEL
+    SEQUENCE_PARALLEL = args.seq
     builders = {"vit": build_vit, "swin": build_swin, "unet3d": build_unet3d}
     model, loss_fn, x, y, desc, batch = builders[args.config](lib, args.gpus, dev, args.scale)
     x, y = x.to(dev), y.to(dev)
