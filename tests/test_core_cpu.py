@@ -216,3 +216,28 @@ def _worker_mesh_gather_convert(rank, world):
 
 def test_mesh_gather_convert_reshard():
     run_distributed(_worker_mesh_gather_convert, 4)
+
+
+def _worker_log_collectives(rank, world):
+    """The collective parts of the logger on real ranks: a disagreement is seen by every rank, and
+    ``log_ranks`` prints one line per rank in rank order from rank 0."""
+    from jigsaw_b200 import log
+
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = str(rank), str(world)
+    logger = log.configure_logging("DEBUG", as_json=True, install_excepthook=False, enable_faulthandler=False, force=True)
+    stream = io.StringIO()
+    logger.handlers[0].stream = stream
+    assert log.assert_all_agree("depth", 12) is True
+    assert log.assert_all_agree("seed", rank, fatal=False) is False          # every rank learns of it
+    log.log_ranks("tile %d", rank, level=logging.INFO)
+    lines = [json.loads(l) for l in stream.getvalue().splitlines()]
+    if rank == 0:
+        assert any("ranks disagree on seed" in l["msg"] and "r2=2" in l["msg"] for l in lines)
+        dump = [l["msg"] for l in lines if l["msg"].startswith("rank dump")][0]
+        assert dump.index("[0] tile 0") < dump.index("[1] tile 1") < dump.index("[2] tile 2")
+    else:
+        assert not any(l["msg"].startswith("rank dump") for l in lines)
+
+
+def test_logging_collectives_on_ranks():
+    run_distributed(_worker_log_collectives, 3)
