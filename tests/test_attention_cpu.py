@@ -204,3 +204,50 @@ def test_fused_ulysses_output_projection_layouts(parts):
         inbox = torch.stack([f[:, p * kp:(p + 1) * kp] for f in full]).contiguous()
         do = inbox.view(parts, b, sl, hl, d).permute(1, 0, 2, 3, 4).reshape(b, s, hl, d)
         assert torch.allclose(do, grads[p], atol=1e-12), f"gradient of rank {p}'s heads"
+
+
+def _worker_ring_dropout(rank, world):
+    """Ring attention with dropout: the masks are reproducible from the seed (forward and the chunk
+    re-visits of the backward pass use the same ones), so for a fixed seed the layer is linear in the values
+    and its gradient matches a finite difference taken under the same seed."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention, RingAttentionConfig
+
+    mesh = jb.make_process_mesh({"row": 4, "col": 1})
+    torch.manual_seed(0)
+    att = Attention(8, 16, 8, 4, "cpu", dropout_p=0.3, dtype=torch.float64, attn_backend="math")
+    x = torch.randn(2, 16, 8, dtype=torch.float64)
+    xl = split(x, {1: mesh["row"]})
+    for scope in ("local", "global"):
+        cfg = RingAttentionConfig(device="cpu", send_in_forward="kv", save_scope=scope, attn_backend="math")
+        layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
+        layer.train()
+
+        def run(inp):
+            torch.manual_seed(123)                       # the layer draws its base seed from the global generator
+            return layer(inp)
+
+        y1, y2 = run(xl), run(xl)
+        assert_close(y2.detach(), y1.detach(), f"{scope}: same seed, same masks", 0, 0)
+        layer.eval()
+        assert float((layer(xl) - y1).abs().max()) > 1e-3, "dropout changed nothing"
+        layer.train()
+        # directional derivative with respect to the input against autograd, under the same seed
+        xg = xl.clone().requires_grad_(True)
+        g = torch.randn_like(y1)
+        (run(xg) * g).sum().backward()
+        d = torch.randn_like(xl)
+        eps = 1e-6
+        fd = ((run(xl + eps * d) - run(xl - eps * d)) * g).sum() / (2 * eps)
+        # the input of one rank feeds the outputs of all ranks (it is their K / V): sum both sides over the ring
+        import torch.distributed as dist
+
+        lhs = fd.detach().reshape(1)
+        rhs = (xg.grad * d).sum().reshape(1)
+        dist.all_reduce(lhs, group=mesh["row"])
+        dist.all_reduce(rhs, group=mesh["row"])
+        assert_close(rhs, lhs, f"{scope}: gradient under dropout", 1e-5, 1e-7)
+
+
+def test_ring_attention_dropout_is_reproducible_and_differentiable():
+    run_distributed(_worker_ring_dropout, 4)
