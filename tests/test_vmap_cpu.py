@@ -3,7 +3,7 @@ loop over the ensemble members, forward and gradients."""
 
 import torch
 
-from dist_utils import assert_close, run_distributed
+from dist_utils import assert_close, run_distributed, split
 
 
 def _worker_vmap(rank, world):
@@ -44,3 +44,54 @@ def _worker_vmap(rank, world):
 
 def test_vmap_over_distributed_layers():
     run_distributed(_worker_vmap, 4)
+
+
+def _worker_ensemble(rank, world):
+    """An ensemble as stacked weights: ``torch.vmap`` over ``functional_call`` with the members' parameters
+    stacked along a new first axis.  Outputs equal the members run one by one; ``functional_call`` hands the
+    layers tensors without replica marks, so the gradients of replicated parameters are summed afterwards
+    with ``reduce_replica_grads`` (marks copied from a member)."""
+    import jigsaw_b200 as jb
+    from torch.func import functional_call, stack_module_state
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    row, col, model = mesh["row"], mesh["col"], mesh["model"]
+
+    def member(seed):
+        jb.launch.set_all_seeds(seed * 10 + model.rank())
+        net = torch.nn.Sequential(jb.modules.DistributedLinear(8, 8, "cpu", model, row, col),
+                                  jb.modules.DistributedLayerNorm(8, model.rank(), "cpu", row, col))
+        with torch.no_grad():
+            for p in net[1].parameters():
+                p.add_(torch.randn_like(p) * 0.1)
+        jb.parallel.broadcast_replicas(net)
+        return net
+
+    members = [member(s) for s in range(3)]
+    torch.manual_seed(0)
+    x = split(torch.randn(6, 8), {0: row, 1: col})
+    g = split(torch.randn(6, 8), {0: row, 1: col})
+    outs, grads = [], []
+    for net in members:
+        y = net(x)
+        (y * g).sum().backward()
+        outs.append(y.detach())
+        grads.append({n: p.grad.clone() for n, p in net.named_parameters()})
+    params, buffers = stack_module_state(members)
+    params = {k: v.detach().clone().requires_grad_(True) for k, v in params.items()}
+    base = members[0]
+    y = torch.vmap(lambda p, b: functional_call(base, (p, b), (x,)), in_dims=(0, 0))(params, buffers)
+    assert_close(y.detach(), torch.stack(outs), "ensemble output", 1e-5, 1e-6)
+    (y * g).sum().backward()
+    named = dict(base.named_parameters())
+    for n, p in params.items():
+        groups = jb.parallel.replica_groups(named[n])
+        if groups:
+            jb.parallel.mark_replicated(p, groups)
+    jb.parallel.reduce_replica_grads(params.values())
+    for n, p in params.items():
+        assert_close(p.grad, torch.stack([gr[n] for gr in grads]), f"ensemble gradient of {n}", 1e-4, 1e-5)
+
+
+def test_ensemble_of_stacked_weights():
+    run_distributed(_worker_ensemble, 4)
