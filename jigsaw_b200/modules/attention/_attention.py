@@ -352,6 +352,31 @@ class DistributedAttention(torch.nn.Module):
                 out.k_norm.load_state_dict(self.k_norm.state_dict())
         return out
 
+    def reshard_parameters(self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, row_kw: str = "row",
+                           col_kw: str = "col", model_kw: str = "model") -> None:
+        """Move this layer from one mesh to another (collective on both meshes).  The weights travel through
+        the serial layout, because the row order of the qkv projection depends on the channel split; the
+        layer then adopts the state of a layer built for the new mesh, so heads per rank, groups and the
+        sequence-parallel scheme all follow.  On a mesh whose spatial group has one rank the layer runs
+        dense attention and returns to ring / Ulysses when a later mesh splits the sequence again.  If the
+        new mesh does not divide the layer, the error comes before anything is changed.
+
+        Reference parity: none (the reference reshards attention through ``convert_to_torch`` and
+        ``convert_to_jigsaw`` by hand, examples/reshard.py:78-107)."""
+        want_ring, want_ulysses, ring_cfg = getattr(self, "_requested_sequence_parallel", (self.ring, self.ulysses, self.config))
+        serial = self.convert_to_torch(from_process_mesh_dict, row_kw, col_kw, model_kw)
+        split = to_process_mesh_dict[row_kw].size() > 1
+        new = Attention.convert_to_jigsaw(
+            serial, to_process_mesh_dict, self.device, row_kw, col_kw, model_kw, ring=want_ring and split,
+            ulysses=want_ulysses and split, ulysses_intra_size=self.ulysses_intra_size if split else 0,
+            ulysses_inter_save_scope=self.ulysses_inter_save_scope, ulysses_inter_overlap=self.ulysses_inter_overlap,
+            ulysses_inter_offload=self.ulysses_inter_offload, attn_backend=self.attn_backend,
+            config=ring_cfg if want_ring and split else None,
+        )
+        new.train(self.training)
+        new._requested_sequence_parallel = (want_ring, want_ulysses, ring_cfg)
+        self.__dict__ = new.__dict__
+
     def row_order_tags(self) -> dict[str, str]:
         """The qkv rows are stored channel-rank-major (``C, 3, heads / C, head_dim``), which
         depends on the channel split; a checkpoint records the split so that another mesh can

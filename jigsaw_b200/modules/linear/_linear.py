@@ -84,21 +84,22 @@ class DistributedLinear(torch.nn.Module):
         self._mark()
 
     def _bind_groups(self, model_group: dist.ProcessGroup, row_group: dist.ProcessGroup, col_group: dist.ProcessGroup) -> None:
-        self.model_group, self.row_group, self.col_group = model_group, row_group, col_group
+        """Check that the groups fit this layer, then adopt them (nothing changes when a check fails)."""
         C = col_group.size()
         if model_group.size() % C:
             raise ValueError("model group size must be a multiple of the column group size")
-        self.col_split = C
-        self.row_split = model_group.size() // C       # weight row blocks
-        self.weight_replicated_over_rows = self.row_split == 1
-        if self.row_split > 1 and self.row_split != row_group.size():
+        row_split = model_group.size() // C            # weight row blocks
+        if row_split > 1 and row_split != row_group.size():
             raise NotImplementedError(
-                f"weight rows are split {self.row_split}-way but row_group has {row_group.size()} ranks; "
+                f"weight rows are split {row_split}-way but row_group has {row_group.size()} ranks; "
                 "model_group must span row_group x col_group or equal col_group"
             )
         check_divisible(self.in_dim, C, "in_dim")
         check_divisible(self.out_dim, C, "out_dim")
-        check_divisible(self.out_dim, self.row_split, "out_dim")
+        check_divisible(self.out_dim, row_split, "out_dim")
+        self.model_group, self.row_group, self.col_group = model_group, row_group, col_group
+        self.col_split, self.row_split = C, row_split
+        self.weight_replicated_over_rows = row_split == 1
 
     def _mark(self) -> None:
         """Bias is always replicated over ``row_group``; the weight too when its rows are not split."""
@@ -192,9 +193,12 @@ class DistributedLinear(torch.nn.Module):
         self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, pm_row_key: str = "row", pm_col_key: str = "col",
         pm_model_key: str = "model",
     ) -> None:
-        w, b = self.merge_weights(from_process_mesh_dict, pm_row_key, pm_col_key, pm_model_key)
         # a projection built with model_group = col_group keeps its weight unsplit over rows
         new_model = to_process_mesh_dict[pm_col_key] if self._model_is_col else to_process_mesh_dict[pm_model_key]
+        if (self.model_group is new_model and self.row_group is to_process_mesh_dict[pm_row_key]
+                and self.col_group is to_process_mesh_dict[pm_col_key]):
+            return                                  # already there (a parent layer moved this one with itself)
+        w, b = self.merge_weights(from_process_mesh_dict, pm_row_key, pm_col_key, pm_model_key)
         self._bind_groups(new_model, to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key])
         self.config = LinearConfig(new_model, linear_layer=True, device=self.device, comm=self.config.comm)
         self.weight = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))

@@ -251,3 +251,41 @@ def _worker_ring_dropout(rank, world):
 
 def test_ring_attention_dropout_is_reproducible_and_differentiable():
     run_distributed(_worker_ring_dropout, 4)
+
+
+def _worker_attention_reshard(rank, world):
+    """``DistributedAttention.reshard_parameters`` over three meshes: on every mesh the layer (heads per rank,
+    groups, ring / Ulysses or dense attention where the sequence is not split) reproduces the serial layer."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention, RingAttentionConfig
+
+    meshes = [jb.make_process_mesh({"row": 2, "col": 2}), jb.make_process_mesh({"row": 1, "col": 4}),
+              jb.make_process_mesh({"row": 4, "col": 1}), jb.make_process_mesh({"row": 2, "col": 2})]
+    torch.manual_seed(0)
+    att = Attention(8, 16, 8, 4, "cpu", dtype=torch.float64, attn_backend="math")
+    x = torch.randn(2, 16, 8, dtype=torch.float64)
+    y_ref = att(x).detach()
+    for mode in ("ring", "ulysses"):
+        cfg = RingAttentionConfig(device="cpu", send_in_forward="kv", attn_backend="math") if mode == "ring" else None
+        layer = Attention.convert_to_jigsaw(att, meshes[0], "cpu", ring=mode == "ring", ulysses=mode == "ulysses",
+                                            attn_backend="math", config=cfg)
+        for a, b in zip(meshes[:-1], meshes[1:]):
+            layer.reshard_parameters(a, b)
+            cuts = {1: b["row"], 2: b["col"]}
+            y = layer(split(x, cuts))
+            assert_close(y.detach(), split(y_ref, cuts), f"{mode}: output on a {b['row'].size()}x{b['col'].size()} mesh", 1e-9, 1e-9)
+            split_seq = b["row"].size() > 1
+            assert (layer.ring, layer.ulysses) == (mode == "ring" and split_seq, mode == "ulysses" and split_seq)
+        # a mesh that does not divide the heads is refused and changes nothing
+        odd = jb.make_process_mesh({"row": 1, "col": 4})
+        small = Attention.convert_to_jigsaw(Attention(8, 12, 8, 2, "cpu", dtype=torch.float64, attn_backend="math"), meshes[0], "cpu",
+                                            ring=False, attn_backend="math")
+        xs = split(x, {1: meshes[0]["row"], 2: meshes[0]["col"]})
+        before = small(xs).detach()
+        with pytest.raises(ValueError):
+            small.reshard_parameters(meshes[0], odd)
+        assert_close(small(xs).detach(), before, "after a refused reshard", 0, 0)
+
+
+def test_attention_reshard_over_meshes():
+    run_distributed(_worker_attention_reshard, 4)

@@ -176,9 +176,10 @@ def test_sharded_checkpoint_across_meshes(tmp_path):
 
 
 def _worker_reshard_hops(rank, world):
-    """A ViT (patch convolution, layer norms, attention, block linears) carried 2x2 -> 1x4 -> 4x1 -> 2x2 with
-    ``reshard_parameters``: after every hop the gathered state equals the original, and back on the first
-    mesh the model computes what it computed before."""
+    """The layers of a ViT (patch convolution, layer norms, attention, block linears) carried
+    2x2 -> 1x4 -> 4x1 -> 2x2 with ``reshard_parameters``: after every hop the gathered state equals the
+    original, and back on the first mesh the model computes what it computed before.  (On the meshes in
+    between only the layers are valid: the model object keeps its own mesh-dependent buffers.)"""
     import jigsaw_b200 as jb
     from jigsaw_b200 import checkpoint
     from jigsaw_b200.models import ViT, ViTConfig
@@ -321,3 +322,26 @@ def _worker_recompute_swin(rank, world):
 
 def test_swin_layer_recomputation_keeps_gradients():
     run_distributed(_worker_recompute_swin, 4)
+
+
+def _worker_reshard_refused(rank, world):
+    """A mesh that does not divide the layer is refused on every rank, and the layer is left as it was."""
+    import jigsaw_b200 as jb
+
+    a = jb.make_process_mesh({"row": 2, "col": 2})
+    b = jb.make_process_mesh({"row": 1, "col": 4})
+    layers = [jb.modules.DistributedLinear(6, 6, "cpu", a["model"], a["row"], a["col"]),
+              jb.modules.DistributedLayerNorm(6, a["model"].rank(), "cpu", a["row"], a["col"])]
+    x = split(torch.randn(4, 6), {0: a["row"], 1: a["col"]})
+    for layer in layers:
+        before = [p.detach().clone() for p in layer.parameters()]
+        y = layer(x).detach()
+        with pytest.raises(ValueError, match="divisible"):
+            layer.reshard_parameters(a, b)
+        for p, q in zip(layer.parameters(), before):
+            assert_close(p.detach(), q, "parameters after a refused reshard", 0, 0)
+        assert_close(layer(x).detach(), y, "forward after a refused reshard", 0, 0)
+
+
+def test_reshard_onto_a_mesh_that_does_not_divide_is_refused():
+    run_distributed(_worker_reshard_refused, 4)
