@@ -18,6 +18,7 @@ from collections.abc import Mapping
 from dataclasses import dataclass
 
 import torch
+import torch.utils.checkpoint
 import torch.distributed as dist
 from torch import nn
 
@@ -34,6 +35,7 @@ class UNet3dConfig:
     norm_groups: int = 8
     skip: bool = True
     dtype: torch.dtype = torch.float32
+    recompute_stages: bool = False      # activation checkpointing: keep each stage's input, recompute conv + norm + GELU in backward
 
 
 class UNet3d(nn.Module):
@@ -62,8 +64,11 @@ class UNet3d(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         feats = []
+        recompute = self.cfg.recompute_stages and torch.is_grad_enabled()
         for conv, norm in zip(self.down, self.down_norm):
-            x = self.act(norm(conv(x)))
+            stage = lambda t, conv=conv, norm=norm: self.act(norm(conv(t)))  # noqa: E731
+            # the first stage's input needs no gradient, which the non-reentrant form handles
+            x = torch.utils.checkpoint.checkpoint(stage, x, use_reentrant=False) if recompute else stage(x)
             feats.append(x)
         feats.pop()
         for i, conv in enumerate(self.up):
