@@ -192,6 +192,14 @@ def main() -> None:
                 f = lambda: torch.nn.functional.scaled_dot_product_attention(qa, ka, va, scale=0.125)
                 return timed(f, args.warmup, args.reps), None, fa_flops
 
+        @case("sdpa_bwd_library")
+        def _():
+            ql, kl, vl = (t.clone().requires_grad_(True) for t in (qa, ka, va))
+            out = torch.nn.functional.scaled_dot_product_attention(ql, kl, vl, scale=0.125)
+            go = torch.randn_like(out)
+            f = lambda: torch.autograd.grad(out, [ql, kl, vl], go, retain_graph=True)
+            return timed(f, args.warmup, args.reps), None, 2.5 * fa_flops
+
     # ---- GEMM
     for (M, N, K) in ((8192, 8192, 8192), (8192, 4096, 1024), (8192, 1024, 4096)):
         if args.small and M * N * K > 2 ** 36:

@@ -76,7 +76,8 @@ def _elementwise_loss(fn, input, target, reduction, reduce_groups, **kw):
             acc = torch.promote_types(input.dtype, torch.float32)
             total = fn(input.to(acc), target.to(acc), reduction="sum", **kw)
     count = torch.full((), float(input.numel()), dtype=torch.float32, device=input.device)   # device-side fill: capturable
-    return reduce_scalar_loss(total, count, reduction, reduce_groups).to(input.dtype)
+    # result dtype as in torch: the promotion of input and target (a bf16 prediction against an fp32 target gives fp32)
+    return reduce_scalar_loss(total, count, reduction, reduce_groups).to(torch.promote_types(input.dtype, target.dtype))
 
 
 def distributed_mse_loss(input, target, *, reduction: str = "mean", reduce_groups=None) -> torch.Tensor:

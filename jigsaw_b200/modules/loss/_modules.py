@@ -100,12 +100,6 @@ class DistributedMSELoss(_Loss):
         self.reduce_groups, self.reduction = reduce_groups, reduction
 
     def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
-        if input.is_cuda and self.reduction != "none":
-            from ...ops import loss_fused
-
-            out = loss_fused.maybe_fused_mse(input, target, self.reduction, self.reduce_groups)
-            if out is not None:
-                return out
         return LF.distributed_mse_loss(input, target, reduction=self.reduction, reduce_groups=self.reduce_groups)
 
 

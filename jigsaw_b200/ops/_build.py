@@ -29,10 +29,6 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
 ]
-# Build-time variants (each changes the flags and so the rebuild stamp):
-#   JIGSAW_GELU_TANH=1   GELU through one tanh.approx instead of ex2 + rcp (see csrc/ptx.cuh)
-if os.environ.get("JIGSAW_GELU_TANH", "0") == "1":
-    NVCC_FLAGS.append("-DJB_GELU_TANH_MUFU=1")
 
 
 def _nvcc() -> str | None:

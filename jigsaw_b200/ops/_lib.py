@@ -140,7 +140,6 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_gemm_bf16_scatter_staged.restype = c_int
     L.jb_set_staged_epilogue.argtypes = [c_int]
     L.jb_set_staged_epilogue.restype = None
-    L.jb_set_staged_epilogue(1 if os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") == "1" else 0)
     L.jb_sum_slabs.argtypes = [c_void_p, c_longlong, c_int, POINTER(c_void_p), c_uint, c_uint, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_void_p]
     L.jb_sum_slabs.restype = c_int
@@ -150,6 +149,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_all_to_all.restype = c_int
     L.jb_wait_flags.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
     L.jb_wait_flags.restype = c_int
+    L.jb_slot_acquire.argtypes = [POINTER(c_void_p), c_int, c_void_p, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
+    L.jb_slot_acquire.restype = c_int
+    L.jb_slot_release.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]
+    L.jb_slot_release.restype = c_int
     L.jb_flash_attn_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int] + [c_longlong] * 8 + [
         c_float, c_void_p, c_void_p]
     L.jb_flash_attn_fwd.restype = c_int
@@ -260,6 +263,84 @@ LAUNCHES = 0
 def count_launches(n: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += n
+
+
+# ----------------------------------------------------------------------------- audited dispatch
+#: ``{operation: [calls that ran on the fused kernels, calls on CUDA tensors that were declined]}``
+DISPATCH: dict[str, list[int]] = {}
+_strict = os.environ.get("JIGSAW_STRICT_FUSED", "0") == "1"
+_last_reason: str | None = None
+
+
+class FusedPathDeclined(RuntimeError):
+    """A fused operation declined CUDA inputs while strict dispatch was on."""
+
+
+def set_strict(on: bool) -> bool:
+    """Strict dispatch: a fused operation that declines CUDA inputs raises :class:`FusedPathDeclined`
+    (with the reason) instead of handing the call to the ``torch.distributed`` path.  Benchmarks and
+    GPU tests switch it on so that a number or a pass can never come from a silent library fallback;
+    ``JIGSAW_STRICT_FUSED=1`` sets the initial state.  Returns the previous state."""
+    global _strict
+    prev, _strict = _strict, bool(on)
+    return prev
+
+
+class strict_fused:
+    """``with strict_fused():`` - strict dispatch inside the block."""
+
+    def __init__(self, on: bool = True) -> None:
+        self.on = on
+
+    def __enter__(self) -> None:
+        self.prev = set_strict(self.on)
+
+    def __exit__(self, *exc) -> None:
+        set_strict(self.prev)
+
+
+def decline(reason: str) -> None:
+    """``return _lib.decline("why")`` inside a fused entry point: records why the kernels do not cover
+    the call (reported by strict dispatch) and returns ``None``."""
+    global _last_reason
+    _last_reason = reason
+    return None
+
+
+def dispatch_counts(reset: bool = False) -> dict[str, dict[str, int]]:
+    """``{operation: {"fused": n, "fallback": m}}`` since the start (or the last reset)."""
+    out = {k: {"fused": v[0], "fallback": v[1]} for k, v in sorted(DISPATCH.items())}
+    if reset:
+        DISPATCH.clear()
+    return out
+
+
+def audited(name: str):
+    """Decorator of the ``maybe_fused_*`` entry points: counts, per operation, the calls that ran on the
+    kernels and the calls with CUDA tensors that were declined, and raises on the latter under strict
+    dispatch.  Calls without any CUDA tensor (the CPU / gloo path) are not counted."""
+
+    def wrap(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            global _last_reason
+            _last_reason = None
+            out = fn(*args, **kwargs)
+            rec = DISPATCH.setdefault(name, [0, 0])
+            if out is not None:
+                rec[0] += 1
+                return out
+            if any(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+                rec[1] += 1
+                if _strict:
+                    raise FusedPathDeclined(f"{name} declined CUDA inputs: {_last_reason or 'outside the coverage of the kernel'}")
+            return None
+
+        return inner
+
+    return wrap
 
 
 def traced(name: str):

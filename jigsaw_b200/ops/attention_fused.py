@@ -14,13 +14,8 @@ import torch
 from . import _lib
 
 
-def __getattr__(name: str):
-    if name.startswith("maybe_fused_"):
-        return lambda *a, **k: None
-    raise AttributeError(name)
-
-
 @_lib.traced("jb.maybe_fused_merge")
+@_lib.audited("merge")
 def maybe_fused_merge(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor, lse_j: torch.Tensor):
     """In place: ``out += sigmoid(lse_j - lse) (out_j - out)``, ``lse = logaddexp(lse, lse_j)``;
     returns ``(out, lse)``, or ``None`` when the kernel does not apply (the state must be

@@ -282,6 +282,7 @@ def layer_is_eligible(layer: Any, x: torch.Tensor) -> bool:
 
 
 @_lib.traced("jb.maybe_fused_conv2d")
+@_lib.audited("conv2d")
 def maybe_fused_conv2d(layer: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     """Single-layer entry point used by ``DistributedConv2d.forward``."""
     if not layer_is_eligible(layer, x):

@@ -9,6 +9,7 @@
 #include "elementwise.cu"
 #include "roll.cu"
 #include "alltoall.cu"
+#include "signal.cu"
 #include "flash_attn.cu"
 #include "flash_attn_bwd.cu"
 

@@ -17,7 +17,10 @@
 //    JB_NOALLOC_WGRAD_MAX_CTAS thread blocks run, so big tiles are slower than through the
 //    allocating entry point.
 //  * The first call on a device looks up the device address of the scratch array (one
-//    cudaGetSymbolAddress, no allocation).  Make that first call outside any stream capture.
+//    cudaGetSymbolAddress, no allocation; host threads making that first call at the same
+//    time take turns).  Make that first call outside any stream capture.
+//  * check_status != 0 reads the status word back and synchronises the stream; on a stream
+//    that is being captured the call is refused with -8 before anything is enqueued.
 //  * All calls share the one scratch array and it keeps the previous call's contents; the
 //    entry point clears the one word that must start at zero (its status word).  Two calls
 //    that overlap on the GPU (different streams, no ordering between them) race on the
@@ -30,7 +33,9 @@ extern "C" {
 #endif
 
 #define JB_NOALLOC_WGRAD_MAX_CTAS 32
-#define JB_NOALLOC_WGRAD_SCRATCH_BYTES (JB_NOALLOC_WGRAD_MAX_CTAS * 5 * 128 * 64 * 4)   /* 5 MiB */
+/* one block of partial sums (5 x 128 x 64 floats) per thread block: 5 MiB; the source file checks
+   this against the kernel's own constant */
+#define JB_NOALLOC_WGRAD_SCRATCH_BYTES (JB_NOALLOC_WGRAD_MAX_CTAS * 5 * 128 * 64 * 4)
 #define JB_NOALLOC_WGRAD_MAX_PIXELS (4096LL * 4096LL)
 
 // x_padded : [NB][H+2][W+2][64] bf16 input of the layer, halo border filled (or zero)

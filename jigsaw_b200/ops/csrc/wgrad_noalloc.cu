@@ -1,6 +1,11 @@
 // Allocation-free variant of the weight-gradient entry point: see jb_noalloc.h.
 #include "jb_noalloc.h"
 
+#include <mutex>
+
+static_assert(JB_NOALLOC_WGRAD_SCRATCH_BYTES == JB_NOALLOC_WGRAD_MAX_CTAS * jb::WG_PARTIAL_FLOATS * 4,
+              "the static scratch must hold one block of partial sums per thread block");
+
 namespace {
 
 // Scratch of the allocation-free path: per-CTA partial sums and the status word of the
@@ -16,12 +21,14 @@ struct NoallocDevice {
   int sm_count = 0;
 };
 static NoallocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_lock;      // first calls from several host threads fill the table one at a time
 
 // Device addresses of the scratch, looked up once per device with that device current.
 static int noalloc_setup(NoallocDevice** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
   NoallocDevice& d = g_noalloc_dev[dev];
+  std::lock_guard<std::mutex> guard(g_noalloc_lock);
   if (!d.ready) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_partials) != cudaSuccess || p == nullptr) return -7;
@@ -53,6 +60,13 @@ extern "C" int jb_conv3x3_c64_wgrad_noalloc(const void* x_padded, const void* gy
   const int rc = noalloc_setup(&d);
   if (rc != 0) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (check_status) {
+    // reading the status back synchronises the stream, which a capturing stream cannot do:
+    // refuse before anything is enqueued
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) return -3;
+    if (cap != cudaStreamCaptureStatusNone) return -8;
+  }
   // The status word is the only part of the scratch that must start at zero.
   if (cudaMemsetAsync(d->status, 0, 4 * sizeof(int), st) != cudaSuccess) return -3;
 

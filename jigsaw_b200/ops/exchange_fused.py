@@ -31,6 +31,7 @@ def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
 
 
 @_lib.traced("jb.maybe_fused_all_to_all")
+@_lib.audited("all_to_all")
 def maybe_fused_all_to_all(x: torch.Tensor, group: dist.ProcessGroup, split_dim: int, cat_dim: int) -> torch.Tensor | None:
     """``cat(all_to_all(chunks of x along split_dim), dim=cat_dim)`` or ``None`` when the kernel
     does not apply (needs a contiguous CUDA tensor whose trailing dimensions behind both
@@ -63,7 +64,7 @@ def maybe_fused_all_to_all(x: torch.Tensor, group: dist.ProcessGroup, split_dim:
     me = group.rank()
     ranks = dist.get_process_group_ranks(group)
     nbytes = x.numel() * x.element_size()
-    blk = _ring_block(ar, ("a2a", dev.index, nbytes, P), _HEADER + nbytes)
+    blk = _ring_block(ar, ("a2a", dev.index, nbytes, tuple(ranks)), _HEADER + nbytes)
     epoch = ar.next_own_epoch(blk)
     a = _lib.JbA2a()
     a.x = x.data_ptr()
@@ -106,7 +107,7 @@ class PeerChunks:
         self.me = group.rank()
         self.ranks = dist.get_process_group_ranks(group)
         self.nbytes = self.payload.numel() * self.payload.element_size()
-        blk = _ring_block(self.ar, ("chunks", dev.index, self.nbytes, group.size()), _HEADER + self.nbytes)
+        blk = _ring_block(self.ar, ("chunks", dev.index, self.nbytes, tuple(self.ranks)), _HEADER + self.nbytes)
         self.blk = blk
         staged = blk.tensor[_HEADER:_HEADER + self.nbytes].view(self.payload.dtype).view(self.payload.shape)
         staged.copy_(self.payload)

@@ -99,6 +99,7 @@ class _FusedLinear(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_linear")
+@_lib.audited("linear")
 def maybe_fused_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     if not x.is_cuda or w.dim() != 2 or x.numel() == 0:
         return None
@@ -120,7 +121,8 @@ _rings: dict[tuple, list] = {}
 
 
 def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
-    """Two blocks per shape, used alternately: a rank can run at most one gathered layer ahead of
+    """Two blocks per shape and group (the tag carries the group's ranks, so operations over different
+    groups never alternate on one ring), used alternately: a rank can run at most one gathered layer ahead of
     its peers (it needs their flag of the current layer, which they publish after their previous
     GEMM), so the block it overwrites is never one that a peer may still be reading."""
     ring = _rings.get(tag)
@@ -131,14 +133,10 @@ def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block
     return blk
 
 
-# Epilogue of the scatter GEMM: off = every thread stores its own accumulator row (16 bytes per
-# instruction), on = tiles leave through shared memory as 128-byte row pieces, which suits stores into a
-# peer's memory.  The staged form has not run on hardware yet; JIGSAW_STAGED_EPILOGUE=1 selects it.
-STAGED_SCATTER_EPILOGUE = os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") == "1"
-
-
 def scatter_gemm_launcher(L: Any) -> Any:
-    return L.jb_gemm_bf16_scatter_staged if STAGED_SCATTER_EPILOGUE else L.jb_gemm_bf16_scatter
+    """Scatter GEMM whose tiles leave through shared memory as 128-byte row pieces: the form that suits
+    stores into a peer's memory (row-per-thread stores reach about 160 GB/s across NVLink)."""
+    return L.jb_gemm_bf16_scatter_staged
 
 
 def _scatter_gemm(g: torch.Tensor, wb: torch.Tensor, group: Any) -> torch.Tensor:
@@ -153,7 +151,7 @@ def _scatter_gemm(g: torch.Tensor, wb: torch.Tensor, group: Any) -> torch.Tensor
     K = wb.shape[1]
     kp = K // P
     slab = M * kp * 2
-    blk = _staging_block(ar, ("scatter_dx", dev.index, M, kp, P), _HEADER + P * slab)
+    blk = _staging_block(ar, ("scatter_dx", dev.index, M, kp, tuple(ranks)), _HEADER + P * slab)
     epoch = ar.next_own_epoch(blk)
     stride = ar.capture_stride or 0
     replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
@@ -194,7 +192,7 @@ class _GatherLinear(torch.autograd.Function):
         kp = x.shape[-1]
         M = x.numel() // kp
         N = w.shape[0]
-        blk = _staging_block(ar, ("gather_x", dev.index, M, kp, P), _HEADER + M * kp * 2)
+        blk = _staging_block(ar, ("gather_x", dev.index, M, kp, tuple(ranks)), _HEADER + M * kp * 2)
         staged = blk.tensor[_HEADER:].view(torch.bfloat16)[: M * kp].view(M, kp)
         staged.copy_(x.reshape(M, kp))                                   # cast + copy in one kernel
         epoch = ar.next_own_epoch(blk)
@@ -252,6 +250,7 @@ class _GatherLinear(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_gather_linear")
+@_lib.audited("gather_linear")
 def maybe_fused_gather_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, group: Any) -> torch.Tensor | None:
     """``all_gather(x over group, last dim) @ w.T + b`` in one GEMM whose producer reads the other
     ranks' blocks from their memory, or ``None`` when that does not apply.  ``w`` is ``[N, K]``

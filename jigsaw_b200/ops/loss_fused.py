@@ -19,12 +19,6 @@ from . import _lib
 _OK = (torch.float32, torch.bfloat16)
 
 
-def __getattr__(name: str):
-    if name.startswith("maybe_fused_"):
-        return lambda *a, **k: None
-    raise AttributeError(name)
-
-
 def _order(a: torch.Tensor) -> list[int]:
     """Dimension order that walks ``a`` in memory order (largest stride first), so that the kernel's
     innermost loop index is contiguous in ``a``."""
@@ -105,6 +99,7 @@ class _SqDiffSum(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_sq_diff_sum")
+@_lib.audited("sq_diff_sum")
 def maybe_fused_sq_diff_sum(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor | None:
     """``sum((a - b)^2)`` as an fp32 scalar (differentiable in ``a``), or ``None`` when the
     kernel does not apply."""
@@ -171,6 +166,7 @@ class _CrossEntropyRows(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_cross_entropy")
+@_lib.audited("cross_entropy")
 def maybe_fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, dim: int, channel_group: Any,
                               ignore_index: int) -> torch.Tensor | None:
     """Unreduced cross-entropy (shape of ``target``, fp32, zero where ignored) for index targets,

@@ -129,6 +129,7 @@ class _FusedLayerNorm(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_layer_norm")
+@_lib.audited("layer_norm")
 def maybe_fused_layer_norm(x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None,
                            col_group: dist.ProcessGroup | None, eps: float) -> torch.Tensor | None:
     """LayerNorm of the last dimension of ``x`` (split over ``col_group``) with the fused
@@ -231,6 +232,7 @@ class _FusedGroupNorm(torch.autograd.Function):
 
 
 @_lib.traced("jb.maybe_fused_group_norm")
+@_lib.audited("group_norm")
 def maybe_fused_group_norm(x: torch.Tensor, groups_local: int, w: torch.Tensor | None, b: torch.Tensor | None,
                            spatial_groups: list, eps: float) -> torch.Tensor | None:
     """GroupNorm with statistics over the tiles of ``spatial_groups`` on the fused kernels, or

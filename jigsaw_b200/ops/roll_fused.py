@@ -22,12 +22,6 @@ _HEADER = 256
 _rings: dict[tuple, list] = {}
 
 
-def __getattr__(name: str):
-    if name.startswith("maybe_fused_"):
-        return lambda *a, **k: None
-    raise AttributeError(name)
-
-
 def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
     """Two output blocks per shape, used alternately (a rank is at most one roll ahead of its
     neighbours, so it never stores into a block that a neighbour is still copying out of)."""
@@ -94,7 +88,7 @@ def _launch(x: torch.Tensor, shifts: tuple, dims: tuple, groups: tuple) -> torch
         return me + (ranks_h[ih] - ranks_h[rh]) + (ranks_w[iw] - ranks_w[rw])
 
     nbytes = x.numel() * x.element_size()
-    blk = _ring_block(ar, ("roll", dev.index, nbytes, Gh, Gw), _HEADER + nbytes)
+    blk = _ring_block(ar, ("roll", dev.index, nbytes, tuple(ranks_h), tuple(ranks_w)), _HEADER + nbytes)
     epoch = ar.next_own_epoch(blk)
     r = _lib.JbRoll()
     r.x, r.A, r.M, r.I16, r.H, r.W, r.rem_h, r.rem_w = x.data_ptr(), A, M, I16, H, W, rem_h, rem_w
@@ -118,6 +112,7 @@ def _launch(x: torch.Tensor, shifts: tuple, dims: tuple, groups: tuple) -> torch
 
 
 @_lib.traced("jb.maybe_fused_roll")
+@_lib.audited("roll")
 def maybe_fused_roll(x: torch.Tensor, shifts: tuple, dims: tuple, where: dict) -> torch.Tensor | None:
     """Roll ``x`` by ``shifts`` along ``dims``; ``where`` maps a dimension to the group that tiles
     it.  ``None`` when the kernel does not apply."""

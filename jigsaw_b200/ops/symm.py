@@ -29,7 +29,8 @@ import torch.distributed as dist
 from ._lib import JbHalo
 
 _ALIGN = 1024
-_FLAG_WORDS = 16
+_FLAG_WORDS = 32           # words 0..8: halo arrival per direction; words 16..24: release acknowledgements
+_ACK_BASE = 16
 _MAX_SLOTS = 4096
 
 
@@ -40,7 +41,7 @@ def _round_up(n: int, a: int) -> int:
 class Block:
     """A sub-range of the arena: same offset on every rank."""
 
-    __slots__ = ("arena", "segment", "offset", "nbytes", "slot", "epoch", "tensor", "tag", "own_epoch")
+    __slots__ = ("arena", "segment", "offset", "nbytes", "slot", "epoch", "tensor", "tag", "own_epoch", "readers")
 
     def __init__(self, arena: "PeerArena", segment: int, offset: int, nbytes: int, tensor: torch.Tensor) -> None:
         self.arena, self.segment, self.offset, self.nbytes = arena, segment, offset, nbytes
@@ -49,6 +50,7 @@ class Block:
         self.epoch = 0
         self.own_epoch = 0          # epoch of flags that live inside the block itself
         self.tag: object = None
+        self.readers: list | None = None   # neighbour table of the last halo production, until released
 
     @property
     def ptr(self) -> int:
@@ -78,6 +80,8 @@ class PeerArena:
         # CUDA-graph support: kernels inside a captured step take their epochs as
         # ``captured value + replays * productions of the slot per step`` (see begin_capture)
         self.replay = torch.zeros(1, dtype=torch.int32, device=device)
+        # epoch of the latest content produced into each flag slot, kept on the device (see acquire())
+        self.last_epoch = torch.zeros(_MAX_SLOTS, dtype=torch.int32, device=device)
         self._capture_stride: int | None = None
         self._capture_slots: set[int] = set()
         self._capture_blocks: list[Block] = []
@@ -141,10 +145,61 @@ class PeerArena:
         return blk
 
     def free(self, blk: Block) -> None:
-        if blk.slot >= 0:
-            self._free_slots.append(blk.slot)
-            blk.slot = -1
+        """Return ``blk`` to its pool.  Every kernel that reads its content must already be on
+        the current stream: if neighbours pushed a halo into it, they are told here (in stream
+        order) that its border may be overwritten.  The block keeps its flag slot for good."""
+        self.release(blk)
         self._free.setdefault((blk.nbytes, blk.tag), []).append(blk)
+
+    # ------------------------------------------------------------------ write-after-read protection
+    def acquire(self, blk: Block, nbrs: list) -> int:
+        """Take the next epoch of ``blk`` for a production whose edges go to ``nbrs``.  A tiny
+        kernel on the current stream first waits (bounded) until every neighbour has released the
+        previous content of its copy of the block: a rank that runs ahead must not push a new
+        border into memory that its neighbour's kernels still read."""
+        from . import _lib
+
+        self.bind_slot(blk)
+        acks = (ctypes.c_void_p * 8)()
+        n = 0
+        for d, r in enumerate(nbrs):
+            if r is not None:
+                acks[n] = self.flag_ptr(self.rank, blk.slot, _ACK_BASE + d)
+                n += 1
+        epoch = self.next_epoch(blk)
+        stride = self._capture_stride or 0
+        replay = ctypes.c_void_p(self.replay.data_ptr()) if self._capture_stride is not None else None
+        rc = _lib.lib().jb_slot_acquire(acks, n, ctypes.c_void_p(self.last_epoch.data_ptr() + 4 * blk.slot), epoch, stride,
+                                        replay, ctypes.c_void_p(self.status.data_ptr()), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher slot_acquire failed with code {rc}")
+        _lib.count_launches(1)
+        blk.readers = list(nbrs)
+        return epoch
+
+    def release(self, blk: Block) -> None:
+        """Tell the neighbours that pushed into ``blk`` that its current content has been consumed
+        (everything enqueued so far on the current stream).  Idempotent per production."""
+        if blk.readers is None or not self.symmetric:
+            return
+        from . import _lib
+
+        rel = (ctypes.c_void_p * 8)()
+        n = 0
+        for d, r in enumerate(blk.readers):
+            if r is not None:
+                rel[n] = self.flag_ptr(r, blk.slot, _ACK_BASE + 8 - d)
+                n += 1
+        blk.readers = None
+        stride = self._capture_stride or 0
+        replay = ctypes.c_void_p(self.replay.data_ptr()) if self._capture_stride is not None else None
+        try:
+            rc = _lib.lib().jb_slot_release(rel, n, blk.epoch, stride, replay, _lib.stream_ptr())
+        except Exception:                       # interpreter shutdown: the context may be gone
+            return
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher slot_release failed with code {rc}")
+        _lib.count_launches(1)
 
     # ------------------------------------------------------------------ flags
     def bind_slot(self, blk: Block) -> None:
@@ -271,7 +326,7 @@ def make_halo(
         return None
     h = JbHalo()
     if produce is not None:
-        h.push_epoch = ar.next_epoch(produce)
+        h.push_epoch = ar.acquire(produce, nbrs)
         h.push_enabled = 1
         for d, n in enumerate(nbrs):
             if n is not None:

@@ -74,7 +74,7 @@ def _scatter_exchange(a: torch.Tensor, bmat: torch.Tensor, b_mn: bool, cols: int
     ranks = dist.get_process_group_ranks(group)
     M, K = a.shape
     slab = M * cols * 2
-    blk = _staging_block(ar, (tag, dev.index, M, cols, P), _HEADER + P * slab)
+    blk = _staging_block(ar, (tag, dev.index, M, cols, tuple(ranks)), _HEADER + P * slab)
     epoch = ar.next_own_epoch(blk)
     stride = ar.capture_stride or 0
     replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
@@ -172,7 +172,7 @@ class _UlyssesOut(torch.autograd.Function):
         sl, kp = s // P, hl * d
         M, N = b * sl, w.shape[0]
         part = M * kp * 2
-        blk = _staging_block(ar, ("ulysses_out", dev.index, M, kp, P), _HEADER + P * part)
+        blk = _staging_block(ar, ("ulysses_out", dev.index, M, kp, tuple(ranks)), _HEADER + P * part)
         staged = blk.tensor[_HEADER:_HEADER + P * part].view(torch.bfloat16).view(P, b, sl, hl, d)
         staged.copy_(stage_for_owners(o, P))                               # cast + reorder in one kernel
         epoch = ar.next_own_epoch(blk)

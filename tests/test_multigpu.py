@@ -63,6 +63,167 @@ def test_fused_chain_four_gpus_with_corners():
     run_distributed(_worker_chain, 4, (2, 2), backend="nccl", timeout=300)
 
 
+def _delay_kernel(name: str, cycles: int) -> None:
+    """Host-side injection of a lagging rank: every launch of the library function ``name`` is
+    preceded, on the same stream, by a bounded device-side delay, so that this rank's kernels still
+    read a buffer while the other rank is already far ahead."""
+    from jigsaw_b200.ops import _lib
+
+    L = _lib.lib()
+    orig = getattr(L, name)
+
+    def delayed(*args):
+        torch.cuda._sleep(cycles)
+        return orig(*args)
+
+    setattr(L, name, delayed)
+
+
+def _gathered_conv(x_local, layer, cuts, dev):
+    """Oracle: torch convolution of the undivided image (bf16-rounded operands, fp32 accumulation),
+    cut back to this rank's tile."""
+    from dist_utils import merge, split
+
+    xg = merge(x_local.float(), cuts)
+    w = layer.weight.detach().to(torch.bfloat16).float()
+    b = None if layer.bias is None else layer.bias.detach().float()
+    y = torch.nn.functional.conv2d(xg.to(torch.bfloat16).float(), w, b, padding=1)
+    return split(y, cuts)
+
+
+def _worker_recycled_halo_buffers(rank, world, mesh_shape):
+    """Recycled padded buffers must not be overwritten by a neighbour that runs ahead.  Rank 1's
+    convolution kernels start late; rank 0 runs two unchained layers in a forward-only loop, so its
+    next halo push targets the buffer that rank 1 has not read yet.  Every iteration (different
+    inputs) must match torch on the gathered image."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"sh": mesh_shape[0], "sw": mesh_shape[1], "col": 1})
+    cuts = {2: mesh["sh"], 3: mesh["sw"]}
+    torch.manual_seed(0)
+    l1 = jb.modules.DistributedConv2d(64, 64, 3, dev, (mesh["sh"], mesh["sw"]), mesh["col"], padding=1)
+    l2 = jb.modules.DistributedConv2d(64, 64, 3, dev, (mesh["sh"], mesh["sw"]), mesh["col"], padding=1)
+    g = torch.Generator().manual_seed(7 + rank)
+    xs = [torch.randn(1, 64, 40, 136, generator=g).to(dev) for _ in range(6)]
+    if rank == 1:
+        _delay_kernel("jb_conv3x3_c64", 30_000_000)          # about 15 ms per launch
+    outs = []
+    before = _lib.LAUNCHES
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for x in xs:
+            outs.append((l1(x), None))
+            outs[-1] = (outs[-1][0], l2(outs[-1][0]))
+    assert _lib.LAUNCHES > before, "the fused convolution did not run"
+    torch.cuda.synchronize()
+    symm.arena(dev).check_status(collective=True)
+    for i, (x, (y1, y2)) in enumerate(zip(xs, outs)):
+        r1 = _gathered_conv(x, l1, cuts, dev)
+        assert_close(y1.float(), r1, f"iteration {i}: first layer", 0.0, 1e-2 * float(r1.abs().max()))
+        r2 = _gathered_conv(y1.float(), l2, cuts, dev)
+        assert_close(y2.float(), r2, f"iteration {i}: second layer", 0.0, 1e-2 * float(r2.abs().max()))
+
+
+@pytest.mark.multigpu(2)
+def test_recycled_halo_buffers_with_a_lagging_rank():
+    run_distributed(_worker_recycled_halo_buffers, 2, (2, 1), backend="nccl", timeout=300)
+
+
+def _worker_accumulation_with_a_lagging_rank(rank, world, mesh_shape):
+    """Gradient accumulation under ``no_grad_sync`` has no collective between micro-batches that would
+    keep the ranks in step: with rank 1's weight-gradient kernels delayed, the fused chain must still
+    give the gradients of the unfused torch + NCCL path on every micro-batch."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.models import DomainCNN
+    from jigsaw_b200.ops import symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"sh": mesh_shape[0], "sw": mesh_shape[1], "col": 1})
+    torch.manual_seed(0)
+    fused = DomainCNN(mesh, dev, depth=3)
+    plain = DomainCNN(mesh, dev, depth=3, fuse=False)
+    plain.load_state_dict(fused.state_dict())
+    loss_fn = jb.modules.DistributedMSELoss(reduce_groups=(mesh["sh"], mesh["sw"]))
+    g = torch.Generator().manual_seed(11 + rank)
+    batches = [(torch.randn(1, 3, 40, 136, generator=g).to(dev), torch.randn(1, 3, 40, 136, generator=g).to(dev))
+               for _ in range(4)]
+    if rank == 1:
+        _delay_kernel("jb_conv3x3_c64_wgrad", 30_000_000)
+    grads = []
+    with jb.parallel.no_grad_sync():
+        for x, y in batches:
+            fused.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = fused(x)
+            loss_fn(out.float(), y).backward()
+            grads.append([p.grad.clone() for p in fused.parameters()])
+    torch.cuda.synchronize()
+    symm.arena(dev).check_status(collective=True)
+    with jb.parallel.no_grad_sync():
+        for i, (x, y) in enumerate(batches):
+            plain.zero_grad()
+            loss_fn(plain(x), y).backward()
+            for (n, q), gf in zip(plain.named_parameters(), grads[i]):
+                assert_close(gf, q.grad, f"micro-batch {i}: grad {n}", 0.0, 4e-2 * float(q.grad.abs().max()) + 1e-7)
+
+
+@pytest.mark.multigpu(2)
+def test_accumulation_with_a_lagging_rank():
+    run_distributed(_worker_accumulation_with_a_lagging_rank, 2, (2, 1), backend="nccl", timeout=300)
+
+
+def _worker_exact_halo(rank, world, mesh_shape):
+    """Integer-valued inputs and weights: every product and sum is exact in fp32 and the bf16 rounding
+    of the result is deterministic, so the fused layer must equal torch on the gathered image bit for
+    bit; a wrong, stale or missing halo pixel cannot hide inside a tolerance."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import merge, split
+    from jigsaw_b200.ops import symm
+
+    torch.backends.cudnn.allow_tf32 = False
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"sh": mesh_shape[0], "sw": mesh_shape[1], "col": 1})
+    cuts = {2: mesh["sh"], 3: mesh["sw"]}
+    layer = jb.modules.DistributedConv2d(64, 64, 3, dev, (mesh["sh"], mesh["sw"]), mesh["col"], padding=1)
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        layer.weight.copy_(torch.randint(-1, 2, layer.weight.shape, generator=g).float())
+        layer.bias.copy_(torch.randint(-3, 4, layer.bias.shape, generator=g).float())
+    for it in range(3):
+        xg = torch.randint(-2, 3, (2, 64, 40 * mesh_shape[0], 136 * mesh_shape[1]), generator=g).float().to(dev)
+        x = split(xg, cuts)
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            y = layer(x)
+        ref = torch.nn.functional.conv2d(xg, layer.weight.detach(), layer.bias.detach(), padding=1).to(torch.bfloat16)
+        symm.arena(dev).check_status()
+        ok = torch.equal(y, split(ref, cuts))
+        from dist_utils import all_ok
+
+        if not all_ok(ok):
+            bad = (y.float() - split(ref, cuts).float()).abs()
+            raise AssertionError(f"iteration {it}: rank {rank} differs at {int((bad > 0).sum())} elements, max {float(bad.max())}")
+
+
+@pytest.mark.multigpu(2)
+def test_exact_halo_two_gpus():
+    run_distributed(_worker_exact_halo, 2, (2, 1), backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_exact_halo_four_gpus_with_corners():
+    run_distributed(_worker_exact_halo, 4, (2, 2), backend="nccl", timeout=300)
+
+
 def _worker_graphed_step(rank, world, mesh_shape):
     """A whole training step replayed as a CUDA graph must follow the eager run bit for bit
     (same kernels, same order), halo epochs included, and eager steps may follow replays."""

@@ -16,16 +16,13 @@ def _rel(a, b):
 @pytest.mark.parametrize("M,K,part_cols,b_mn", [(300, 256, 256, False), (9516, 128, 256, True), (520, 192, 64, False), (520, 192, 64, True), (1000, 128, 128, True)])
 def test_scatter_epilogue_into_local_slabs(M, K, part_cols, b_mn, staged):
     """The GEMM whose epilogue stores column part ``p`` of the product into slab ``p``; here both slabs
-    are buffers of this GPU, so that the epilogue's addressing is checked without peers.  The staged
-    form (tiles leave through shared memory as 128-byte row pieces) runs only when
-    JIGSAW_STAGED_EPILOGUE=1 is set: it has not been measured on hardware yet."""
+    are buffers of this GPU, so that the epilogue's addressing is checked without peers.  Both forms
+    of the epilogue: row-per-thread stores, and the staged one (tiles leave through shared memory as
+    128-byte row pieces) that the library uses."""
     import ctypes
-    import os
 
     from jigsaw_b200.ops import _lib, symm
 
-    if staged and os.environ.get("JIGSAW_STAGED_EPILOGUE", "0") != "1":
-        pytest.skip("set JIGSAW_STAGED_EPILOGUE=1 to run the staged epilogue")
     dev = torch.device("cuda", 0)
     torch.manual_seed(3)
     parts = 2
