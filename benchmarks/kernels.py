@@ -164,8 +164,9 @@ def main() -> None:
         f = lambda: attention_fused.maybe_fused_merge(o1, l1, o2, l2)
         return timed(f, args.warmup, args.reps), o1.numel() * (4 + 4 + 2), None
 
-    # ---- tcgen05 attention forward (only on request: JIGSAW_FLASH_ATTENTION=1), against SDPA for reference
-    if os.environ.get("JIGSAW_FLASH_ATTENTION", "0") == "1":
+    # ---- tcgen05 attention against the library kernels: PyTorch's default SDPA dispatch and the flash kernel
+    #      that the reference's ring core calls directly (aten._scaled_dot_product_flash_attention)
+    if True:
         qa = torch.randn(8, 16, 4096 // scale, 64, device=dev).bfloat16()
         ka, va = torch.randn_like(qa), torch.randn_like(qa)
         fa_flops = 4.0 * qa.shape[0] * qa.shape[1] * qa.shape[2] * qa.shape[2] * 64
@@ -191,6 +192,22 @@ def main() -> None:
             with torch.no_grad():
                 f = lambda: torch.nn.functional.scaled_dot_product_attention(qa, ka, va, scale=0.125)
                 return timed(f, args.warmup, args.reps), None, fa_flops
+
+        @case("aten_flash_fwd_library")
+        def _():
+            with torch.no_grad():
+                f = lambda: torch.ops.aten._scaled_dot_product_flash_attention(qa, ka, va, 0.0, False, False, scale=0.125)
+                return timed(f, args.warmup, args.reps), None, fa_flops
+
+        @case("aten_flash_bwd_library")
+        def _():
+            res = torch.ops.aten._scaled_dot_product_flash_attention(qa, ka, va, 0.0, False, False, scale=0.125)
+            out, lse, ps, po = res[0], res[1], res[6], res[7]
+            go = torch.randn_like(out)
+            S = qa.shape[2]
+            f = lambda: torch.ops.aten._scaled_dot_product_flash_attention_backward(
+                go, qa, ka, va, out, lse, None, None, S, S, 0.0, False, ps, po, scale=0.125)
+            return timed(f, args.warmup, args.reps), None, 2.5 * fa_flops
 
         @case("sdpa_bwd_library")
         def _():

@@ -54,11 +54,11 @@ def _dense_attention(q, k, v, scale: float, dropout_p: float, backend: AttnBacke
             return MathCore.forward(q, k, v, scale, 0.0, 0)[0] if p == 0.0 and not torch.is_grad_enabled() else \
                 _math_autograd(q, k, v, scale, p, None)
         return _math_autograd(q, k, v, scale, p, attn_mask)
-    if (attn_mask is None and p == 0.0 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 64
-            and os.environ.get("JIGSAW_FLASH_ATTENTION", "0") == "1" and not torch._C._functorch.is_batchedtensor(q)):
+    if attn_mask is None and q.is_cuda:
         from ...ops import attention_fused
 
-        return attention_fused.FlashAttention.apply(q, k, v, scale)       # own tcgen05 kernels (opt-in)
+        if attention_fused.flash_usable(q, k, p) and v.dtype == torch.bfloat16:
+            return attention_fused.FlashAttention.apply(q, k, v, scale)       # own tcgen05 kernels
     return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=p, scale=scale)
 
 

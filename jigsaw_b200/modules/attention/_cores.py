@@ -16,7 +16,6 @@ cores/sdpa.py:17-165, forward.py:23-61 and _merge_kernel.py:37-172 (merge).
 
 from __future__ import annotations
 
-import os
 from typing import Any
 
 import torch
@@ -107,8 +106,8 @@ class SdpaCore:
 
 class Tcgen05Core:
     """Own attention kernels for head dimension 64 (``ops/attention_fused.py``); anything they do not
-    cover (other head sizes, dropout, non-bf16 data, CPU) goes to :class:`SdpaCore`.  Selected instead of
-    ``SdpaCore`` only when ``JIGSAW_FLASH_ATTENTION=1`` is set."""
+    cover (other head sizes, dropout, non-bf16 data, CPU) goes to :class:`SdpaCore`.  The default core
+    of every backend except ``math``."""
 
     name = "tcgen05"
 
@@ -139,7 +138,7 @@ def select_core(backend: Any) -> Any:
     name = getattr(backend, "value", backend)
     if name == "math":
         return MathCore
-    return Tcgen05Core if os.environ.get("JIGSAW_FLASH_ATTENTION", "0") == "1" else SdpaCore
+    return Tcgen05Core
 
 
 def merge_chunks(out: torch.Tensor, lse: torch.Tensor, out_j: torch.Tensor, lse_j: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:

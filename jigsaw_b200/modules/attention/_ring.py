@@ -237,7 +237,19 @@ def ring_attention(
 ) -> torch.Tensor:
     """Attention of local queries against the keys / values of the whole group.
     ``q, k, v``: ``(..., heads, seq_local, d)``.  Grad mode is sampled here because it is
-    always off inside ``Function.forward``."""
+    always off inside ``Function.forward``.
+
+    On CUDA with bf16 operands of head dimension 64 and no dropout the whole ring is one fused forward
+    launch (``ops/attention_fused.py``): every send policy of ``cfg`` describes the same sum, the fused
+    kernels pull each part from its owner, and circulating ``x`` instead of K / V is a transport
+    choice that changes nothing in the result (K and V are differentiable outputs of the local
+    projection), so ``cfg`` only matters to the chunked schedule below."""
+    if q.is_cuda:
+        from ...ops import attention_fused
+
+        out = attention_fused.maybe_fused_ring_attention(q, k, v, scale, group, dropout_p)
+        if out is not None:
+            return out
     return _RingAttention.apply(q, k, v, x, w_qkv, scale, dropout_p, group, cfg, torch.is_grad_enabled())
 
 

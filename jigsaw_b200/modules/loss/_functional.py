@@ -62,15 +62,23 @@ def reduce_scalar_loss(local_sum: torch.Tensor, local_denom: torch.Tensor, reduc
 
 
 # ----------------------------------------------------------------------------- regression
+_FUSED_PAIR_KINDS = {F.l1_loss: "l1", F.smooth_l1_loss: "smooth_l1", F.binary_cross_entropy: "bce",
+                     F.binary_cross_entropy_with_logits: "bce_logits"}
+
+
 def _elementwise_loss(fn, input, target, reduction, reduce_groups, **kw):
     _check_reduction(reduction)
     if reduction == "none":
         return fn(input, target, reduction="none", **kw)
     total = None
-    if fn is F.mse_loss and input.is_cuda and not kw:
+    if input.is_cuda and all(v is None for k, v in kw.items() if k != "beta"):
         from ...ops import loss_fused
 
-        total = loss_fused.maybe_fused_sq_diff_sum(input, target)     # one kernel, any strides / bf16 input
+        # one kernel per direction, any strides / bf16 input (weight and pos_weight stay on the torch path)
+        if fn is F.mse_loss:
+            total = loss_fused.maybe_fused_sq_diff_sum(input, target)
+        elif fn in _FUSED_PAIR_KINDS and (fn is not F.smooth_l1_loss or kw.get("beta", 1.0) > 0.0):
+            total = loss_fused.maybe_fused_pair_loss_sum(input, target, _FUSED_PAIR_KINDS[fn], kw.get("beta", 1.0))
     if total is None:
         with torch.autocast(input.device.type, enabled=False):
             acc = torch.promote_types(input.dtype, torch.float32)

@@ -158,6 +158,16 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_flash_attn_fwd.restype = c_int
     L.jb_flash_attn_bwd.argtypes = [c_void_p] * 10 + [c_int, c_int, c_int, c_float, c_void_p, c_void_p]
     L.jb_flash_attn_bwd.restype = c_int
+    L.jb_flash_attn_fwd_parts.argtypes = [c_void_p, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), c_uint, c_uint,
+                                          c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int] + [c_longlong] * 6 + [
+        c_float, c_void_p, c_void_p]
+    L.jb_flash_attn_fwd_parts.restype = c_int
+    L.jb_flash_attn_delta.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p]
+    L.jb_flash_attn_delta.restype = c_int
+    L.jb_flash_attn_bwd_parts.argtypes = [c_void_p] * 4 + [POINTER(c_void_p)] * 7 + [c_uint, c_uint, c_void_p, c_int, c_int,
+                                                                                  c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                                                  c_float, c_void_p, c_void_p]
+    L.jb_flash_attn_bwd_parts.restype = c_int
     L.jb_peer_fetch.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_uint, c_uint, c_void_p, c_void_p, c_int, c_void_p]
     L.jb_peer_fetch.restype = c_int
     L.jb_roll.argtypes = [POINTER(JbRoll), c_void_p, c_void_p, c_int, c_void_p]
@@ -166,12 +176,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_merge_chunks.restype = c_int
     L.jb_mse_grid.argtypes = [c_longlong, c_int]
     L.jb_mse_grid.restype = c_int
-    L.jb_mse_sum.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_void_p, c_void_p, c_void_p, c_int,
-                             c_void_p]
-    L.jb_mse_sum.restype = c_int
-    L.jb_mse_grad.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_void_p, c_void_p, c_int, c_int,
-                              c_void_p]
-    L.jb_mse_grad.restype = c_int
+    L.jb_pair_loss_sum.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_int, c_float, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_void_p]
+    L.jb_pair_loss_sum.restype = c_int
+    L.jb_pair_loss_grad.argtypes = [POINTER(JbStrided4), POINTER(JbStrided4), POINTER(c_int), c_int, c_float, c_void_p, c_void_p,
+                                    c_int, c_int, c_void_p]
+    L.jb_pair_loss_grad.restype = c_int
     L.jb_increment.argtypes = [c_void_p, c_void_p]
     L.jb_increment.restype = c_int
     L.jb_adam_multi.argtypes = [POINTER(JbAdamTensors), c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_void_p,

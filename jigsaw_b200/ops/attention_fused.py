@@ -1,15 +1,29 @@
-"""Attention helpers on the GPU: the online-softmax merge of ring-attention chunks
-(``csrc/elementwise.cu``), one launch instead of half a dozen elementwise kernels.
+"""Attention on the GPU.
 
-Reference parity: the Triton merge kernel of
-jigsaw/modules/attention/_merge_kernel.py:37-82 (launch :140-163), here as a CUDA kernel.
+* :class:`FlashAttention` / :func:`flash_attention_forward` / :func:`flash_attention_backward`: attention
+  for head dimension 64 on the tcgen05 kernels of ``csrc/flash_attn.cu`` and ``csrc/flash_attn_bwd.cu``.
+* :func:`maybe_fused_ring_attention`: sequence-parallel (ring) attention as ONE forward launch and two
+  backward launches.  Every rank stages its keys / values (backward: also queries, output gradients,
+  log-sum-exp and D) in symmetric memory and raises a flag on its peers; the kernels walk over the parts of
+  all ranks and load each block by TMA straight from its owner's memory while the previous block is in the
+  tensor cores.  The running softmax state stays on chip across the parts, so there is no per-chunk
+  merge, and every rank computes the complete gradient of its own keys and values by pulling the other
+  ranks' queries, so no gradient travels back.
+* :func:`maybe_fused_merge`: the online-softmax merge of per-chunk results (``csrc/elementwise.cu``), used
+  by the chunked ring schedule that remains for what the fused kernels do not cover (other head sizes,
+  dropout, circulating ``x``, CPU).
+
+Reference parity: jigsaw/modules/attention/_functional/forward.py:102-200 and backward.py:109-312 (ring
+drivers), cores/sdpa.py:17-165 (per-chunk core), _merge_kernel.py:37-82 (merge).
 """
 
 from __future__ import annotations
 
 import ctypes
+from typing import Any
 
 import torch
+import torch.distributed as dist
 
 from . import _lib
 
@@ -45,9 +59,7 @@ def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     """``softmax(scale * q k^T) v`` and the row-wise log-sum-exp on the tcgen05 kernel of
     ``csrc/flash_attn.cu``.  ``q`` is ``(..., sq, 64)``, ``k`` and ``v`` are ``(..., sk, 64)``, all bf16 on
     one CUDA device with equal leading dimensions; returns ``(out bf16 (..., sq, 64), lse fp32 (..., sq))``.
-    Forward only (no autograd): the cores of ``jigsaw_b200.modules.attention`` do not call it yet, because
-    the kernel has not run on hardware; ``tests/test_elementwise_gpu.py`` holds its numerics test, which
-    runs when ``JIGSAW_FLASH_ATTENTION=1`` is set.
+    Forward only (no autograd): :class:`FlashAttention` is the differentiable form.
 
     Reference parity: the role of the SDPA flash core, jigsaw/modules/attention/_functional/cores/sdpa.py:17-165.
     """
@@ -104,9 +116,7 @@ def flash_attention_backward(dout: torch.Tensor, q: torch.Tensor, k: torch.Tenso
 
 class FlashAttention(torch.autograd.Function):
     """``softmax(scale * q k^T) v`` with forward and backward on the tcgen05 kernels
-    (``csrc/flash_attn.cu``, ``csrc/flash_attn_bwd.cu``); same shapes as :func:`flash_attention_forward`.
-    Not called by the attention layers unless ``JIGSAW_FLASH_ATTENTION=1`` (the kernels have not run on
-    hardware)."""
+    (``csrc/flash_attn.cu``, ``csrc/flash_attn_bwd.cu``); same shapes as :func:`flash_attention_forward`."""
 
     @staticmethod
     def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
@@ -119,3 +129,149 @@ class FlashAttention(torch.autograd.Function):
     def backward(ctx, g: torch.Tensor) -> tuple:
         q, k, v, out, lse = ctx.saved_tensors
         return (*flash_attention_backward(g, q, k, v, out, lse, ctx.scale), None)
+
+
+def flash_usable(q: torch.Tensor, k: torch.Tensor, dropout_p: float = 0.0) -> bool:
+    """Whether the tcgen05 attention kernels cover these operands."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and q.shape[-1] == 64 and k.shape[-1] == 64
+            and dropout_p == 0.0 and q.shape[:-2] == k.shape[:-2] and q.numel() > 0 and k.numel() > 0
+            and not torch._C._functorch.is_batchedtensor(q) and _lib.available())
+
+
+# ----------------------------------------------------------------------------- ring attention in one launch
+_HEADER = 256            # bytes of flag words in front of the staged tensors
+_rings: dict[tuple, list] = {}
+
+
+def _ring_block(ar: Any, tag: tuple, nbytes: int) -> Any:
+    """Two staging blocks per (shape, group), used alternately.  A rank stages its next payload only after
+    its previous attention kernel has finished, and that kernel needed every peer's flag of the same call;
+    so when a block is overwritten, the call that last used it (two calls ago) has completed on every rank."""
+    ring = _rings.get(tag)
+    if ring is None:
+        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
+    blk = ring[0][ring[1] & 1]
+    ring[1] += 1
+    return blk
+
+
+def _publish(ar: Any, blk: Any, ranks: list, me: int) -> tuple[int, int, Any]:
+    """Raise this rank's flag in every peer's copy of ``blk`` once the staging copies are done (stream order)."""
+    epoch = ar.next_own_epoch(blk)
+    stride = ar.capture_stride or 0
+    replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+    flags = (ctypes.c_void_p * 8)()
+    n = 0
+    for i, r in enumerate(ranks):
+        if i != me:
+            flags[n] = blk.peer_ptr(r) + 4 * me
+            n += 1
+    rc = _lib.lib().jb_publish(flags, n, epoch, stride, replay, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200 kernel launcher publish failed with code {rc}")
+    _lib.count_launches(1)
+    return epoch, stride, replay
+
+
+def _part_ptrs(blk: Any, ranks: list, me: int, offset: int) -> Any:
+    arr = (ctypes.c_void_p * 8)()
+    for i, r in enumerate(ranks):
+        arr[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + offset
+    return arr
+
+
+def _flag_ptrs(blk: Any, ranks: list, me: int) -> Any:
+    arr = (ctypes.c_void_p * 8)()
+    for i in range(len(ranks)):
+        arr[i] = None if i == me else blk.ptr + 4 * i
+    return arr
+
+
+class _RingFlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, group: Any) -> torch.Tensor:
+        from . import symm
+
+        L, dev = _lib.lib(), q.device
+        ar = symm.arena(dev)
+        P, me = group.size(), group.rank()
+        ranks = dist.get_process_group_ranks(group)
+        s = q.shape[-2]
+        q3, k3, v3 = (t.reshape(-1, s, 64).contiguous() for t in (q, k, v))
+        bh = q3.shape[0]
+        n = bh * s * 64 * 2                                   # bytes of one staged operand
+        blk = _ring_block(ar, ("ring_fwd", dev.index, bh, s, tuple(ranks)), _HEADER + 2 * n)
+        staged = blk.tensor[_HEADER:_HEADER + 2 * n].view(torch.bfloat16).view(2, bh, s, 64)
+        staged[0].copy_(k3)
+        staged[1].copy_(v3)
+        epoch, stride, replay = _publish(ar, blk, ranks, me)
+        out = torch.empty_like(q3)
+        lse = torch.empty(bh, s, dtype=torch.float32, device=dev)
+        rc = L.jb_flash_attn_fwd_parts(
+            ctypes.c_void_p(q3.data_ptr()), _part_ptrs(blk, ranks, me, _HEADER), _part_ptrs(blk, ranks, me, _HEADER + n),
+            _flag_ptrs(blk, ranks, me), epoch, stride, replay, P, me, ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_void_p(lse.data_ptr()), bh, s, s, 64, s * 64, 64, s * 64, 64, s * 64, float(scale),
+            ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_fwd_parts failed with code {rc}")
+        _lib.count_launches(1)
+        ctx.save_for_backward(q3, k3, v3, out, lse)
+        ctx.scale, ctx.group, ctx.shape = float(scale), group, q.shape
+        return out.view(q.shape)
+
+    @staticmethod
+    def backward(ctx: Any, g: torch.Tensor) -> tuple:
+        from . import symm
+
+        q3, k3, v3, out, lse = ctx.saved_tensors
+        group = ctx.group
+        L, dev = _lib.lib(), q3.device
+        ar = symm.arena(dev)
+        P, me = group.size(), group.rank()
+        ranks = dist.get_process_group_ranks(group)
+        bh, s, _ = q3.shape
+        n = bh * s * 64 * 2
+        nf = bh * s * 4
+        blk = _ring_block(ar, ("ring_bwd", dev.index, bh, s, tuple(ranks)), _HEADER + 4 * n + 2 * nf)
+        ops = blk.tensor[_HEADER:_HEADER + 4 * n].view(torch.bfloat16).view(4, bh, s, 64)       # q, dO, k, v
+        rows = blk.tensor[_HEADER + 4 * n:_HEADER + 4 * n + 2 * nf].view(torch.float32).view(2, bh, s)   # lse, D
+        ops[0].copy_(q3)
+        ops[1].copy_(g.reshape(bh, s, 64))
+        ops[2].copy_(k3)
+        ops[3].copy_(v3)
+        rows[0].copy_(lse)
+        P_ = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        rc = L.jb_flash_attn_delta(P_(out), P_(ops[1]), P_(rows[1]), bh * s, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_delta failed with code {rc}")
+        epoch, stride, replay = _publish(ar, blk, ranks, me)
+        dq, dk, dv = torch.empty_like(q3), torch.empty_like(k3), torch.empty_like(v3)
+        at = lambda i: _part_ptrs(blk, ranks, me, _HEADER + i * n)  # noqa: E731
+        lse_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n)
+        delta_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n + nf)
+        rc = L.jb_flash_attn_bwd_parts(
+            P_(ops[0]), P_(ops[2]), P_(ops[3]), P_(ops[1]), at(0), at(1), lse_parts, delta_parts, at(2), at(3),
+            _flag_ptrs(blk, ranks, me), epoch, stride, replay, P, me, P_(dq), P_(dk), P_(dv), bh, s, ctx.scale,
+            ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_bwd_parts failed with code {rc}")
+        _lib.count_launches(3)
+        return dq.view(ctx.shape), dk.view(ctx.shape), dv.view(ctx.shape), None, None
+
+
+@_lib.traced("jb.maybe_fused_ring_attention")
+@_lib.audited("ring_attention")
+def maybe_fused_ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, group: Any,
+                               dropout_p: float = 0.0) -> torch.Tensor | None:
+    """Attention of the local queries ``(..., h, s, 64)`` against the keys / values of every rank of
+    ``group`` (each holding ``s`` positions), differentiable, on the multi-part tcgen05 kernels; ``None``
+    when they do not apply (then the chunked schedule of ``modules/attention/_ring.py`` runs)."""
+    if not q.is_cuda:
+        return None
+    if group is None or not 2 <= group.size() <= 8:
+        return _lib.decline("the group must have 2 to 8 ranks")
+    if not flash_usable(q, k, dropout_p) or v.dtype != torch.bfloat16:
+        return _lib.decline("needs bf16 operands with head dimension 64 and no dropout")
+    if q.shape != k.shape or k.shape != v.shape or q.shape[-2] % 8:
+        return _lib.decline("needs equal shapes of q, k, v on every rank and a local sequence that is a multiple of 8")
+    return _RingFlashAttention.apply(q, k, v, scale, group)

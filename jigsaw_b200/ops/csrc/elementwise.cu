@@ -79,10 +79,39 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(float* __restrict__ o1,
 }
 
 // ------------------------------------------------------------------------------------------
-// Squared-error loss on tensors of up to four dimensions with arbitrary strides.
-//   forward : out[0] = sum (a - b)^2          (deterministic two-level reduction)
-//   backward: ga = scale[0] * 2 (a - b), written with the strides of a
+// Element-wise losses f(a, b) on tensors of up to four dimensions with arbitrary strides:
+//   forward : out[0] = sum f(a, b)            (deterministic two-level reduction)
+//   backward: ga = scale[0] * df/da, written with the strides of a
+// f is chosen by `op`: squared error, absolute error, smooth L1 (beta), binary cross-entropy of
+// probabilities (logarithms clamped at -100, as PyTorch does) and of logits.
 // ------------------------------------------------------------------------------------------
+enum : int { PAIR_SQ = 0, PAIR_L1 = 1, PAIR_SMOOTH_L1 = 2, PAIR_BCE = 3, PAIR_BCE_LOGITS = 4 };
+
+__device__ __forceinline__ float pair_value(int op, float a, float b, float beta) {
+  const float d = a - b;
+  switch (op) {
+    case PAIR_SQ: return d * d;
+    case PAIR_L1: return fabsf(d);
+    case PAIR_SMOOTH_L1: {
+      const float ad = fabsf(d);
+      return ad < beta ? 0.5f * d * d / beta : ad - 0.5f * beta;
+    }
+    case PAIR_BCE: return -(b * fmaxf(logf(a), -100.f) + (1.f - b) * fmaxf(logf(1.f - a), -100.f));
+    default: return fmaxf(a, 0.f) - a * b + log1pf(expf(-fabsf(a)));           // PAIR_BCE_LOGITS
+  }
+}
+
+__device__ __forceinline__ float pair_grad(int op, float a, float b, float beta) {
+  const float d = a - b;
+  switch (op) {
+    case PAIR_SQ: return 2.f * d;
+    case PAIR_L1: return d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
+    case PAIR_SMOOTH_L1: return fabsf(d) < beta ? d / beta : (d > 0.f ? 1.f : -1.f);
+    case PAIR_BCE: return d / fmaxf((1.f - a) * a, 1e-12f);
+    default: return 1.f / (1.f + expf(-a)) - b;                                 // PAIR_BCE_LOGITS
+  }
+}
+
 struct Strided4 {
   const void* ptr;
   int is_bf16;
@@ -100,6 +129,8 @@ struct MseArgs {
   void* ga;             // backward: gradient of a (strides of a)
   int ga_bf16;
   int a_dense;          // a's offset equals the linear index in the given dimension order
+  int op;               // PAIR_*
+  float beta;           // smooth L1
 };
 
 __device__ __forceinline__ float load_strided(const Strided4& t, long long off) {
@@ -136,8 +167,7 @@ __global__ void __launch_bounds__(256) mse_fwd_kernel(const MseArgs p) {
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     long long oa, ob;
     mse_offsets(p, i, &oa, &ob);
-    const float d = load_strided(p.a, oa) - load_strided(p.b, ob);
-    s += d * d;
+    s += pair_value(p.op, load_strided(p.a, oa), load_strided(p.b, ob), p.beta);
   }
   __shared__ float red[8];
   __shared__ bool last;
@@ -175,7 +205,7 @@ __global__ void __launch_bounds__(256) mse_pix_kernel(const MseArgs p) {
   const int C = p.size[3];
   const unsigned int s2 = p.size[2], s1 = p.size[1];
   const long long pixels = p.numel / C;
-  const float k = BWD ? 2.f * __ldg(p.scale) : 0.f;
+  const float k = BWD ? __ldg(p.scale) : 0.f;
   float s = 0.f;
   for (long long j = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; j < pixels;
        j += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -186,12 +216,13 @@ __global__ void __launch_bounds__(256) mse_pix_kernel(const MseArgs p) {
     const long long ob = i0 * p.b.stride[0] + i1 * p.b.stride[1] + i2 * p.b.stride[2];
     const long long oa = j * C;
     for (int c = 0; c < C; ++c) {
-      const float d = load_strided(p.a, oa + c) - load_strided(p.b, ob + c * p.b.stride[3]);
+      const float av = load_strided(p.a, oa + c), bv = load_strided(p.b, ob + c * p.b.stride[3]);
       if (BWD) {
-        if (p.ga_bf16) static_cast<__nv_bfloat16*>(p.ga)[oa + c] = __float2bfloat16(k * d);
-        else static_cast<float*>(p.ga)[oa + c] = k * d;
+        const float gv = k * pair_grad(p.op, av, bv, p.beta);
+        if (p.ga_bf16) static_cast<__nv_bfloat16*>(p.ga)[oa + c] = __float2bfloat16(gv);
+        else static_cast<float*>(p.ga)[oa + c] = gv;
       } else {
-        s += d * d;
+        s += pair_value(p.op, av, bv, p.beta);
       }
     }
   }
@@ -224,12 +255,12 @@ __global__ void __launch_bounds__(256) mse_pix_kernel(const MseArgs p) {
 }
 
 __global__ void __launch_bounds__(256) mse_bwd_kernel(const MseArgs p) {
-  const float k = 2.f * __ldg(p.scale);
+  const float k = __ldg(p.scale);
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     long long oa, ob;
     mse_offsets(p, i, &oa, &ob);
-    const float g = k * (load_strided(p.a, oa) - load_strided(p.b, ob));
+    const float g = k * pair_grad(p.op, load_strided(p.a, oa), load_strided(p.b, ob), p.beta);
     if (p.ga_bf16) static_cast<__nv_bfloat16*>(p.ga)[oa] = __float2bfloat16(g);
     else static_cast<float*>(p.ga)[oa] = g;
   }
@@ -396,12 +427,14 @@ extern "C" int jb_mse_grid(long long numel, int sm_count) {
   return static_cast<int>(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
-// out[0] = sum (a - b)^2.  partial: jb_mse_grid() floats; counter: zeroed word (left zero).
-extern "C" int jb_mse_sum(const JbStrided4* a, const JbStrided4* b, const int* size, float* partial,
-                          unsigned int* counter, float* out, int sm_count, void* stream) {
+// out[0] = sum f(a, b), f chosen by op (0 squared error, 1 absolute error, 2 smooth L1 with `beta`, 3 binary
+// cross-entropy of probabilities, 4 of logits).  partial: jb_mse_grid() floats; counter: zeroed word (left zero).
+extern "C" int jb_pair_loss_sum(const JbStrided4* a, const JbStrided4* b, const int* size, int op, float beta,
+                                float* partial, unsigned int* counter, float* out, int sm_count, void* stream) {
   MseArgs p{};
   mse_fill(&p, a, b, size);
-  if (p.numel <= 0) return -1;
+  if (p.numel <= 0 || op < 0 || op > 4 || (op == PAIR_SMOOTH_L1 && !(beta > 0.f))) return -1;
+  p.op = op; p.beta = beta;
   p.partial = partial; p.counter = counter; p.out = out;
   if (p.a_dense && p.size[3] <= 4)
     mse_pix_kernel<false><<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
@@ -410,12 +443,13 @@ extern "C" int jb_mse_sum(const JbStrided4* a, const JbStrided4* b, const int* s
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-// ga = 2 * scale[0] * (a - b), written with the strides of a.
-extern "C" int jb_mse_grad(const JbStrided4* a, const JbStrided4* b, const int* size, const float* scale, void* ga,
-                           int ga_bf16, int sm_count, void* stream) {
+// ga = scale[0] * df/da, written with the strides of a.
+extern "C" int jb_pair_loss_grad(const JbStrided4* a, const JbStrided4* b, const int* size, int op, float beta,
+                                 const float* scale, void* ga, int ga_bf16, int sm_count, void* stream) {
   MseArgs p{};
   mse_fill(&p, a, b, size);
-  if (p.numel <= 0) return -1;
+  if (p.numel <= 0 || op < 0 || op > 4 || (op == PAIR_SMOOTH_L1 && !(beta > 0.f))) return -1;
+  p.op = op; p.beta = beta;
   p.scale = scale; p.ga = ga; p.ga_bf16 = ga_bf16;
   if (p.a_dense && p.size[3] <= 4)
     mse_pix_kernel<true><<<jb_mse_grid(p.numel, sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -60,21 +60,27 @@ def _dense(t: torch.Tensor) -> bool:
     return True
 
 
-class _SqDiffSum(torch.autograd.Function):
+PAIR_OPS = {"mse": 0, "l1": 1, "smooth_l1": 2, "bce": 3, "bce_logits": 4}
+
+
+class _PairLossSum(torch.autograd.Function):
+    """``sum f(a, b)`` over all elements for one of the element-wise losses of ``PAIR_OPS``."""
+
     @staticmethod
-    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, op: int, beta: float) -> torch.Tensor:
         L, dev = _lib.lib(), a.device
         partial, counter = _scratch_for(dev)
         out = torch.empty((), dtype=torch.float32, device=dev)
         order = _order(a)
         da, db = _desc(a, order), _desc(b, order)
-        rc = L.jb_mse_sum(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), ctypes.c_void_p(partial.data_ptr()),
-                          ctypes.c_void_p(counter.data_ptr()), ctypes.c_void_p(out.data_ptr()), _lib.sm_count(dev.index),
-                          _lib.stream_ptr())
+        rc = L.jb_pair_loss_sum(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), op, float(beta),
+                                ctypes.c_void_p(partial.data_ptr()), ctypes.c_void_p(counter.data_ptr()),
+                                ctypes.c_void_p(out.data_ptr()), _lib.sm_count(dev.index), _lib.stream_ptr())
         if rc != 0:
-            raise RuntimeError(f"jigsaw_b200 kernel launcher mse_sum failed with code {rc}")
+            raise RuntimeError(f"jigsaw_b200 kernel launcher pair_loss_sum failed with code {rc}")
         _lib.count_launches(1)
         ctx.save_for_backward(a, b)
+        ctx.op, ctx.beta = op, float(beta)
         return out
 
     @staticmethod
@@ -87,15 +93,17 @@ class _SqDiffSum(torch.autograd.Function):
             ga = torch.empty_strided(a.shape, a.stride(), dtype=a.dtype, device=dev)
             order = _order(a)
             da, db = _desc(a, order), _desc(b, order)
-            rc = L.jb_mse_grad(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), ctypes.c_void_p(scale.data_ptr()),
-                               ctypes.c_void_p(ga.data_ptr()), int(ga.dtype == torch.bfloat16), _lib.sm_count(dev.index),
-                               _lib.stream_ptr())
+            rc = L.jb_pair_loss_grad(ctypes.byref(da), ctypes.byref(db), _sizes(a, order), ctx.op, ctx.beta,
+                                     ctypes.c_void_p(scale.data_ptr()), ctypes.c_void_p(ga.data_ptr()),
+                                     int(ga.dtype == torch.bfloat16), _lib.sm_count(dev.index), _lib.stream_ptr())
             if rc != 0:
-                raise RuntimeError(f"jigsaw_b200 kernel launcher mse_grad failed with code {rc}")
+                raise RuntimeError(f"jigsaw_b200 kernel launcher pair_loss_grad failed with code {rc}")
             _lib.count_launches(1)
         if ctx.needs_input_grad[1]:
+            if ctx.op != 0:
+                raise NotImplementedError("only the squared error is differentiable in its target on the fused path")
             gb = (-2.0 * scale) * (a.float() - b.float()).to(b.dtype)
-        return ga, gb
+        return ga, gb, None, None
 
 
 @_lib.traced("jb.maybe_fused_sq_diff_sum")
@@ -103,16 +111,35 @@ class _SqDiffSum(torch.autograd.Function):
 def maybe_fused_sq_diff_sum(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor | None:
     """``sum((a - b)^2)`` as an fp32 scalar (differentiable in ``a``), or ``None`` when the
     kernel does not apply."""
-    if not a.is_cuda or a.shape != b.shape or a.dim() > 4 or a.dim() == 0 or a.numel() == 0:
+    return _pair_loss_sum(a, b, "mse", 1.0)
+
+
+@_lib.traced("jb.maybe_fused_pair_loss_sum")
+@_lib.audited("pair_loss_sum")
+def maybe_fused_pair_loss_sum(a: torch.Tensor, b: torch.Tensor, kind: str, beta: float = 1.0) -> torch.Tensor | None:
+    """``sum f(a, b)`` as an fp32 scalar, differentiable in ``a``, for ``kind`` in ``"l1"``, ``"smooth_l1"``
+    (with ``beta``), ``"bce"`` (``a`` holds probabilities), ``"bce_logits"`` (``a`` holds logits); one kernel
+    per direction on tensors of any strides; ``None`` when the kernel does not apply."""
+    return _pair_loss_sum(a, b, kind, beta)
+
+
+def _pair_loss_sum(a: torch.Tensor, b: torch.Tensor, kind: str, beta: float) -> torch.Tensor | None:
+    if not a.is_cuda:
         return None
+    if a.shape != b.shape or a.dim() > 4 or a.dim() == 0 or a.numel() == 0:
+        return _lib.decline("needs two tensors of the same shape with 1 to 4 dimensions")
     if a.dtype not in _OK or b.dtype not in _OK or torch._C._functorch.is_batchedtensor(a):
-        return None
+        return _lib.decline("needs fp32 or bf16 tensors outside vmap")
+    if b.requires_grad and kind != "mse":
+        return _lib.decline("the target needs a gradient")
+    if kind == "smooth_l1" and not beta > 0.0:
+        return _lib.decline("smooth L1 with beta = 0 is the absolute error")
     # the gradient is written with the strides of ``a``: they must address distinct elements
     if not _dense(a):
-        return None
+        return _lib.decline("the prediction overlaps itself in memory")
     if not _lib.available():
         raise RuntimeError("jigsaw_b200: the sm_100a kernel library is missing on a CUDA machine")
-    return _SqDiffSum.apply(a, b)
+    return _PairLossSum.apply(a, b, PAIR_OPS[kind], float(beta))
 
 
 # ----------------------------------------------------------------------------- cross-entropy

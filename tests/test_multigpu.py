@@ -669,3 +669,49 @@ def test_ulysses_fused_projection_two_gpus():
 @pytest.mark.multigpu(4)
 def test_ulysses_fused_projection_four_gpus():
     run_distributed(_worker_ulysses_qkv, 4, backend="nccl", timeout=300)
+
+
+def _worker_ring_flash_attention(rank, world):
+    """Ring attention as one fused launch: keys / values (backward: queries, output gradients, log-sum-exp,
+    D) are pulled by TMA from the owners' memory.  Output and the three gradients of the local sequence
+    part against fp32 attention over the gathered sequence; several calls in a row (the staging blocks
+    alternate) with different data."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from dist_utils import merge
+    from jigsaw_b200.ops import _lib, attention_fused, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": world, "col": 1})
+    group = mesh["row"]
+    b, h, s = 2, 3, 384
+    gen = torch.Generator().manual_seed(50 + rank)
+    for it in range(3):
+        q, k, v, g = (torch.randn(b, h, s, 64, generator=gen).to(dev).bfloat16() for _ in range(4))
+        ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
+        before = _lib.LAUNCHES
+        with _lib.strict_fused():
+            out = attention_fused.maybe_fused_ring_attention(ql, kl, vl, 0.125, group)
+        assert _lib.LAUNCHES - before == 2, "one publish and ONE attention launch for the whole ring"
+        out.backward(g)
+        symm.arena(dev).check_status(collective=True)
+        cuts = {2: group}
+        qa, ka, va, ga = (merge(t.float(), cuts).requires_grad_(True) for t in (q, k, v, g))
+        ref = torch.softmax(0.125 * (qa @ ka.transpose(-1, -2)), dim=-1) @ va
+        ref.backward(ga.detach())
+        sl = slice(rank * s, (rank + 1) * s)
+        assert_close(out.float(), ref.detach()[:, :, sl], f"call {it}: output", 0.0, 2e-2 * float(ref.abs().max()))
+        for name, mine, full in (("dq", ql.grad, qa.grad), ("dk", kl.grad, ka.grad), ("dv", vl.grad, va.grad)):
+            assert_close(mine.float(), full[:, :, sl], f"call {it}: {name}", 0.0, 2e-2 * float(full.abs().max()))
+
+
+@pytest.mark.multigpu(2)
+def test_ring_flash_attention_two_gpus():
+    run_distributed(_worker_ring_flash_attention, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_ring_flash_attention_four_gpus():
+    run_distributed(_worker_ring_flash_attention, 4, backend="nccl", timeout=300)
