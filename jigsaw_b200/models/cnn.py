@@ -63,10 +63,16 @@ class DomainCNN(nn.Module):
         kinds = conv_fused.chain_kinds([(c.in_channels, c.out_channels) for c in self.convs])
         if kinds is None:
             return None
-        # one call: all replicated gradients travel in a single flattened all-reduce per group
-        params = list(parallel.sync_grad(*[t for c in self.convs for t in (c.weight, c.bias)]))
+        raw = [t for c in self.convs for t in (c.weight, c.bias)]
         geom = conv_fused.geometry_for(x, *self.spatial)
         acts = [True] * (len(self.convs) - 1) + [False]
+        ranks = parallel.overlapped_sum_plan(raw)
+        if ranks is not None:
+            # every layer's gradients are summed over the tile ranks by the chain itself, on a side stream,
+            # while the rest of its backward pass runs
+            return conv_fused.conv_chain(x, geom, kinds, acts, raw[0::2], raw[1::2], reduce_ranks=ranks)
+        # one call: all replicated gradients travel in a single flattened all-reduce per group
+        params = list(parallel.sync_grad(*raw))
         return conv_fused.conv_chain(x, geom, kinds, acts, params[0::2], params[1::2])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -74,6 +74,13 @@ class JbA2a(ctypes.Structure):
                 ("stride", c_uint), ("replay", c_void_p)]
 
 
+class JbAllReduce(ctypes.Structure):
+    """Arguments of the peer-memory all-reduce (see ``csrc/allreduce.cu``)."""
+
+    _fields_ = [("buf", c_void_p * 8), ("notice_out", c_void_p * 8), ("notice_in", c_void_p * 8), ("epoch", c_uint),
+                ("stride", c_uint), ("replay", c_void_p), ("ranks", c_int), ("me", c_int), ("n", c_longlong), ("scale", c_float)]
+
+
 class JbStrided4(ctypes.Structure):
     """A tensor of up to four dimensions: base pointer, element type, element strides."""
 
@@ -149,6 +156,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_all_to_all.restype = c_int
     L.jb_wait_flags.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
     L.jb_wait_flags.restype = c_int
+    L.jb_all_reduce_sum.argtypes = [POINTER(JbAllReduce), c_void_p, c_void_p, c_int, c_void_p]
+    L.jb_all_reduce_sum.restype = c_int
     L.jb_slot_acquire.argtypes = [POINTER(c_void_p), c_int, c_void_p, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
     L.jb_slot_acquire.restype = c_int
     L.jb_slot_release.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]

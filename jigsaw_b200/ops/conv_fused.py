@@ -131,7 +131,8 @@ class _BlockHolder:
 
 class _ConvChain(torch.autograd.Function):
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, geom: Geometry, kinds: tuple, acts: tuple, *params: torch.Tensor | None) -> torch.Tensor:
+    def forward(ctx: Any, x: torch.Tensor, geom: Geometry, kinds: tuple, acts: tuple, reduce_ranks: tuple | None,
+                *params: torch.Tensor | None) -> torch.Tensor:
         L = _lib.lib()
         ar, st = geom.arena, _lib.stream_ptr()
         NB, H, W = geom.NB, geom.H, geom.W
@@ -179,6 +180,7 @@ class _ConvChain(torch.autograd.Function):
             ctx.shapes = [tuple(w.shape) for w in weights]
             ctx.has_bias = [b is not None for b in biases]
             ctx.x_needs_grad = ctx.needs_input_grad[0]
+            ctx.reduce_ranks = reduce_ranks
             ctx.holder = _BlockHolder(ar, acts_in)
         else:
             for blk in acts_in:
@@ -204,6 +206,13 @@ class _ConvChain(torch.autograd.Function):
                               _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
         scratch = None
         gx = None
+        # replicated weights: every layer's gradient is summed over the tile ranks on a side stream as soon
+        # as its kernel has been launched, under the remaining data- and weight-gradient kernels
+        reducer = None
+        if ctx.reduce_ranks is not None:
+            from . import reduce_fused
+
+            reducer = reduce_fused.OverlappedReducer(dev, ctx.reduce_ranks)
         for i in range(n - 1, -1, -1):
             kind = kinds[i]
             cout, cin = ctx.shapes[i][0], ctx.shapes[i][1]
@@ -222,6 +231,8 @@ class _ConvChain(torch.autograd.Function):
                 gw, gb = gw[:cout].contiguous(), gb[:cout].contiguous()
             grads[2 * i] = gw
             grads[2 * i + 1] = gb if ctx.has_bias[i] else None
+            if reducer is not None:
+                reducer.add([gw, gb] if ctx.has_bias[i] else [gw])
             # ---- data gradient
             if i == 0:
                 if ctx.x_needs_grad and kind == "mid":
@@ -241,18 +252,24 @@ class _ConvChain(torch.autograd.Function):
             ar.free(g)
             g = gnext
         ctx.holder.release()
-        return (gx, None, None, None, *grads)
+        if reducer is not None:
+            reducer.finish()
+        return (gx, None, None, None, None, *grads)
 
 
 @_lib.traced("jb.conv_chain")
-def conv_chain(x: torch.Tensor, geom: Geometry, kinds: list[str], acts: list[bool], weights: list, biases: list) -> torch.Tensor:
+def conv_chain(x: torch.Tensor, geom: Geometry, kinds: list[str], acts: list[bool], weights: list, biases: list,
+               reduce_ranks: list[int] | None = None) -> torch.Tensor:
     """Run an eligible chain on the fused kernels.  ``x``: ``(N, C, H, W)`` local tile (any
     strides, fp32 or bf16).  Returns the output tile as a bf16 ``(N, C_out, H, W)`` tensor in
-    channels-last memory."""
+    channels-last memory.  With ``reduce_ranks`` (world ranks holding copies of the weights, see
+    ``parallel.overlapped_sum_plan``) the weight and bias gradients come back already summed over those
+    ranks, each layer's sum overlapped with the rest of the backward pass; the parameters must then NOT
+    also go through ``sync_grad``."""
     flat: list = []
     for w, b in zip(weights, biases):
         flat += [w, b]
-    return _ConvChain.apply(x, geom, tuple(kinds), tuple(acts), *flat)
+    return _ConvChain.apply(x, geom, tuple(kinds), tuple(acts), None if reduce_ranks is None else tuple(reduce_ranks), *flat)
 
 
 _geoms: dict[tuple, Geometry] = {}

@@ -10,6 +10,7 @@
 #include "roll.cu"
 #include "alltoall.cu"
 #include "signal.cu"
+#include "allreduce.cu"
 #include "flash_attn.cu"
 #include "flash_attn_bwd.cu"
 

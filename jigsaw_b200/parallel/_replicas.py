@@ -45,6 +45,17 @@ def merged_group(groups: "Sequence[dist.ProcessGroup]") -> "dist.ProcessGroup | 
     return _MERGED.get(frozenset(tuple(dist.get_process_group_ranks(g)) for g in groups))
 
 
+def replica_rank_set(groups: "Sequence[dist.ProcessGroup]") -> list[int]:
+    """World ranks that hold a copy of a parameter replicated over ``groups`` (orthogonal axes of a
+    regular mesh: the offsets along the axes add up), this rank included, sorted."""
+    ranks = {dist.get_rank()}
+    for g in groups:
+        members = dist.get_process_group_ranks(g)
+        mine = members[g.rank()]
+        ranks = {r + (m - mine) for r in ranks for m in members}
+    return sorted(ranks)
+
+
 def _real_groups(groups: "dist.ProcessGroup | Iterable[dist.ProcessGroup | None] | None") -> Groups:
     if groups is None:
         return ()

@@ -25,19 +25,36 @@ import torch.distributed as dist
 
 from ._ddp import check_active_ddp
 from ._joint import JointCommHookState, active_joint_state, joint_state_of
-from ._replicas import Groups, merged_group, replica_groups
+from ._replicas import Groups, merged_group, replica_groups, replica_rank_set
 
 _SYNC_DISABLED = os.environ.get("JIGSAW_DISABLE_GRAD_SYNC", "") == "1"
 _deferred = 0          # nesting depth of no_grad_sync()
 
 
+def _all_reduce_sum(flat: torch.Tensor, group: dist.ProcessGroup) -> None:
+    if flat.is_cuda and group.size() > 1:
+        from ..ops import reduce_fused
+
+        # one own kernel over peer memory (bit-identical on every rank) instead of the library collective
+        if reduce_fused.maybe_fused_all_reduce([flat], dist.get_process_group_ranks(group)):
+            return
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+
+
 def _reduce_flat(flat: torch.Tensor, groups: Groups) -> None:
+    if flat.is_cuda and len(groups) > 1:
+        from ..ops import reduce_fused
+
+        # all axes in one launch: the kernel addresses the copies by rank, it needs no process group
+        ranks = replica_rank_set(groups)
+        if len(ranks) <= 8 and reduce_fused.usable([flat], ranks) and reduce_fused.maybe_fused_all_reduce([flat], ranks):
+            return
     whole = merged_group(groups)
     if whole is not None:
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=whole)
+        _all_reduce_sum(flat, whole)
         return
     for g in groups:
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=g)
+        _all_reduce_sum(flat, g)
 
 
 class _SumGradOverGroups(torch.autograd.Function):
@@ -122,6 +139,34 @@ def sync_grad(*tensors: torch.Tensor | None) -> tuple[torch.Tensor | None, ...]:
         for i, r in zip(idx, routed):
             result[i] = r
     return tuple(result)
+
+
+def overlapped_sum_plan(tensors: Iterable[torch.Tensor | None]) -> list[int] | None:
+    """For fused multi-layer operations that produce the gradients of several replicated parameters one
+    after another: the world ranks over which ALL of ``tensors`` must be summed, when that sum may be
+    started per layer on a side stream while the operation's backward pass continues (CUDA, one common
+    set of replica groups, at most eight copies, no gradient accumulation in progress, no DDP joint hook
+    in charge).  ``None`` means: route the parameters through :func:`sync_grad` instead."""
+    if not dist.is_initialized() or _SYNC_DISABLED or _deferred or not torch.is_grad_enabled():
+        return None
+    if active_joint_state() is not None:
+        return None
+    common = None
+    for t in tensors:
+        if t is None or not t.requires_grad:
+            continue
+        if not t.is_cuda or t.dtype != torch.float32:
+            return None
+        groups = replica_groups(t)
+        key = tuple(sorted(tuple(dist.get_process_group_ranks(g)) for g in groups))
+        if common is None:
+            common = (key, groups)
+        elif common[0] != key:
+            return None
+    if common is None or not common[1]:
+        return None
+    ranks = replica_rank_set(common[1])
+    return ranks if 2 <= len(ranks) <= 8 else None
 
 
 @contextlib.contextmanager

@@ -16,7 +16,7 @@ EXPECTED = {
     "jigsaw_b200": {"ProcessMesh", "make_process_mesh", "checkpoint", "convert", "data", "models", "optim", "utils", "debug", "gather", "init", "launch", "log", "modules",
                     "parallel"},
     "jigsaw_b200.parallel": {"JointCommHookState", "broadcast_replicas", "check_ddp", "clip_grad_norm_", "joint_comm_hook",
-                             "mark_replicated", "no_grad_sync", "reduce_replica_grads", "register_joint_comm_hook",
+                             "mark_replicated", "no_grad_sync", "overlapped_sum_plan", "reduce_replica_grads", "register_joint_comm_hook",
                              "replica_groups", "sync_grad", "synced_call", "synced_parameters", "wrap_ddp"},
     "jigsaw_b200.modules.functional": {"confusion_to_metrics", "distributed_argmax", "distributed_binary_cross_entropy",
                                        "distributed_binary_cross_entropy_with_logits", "distributed_confusion_matrix",

@@ -715,3 +715,61 @@ def test_ring_flash_attention_two_gpus():
 @pytest.mark.multigpu(4)
 def test_ring_flash_attention_four_gpus():
     run_distributed(_worker_ring_flash_attention, 4, backend="nccl", timeout=300)
+
+
+def _worker_all_reduce_kernel(rank, world):
+    """The peer-memory all-reduce kernel against NCCL on integer-valued data (every partial sum is exact, so
+    the results must agree bit for bit): whole world and sub-groups, several sizes, twice in a row, and
+    through the overlapped reducer on its side stream."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+
+    from jigsaw_b200.ops import _lib, reduce_fused, symm
+
+    dev = torch.device("cuda", rank)
+    groups = [(list(range(world)), dist.group.WORLD)]
+    if world == 4:
+        for members in ([0, 1], [2, 3], [0, 2], [1, 3]):
+            g = dist.new_group(members)
+            if rank in members:
+                groups.append((members, g))
+    gen = torch.Generator().manual_seed(rank)
+    for ranks, pg in groups:
+        for it, sizes in enumerate(((36928,), (5, 1733, 64), (1 << 20, 3), (36928,))):
+            ts = [torch.randint(-50, 50, (n,), generator=gen).float().to(dev) for n in sizes]
+            ref = [t.clone() for t in ts]
+            for r in ref:
+                dist.all_reduce(r, group=pg)
+            before = _lib.LAUNCHES
+            with _lib.strict_fused():
+                assert reduce_fused.maybe_fused_all_reduce(ts, ranks)
+            assert _lib.LAUNCHES == before + 1
+            for t, r in zip(ts, ref):
+                assert torch.equal(t, r), (ranks, it)
+    # side stream: reductions of several buckets in flight while the main stream keeps working
+    red = reduce_fused.OverlappedReducer(dev, list(range(world)), scale=0.5)
+    buckets = [[torch.randint(-9, 9, (4000 + 100 * i,), generator=gen).float().to(dev), torch.randint(-9, 9, (64,), generator=gen).float().to(dev)]
+               for i in range(5)]
+    refs = [[t.clone() for t in b] for b in buckets]
+    busy = torch.randn(2048, 2048, device=dev)
+    for b in buckets:
+        red.add(b)
+        busy = busy @ busy * 1e-3
+    red.finish()
+    for b, rb in zip(buckets, refs):
+        for t, r in zip(b, rb):
+            dist.all_reduce(r)
+            assert torch.equal(t, r * 0.5)
+    symm.arena(dev).check_status(collective=True)
+
+
+@pytest.mark.multigpu(2)
+def test_all_reduce_kernel_two_gpus():
+    run_distributed(_worker_all_reduce_kernel, 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(4)
+def test_all_reduce_kernel_four_gpus():
+    run_distributed(_worker_all_reduce_kernel, 4, backend="nccl", timeout=300)
