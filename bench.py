@@ -43,6 +43,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--image", type=int, default=IMAGE, help="global image edge (default: the benchmark size)")
+    ap.add_argument("--model", choices=("domaincnn", "sequential"), default="domaincnn",
+                    help="ours: the DomainCNN model class, or the same nn.Sequential of DistributedConv2d + nn.GELU layers "
+                         "that the reference arm builds (its layers join into the same fused chain)")
     return ap.parse_args()
 
 
@@ -107,7 +110,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build(impl: str, mesh_shape: tuple[int, int], dev: torch.device):
+def build(impl: str, mesh_shape: tuple[int, int], dev: torch.device, model_kind: str = "domaincnn"):
     """Model, loss and mesh of the chosen implementation, through its public API."""
     if impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
@@ -116,7 +119,7 @@ def build(impl: str, mesh_shape: tuple[int, int], dev: torch.device):
         import jigsaw_b200 as lib
     mesh = lib.make_process_mesh({"sh": mesh_shape[0], "sw": mesh_shape[1], "col": 1})
     torch.manual_seed(0)
-    if impl == "reference":
+    if impl == "reference" or model_kind == "sequential":
         chans = [CIN] + [WIDTH] * (DEPTH - 1) + [COUT]
         layers = []
         for i in range(DEPTH):
@@ -142,7 +145,11 @@ def main() -> None:
         raise SystemExit("--gpus must be 1, 2, 4 or 8")
     rank, world, dev = init_dist(args.gpus)
     ph, pw = MESHES[args.gpus]
-    model, loss_fn, mesh = build(args.impl, (ph, pw), dev)
+    model, loss_fn, mesh = build(args.impl, (ph, pw), dev, args.model)
+    if args.impl == "ours":
+        from jigsaw_b200.ops import _lib as _jb_lib
+
+        _jb_lib.set_strict(True)       # a fused operation that declines its inputs raises: no silent library fallback
     graphed = args.impl == "ours" and not args.no_graph
     if args.impl == "ours":
         from jigsaw_b200.optim import FusedAdam
@@ -269,12 +276,14 @@ def main() -> None:
                 "seq_len": None,
                 "parallelism": f"domain sh{ph} x sw{pw}",
                 "cuda_graph": bool(graphed),
+                "model_api": args.model if args.impl == "ours" else "sequential",
                 "l2": "per-rank activations (>= 270 MB per layer) exceed the 126 MB L2; no explicit flush",
             },
             "clocks": clocks,
             "e2e": {"value": 1000.0 / ms_e2e, "unit": "images/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": loss_bytes},
             "gpu_launches": launches,
+            "dispatch": _jb_lib.dispatch_counts() if args.impl == "ours" else None,
             "loss": loss_val,
         }
         print(json.dumps(line), flush=True)

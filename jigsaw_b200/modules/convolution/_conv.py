@@ -373,11 +373,11 @@ class _DistributedConvBase(torch.nn.Module):
         unbatched = x.dim() == n + 1
         if unbatched:
             x = x.unsqueeze(0)
+        lazy, x = self._try_fused(x)
+        if lazy is not None:
+            return lazy            # computed when something other than GELU / the next eligible layer touches it
         w, b = parallel.sync_grad(self.weight, self.bias)
-        fused = self._try_fused(x, w, b)
-        if fused is not None:
-            y = fused
-        elif not self._needs_halo():
+        if not self._needs_halo():
             if self._is_patchify() and not self._transposed:
                 for i, g in self._split_axes():
                     if x.shape[i - n] % self.stride[i]:
@@ -401,19 +401,29 @@ class _DistributedConvBase(torch.nn.Module):
             y = self._channel_conv(x, w, b)
         return y.squeeze(0) if unbatched else y
 
-    def _try_fused(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
-        return None
+    def _try_fused(self, x: torch.Tensor) -> tuple[torch.Tensor | None, torch.Tensor]:
+        """``(pending fused result or None, input to continue with)``; the input comes back computed if it
+        arrived as a pending fused chain that this layer cannot join."""
+        if x.is_cuda:
+            from ...ops.lazy_chain import materialize
+
+            x = materialize(x)
+        return None, x
 
 
 class _DistributedConvNd(_DistributedConvBase):
     _transposed = False
 
-    def _try_fused(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
-        if not x.is_cuda or self._n_spatial != 2:
-            return None
+    def _try_fused(self, x: torch.Tensor) -> tuple[torch.Tensor | None, torch.Tensor]:
+        if not x.is_cuda:
+            return None, x
         from ...ops import conv_fused
 
-        return conv_fused.maybe_fused_conv2d(self, x, w, b)
+        if self._n_spatial != 2 or x.dim() != 4:
+            from ...ops.lazy_chain import materialize
+
+            return None, materialize(x)
+        return conv_fused.fused_or_lazy_conv2d(self, x)
 
 
 class _DistributedConvTransposeNd(_DistributedConvBase):

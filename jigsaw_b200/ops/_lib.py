@@ -334,6 +334,14 @@ def dispatch_counts(reset: bool = False) -> dict[str, dict[str, int]]:
     return out
 
 
+def record(name: str, fused: bool) -> None:
+    """Count one call of operation ``name`` on CUDA inputs; under strict dispatch a declined call raises."""
+    rec = DISPATCH.setdefault(name, [0, 0])
+    rec[0 if fused else 1] += 1
+    if not fused and _strict:
+        raise FusedPathDeclined(f"{name} declined CUDA inputs: {_last_reason or 'outside the coverage of the kernel'}")
+
+
 def audited(name: str):
     """Decorator of the ``maybe_fused_*`` entry points: counts, per operation, the calls that ran on the
     kernels and the calls with CUDA tensors that were declined, and raises on the latter under strict
@@ -346,15 +354,17 @@ def audited(name: str):
         def inner(*args, **kwargs):
             global _last_reason
             _last_reason = None
+            # a pending fused convolution chain among the arguments is computed first
+            if any(type(a).__name__ == "LazyConvChain" for a in args):
+                from .lazy_chain import materialize
+
+                args = tuple(materialize(a) for a in args)
             out = fn(*args, **kwargs)
-            rec = DISPATCH.setdefault(name, [0, 0])
             if out is not None:
-                rec[0] += 1
+                record(name, True)
                 return out
             if any(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
-                rec[1] += 1
-                if _strict:
-                    raise FusedPathDeclined(f"{name} declined CUDA inputs: {_last_reason or 'outside the coverage of the kernel'}")
+                record(name, False)
             return None
 
         return inner

@@ -298,17 +298,60 @@ def layer_is_eligible(layer: Any, x: torch.Tensor) -> bool:
     return _lib.available()
 
 
-@_lib.traced("jb.maybe_fused_conv2d")
-@_lib.audited("conv2d")
-def maybe_fused_conv2d(layer: Any, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
-    """Single-layer entry point used by ``DistributedConv2d.forward``."""
+# ----------------------------------------------------------------------------- chains written as separate layers
+def _run_lazy_chain(source: torch.Tensor, layers: tuple, acts: tuple) -> torch.Tensor:
+    """Materialise a :class:`lazy_chain.LazyConvChain`: the layers as one fused chain.  A trailing
+    activation (a chain whose last GELU feeds something other than a convolution) runs as a separate
+    kernel, because the chain's last epilogue writes the dense output without one."""
+    from .. import parallel
+
+    kinds = chain_kinds([(l.in_channels, l.out_channels) for l in layers])
+    geom = geometry_for(source, *layers[0].spatial_groups)
+    raw = [t for l in layers for t in (l.weight, l.bias)]
+    inner = list(acts[:-1]) + [False]
+    ranks = parallel.overlapped_sum_plan(raw)
+    if ranks is not None:
+        out = conv_chain(source, geom, kinds, inner, raw[0::2], raw[1::2], reduce_ranks=ranks)
+    else:
+        params = list(parallel.sync_grad(*raw))
+        out = conv_chain(source, geom, kinds, inner, params[0::2], params[1::2])
+    return torch.nn.functional.gelu(out) if acts[-1] else out
+
+
+def lazy_conv2d(layer: Any, x: torch.Tensor) -> tuple[Any, torch.Tensor]:
+    """Entry point of ``DistributedConv2d.forward``.  Returns ``(result, x)``: ``result`` is a pending
+    :class:`lazy_chain.LazyConvChain` that ends with ``layer`` (a new chain, or the chain ``x`` extended), or
+    ``None`` when the fused kernels do not cover the layer; ``x`` is then the input to continue with (the
+    computed tensor if it came in as a pending chain that ``layer`` cannot join)."""
+    from .lazy_chain import LazyConvChain
+
+    act = getattr(layer, "fused_activation", None) == "gelu"
+    grad_mode = torch.is_grad_enabled()
+    if isinstance(x, LazyConvChain) and x.pending:
+        prev = x
+        same_place = layer.spatial_groups == prev.layers[0].spatial_groups and prev.grad_mode == grad_mode
+        channels = [(l.in_channels, l.out_channels) for l in prev.layers] + [(layer.in_channels, layer.out_channels)]
+        if same_place and layer_is_eligible(layer, x) and chain_kinds(channels) is not None:
+            shape = (x.shape[0], layer.out_channels, x.shape[2], x.shape[3])
+            return prev.extended(layer, act, shape), x
+        x = prev.materialize()
+    elif isinstance(x, LazyConvChain):
+        x = x.materialize()
     if not layer_is_eligible(layer, x):
-        return None
+        return None, x
     kinds = chain_kinds([(layer.in_channels, layer.out_channels)])
     if kinds is None:
-        return None
+        return _lib.decline(f"{layer.in_channels} -> {layer.out_channels} channels (covered: <= 4 -> 64, 64 -> 64, 64 -> <= 4)"), x
     if kinds[0] != "mid" and x.requires_grad:
-        return None
-    gh, gw = layer.spatial_groups
-    geom = geometry_for(x, gh, gw)
-    return conv_chain(x, geom, kinds, [False], [w], [b])
+        return _lib.decline("a thin first layer whose input needs a gradient"), x
+    shape = (x.shape[0], layer.out_channels, x.shape[2], x.shape[3])
+    return LazyConvChain(x, (layer,), (act,), shape, grad_mode, _run_lazy_chain), x
+
+
+@_lib.traced("jb.fused_or_lazy_conv2d")
+def fused_or_lazy_conv2d(layer: Any, x: torch.Tensor) -> tuple[Any, torch.Tensor]:
+    """:func:`lazy_conv2d` with the dispatch audit (counted as ``conv2d``; raises under strict dispatch when
+    the kernels do not cover the layer)."""
+    result, x = lazy_conv2d(layer, x)
+    _lib.record("conv2d", result is not None)
+    return result, x
