@@ -101,8 +101,11 @@ class ViT(nn.Module):
         return self.head(pooled / self.tokens)
 
 
+MESH_OVERRIDE: tuple[int, int] | None = None   # --mesh RxC for the ViT (e.g. 2x1: ring attention on two GPUs)
+
+
 def build_vit(lib, n, dev, scale):
-    r, c = MESH2D[n]
+    r, c = MESH_OVERRIDE or MESH2D[n]
     mesh = lib.make_process_mesh({"row": r, "col": c})
     small = scale == "small"
     image, patch, chans = (256 if small else 1024), 16, 4
@@ -290,10 +293,11 @@ def main() -> None:
     ap.add_argument("--config", choices=("vit", "swin", "unet3d"), default="vit")
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", default="default")
     ap.add_argument("--seq", choices=("ring", "ulysses"), default="ring", help="sequence parallelism of the ViT's attention")
+    ap.add_argument("--mesh", default=None, help="ViT only: rows x columns of the mesh, e.g. 2x1 (default: 1x1, 1x2, 2x2, 4x2)")
     ap.add_argument("--graph", action="store_true",
                     help="replay the whole step as one CUDA graph (this framework only; GraphedStep)")
     args = ap.parse_args()
@@ -309,8 +313,13 @@ def main() -> None:
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     lib = load(args.impl)
-    global SEQUENCE_PARALLEL
+    global SEQUENCE_PARALLEL, MESH_OVERRIDE
     SEQUENCE_PARALLEL = args.seq
+    if args.mesh:
+        r, c = (int(v) for v in args.mesh.lower().split("x"))
+        if r * c != args.gpus:
+            raise SystemExit(f"--mesh {args.mesh} does not have {args.gpus} ranks")
+        MESH_OVERRIDE = (r, c)
     builders = {"vit": build_vit, "swin": build_swin, "unet3d": build_unet3d}
     model, loss_fn, x, y, desc, batch = builders[args.config](lib, args.gpus, dev, args.scale)
     x, y = x.to(dev), y.to(dev)
@@ -344,6 +353,11 @@ def main() -> None:
         from jigsaw_b200.ops import _lib
 
         launches0 = _lib.LAUNCHES
+    from bench import ClockSampler       # nvidia-smi clock / throttle-reason samples during the timed region (read-only)
+
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -354,6 +368,8 @@ def main() -> None:
     torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else {}
+    dispatch = None
     launches = (_lib.LAUNCHES - launches0) if args.impl == "ours" else 0
     if graphed is not None:
         launches = graphed.launches_per_step * args.steps
@@ -361,11 +377,12 @@ def main() -> None:
         from jigsaw_b200.ops import symm
 
         symm.arena(dev).check_status(collective=True)      # every rank raises if any rank saw a kernel error
+        dispatch = _lib.dispatch_counts()                   # per operation: calls on the fused kernels / declined
     if rank == 0:
         print(json.dumps({"metric": f"{args.config} samples/sec (fwd+bwd+AdamW)", "value": batch * 1000.0 / float(ms), "unit": "samples/s",
                           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(ms), "impl": args.impl,
                           "dtype": "bf16", "data": "synthetic", "config": desc, "gpu_launches": launches,
-                          "graph": graphed is not None, "loss": float(loss)}), flush=True)
+                          "graph": graphed is not None, "loss": float(loss), "clocks": clocks, "dispatch": dispatch}), flush=True)
     if graphed is not None:
         graphed.close()                      # a live graph that holds collectives blocks the teardown
     dist.destroy_process_group()

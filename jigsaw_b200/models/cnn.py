@@ -56,13 +56,14 @@ class DomainCNN(nn.Module):
     def _fused(self, x: torch.Tensor) -> torch.Tensor | None:
         if not (self.fuse and x.is_cuda):
             return None
-        from ..ops import conv_fused
+        from ..ops import _lib, conv_fused
 
-        if x.requires_grad or not all(conv_fused.layer_is_eligible(c, x) for c in self.convs):
-            return None
         kinds = conv_fused.chain_kinds([(c.in_channels, c.out_channels) for c in self.convs])
-        if kinds is None:
+        if x.requires_grad or kinds is None or not all(conv_fused.layer_is_eligible(c, x) for c in self.convs):
+            _lib.decline("the stack needs bf16 numerics, 3x3 / stride 1 / padding 1 layers and 64 inner channels")
+            _lib.record("conv_chain", False)          # raises under strict dispatch
             return None
+        _lib.record("conv_chain", True)
         raw = [t for c in self.convs for t in (c.weight, c.bias)]
         geom = conv_fused.geometry_for(x, *self.spatial)
         acts = [True] * (len(self.convs) - 1) + [False]
