@@ -297,7 +297,7 @@ class DistributedAttention(torch.nn.Module):
         else:
             qkv = qkv.to(core)
         if self.ring:
-            q, k, v = (t.contiguous() for t in qkv.unbind(0))
+            q, k, v = qkv.unbind(0)             # head-transposed views; the ring makes the copies it needs
             send_x = self.config.send_in_forward is SendForward.X and isinstance(self.qkv, torch.nn.Linear)
             out = ring_attention(
                 q, k, v, self.scale, self.spatial_group, self.config, p,

@@ -7,8 +7,9 @@ marked, when ``model_group is col_group`` as in attention projections); the bias
 ``out / C`` entries, replicated over ``row_group``.  The output is again (row, col)-blocked
 so layers chain without gathers.
 
-Forward = all-gather(x over col) -> all-gather(W block rows) -> one local GEMM (+ bias);
-any R x C that divides the shapes is accepted (the reference implements 1x1, 1x2, 2x2 and
+Forward = all-gather(x over col) -> fetch of the weight rows that make this rank's output block (straight
+from the blocks' owners, in the compute dtype) -> one local GEMM (+ bias); any R x C that divides the shapes
+is accepted (the reference implements 1x1, 1x2, 2x2 and
 4x2 only).  On CUDA the local GEMM runs on the tcgen05 kernel of ``jigsaw_b200.ops``.
 
 Reference parity: jigsaw/modules/linear/_linear.py:55-594 (DistributedLinear), :597-761
@@ -31,7 +32,7 @@ from ..._core.config import check_config
 from ..._core.placement import check_divisible, gather_dim
 from ..._core.shard_repr import shard_repr
 from ._config import LinearConfig, default_grid
-from ._functional import block_matmul
+from ._functional import block_matmul, fetch_region
 
 
 def _local_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor:
@@ -124,16 +125,23 @@ class DistributedLinear(torch.nn.Module):
             init.uniform_(self.bias, -bound, bound)
 
     # ------------------------------------------------------------------ forward
+    def _out_block_weight(self, w: torch.Tensor) -> torch.Tensor:
+        """The ``(out / C, in)`` rows of the global weight that make this rank's output block, fetched block by
+        block from their owners (in the compute dtype): ``R / C`` row blocks times ``C`` column blocks, i.e.
+        ``out * in / C`` elements in flight, never the whole matrix."""
+        (w,) = cast_to_autocast_dtype(w)
+        C, n = self.col_split, self.out_dim // self.col_split
+        h, k = w.shape
+        if self.row_split > 1:
+            # the weight is cut R x C over the model group (rank i * C + j holds block (i, j))
+            return fetch_region(w, self.model_group, self.row_split, C, lambda p: ((p % C) * n, (p % C + 1) * n, 0, k * C),
+                                self.config.comm)
+        # replicated over rows: cut 1 x C over the column group
+        return fetch_region(w, self.col_group, 1, C, lambda p: (p * n, (p + 1) * n, 0, k * C), self.config.comm)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = parallel.sync_grad(self.weight, self.bias)
-        w_rows = all_gather_cat(w, self.col_group, 1)                       # (N/Rw, K)
-        j = self.col_group.rank()
-        n = self.out_dim // self.col_split
-        if self.row_split > 1:
-            w_all = all_gather_cat(w_rows, self.row_group, 0)               # (N, K)
-            w_j = w_all.narrow(0, j * n, n)
-        else:
-            w_j = w_rows.narrow(0, j * n, n)
+        w_j = self._out_block_weight(w)                                     # (N/C, K)
         if x.is_cuda and self.col_split > 1:
             from ...ops import linear_fused
 
@@ -240,7 +248,7 @@ class _DistributedMatMul(torch.nn.Module):
         self.config = config or LinearConfig(model_group, linear_layer=False, device=self.device)
 
     def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        return block_matmul(self._kind, x, w, self.model_group, *self.grid)
+        return block_matmul(self._kind, x, w, self.model_group, *self.grid, comm=self.config.comm)
 
     def get_parameter_count(self) -> int:
         return 0

@@ -197,13 +197,13 @@ class _RingFlashAttention(torch.autograd.Function):
         P, me = group.size(), group.rank()
         ranks = dist.get_process_group_ranks(group)
         s = q.shape[-2]
-        q3, k3, v3 = (t.reshape(-1, s, 64).contiguous() for t in (q, k, v))
+        q3 = q.reshape(-1, s, 64).contiguous()
         bh = q3.shape[0]
         n = bh * s * 64 * 2                                   # bytes of one staged operand
         blk = _ring_block(ar, ("ring_fwd", dev.index, bh, s, tuple(ranks)), _HEADER + 2 * n)
-        staged = blk.tensor[_HEADER:_HEADER + 2 * n].view(torch.bfloat16).view(2, bh, s, 64)
-        staged[0].copy_(k3)
-        staged[1].copy_(v3)
+        staged = blk.tensor[_HEADER:_HEADER + 2 * n].view(torch.bfloat16).view(2, *k.shape)
+        staged[0].copy_(k)                                    # any strides (e.g. a head-transposed view): one copy
+        staged[1].copy_(v)
         epoch, stride, replay = _publish(ar, blk, ranks, me)
         out = torch.empty_like(q3)
         lse = torch.empty(bh, s, dtype=torch.float32, device=dev)
@@ -215,7 +215,7 @@ class _RingFlashAttention(torch.autograd.Function):
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_fwd_parts failed with code {rc}")
         _lib.count_launches(1)
-        ctx.save_for_backward(q3, k3, v3, out, lse)
+        ctx.save_for_backward(q3, k, v, out, lse)
         ctx.scale, ctx.group, ctx.shape = float(scale), group, q.shape
         return out.view(q.shape)
 
@@ -223,7 +223,7 @@ class _RingFlashAttention(torch.autograd.Function):
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
         from . import symm
 
-        q3, k3, v3, out, lse = ctx.saved_tensors
+        q3, k, v, out, lse = ctx.saved_tensors
         group = ctx.group
         L, dev = _lib.lib(), q3.device
         ar = symm.arena(dev)
@@ -236,16 +236,16 @@ class _RingFlashAttention(torch.autograd.Function):
         ops = blk.tensor[_HEADER:_HEADER + 4 * n].view(torch.bfloat16).view(4, bh, s, 64)       # q, dO, k, v
         rows = blk.tensor[_HEADER + 4 * n:_HEADER + 4 * n + 2 * nf].view(torch.float32).view(2, bh, s)   # lse, D
         ops[0].copy_(q3)
-        ops[1].copy_(g.reshape(bh, s, 64))
-        ops[2].copy_(k3)
-        ops[3].copy_(v3)
+        ops[1].view(ctx.shape).copy_(g)
+        ops[2].view(ctx.shape).copy_(k)
+        ops[3].view(ctx.shape).copy_(v)
         rows[0].copy_(lse)
         P_ = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
         rc = L.jb_flash_attn_delta(P_(out), P_(ops[1]), P_(rows[1]), bh * s, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_delta failed with code {rc}")
         epoch, stride, replay = _publish(ar, blk, ranks, me)
-        dq, dk, dv = torch.empty_like(q3), torch.empty_like(k3), torch.empty_like(v3)
+        dq, dk, dv = (torch.empty(bh, s, 64, dtype=torch.bfloat16, device=dev) for _ in range(3))
         at = lambda i: _part_ptrs(blk, ranks, me, _HEADER + i * n)  # noqa: E731
         lse_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n)
         delta_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n + nf)

@@ -115,6 +115,56 @@ def maybe_fused_linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None)
     return _FusedLinear.apply(x, w, b)
 
 
+class _FusedMatmul(torch.autograd.Function):
+    """``op(a) @ op(b)`` for 2-D operands (``op`` = transpose when the flag is set) on the tcgen05 GEMM, which reads
+    either operand in either major order: no transposed copy in the forward or in the two gradient products."""
+
+    @staticmethod
+    def forward(ctx: Any, a: torch.Tensor, b: torch.Tensor, a_t: bool, b_t: bool) -> torch.Tensor:
+        ab = (a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)).contiguous()
+        bb = (b if b.dtype == torch.bfloat16 else b.to(torch.bfloat16)).contiguous()
+        ctx.save_for_backward(ab, bb)
+        ctx.a_t, ctx.b_t, ctx.a_dtype, ctx.b_dtype = a_t, b_t, a.dtype, b.dtype
+        return gemm(ab, bb, a_mn=a_t, b_mn=not b_t)
+
+    @staticmethod
+    def backward(ctx: Any, gy: torch.Tensor) -> tuple:
+        ab, bb = ctx.saved_tensors
+        g = (gy if gy.dtype == torch.bfloat16 else gy.to(torch.bfloat16)).contiguous()      # [M, N]
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            if ctx.a_t:      # a is [K, M]: da = op(b) g^T
+                da = gemm(bb, g, a_mn=ctx.b_t, b_mn=False, out_dtype=torch.float32)
+            else:            # a is [M, K]: da = g op(b)^T
+                da = gemm(g, bb, a_mn=False, b_mn=ctx.b_t, out_dtype=torch.float32)
+            da = da.to(ctx.a_dtype)
+        if ctx.needs_input_grad[1]:
+            if ctx.b_t:      # b is [N, K]: db = g^T op(a)
+                db = gemm(g, ab, a_mn=True, b_mn=not ctx.a_t, out_dtype=torch.float32)
+            else:            # b is [K, N]: db = op(a)^T g
+                db = gemm(ab, g, a_mn=not ctx.a_t, b_mn=True, out_dtype=torch.float32)
+            db = db.to(ctx.b_dtype)
+        return da, db, None, None
+
+
+@_lib.traced("jb.maybe_fused_matmul")
+@_lib.audited("matmul")
+def maybe_fused_matmul(a: torch.Tensor, b: torch.Tensor, a_t: bool = False, b_t: bool = False) -> torch.Tensor | None:
+    """``op(a) @ op(b)`` for 2-D operands under bf16 autocast (or for bf16 operands) on the tcgen05 GEMM, differentiable;
+    ``None`` when it does not apply."""
+    if not a.is_cuda or a.dim() != 2 or b.dim() != 2 or a.numel() == 0 or b.numel() == 0:
+        return None
+    bf16 = (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16) or (
+        torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    if not bf16 or a.dtype not in (torch.float32, torch.bfloat16) or b.dtype not in (torch.float32, torch.bfloat16):
+        return _lib.decline("needs bf16 numerics")
+    M, K = (a.shape[1], a.shape[0]) if a_t else a.shape
+    N = b.shape[0] if b_t else b.shape[1]
+    if K % 8 or N % 8 or M % 8 or K < 64 or N < 16 or torch._C._functorch.is_batchedtensor(a):
+        return _lib.decline("needs M, N, K multiples of 8, K >= 64 and N >= 16")
+    return _FusedMatmul.apply(a, b, a_t, b_t)
+
+
 # ----------------------------------------------------------------------------- all-gather -> GEMM
 _HEADER = 256          # bytes of flag words in front of the staged block
 _rings: dict[tuple, list] = {}
