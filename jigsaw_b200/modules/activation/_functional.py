@@ -32,6 +32,12 @@ def distributed_softmax(x: torch.Tensor, dim: int = -1, group: dist.ProcessGroup
     """``softmax`` along ``dim`` whose extent is split over ``group`` (local shard in, local shard out)."""
     if not _live(group):
         return torch.softmax(x, dim=dim)
+    if x.is_cuda:
+        from ...ops import softmax_fused
+
+        y = softmax_fused.maybe_fused_softmax(x, dim, group, log=False)      # statistics exchanged inside the kernel
+        if y is not None:
+            return y
     in_dtype = x.dtype
     (x,) = promote_to_fp32_under_autocast(x)
     e = torch.exp(x - _global_max(x, dim, group))
@@ -44,6 +50,12 @@ def distributed_log_softmax(x: torch.Tensor, dim: int = -1, group: dist.ProcessG
     """``log_softmax`` along ``dim`` whose extent is split over ``group``."""
     if not _live(group):
         return torch.log_softmax(x, dim=dim)
+    if x.is_cuda:
+        from ...ops import softmax_fused
+
+        y = softmax_fused.maybe_fused_softmax(x, dim, group, log=True)
+        if y is not None:
+            return y
     in_dtype = x.dtype
     (x,) = promote_to_fp32_under_autocast(x)
     shifted = x - _global_max(x, dim, group)

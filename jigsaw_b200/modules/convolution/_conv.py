@@ -324,6 +324,13 @@ class _DistributedConvBase(torch.nn.Module):
 
     def _primitive(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor:
         fn = self.config.native_fn
+        if x.is_cuda and not self._transposed and self._is_patchify() and self._groups_local == 1:
+            from ...ops import conv_fused
+
+            # patch embedding (kernel == stride): one patch-gather copy and one tcgen05 GEMM with the bias in its epilogue
+            y = conv_fused.maybe_fused_patch_embed(x, w, b, self.kernel_size)
+            if y is not None:
+                return y
         if self._transposed:
             return fn(x, w, b, self.stride, self._local_padding(), 0, self._groups_local, self.dilation)
         return fn(x, w, b, self.stride, self._local_padding(), self.dilation, self._groups_local)
@@ -419,10 +426,10 @@ class _DistributedConvNd(_DistributedConvBase):
             return None, x
         from ...ops import conv_fused
 
-        if self._n_spatial != 2 or x.dim() != 4:
+        if self._n_spatial != 2 or x.dim() != 4 or self._is_patchify():
             from ...ops.lazy_chain import materialize
 
-            return None, materialize(x)
+            return None, materialize(x)          # patch embedding has its own fused path (see _primitive)
         return conv_fused.fused_or_lazy_conv2d(self, x)
 
 

@@ -3,12 +3,13 @@
 * :class:`FlashAttention` / :func:`flash_attention_forward` / :func:`flash_attention_backward`: attention
   for head dimension 64 on the tcgen05 kernels of ``csrc/flash_attn.cu`` and ``csrc/flash_attn_bwd.cu``.
 * :func:`maybe_fused_ring_attention`: sequence-parallel (ring) attention as ONE forward launch and two
-  backward launches.  Every rank stages its keys / values (backward: also queries, output gradients,
-  log-sum-exp and D) in symmetric memory and raises a flag on its peers; the kernels walk over the parts of
-  all ranks and load each block by TMA straight from its owner's memory while the previous block is in the
-  tensor cores.  The running softmax state stays on chip across the parts, so there is no per-chunk
-  merge, and every rank computes the complete gradient of its own keys and values by pulling the other
-  ranks' queries, so no gradient travels back.
+  backward launches.  Every rank pushes its keys / values (backward: also queries, output gradients,
+  log-sum-exp and D) into its slot of every peer's staging block with the copy engines, followed by a flag,
+  so each part crosses NVLink once per destination and no SM moves data; the kernels start on their own part
+  at once, walk over the parts of all ranks as their flags arrive (bounded waits) and load every block by TMA
+  from local memory while the previous block is in the tensor cores.  The running softmax state stays on chip
+  across the parts, so there is no per-chunk merge, and every rank computes the complete gradient of its own
+  keys and values from the other ranks' queries, so no gradient travels back.
 * :func:`maybe_fused_merge`: the online-softmax merge of per-chunk results (``csrc/elementwise.cu``), used
   by the chunked ring schedule that remains for what the fused kernels do not cover (other head sizes,
   dropout, circulating ``x``, CPU).
@@ -155,34 +156,61 @@ def _ring_block(ar: Any, tag: tuple, nbytes: int) -> Any:
     return blk
 
 
-def _publish(ar: Any, blk: Any, ranks: list, me: int) -> tuple[int, int, Any]:
-    """Raise this rank's flag in every peer's copy of ``blk`` once the staging copies are done (stream order)."""
+_side: dict[int, torch.cuda.Stream] = {}
+_epoch_words: dict[int, torch.Tensor] = {}
+
+
+def _push_to_peers(ar: Any, blk: Any, ranks: list, me: int, offset: int, nbytes: int) -> tuple[int, int, Any, Any]:
+    """Give every peer this rank's slot of ``blk`` (``nbytes`` at ``offset``, already written locally on the
+    current stream) and then raise this rank's flag in the peer's copy of the block.  Both travel by the copy
+    engines on a side stream: every staged byte crosses NVLink once per destination, no SM is used, and
+    the caller's attention kernel (launched next on the current stream) starts on its own part at once while
+    the pushes of all ranks are in flight.  Returns ``(epoch, stride, replay, done event)``; the caller makes
+    its stream wait for the event AFTER launching its kernel."""
+    L, dev = _lib.lib(), blk.tensor.device
     epoch = ar.next_own_epoch(blk)
     stride = ar.capture_stride or 0
     replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
-    flags = (ctypes.c_void_p * 8)()
-    n = 0
-    for i, r in enumerate(ranks):
-        if i != me:
-            flags[n] = blk.peer_ptr(r) + 4 * me
-            n += 1
-    rc = _lib.lib().jb_publish(flags, n, epoch, stride, replay, _lib.stream_ptr())
+    idx = dev.index
+    if idx not in _side:
+        _side[idx] = torch.cuda.Stream(dev)
+        _epoch_words[idx] = torch.zeros(64, dtype=torch.int32, device=dev)
+    side = _side[idx]
+    # the flag value as it must read on this replay: one word per block (the two blocks of a ring alternate)
+    word = _epoch_words[idx][(blk.offset // 1024) % 64:][:1]
+    one = (ctypes.c_void_p * 8)()
+    one[0] = word.data_ptr()
+    rc = L.jb_publish(one, 1, epoch, stride, replay, _lib.stream_ptr())
+    staged = torch.cuda.Event()
+    staged.record()
+    side.wait_event(staged)
+    with torch.cuda.stream(side):
+        st = _lib.stream_ptr()
+        for i, r in enumerate(ranks):
+            if i == me or rc != 0:
+                continue
+            rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + offset), ctypes.c_void_p(blk.ptr + offset), nbytes, st)
+            if rc == 0:
+                rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + 4 * me), ctypes.c_void_p(word.data_ptr()), 4, st)
+        done = torch.cuda.Event()
+        done.record()
     if rc != 0:
-        raise RuntimeError(f"jigsaw_b200 kernel launcher publish failed with code {rc}")
+        raise RuntimeError(f"jigsaw_b200: pushing a staged block to the peers failed with code {rc}")
     _lib.count_launches(1)
-    return epoch, stride, replay
+    return epoch, stride, replay, done
 
 
-def _part_ptrs(blk: Any, ranks: list, me: int, offset: int) -> Any:
+def _local_parts(blk: Any, P: int, base: int, slot: int, inner: int) -> Any:
+    """Pointers to one operand (at ``inner`` inside a slot) in each of the ``P`` slots of this rank's block."""
     arr = (ctypes.c_void_p * 8)()
-    for i, r in enumerate(ranks):
-        arr[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + offset
+    for i in range(P):
+        arr[i] = blk.ptr + base + i * slot + inner
     return arr
 
 
-def _flag_ptrs(blk: Any, ranks: list, me: int) -> Any:
+def _flag_ptrs(blk: Any, P: int, me: int) -> Any:
     arr = (ctypes.c_void_p * 8)()
-    for i in range(len(ranks)):
+    for i in range(P):
         arr[i] = None if i == me else blk.ptr + 4 * i
     return arr
 
@@ -200,18 +228,20 @@ class _RingFlashAttention(torch.autograd.Function):
         q3 = q.reshape(-1, s, 64).contiguous()
         bh = q3.shape[0]
         n = bh * s * 64 * 2                                   # bytes of one staged operand
-        blk = _ring_block(ar, ("ring_fwd", dev.index, bh, s, tuple(ranks)), _HEADER + 2 * n)
-        staged = blk.tensor[_HEADER:_HEADER + 2 * n].view(torch.bfloat16).view(2, *k.shape)
-        staged[0].copy_(k)                                    # any strides (e.g. a head-transposed view): one copy
-        staged[1].copy_(v)
-        epoch, stride, replay = _publish(ar, blk, ranks, me)
+        slot = 2 * n                                          # K and V of one rank
+        blk = _ring_block(ar, ("ring_fwd", dev.index, bh, s, tuple(ranks)), _HEADER + P * slot)
+        mine = blk.tensor[_HEADER + me * slot:_HEADER + (me + 1) * slot].view(torch.bfloat16).view(2, *k.shape)
+        mine[0].copy_(k)                                      # any strides (e.g. a head-transposed view): one copy
+        mine[1].copy_(v)
+        epoch, stride, replay, pushed = _push_to_peers(ar, blk, ranks, me, _HEADER + me * slot, slot)
         out = torch.empty_like(q3)
         lse = torch.empty(bh, s, dtype=torch.float32, device=dev)
         rc = L.jb_flash_attn_fwd_parts(
-            ctypes.c_void_p(q3.data_ptr()), _part_ptrs(blk, ranks, me, _HEADER), _part_ptrs(blk, ranks, me, _HEADER + n),
-            _flag_ptrs(blk, ranks, me), epoch, stride, replay, P, me, ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_void_p(q3.data_ptr()), _local_parts(blk, P, _HEADER, slot, 0), _local_parts(blk, P, _HEADER, slot, n),
+            _flag_ptrs(blk, P, me), epoch, stride, replay, P, me, ctypes.c_void_p(out.data_ptr()),
             ctypes.c_void_p(lse.data_ptr()), bh, s, s, 64, s * 64, 64, s * 64, 64, s * 64, float(scale),
             ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+        torch.cuda.current_stream(dev).wait_event(pushed)
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_fwd_parts failed with code {rc}")
         _lib.count_launches(1)
@@ -232,9 +262,11 @@ class _RingFlashAttention(torch.autograd.Function):
         bh, s, _ = q3.shape
         n = bh * s * 64 * 2
         nf = bh * s * 4
-        blk = _ring_block(ar, ("ring_bwd", dev.index, bh, s, tuple(ranks)), _HEADER + 4 * n + 2 * nf)
-        ops = blk.tensor[_HEADER:_HEADER + 4 * n].view(torch.bfloat16).view(4, bh, s, 64)       # q, dO, k, v
-        rows = blk.tensor[_HEADER + 4 * n:_HEADER + 4 * n + 2 * nf].view(torch.float32).view(2, bh, s)   # lse, D
+        slot = 4 * n + 2 * nf                                  # q, dO, k, v, lse, D of one rank
+        blk = _ring_block(ar, ("ring_bwd", dev.index, bh, s, tuple(ranks)), _HEADER + P * slot)
+        base = _HEADER + me * slot
+        ops = blk.tensor[base:base + 4 * n].view(torch.bfloat16).view(4, bh, s, 64)
+        rows = blk.tensor[base + 4 * n:base + slot].view(torch.float32).view(2, bh, s)
         ops[0].copy_(q3)
         ops[1].view(ctx.shape).copy_(g)
         ops[2].view(ctx.shape).copy_(k)
@@ -244,15 +276,14 @@ class _RingFlashAttention(torch.autograd.Function):
         rc = L.jb_flash_attn_delta(P_(out), P_(ops[1]), P_(rows[1]), bh * s, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_delta failed with code {rc}")
-        epoch, stride, replay = _publish(ar, blk, ranks, me)
+        epoch, stride, replay, pushed = _push_to_peers(ar, blk, ranks, me, base, slot)
         dq, dk, dv = (torch.empty(bh, s, 64, dtype=torch.bfloat16, device=dev) for _ in range(3))
-        at = lambda i: _part_ptrs(blk, ranks, me, _HEADER + i * n)  # noqa: E731
-        lse_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n)
-        delta_parts = _part_ptrs(blk, ranks, me, _HEADER + 4 * n + nf)
+        at = lambda i: _local_parts(blk, P, _HEADER, slot, i * n)  # noqa: E731
         rc = L.jb_flash_attn_bwd_parts(
-            P_(ops[0]), P_(ops[2]), P_(ops[3]), P_(ops[1]), at(0), at(1), lse_parts, delta_parts, at(2), at(3),
-            _flag_ptrs(blk, ranks, me), epoch, stride, replay, P, me, P_(dq), P_(dk), P_(dv), bh, s, ctx.scale,
-            ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+            P_(ops[0]), P_(ops[2]), P_(ops[3]), P_(ops[1]), at(0), at(1), _local_parts(blk, P, _HEADER, slot, 4 * n),
+            _local_parts(blk, P, _HEADER, slot, 4 * n + nf), at(2), at(3), _flag_ptrs(blk, P, me), epoch, stride, replay, P, me,
+            P_(dq), P_(dk), P_(dv), bh, s, ctx.scale, ctypes.c_void_p(ar.status.data_ptr()), _lib.stream_ptr())
+        torch.cuda.current_stream(dev).wait_event(pushed)
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_bwd_parts failed with code {rc}")
         _lib.count_launches(3)

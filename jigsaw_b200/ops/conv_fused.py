@@ -355,3 +355,45 @@ def fused_or_lazy_conv2d(layer: Any, x: torch.Tensor) -> tuple[Any, torch.Tensor
     result, x = lazy_conv2d(layer, x)
     _lib.record("conv2d", result is not None)
     return result, x
+
+
+@_lib.traced("jb.maybe_fused_patch_embed")
+@_lib.audited("patch_embed")
+def maybe_fused_patch_embed(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, patch: tuple) -> torch.Tensor | None:
+    """Convolution whose kernel equals its stride (no padding, no dilation): every output pixel sees its own
+    patch, so the layer is a matrix product.  The patches are gathered into rows by one strided copy (in
+    bf16) and multiplied with the ``(C_out, C_in * prod(patch))`` weight on the tcgen05 GEMM (bias in its
+    epilogue; differentiable through the fused linear Function).  ``x``: ``(N, C_in, *spatial)`` with every
+    spatial extent a multiple of the patch; returns ``(N, C_out, *spatial / patch)`` (channels-last memory),
+    or ``None`` when the GEMM does not cover the shapes.
+
+    Reference parity: the kernel == stride fast path of jigsaw/modules/convolution/_conv/distributed.py:39-106
+    (there: a cuDNN convolution without halo exchange)."""
+    from . import linear_fused
+
+    if not x.is_cuda:
+        return None
+    nd = len(patch)
+    if x.dim() != nd + 2 or any(x.shape[2 + i] % patch[i] for i in range(nd)):
+        return _lib.decline("the spatial extents must be multiples of the patch")
+    bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    if not bf16:
+        return _lib.decline("needs bf16 numerics")
+    N, C = x.shape[0], x.shape[1]
+    grid = [x.shape[2 + i] // patch[i] for i in range(nd)]
+    # (N, C, g0, p0, g1, p1, ...) -> (N, g0, g1, ..., C, p0, p1, ...)
+    split: list[int] = []
+    for i in range(nd):
+        split += [grid[i], patch[i]]
+    v = x.reshape(N, C, *split)
+    order = [0] + [2 + 2 * i for i in range(nd)] + [1] + [3 + 2 * i for i in range(nd)]
+    K = C
+    for p_ in patch:
+        K *= p_
+    rows = v.permute(*order).to(torch.bfloat16).reshape(-1, K)            # one copy: gather + cast
+    out = linear_fused.maybe_fused_linear(rows, w.reshape(w.shape[0], K), b)
+    if out is None:
+        return _lib.decline("the GEMM does not cover these sizes (C_in * prod(patch) >= 64 and multiples of 8 are needed)")
+    out = out.view(N, *grid, w.shape[0])
+    back = [0, nd + 1] + list(range(1, nd + 1))
+    return out.permute(*back)

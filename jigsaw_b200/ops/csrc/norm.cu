@@ -489,9 +489,11 @@ __device__ __forceinline__ void ce_row_partials(const CeArgs& a, long long r, in
   if (mx != -INFINITY)
     for (int c = lane; c < a.C; c += nl) sum += __expf(ce_load(a, base + static_cast<long long>(c) * a.S) - mx);
   if (nl == 32) sum = warp_sum(sum);
-  const long long tg = a.target[r] - a.class_lo;
   float tv = 0.f;
-  if (a.target[r] != a.ignore_index && tg >= 0 && tg < a.C) tv = ce_load(a, base + tg * a.S);
+  if (a.target != nullptr) {                    // null: only the log-sum-exp is wanted (softmax / log-softmax)
+    const long long tg = a.target[r] - a.class_lo;
+    if (a.target[r] != a.ignore_index && tg >= 0 && tg < a.C) tv = ce_load(a, base + tg * a.S);
+  }
   *m = mx; *s = sum; *t = tv;
 }
 
@@ -514,7 +516,7 @@ __global__ void __launch_bounds__(LN_THREADS) ce_fwd_kernel(const CeArgs a) {
       if (!WARP_PER_ROW || lane == 0) {
         const float lse = m + __logf(s);
         a.lse[r] = lse;
-        a.loss[r] = (a.target[r] != a.ignore_index) ? lse - t : 0.f;
+        if (a.loss != nullptr) a.loss[r] = (a.target != nullptr && a.target[r] != a.ignore_index) ? lse - t : 0.f;
       }
     } else {
       const float4 v = make_float4(m, s, t, 0.f);
@@ -546,7 +548,76 @@ __global__ void __launch_bounds__(LN_THREADS) ce_fwd_kernel(const CeArgs a) {
     }
     const float lse = M + __logf(S);
     a.lse[r] = lse;
-    a.loss[r] = (a.target[r] != a.ignore_index) ? lse - T : 0.f;
+    if (a.loss != nullptr) a.loss[r] = (a.target != nullptr && a.target[r] != a.ignore_index) ? lse - T : 0.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Softmax / log-softmax over a class dimension that may be split across GPUs.  The row-wise
+// log-sum-exp comes from ce_fwd_kernel above (null targets: local partials, in-kernel exchange,
+// finish); these kernels are the element-wise rest.  x, y, g: [B][C][S]; rows are (b, s) pairs.
+//   apply   : y = x - lse (log) or exp(x - lse)
+//   rowdot  : d[row] = sum_c g (log) or sum_c g y   (local classes; the caller sums d over the ranks)
+//   backward: dx = g - exp(y) d (log) or y (g - d)
+// ------------------------------------------------------------------------------------------
+struct SmArgs {
+  const void* x; int x_bf16;        // apply: logits; rowdot / backward: the saved output y
+  const void* g; int g_bf16;
+  const float* row;                 // apply: lse; backward: d
+  void* out; int out_bf16;
+  float* rowout;                    // rowdot
+  int B, C, S;
+  int log_mode;
+};
+
+__device__ __forceinline__ float sm_load(const void* p, int bf16, long long off) {
+  return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[off]) : static_cast<const float*>(p)[off];
+}
+__device__ __forceinline__ void sm_store(void* p, int bf16, long long off, float v) {
+  if (bf16) static_cast<__nv_bfloat16*>(p)[off] = __float2bfloat16(v);
+  else static_cast<float*>(p)[off] = v;
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(256) softmax_elementwise_kernel(const SmArgs a) {
+  const long long cs = static_cast<long long>(a.C) * a.S;
+  const long long n = cs * a.B;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long b = i / cs;
+    const long long r = b * a.S + (i - b * cs) % a.S;
+    const float v = sm_load(a.x, a.x_bf16, i);
+    const float rv = __ldg(a.row + r);
+    float o;
+    if (!BWD) {
+      o = a.log_mode ? v - rv : __expf(v - rv);
+    } else {
+      const float gv = sm_load(a.g, a.g_bf16, i);
+      o = a.log_mode ? gv - __expf(v) * rv : v * (gv - rv);
+    }
+    sm_store(a.out, a.out_bf16, i, o);
+  }
+}
+
+template <bool WARP_PER_ROW>
+__global__ void __launch_bounds__(256) softmax_rowdot_kernel(const SmArgs a) {
+  const long long R = static_cast<long long>(a.B) * a.S;
+  const int lane = WARP_PER_ROW ? (threadIdx.x & 31) : 0;
+  const int nl = WARP_PER_ROW ? 32 : 1;
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long first = WARP_PER_ROW ? (t >> 5) : t;
+  const long long step = (static_cast<long long>(gridDim.x) * blockDim.x) / nl;
+  for (long long r = first; r < R; r += step) {
+    const long long b = r / a.S, sp = r % a.S;
+    const long long base = b * a.C * static_cast<long long>(a.S) + sp;
+    float d = 0.f;
+    for (int c = lane; c < a.C; c += nl) {
+      const long long off = base + static_cast<long long>(c) * a.S;
+      const float gv = sm_load(a.g, a.g_bf16, off);
+      d += a.log_mode ? gv : gv * sm_load(a.x, a.x_bf16, off);
+    }
+    if (WARP_PER_ROW) d = warp_sum(d);
+    if (lane == 0) a.rowout[r] = d;
   }
 }
 
@@ -985,6 +1056,49 @@ extern "C" int jb_cross_entropy_fwd(const void* x, int x_bf16, const long long* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (warp_rows) ce_fwd_kernel<true><<<grid, LN_THREADS, 0, st>>>(a);
   else ce_fwd_kernel<false><<<grid, LN_THREADS, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static unsigned int sm_grid(long long threads, int sm_count) {
+  long long grid = (threads + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count) * 16;
+  return static_cast<unsigned int>(grid < 1 ? 1 : (grid > cap ? cap : grid));
+}
+
+// y = x - lse[row] (log_mode) or exp(x - lse[row]) for x [B][C][S], rows = (b, s).
+extern "C" int jb_softmax_apply(const void* x, int x_bf16, const float* lse, void* y, int y_bf16, int B, int C, int S,
+                                int log_mode, int sm_count, void* stream) {
+  if (B <= 0 || C <= 0 || S <= 0) return -1;
+  SmArgs a{};
+  a.x = x; a.x_bf16 = x_bf16; a.row = lse; a.out = y; a.out_bf16 = y_bf16; a.B = B; a.C = C; a.S = S; a.log_mode = log_mode;
+  softmax_elementwise_kernel<false><<<sm_grid(static_cast<long long>(B) * C * S, sm_count), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// d[row] = sum over the local classes of g (log_mode) or of g * y.
+extern "C" int jb_softmax_rowdot(const void* y, int y_bf16, const void* g, int g_bf16, float* d, int B, int C, int S,
+                                 int log_mode, int sm_count, void* stream) {
+  if (B <= 0 || C <= 0 || S <= 0) return -1;
+  SmArgs a{};
+  a.x = y; a.x_bf16 = y_bf16; a.g = g; a.g_bf16 = g_bf16; a.rowout = d; a.B = B; a.C = C; a.S = S; a.log_mode = log_mode;
+  const bool warp_rows = (S == 1 && C >= 64);
+  const long long threads = static_cast<long long>(B) * S * (warp_rows ? 32 : 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (warp_rows) softmax_rowdot_kernel<true><<<sm_grid(threads, sm_count), 256, 0, st>>>(a);
+  else softmax_rowdot_kernel<false><<<sm_grid(threads, sm_count), 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// dx = g - exp(y) d[row] (log_mode) or y (g - d[row]).
+extern "C" int jb_softmax_bwd(const void* y, int y_bf16, const void* g, int g_bf16, const float* d, void* dx, int dx_bf16,
+                              int B, int C, int S, int log_mode, int sm_count, void* stream) {
+  if (B <= 0 || C <= 0 || S <= 0) return -1;
+  SmArgs a{};
+  a.x = y; a.x_bf16 = y_bf16; a.g = g; a.g_bf16 = g_bf16; a.row = d; a.out = dx; a.out_bf16 = dx_bf16;
+  a.B = B; a.C = C; a.S = S; a.log_mode = log_mode;
+  softmax_elementwise_kernel<true><<<sm_grid(static_cast<long long>(B) * C * S, sm_count), 256, 0,
+                                    static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

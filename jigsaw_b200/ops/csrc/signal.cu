@@ -57,6 +57,16 @@ __global__ void slot_release_kernel(uint32_t* r0, uint32_t* r1, uint32_t* r2, ui
 
 }  // namespace jb
 
+// Copy `bytes` from `src` to `dst` (either may be a peer's memory mapped into this process) with the copy
+// engines, in stream order: no SM is involved, so the copy runs beside whatever kernels occupy the GPU.
+extern "C" int jb_memcpy_async(void* dst, const void* src, long long bytes, void* stream) {
+  if (bytes <= 0) return -1;
+  return cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess
+             ? 0
+             : -4;
+}
+
 // Before producing content `new_epoch` into a buffer slot: wait until the (up to eight) local
 // acknowledgement words have reached the epoch of the slot's previous content, then record the new
 // epoch in `last_epoch` (a device word owned by the slot).

@@ -186,3 +186,39 @@ def test_converted_torch_cnn_takes_the_fused_path():
     ref = _ref_chain(x, [m.weight for m in plain if isinstance(m, torch.nn.Conv2d)], [m.bias for m in plain if isinstance(m, torch.nn.Conv2d)])
     assert _rel(out, ref) < 1e-2
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dims", [2, 3])
+def test_patch_embedding_runs_on_the_own_gemm(dims):
+    """A convolution whose kernel equals its stride (patch embedding) is one patch-gather copy and one tcgen05
+    GEMM: output and all gradients against torch's convolution on bf16-rounded operands, strict dispatch."""
+    import torch.distributed as dist
+
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib
+
+    mesh, dev = _one_rank_mesh(29536 + dims)
+    torch.manual_seed(2)
+    if dims == 2:
+        layer = jb.modules.DistributedConv2d(4, 128, 16, dev, (mesh["sh"], mesh["sw"]), mesh["col"], stride=16)
+        x = torch.randn(2, 4, 64, 96, device=dev, requires_grad=True)
+        conv = torch.nn.functional.conv2d
+    else:
+        layer = jb.modules.DistributedConv3d(2, 64, 4, dev, (None, mesh["sh"], mesh["sw"]), mesh["col"], stride=4)
+        x = torch.randn(1, 2, 8, 16, 24, device=dev, requires_grad=True)
+        conv = torch.nn.functional.conv3d
+    before = _lib.LAUNCHES
+    with _lib.strict_fused(), torch.autocast("cuda", dtype=torch.bfloat16):
+        y = layer(x)
+    assert _lib.LAUNCHES == before + 1 and y.dtype == torch.bfloat16
+    g = torch.randn_like(y)
+    y.backward(g)
+    got = (x.grad.clone(), layer.weight.grad.clone(), layer.bias.grad.clone())
+    x.grad = None
+    layer.zero_grad()
+    ref = conv(_round(x), _round(layer.weight), layer.bias, stride=layer.stride)
+    ref.backward(g.float())
+    assert _rel(y, ref) < 1e-2
+    for mine, theirs in zip(got, (x.grad, layer.weight.grad, layer.bias.grad)):
+        assert _rel(mine, theirs) < 2e-2
+    dist.destroy_process_group()

@@ -773,3 +773,54 @@ def test_all_reduce_kernel_two_gpus():
 @pytest.mark.multigpu(4)
 def test_all_reduce_kernel_four_gpus():
     run_distributed(_worker_all_reduce_kernel, 4, backend="nccl", timeout=300)
+
+
+def _worker_fused_softmax(rank, world):
+    """Softmax and log-softmax over a class dimension cut over the GPUs (row statistics exchanged inside the
+    kernel, gradient row sums through the peer-memory all-reduce) against the undivided torch ops: trailing
+    and inner class dimensions, fp32 and bf16, forward and backward; and the single-GPU form of the same kernels."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, softmax_fused, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"row": 1, "col": world})
+    col = mesh["col"]
+    torch.manual_seed(0)
+    for shape, dim in (((16, 1000), 1), ((2, 20, 24, 40), 1), ((3, 5, 128), -1)):
+        for dtype in (torch.float32, torch.bfloat16):
+            for log in (False, True):
+                x = (torch.randn(*shape, device=dev) * 3).to(dtype)
+                g = torch.randn(*shape, device=dev)
+                C = shape[dim]
+                sl = [slice(None)] * len(shape)
+                sl[dim] = slice(rank * C // world, (rank + 1) * C // world)
+                xl = x[tuple(sl)].contiguous().requires_grad_(True)
+                fn = jb.modules.functional.distributed_log_softmax if log else jb.modules.activation.distributed_softmax
+                before = _lib.LAUNCHES
+                with _lib.strict_fused():
+                    y = fn(xl, dim, col)
+                assert _lib.LAUNCHES == before + 2
+                y.backward(g[tuple(sl)].to(y.dtype))
+                symm.arena(dev).check_status()
+                xr = x.float().requires_grad_(True)
+                ref = torch.log_softmax(xr, dim) if log else torch.softmax(xr, dim)
+                ref.backward(g)
+                tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+                assert_close(y.float(), ref.detach()[tuple(sl)], f"{shape} {dtype} log={log}: output", tol, tol)
+                assert_close(xl.grad.float(), xr.grad[tuple(sl)], f"{shape} {dtype} log={log}: gradient", tol, tol * max(float(xr.grad.abs().max()), 1e-3))
+    # one GPU, no group: the same kernels without an exchange
+    x = torch.randn(7, 300, device=dev, requires_grad=True)
+    y = softmax_fused.maybe_fused_softmax(x, -1, None, log=False)
+    y.backward(torch.ones_like(y) * torch.arange(300, device=dev))
+    xr = x.detach().clone().requires_grad_(True)
+    torch.softmax(xr, -1).backward(torch.ones_like(y) * torch.arange(300, device=dev))
+    assert_close(y, torch.softmax(xr, -1).detach(), "local softmax", 1e-5, 1e-6)
+    assert_close(x.grad, xr.grad, "local softmax gradient", 1e-4, 1e-5)
+
+
+@pytest.mark.multigpu(2)
+def test_fused_softmax_two_gpus():
+    run_distributed(_worker_fused_softmax, 2, backend="nccl", timeout=300)
