@@ -1,13 +1,15 @@
 """In-place conversion of a plain PyTorch model into its distributed counterpart.
 
-The converter walks the module tree once *before* touching anything and classifies every
-module: exact-type matches of ``mapped_modules`` are replaced by the class method
-``convert_to_jigsaw`` of the distributed layer; ``container_converters`` replace a whole
-sub-tree (``Attention``); ``shard_safe_modules`` (elementwise) stay as they are;
-``shard_unsafe_modules`` (anything that reduces over, mixes along or reshapes a dimension
-that may be sharded) abort the conversion unless ``non_safe=True``; everything else is
-reported according to ``on_unrecognized``.  Extra keyword arguments (``comm=``, ``ring=``,
-``ulysses=``, ``dim_to_mesh_axis=`` ...) are forwarded to every layer converter.
+Conversion is plan-then-apply: :class:`ConversionPlan` decides, in one flat pass over
+``named_modules`` and before anything is touched, what happens to every module (replace, keep,
+report, block); ``apply`` then builds the replacements deepest-first and re-binds them on their
+parents.  Exact-type matches of ``mapped_modules`` are replaced through the class method
+``convert_to_jigsaw`` of the distributed layer; ``container_converters`` replace a whole sub-tree
+(``Attention``); ``shard_safe_modules`` (elementwise) stay as they are; ``shard_unsafe_modules``
+(anything that reduces over, mixes along or reshapes a dimension that may be sharded) block the
+conversion unless ``non_safe=True``; everything else is reported according to ``on_unrecognized``.
+Extra keyword arguments (``comm=``, ``ring=``, ``ulysses=``, ``dim_to_mesh_axis=`` ...) are forwarded
+to every layer converter.
 
 Reference parity: jigsaw/convert.py:20-38 (tables), :41-171 (safe / unsafe lists),
 :174-209 (pre-flight walk), :212-315 (convert_to_jigsaw), :318-371 (recursive worker).
@@ -16,7 +18,8 @@ Reference parity: jigsaw/convert.py:20-38 (tables), :41-171 (safe / unsafe lists
 from __future__ import annotations
 
 import warnings
-from collections.abc import Callable, Iterator
+from collections.abc import Callable
+from dataclasses import dataclass
 from typing import Any, Literal
 
 import torch
@@ -25,6 +28,7 @@ from torch import nn
 from .modules import activation, attention, convolution, linear, normalization, roll
 
 __all__ = [
+    "ConversionPlan",
     "convert_to_jigsaw",
     "mapped_modules",
     "container_converters",
@@ -90,44 +94,80 @@ def _is_ours(m: nn.Module) -> bool:
     return mod.startswith("jigsaw_b200.") or mod.startswith("jigsaw.")
 
 
-def _preflight(model: nn.Module, prefix: str, convert_layer_norm: bool) -> Iterator[tuple[str, str, bool]]:
-    """``(qualified name, reason, unsafe)`` for every module the converter will leave alone."""
-    name = prefix or "<root>"
-    kind = type(model)
-    if kind in container_converters or kind in mapped_modules:
-        if not (kind is nn.LayerNorm and not convert_layer_norm):
-            return
-    if isinstance(model, nn.LayerNorm) and not convert_layer_norm:
-        return
-    if _is_ours(model):
-        return
-    if isinstance(model, shard_unsafe_modules):
-        yield name, f"non-elementwise module {kind.__name__}", True
-        return
-    children = list(model.named_children())
-    if not children:
-        if not isinstance(model, shard_safe_modules):
-            yield name, f"unrecognized leaf module {kind.__name__}", False
-        return
-    if any(True for _ in model.parameters(recurse=False)):
-        yield name, f"{kind.__name__} owns parameters directly, which are not sharded", False
-    for child_name, child in children:
-        yield from _preflight(child, f"{prefix}.{child_name}" if prefix else child_name, convert_layer_norm)
+# ----------------------------------------------------------------------------- plan, then apply
+@dataclass
+class _Step:
+    """What happens to one module of the tree."""
+
+    path: str                      # dotted name ("" = the root)
+    module: nn.Module
+    action: str                    # "replace" | "keep" | "report" | "block"
+    reason: str = ""
+    maker: Callable[..., nn.Module] | None = None
 
 
-def _walk_and_replace(model: nn.Module, mesh: dict, device: Any, convert_layer_norm: bool, keys: dict, kwargs: dict) -> nn.Module:
-    kind = type(model)
-    if kind in container_converters:
-        return container_converters[kind](model, mesh, device, **keys, **kwargs)
-    if kind in mapped_modules and not (kind is nn.LayerNorm and not convert_layer_norm):
-        return mapped_modules[kind].convert_to_jigsaw(model, mesh, device, **keys, **kwargs)
-    if _is_ours(model):
-        return model
-    for child_name, child in list(model.named_children()):
-        new = _walk_and_replace(child, mesh, device, convert_layer_norm, keys, kwargs)
-        if new is not child:
-            setattr(model, child_name, new)
-    return model
+class ConversionPlan:
+    """The decision for every module of ``model``, made in ONE flat pass over ``named_modules`` before
+    anything is touched.  A module is settled by the first rule that applies, and a settled module settles
+    its whole sub-tree (the pass skips every path below it):
+
+    1. exact type in ``container_converters`` or ``mapped_modules``  -> replace (built by the layer's
+       ``convert_to_jigsaw``);
+    2. already a layer of this library                              -> keep;
+    3. instance of ``shard_unsafe_modules``                          -> block (conversion refuses unless ``non_safe``);
+    4. a leaf: elementwise (``shard_safe_modules``) -> keep, otherwise -> report;
+    5. a container: descend; if it owns parameters itself           -> also report.
+
+    ``apply`` then builds the replacements and re-binds them on their parents, deepest paths first, so a
+    replaced child never invalidates a path still to be visited."""
+
+    def __init__(self, model: nn.Module, convert_layer_norm: bool = True) -> None:
+        self.model = model
+        self.steps: list[_Step] = []
+        settled: list[str] = []
+        for path, module in model.named_modules():
+            if any(path == root or path.startswith(root + ".") for root in settled if root) or "" in settled:
+                continue
+            step = self._decide(path, module, convert_layer_norm)
+            if step is None:
+                continue                                     # a plain container: its children are visited next
+            self.steps.append(step)
+            if step.action != "report" or not any(True for _ in module.children()):
+                settled.append(path)
+
+    @staticmethod
+    def _decide(path: str, module: nn.Module, convert_layer_norm: bool) -> _Step | None:
+        kind = type(module)
+        skip_norm = isinstance(module, nn.LayerNorm) and not convert_layer_norm
+        if kind in container_converters:
+            return _Step(path, module, "replace", maker=container_converters[kind])
+        if kind in mapped_modules and not skip_norm:
+            return _Step(path, module, "replace", maker=mapped_modules[kind].convert_to_jigsaw)
+        if skip_norm or _is_ours(module):
+            return _Step(path, module, "keep")
+        if isinstance(module, shard_unsafe_modules):
+            return _Step(path, module, "block", f"non-elementwise module {kind.__name__}")
+        if not any(True for _ in module.children()):
+            if isinstance(module, shard_safe_modules):
+                return _Step(path, module, "keep")
+            return _Step(path, module, "report", f"unrecognized leaf module {kind.__name__}")
+        if any(True for _ in module.parameters(recurse=False)):
+            return _Step(path, module, "report", f"{kind.__name__} owns parameters directly, which are not sharded")
+        return None
+
+    def findings(self, action: str) -> list[tuple[str, str]]:
+        return [(s.path or "<root>", s.reason) for s in self.steps if s.action == action]
+
+    def apply(self, mesh: dict, device: Any, keys: dict, kwargs: dict) -> nn.Module:
+        root = self.model
+        for step in sorted((s for s in self.steps if s.action == "replace"), key=lambda s: -s.path.count(".")):
+            new = step.maker(step.module, mesh, device, **keys, **kwargs)
+            if step.path == "":
+                root = new
+                continue
+            parent_path, _, name = step.path.rpartition(".")
+            setattr(root.get_submodule(parent_path) if parent_path else root, name, new)
+        return root
 
 
 def convert_to_jigsaw(
@@ -147,22 +187,22 @@ def convert_to_jigsaw(
     slice the same global weights.  Nothing is modified if the pre-flight check fails."""
     if on_unrecognized not in ("warn", "raise", "ignore"):
         raise ValueError(f"on_unrecognized must be 'warn', 'raise' or 'ignore', got {on_unrecognized!r}")
-    found = list(_preflight(model, "", convert_layer_norm))
-    unsafe = [(n, r) for n, r, bad in found if bad]
-    if unsafe and not non_safe:
+    plan = ConversionPlan(model, convert_layer_norm)
+    blocked = plan.findings("block")
+    if blocked and not non_safe:
         raise ValueError(
             "convert_to_jigsaw has no distributed version of these modules; as plain torch they compute on "
             "the local shard only and give wrong results if the dimension they reduce over, mix along or "
-            "reshape is sharded. Pass non_safe=True if it is not:\n" + "\n".join(f"  {n}: {r}" for n, r in unsafe)
+            "reshape is sharded. Pass non_safe=True if it is not:\n" + "\n".join(f"  {n}: {r}" for n, r in blocked)
         )
-    if found and on_unrecognized != "ignore":
+    left_alone = blocked + plan.findings("report")
+    if left_alone and on_unrecognized != "ignore":
         msg = (
             "convert_to_jigsaw leaves these modules as plain torch; they compute on the local shard only, "
             "which is wrong if they reduce over or mix along a sharded dimension:\n"
-            + "\n".join(f"  {n}: {r}" for n, r, _ in found)
+            + "\n".join(f"  {n}: {r}" for n, r in left_alone)
         )
         if on_unrecognized == "raise":
             raise ValueError(msg)
         warnings.warn(msg, stacklevel=2)
-    keys = dict(row_kw=row_kw, col_kw=col_kw, model_kw=model_kw)
-    return _walk_and_replace(model, process_mesh_dict, device, convert_layer_norm, keys, kwargs)
+    return plan.apply(process_mesh_dict, device, dict(row_kw=row_kw, col_kw=col_kw, model_kw=model_kw), kwargs)
