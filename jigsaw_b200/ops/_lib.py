@@ -126,17 +126,20 @@ def _declare(L: ctypes.CDLL) -> None:
         c_void_p, POINTER(JbHalo), c_void_p, c_void_p,  # dst halo done_counter stream
     ]
     L.jb_halo_pack.restype = c_int
-    L.jb_conv3x3_thin.argtypes = [
-        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # in w bias gelu_src pre padded dense
+    L.jb_conv3x3_thin_in.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # in4 w bias gelu_src pre padded dense
         c_int, c_int, c_int, c_int,  # NB H W act
         POINTER(JbHalo), c_void_p, c_void_p, c_int, c_void_p,
     ]
-    L.jb_conv3x3_thin.restype = c_int
-    L.jb_wgrad_thin.argtypes = [
-        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,  # big small out NB H W sign
+    L.jb_conv3x3_thin_in.restype = c_int
+    L.jb_conv3x3_wgrad_thin_scratch_floats.argtypes = [c_int]
+    L.jb_conv3x3_wgrad_thin_scratch_floats.restype = c_longlong
+    L.jb_conv3x3_wgrad_thin.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # big small gw gb scratch
+        c_int, c_int, c_int, c_int, c_int,  # NB H W side cs
         POINTER(JbHalo), c_void_p, c_int, c_void_p,
     ]
-    L.jb_wgrad_thin.restype = c_int
+    L.jb_conv3x3_wgrad_thin.restype = c_int
     L.jb_gemm_bf16_gather.argtypes = [POINTER(JbGather), c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong,
                                       c_int, c_int, c_int, c_void_p, c_void_p]
     L.jb_gemm_bf16_gather.restype = c_int
@@ -156,6 +159,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_all_to_all.restype = c_int
     L.jb_wait_flags.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
     L.jb_wait_flags.restype = c_int
+    L.jb_softmax_apply.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    L.jb_softmax_apply.restype = c_int
+    L.jb_softmax_rowdot.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    L.jb_softmax_rowdot.restype = c_int
+    L.jb_softmax_bwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_void_p]
+    L.jb_softmax_bwd.restype = c_int
     L.jb_all_reduce_sum.argtypes = [POINTER(JbAllReduce), c_void_p, c_void_p, c_int, c_void_p]
     L.jb_all_reduce_sum.restype = c_int
     L.jb_memcpy_async.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p]

@@ -61,6 +61,11 @@ class Geometry:
         n = self.NB * (self.H + 2) * (self.W + 2) * channels * 2
         return self.arena.alloc(n, tag=("padded", self.NB, self.H, self.W, channels, live))
 
+    def padded4(self) -> "symm.Block":
+        """A padded buffer with four channels per pixel (thin first / last layers)."""
+        n = self.NB * (self.H + 2) * (self.W + 2) * 4 * 2
+        return self.arena.alloc(n, tag=("padded4", self.NB, self.H, self.W))
+
     def halo(self, produce: "symm.Block | None", consume: "symm.Block | None") -> Any:
         return symm.make_halo(self.arena, self.nbrs, produce, consume)
 
@@ -80,16 +85,24 @@ def chain_kinds(channels: list[tuple[int, int]]) -> list[str] | None:
     return kinds
 
 
-def _prep_weights(kind: str, w: torch.Tensor, b: torch.Tensor | None) -> dict:
+def _prep_weights(kind: str, w: torch.Tensor, b: torch.Tensor | None, thin: bool = False) -> dict:
     """Kernel-side weight layouts of one layer (small tensors, rebuilt every step).
 
-    Thin layers run on the 64-channel tensor-core kernels with their missing channels
-    zero-filled: the tensor cores have ample headroom there (these layers are bound by the
-    64-channel tensor they read or write), and it keeps every layer on one code path.
+    ``thin``: the layer's few channels live in a four-channel padded buffer and the thin-channel kernels run
+    (one [64][64] weight tile whose column ``tap * 4 + c`` holds channel ``c`` of the thin side).  Otherwise thin
+    layers run on the 64-channel kernels with their missing channels zero-filled (odd tile widths, which the
+    16-byte granularity of the four-channel rows does not cover).
     """
     dev = w.device
     cout, cin = w.shape[0], w.shape[1]
     out: dict = {}
+    if thin and kind == "thin_in":
+        t = torch.zeros(64, 9, 4, device=dev, dtype=torch.bfloat16)
+        t[:, :, :cin] = w.detach().permute(0, 2, 3, 1).reshape(64, 9, cin).to(torch.bfloat16)      # [co][tap][ci]
+        out["w"] = t.view(64, 36).contiguous()
+        out["w"] = torch.nn.functional.pad(out["w"], (0, 28))                                     # [64][64]
+        out["b"] = None if b is None else b.detach().float().contiguous()
+        return out
     wt = w.detach().permute(2, 3, 0, 1).to(torch.bfloat16)                                  # [3,3,co,ci]
     if kind == "mid":
         out["w"] = wt.contiguous()
@@ -107,9 +120,15 @@ def _prep_weights(kind: str, w: torch.Tensor, b: torch.Tensor | None) -> dict:
         if b is not None:
             bb[:cout] = b.detach().float()
         out["b"] = bb
-        d = torch.zeros(3, 3, 64, 64, device=dev, dtype=torch.bfloat16)
-        d[:, :, :cout] = wt
-        out["w_dgrad"] = d                                                                  # backward: 64 (zero-filled) gradient channels
+        if thin:
+            # data gradient on the thin-input kernel: row = input channel, column = mirrored tap * 4 + output channel
+            t = torch.zeros(64, 9, 4, device=dev, dtype=torch.bfloat16)
+            t[:, :, :cout] = w.detach().flip(2, 3).permute(1, 2, 3, 0).reshape(64, 9, cout).to(torch.bfloat16)
+            out["w_dgrad"] = torch.nn.functional.pad(t.view(64, 36), (0, 28)).contiguous()
+        else:
+            d = torch.zeros(3, 3, 64, 64, device=dev, dtype=torch.bfloat16)
+            d[:, :, :cout] = wt
+            out["w_dgrad"] = d                                                              # backward: 64 (zero-filled) gradient channels
     return out
 
 
@@ -144,15 +163,21 @@ class _ConvChain(torch.autograd.Function):
             raise ValueError("the last layer of a fused chain must not have an activation")
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.float()
-        prep = [_prep_weights(kinds[i], weights[i], biases[i]) for i in range(n)]
+        thin = W % 2 == 0          # the four-channel rows are read in 16-byte units (pixel pairs)
+        prep = [_prep_weights(kinds[i], weights[i], biases[i], thin) for i in range(n)]
         cin0 = weights[0].shape[1]
-        cp0 = 64
+        thin_first = thin and kinds[0] == "thin_in"
         # ---- pack the input into the padded layout (+ halo push)
-        cw0 = min(64, (cin0 + 3) // 4 * 4)
-        a = geom.padded(cp0, None if cw0 == 64 else cw0)
         sn, sc, sh, sw = x.stride()
-        _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, cp0, cw0, _bp(a),
-                              geom.halo(a, None), _p(ar.done_counter), st), "halo_pack")
+        if thin_first:
+            a = geom.padded4()
+            _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, 4, 4, _bp(a),
+                                  geom.halo(a, None), _p(ar.done_counter), st), "halo_pack")
+        else:
+            cw0 = min(64, (cin0 + 3) // 4 * 4)
+            a = geom.padded(64, None if cw0 == 64 else cw0)
+            _check(L.jb_halo_pack(_p(x), int(x.dtype == torch.float32), sn, sc, sh, sw, NB, cin0, H, W, 64, cw0, _bp(a),
+                                  geom.halo(a, None), _p(ar.done_counter), st), "halo_pack")
         acts_in: list[symm.Block] = [a]
         pres: list[torch.Tensor | None] = []
         out = None
@@ -168,9 +193,14 @@ class _ConvChain(torch.autograd.Function):
             halo = geom.halo(nxt, acts_in[i])
             act = 1 if acts[i] else 0
             nout = 16 if kinds[i] == "thin_out" else 64
-            _check(L.jb_conv3x3_c64(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
-                                    _p(out) if last else None, NB, H, W, nout, cout, act, 0, halo,
-                                    _p(ar.done_counter), _p(ar.status), geom.sm, st), "conv3x3_c64")
+            if i == 0 and thin_first:
+                _check(L.jb_conv3x3_thin_in(_bp(acts_in[0]), _p(prep[0]["w"]), _p(prep[0]["b"]), None, _p(pre), _bp(nxt),
+                                            _p(out) if last else None, NB, H, W, act, halo, _p(ar.done_counter),
+                                            _p(ar.status), geom.sm, st), "conv3x3_thin_in")
+            else:
+                _check(L.jb_conv3x3_c64(_bp(acts_in[i]), _p(prep[i]["w"]), _p(prep[i]["b"]), None, _p(pre), _bp(nxt),
+                                        _p(out) if last else None, NB, H, W, nout, cout, act, 0, halo,
+                                        _p(ar.done_counter), _p(ar.status), geom.sm, st), "conv3x3_c64")
             pres.append(pre)
             if nxt is not None:
                 acts_in.append(nxt)
@@ -180,6 +210,7 @@ class _ConvChain(torch.autograd.Function):
             ctx.shapes = [tuple(w.shape) for w in weights]
             ctx.has_bias = [b is not None for b in biases]
             ctx.x_needs_grad = ctx.needs_input_grad[0]
+            ctx.thin = thin
             ctx.reduce_ranks = reduce_ranks
             ctx.holder = _BlockHolder(ar, acts_in)
         else:
@@ -198,13 +229,21 @@ class _ConvChain(torch.autograd.Function):
         dev = gout.device
         grads: list[torch.Tensor | None] = [None] * (2 * n)
         cout_last = ctx.shapes[-1][0]
-        cpg = 64
-        cwg = min(64, (cout_last + 3) // 4 * 4)
-        g = geom.padded(cpg, None if cwg == 64 else cwg)
+        thin = ctx.thin
+        thin_last = thin and kinds[-1] == "thin_out"
+        thin_first = thin and kinds[0] == "thin_in"
         sn, sc, sh, sw = gout.stride()
-        _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, cpg, cwg,
-                              _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
+        if thin_last:
+            g = geom.padded4()
+            _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, 4, 4,
+                                  _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
+        else:
+            cwg = min(64, (cout_last + 3) // 4 * 4)
+            g = geom.padded(64, None if cwg == 64 else cwg)
+            _check(L.jb_halo_pack(_p(gout), int(gout.dtype == torch.float32), sn, sc, sh, sw, NB, cout_last, H, W, 64, cwg,
+                                  _bp(g), geom.halo(g, None), _p(ar.done_counter), st), "halo_pack(grad)")
         scratch = None
+        scratch_thin = None
         gx = None
         # replicated weights: every layer's gradient is summed over the tile ranks on a side stream as soon
         # as its kernel has been launched, under the remaining data- and weight-gradient kernels
@@ -219,16 +258,30 @@ class _ConvChain(torch.autograd.Function):
             # gradient of the layer above flows through the GELU that precedes this layer's input
             src = pres[i - 1] if i > 0 else None
             # ---- weight / bias gradient
-            gw = torch.empty(64, 64, 3, 3, device=dev, dtype=torch.float32)
-            gb = torch.empty(64, device=dev, dtype=torch.float32)
-            if scratch is None:
-                scratch = torch.empty(L.jb_conv3x3_wgrad_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
-            _check(L.jb_conv3x3_c64_wgrad(_bp(acts_in[i]), _bp(g), _p(gw), _p(gb), _p(scratch), NB, H, W,
-                                          geom.halo(None, g), _p(ar.status), geom.sm, st), "wgrad")
-            if kind == "thin_in":
-                gw = gw[:, :cin].contiguous()
-            elif kind == "thin_out":
-                gw, gb = gw[:cout].contiguous(), gb[:cout].contiguous()
+            thin_here = (kind == "thin_out" and thin_last) or (kind == "thin_in" and thin_first and i == 0)
+            if thin_here:
+                # one side of the layer has at most four channels: the thin-channel kernel pairs the interior of the
+                # 64-channel tensor with the shifted pixels of the four-channel one (read with its halo)
+                side = 0 if kind == "thin_in" else 1
+                cs = cin if side == 0 else cout
+                big, small = (g, acts_in[i]) if side == 0 else (acts_in[i], g)
+                gw = torch.empty((64, cs, 3, 3) if side == 0 else (cs, 64, 3, 3), device=dev, dtype=torch.float32)
+                gb = torch.empty(64 if side == 0 else cs, device=dev, dtype=torch.float32)
+                if scratch_thin is None:
+                    scratch_thin = torch.empty(L.jb_conv3x3_wgrad_thin_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
+                _check(L.jb_conv3x3_wgrad_thin(_bp(big), _bp(small), _p(gw), _p(gb), _p(scratch_thin), NB, H, W, side, cs,
+                                               geom.halo(None, small), _p(ar.status), geom.sm, st), "wgrad")
+            else:
+                gw = torch.empty(64, 64, 3, 3, device=dev, dtype=torch.float32)
+                gb = torch.empty(64, device=dev, dtype=torch.float32)
+                if scratch is None:
+                    scratch = torch.empty(L.jb_conv3x3_wgrad_scratch_floats(geom.sm), device=dev, dtype=torch.float32)
+                _check(L.jb_conv3x3_c64_wgrad(_bp(acts_in[i]), _bp(g), _p(gw), _p(gb), _p(scratch), NB, H, W,
+                                              geom.halo(None, g), _p(ar.status), geom.sm, st), "wgrad")
+                if kind == "thin_in":
+                    gw = gw[:, :cin].contiguous()
+                elif kind == "thin_out":
+                    gw, gb = gw[:cout].contiguous(), gb[:cout].contiguous()
             grads[2 * i] = gw
             grads[2 * i + 1] = gb if ctx.has_bias[i] else None
             if reducer is not None:
@@ -247,8 +300,12 @@ class _ConvChain(torch.autograd.Function):
             halo = geom.halo(gnext, g)
             gsrc = src if acts[i - 1] else None
             wd = prep[i]["w_dgrad"] if kind == "thin_out" else prep[i]["w"]
-            _check(L.jb_conv3x3_c64(_bp(g), _p(wd), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 64, 64,
-                                    0, 1, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
+            if kind == "thin_out" and thin_last:
+                _check(L.jb_conv3x3_thin_in(_bp(g), _p(wd), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 0, halo,
+                                            _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
+            else:
+                _check(L.jb_conv3x3_c64(_bp(g), _p(wd), None, _p(gsrc), None, _bp(gnext), None, NB, H, W, 64, 64,
+                                        0, 1, halo, _p(ar.done_counter), _p(ar.status), geom.sm, st), "dgrad")
             ar.free(g)
             g = gnext
         ctx.holder.release()

@@ -256,14 +256,27 @@ __device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW]
 // ------------------------------------------------------------------------------------------
 // Forward (B_MN = 0, weights [9][NOUT][64] = tap, cout, cin) and data gradient
 // (B_MN = 1, same weight tensor read as tap, K = cout, N = cin, taps mirrored).
+//
+// THIN = 1: the input has at most four channels and lives in a padded buffer [NB][H+2][W+2][4].
+// Nine taps x four channels are only 36 values per output pixel, so the issuing warp first gathers
+// them into one K-major operand row per pixel (an im2col tile of 128 pixels x 64 values, the last
+// 28 zero, 128-byte swizzled) and then issues ONE product of K = 48 instead of nine of K = 64;
+// the weights are a single [64][64] tile (row = output channel, column = tap * 4 + input channel).
+// Everything after the accumulator (bias, GELU, saved derivative, padded output, halo push) is shared.
 // ------------------------------------------------------------------------------------------
-template <int NOUT, int B_MN>
+constexpr int CV_THIN_SLOT_BYTES = 1280;           // 130 pixels x 8 bytes, rounded up
+constexpr int CV_THIN_ROW_BYTES = CV_BOXW * 8;
+
+template <int NOUT, int B_MN, int THIN = 0>
 __global__ void __launch_bounds__(CV_THREADS, 1)
 conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmAux,
                   const ConvArgs a) {
+  static_assert(THIN == 0 || (NOUT == 64 && B_MN == 0), "the thin-input variant writes 64 channels");
   constexpr int WTAP_BYTES = (B_MN ? 64 : NOUT) * 128;
-  constexpr int W_BYTES = 9 * WTAP_BYTES;
+  constexpr int W_BYTES = (THIN ? 1 : 9) * WTAP_BYTES;
+  constexpr int SLOT_BYTES = THIN ? CV_THIN_SLOT_BYTES : CV_SLOT_BYTES;
+  constexpr int ROW_TX_BYTES = THIN ? CV_THIN_ROW_BYTES : CV_BOXW * 128;
   constexpr uint32_t ACC_COLS = CV_MMA_WARPS * NOUT;
   constexpr uint32_t TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
   // Wide layers stage their output tiles in shared memory and write them with TMA stores
@@ -273,7 +286,8 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* w_smem = smem;
   uint8_t* slots = smem + ((W_BYTES + 1023) & ~1023);
-  uint8_t* stage_out = slots + CV_SLOTS * CV_SLOT_BYTES;           // [128 px][64 ch] padded-output tile
+  uint8_t* a_tiles = slots + ((CV_SLOTS * SLOT_BYTES + 1023) & ~1023);   // THIN: one im2col tile per issuing warp
+  uint8_t* stage_out = a_tiles + (THIN ? CV_MMA_WARPS * CV_STAGE_BYTES : 0);   // [128 px][64 ch] padded-output tile
   uint8_t* stage_aux = stage_out + (STAGED ? CV_STAGE_BYTES : 0);  // dense output tile, or GELU'-source tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_aux + (STAGED ? CV_STAGE_BYTES : 0));
   uint64_t* full = bars;                  // [8]   TMA landed in window slot j
@@ -313,6 +327,12 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
+  if constexpr (THIN != 0) {
+    // columns 36..63 of the im2col tiles are never written again: zero the tiles once
+    for (int i = threadIdx.x; i < CV_MMA_WARPS * CV_STAGE_BYTES / 16; i += CV_THREADS)
+      reinterpret_cast<uint4*>(a_tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -322,7 +342,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       mbar_expect_tx(wbar, W_BYTES);
-      for (int t = 0; t < 9; ++t) tma_load_2d(w_smem + t * WTAP_BYTES, &tmW, wbar, 0, t * (B_MN ? 64 : NOUT));
+      for (int t = 0; t < (THIN ? 1 : 9); ++t) tma_load_2d(w_smem + t * WTAP_BYTES, &tmW, wbar, 0, t * (B_MN ? 64 : NOUT));
       halo_wait_all(a.wait, abort_flag, a.status);
       uint32_t eph = 0;   // per-slot phase bits of the empty barriers
       uint32_t sph = 0;   // phase of src_empty
@@ -339,8 +359,9 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
             for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
               mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status, 10 + j);
               eph ^= (1u << j);
-              mbar_expect_tx(&full[j], CV_BOXW * 128);
-              tma_load_4d(slots + j * CV_SLOT_BYTES, &tmIn, &full[j], 0, tw * CV_TW, hc + j, n);
+              mbar_expect_tx(&full[j], ROW_TX_BYTES);
+              // THIN: the tensor map counts pixel PAIRS (16 bytes) along its second dimension
+              tma_load_4d(slots + j * SLOT_BYTES, &tmIn, &full[j], 0, THIN ? tw * (CV_TW / 2) : tw * CV_TW, hc + j, n);
             }
             if (has_src) {
               mbar_wait(src_empty, sph ^ 1u, abort_flag, a.status, 20);
@@ -387,6 +408,44 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
           mbar_wait(&acc_empty[mi], aph ^ 1u, abort_flag, a.status, 30 + mi);
           if (*abort_flag) continue;         // after a timeout: issue nothing more
           tc_fence_after_sync();
+          if constexpr (THIN != 0) {
+            // gather the 3 x 3 x 4 inputs of 128 pixels into this warp's im2col tile (the previous product
+            // that read it has completed: its accumulator has been drained), then one product of K = 48
+            uint8_t* tile = a_tiles + mi * CV_STAGE_BYTES;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int m = q * 32 + lane;
+              uint8_t* row = tile + m * 128;
+#pragma unroll
+              for (int dy = 0; dy < 3; ++dy) {
+                const uint8_t* src = slots + (i + dy) * SLOT_BYTES + m * 8;
+#pragma unroll
+                for (int dx = 0; dx < 3; ++dx) {
+                  const int t = dy * 3 + dx;
+                  const uint2 v = *reinterpret_cast<const uint2*>(src + dx * 8);
+                  *reinterpret_cast<uint2*>(row + (((t >> 1) ^ (m & 7)) << 4) + (t & 1) * 8) = v;
+                }
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            const uint64_t ad0 = make_smem_desc_sw128(smem_u32(tile), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < 3; ++k)
+              umma_f16_elect(d_tmem, desc_advance(ad0, k * 32), desc_advance(b_desc0, k * 32), idesc, k != 0 ? 1u : 0u);
+            umma_commit_elect(&acc_full[mi]);
+            // the window slots were read by ordinary loads: release them with plain arrivals
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+              const int j = i + d;
+              const int lo = max(0, j - 2), hi = min(n_out - 1, j);
+              if (lane == 0) {
+                mbar_arrive(&empty[j]);
+                if (i == lo)
+                  for (int e = hi - lo + 1; e < 3; ++e) mbar_arrive(&empty[j]);
+              }
+            }
+          } else {
           const uint64_t a_row = desc_advance(a_desc0, static_cast<uint32_t>(i * CV_SLOT_BYTES));
 #pragma unroll
           for (int dy = 0; dy < 3; ++dy) {
@@ -413,6 +472,7 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
             if (i == lo && lane == 0) {
               for (int e = hi - lo + 1; e < 3; ++e) mbar_arrive(&empty[j]);
             }
+          }
           }
         }
         fph ^= (1u << (n_out + 2)) - 1u;
@@ -797,6 +857,267 @@ __global__ void conv3x3_wgrad_reduce_kernel(const float* __restrict__ partials, 
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Weight gradient of a layer with at most four channels on one side (first / last layer of a network).
+//   R[m][tap * 4 + c] = sum over this rank's pixels q of  big[q][m] * small[q + (ty - 1, tx - 1)][c]
+// big:   padded [NB][H+2][W+2][64] buffer, interior pixels only (no halo needed);
+// small: padded [NB][H+2][W+2][4] buffer read with its halo (a three-row window per output row).
+// The issuing warp gathers the 36 shifted values of 128 pixels into an im2col tile (column 36 = 1, so
+// that R[m][36] = sum_q big[q][m]) and multiplies: A = the big tile read MN-major (M = 64 channels, the
+// upper 64 rows of M = a tile of ones, so that R[64][n] = sum_q im2col[q][n]), B = the im2col tile read
+// MN-major (N = 64), K = 128 pixels per tile.  Each of the four issuing warps owns every fourth tile and
+// its own accumulator; the epilogue adds the four and writes one partial per CTA, summed in CTA order by
+// conv3x3_wgrad_thin_reduce_kernel into the torch layouts:
+//   side 0 (thin input,  big = gradient of the output, small = input):   gw[m][c][ty][tx] = R[m][t * 4 + c],       gb[m] = R[m][36]
+//   side 1 (thin output, big = input, small = gradient of the output):   gw[c][m][ty][tx] = R[m][(8 - t) * 4 + c], gb[c] = R[64][16 + c]
+// (side 1 sums over the pixels of the INPUT this rank owns, pairing each with output-gradient pixels that may
+// belong to a neighbour: over all ranks every pair is counted once, which is what the summed gradient needs).
+// ------------------------------------------------------------------------------------------
+constexpr int WT_WARPS = CV_MMA_WARPS;             // issuing warps = big-tile stages = im2col tiles
+constexpr int WT_THREADS = 32 * (1 + WT_WARPS + 4);
+constexpr int WT_PARTIAL_FLOATS = 128 * 64;
+
+struct WgradThinArgs {
+  int NB, H, W, tiles_w, rows_per_strip, nstrips;
+  float* partials;   // [gridDim.x][128][64]
+  HaloWait wait;     // the small buffer is read with its halo
+  int* status;
+};
+
+__global__ void __launch_bounds__(WT_THREADS, 1)
+conv3x3_wgrad_thin_kernel(const __grid_constant__ CUtensorMap tmBig, const __grid_constant__ CUtensorMap tmSmall,
+                          const WgradThinArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* big = smem;                                            // WT_WARPS stages of [128 px][64 ch]
+  uint8_t* im2col = big + WT_WARPS * CV_STAGE_BYTES;              // WT_WARPS tiles of [128 px][64 values]
+  uint8_t* ones = im2col + WT_WARPS * CV_STAGE_BYTES;             // 2 KB
+  uint8_t* slots = ones + 2048;                                   // CV_SLOTS rows of the small buffer
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + ((CV_SLOTS * CV_THIN_SLOT_BYTES + 1023) & ~1023));
+  uint64_t* full = bars;              // [8]
+  uint64_t* empty = bars + 8;         // [8]
+  uint64_t* gfull = bars + 16;        // [WT_WARPS]
+  uint64_t* gempty = bars + 20;       // [WT_WARPS]
+  uint64_t* acc_full = bars + 24;     // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  constexpr uint32_t TMEM_COLS = 256;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int items = a.NB * a.tiles_w * a.nstrips;
+
+  for (int i = threadIdx.x; i < 2048 / 4; i += WT_THREADS) reinterpret_cast<uint32_t*>(ones)[i] = 0x3F803F80u;
+  // im2col tiles: zero, then the constant column 36 = 1.0 (16-byte chunk 4, second half, first value)
+  for (int i = threadIdx.x; i < WT_WARPS * CV_STAGE_BYTES / 16; i += WT_THREADS)
+    reinterpret_cast<uint4*>(im2col)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  for (int r = threadIdx.x; r < WT_WARPS * 128; r += WT_THREADS) {
+    const int m = r & 127;
+    uint8_t* row = im2col + (r >> 7) * CV_STAGE_BYTES + m * 128;
+    *reinterpret_cast<uint16_t*>(row + ((4 ^ (m & 7)) << 4) + 8) = 0x3F80;
+  }
+  fence_proxy_async_smem();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 3);
+    }
+    for (int s = 0; s < WT_WARPS; ++s) {
+      mbar_init(&gfull[s], 1);
+      mbar_init(&gempty[s], 1);
+    }
+    mbar_init(acc_full, WT_WARPS);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmBig);
+    tma_prefetch_desc(&tmSmall);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      halo_wait_all(a.wait, abort_flag, a.status);
+      uint32_t eph = 0;
+      int it = 0;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int tw = (item / a.nstrips) % a.tiles_w;
+        const int n = item / (a.nstrips * a.tiles_w);
+        const int h0 = s * a.rows_per_strip;
+        const int h1 = min(a.H, h0 + a.rows_per_strip);
+        for (int hc = h0; hc < h1; hc += CV_CHUNK) {
+          const int n_out = min(CV_CHUNK, h1 - hc);
+          for (int i = 0; i < n_out; ++i, ++it) {
+            if (*abort_flag) break;
+            for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j) {
+              mbar_wait(&empty[j], ((eph >> j) & 1u) ^ 1u, abort_flag, a.status, 210 + j);
+              eph ^= (1u << j);
+              mbar_expect_tx(&full[j], CV_THIN_ROW_BYTES);
+              tma_load_4d(slots + j * CV_THIN_SLOT_BYTES, &tmSmall, &full[j], 0, tw * (CV_TW / 2), hc + j, n);
+            }
+            const int gs = it % WT_WARPS;
+            mbar_wait(&gempty[gs], (static_cast<uint32_t>(it / WT_WARPS) & 1u) ^ 1u, abort_flag, a.status, 220 + gs);
+            if (*abort_flag) break;
+            mbar_expect_tx(&gfull[gs], CV_STAGE_BYTES);
+            // interior pixel (h, w) of the big buffer sits at (h + 1, w + 1)
+            tma_load_4d(big + gs * CV_STAGE_BYTES, &tmBig, &gfull[gs], 0, tw * CV_TW + 1, hc + i + 1, n);
+          }
+        }
+      }
+    }
+  } else if (warp <= WT_WARPS) {
+    // ---------------------------------------------------------------- gather + UMMA issue (warp mi owns tile it % 4 == mi)
+    const int mi = warp - 1;
+    constexpr uint32_t idesc = make_idesc_bf16(128, 64, 1, 1);
+    uint32_t fph = 0;
+    int it = 0;
+    bool first = true;
+    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(64 * mi);
+    uint8_t* tile = im2col + mi * CV_STAGE_BYTES;
+    const uint32_t big_addr = smem_u32(big + mi * CV_STAGE_BYTES);
+    const uint32_t ones_addr = smem_u32(ones);
+    const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(tile), 8192, 1024);
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const int s = item % a.nstrips;
+      const int h0 = s * a.rows_per_strip;
+      const int h1 = min(a.H, h0 + a.rows_per_strip);
+      for (int hc = h0; hc < h1; hc += CV_CHUNK) {
+        const int n_out = min(CV_CHUNK, h1 - hc);
+        for (int i = 0; i < n_out; ++i, ++it) {
+          for (int j = (i == 0 ? 0 : i + 2); j <= i + 2; ++j)
+            mbar_wait(&full[j], (fph >> j) & 1u, abort_flag, a.status, 240 + j);
+          if ((it % WT_WARPS) != mi) continue;
+          const uint32_t gph = static_cast<uint32_t>(it / WT_WARPS) & 1u;
+          // the previous product of this warp (which read this im2col tile) has completed when its stage was
+          // released: the producer refilled the stage only after that commit
+          mbar_wait(&gfull[mi], gph, abort_flag, a.status, 250 + mi);
+          if (*abort_flag) continue;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int m = q * 32 + lane;
+            uint8_t* row = tile + m * 128;
+#pragma unroll
+            for (int dy = 0; dy < 3; ++dy) {
+              const uint8_t* src = slots + (i + dy) * CV_THIN_SLOT_BYTES + m * 8;
+#pragma unroll
+              for (int dx = 0; dx < 3; ++dx) {
+                const int t = dy * 3 + dx;
+                const uint2 v = *reinterpret_cast<const uint2*>(src + dx * 8);
+                *reinterpret_cast<uint2*>(row + (((t >> 1) ^ (m & 7)) << 4) + (t & 1) * 8) = v;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t ko = k * 2048;  // 16 pixels x 128 bytes
+            const uint64_t ad = make_smem_desc_sw128(big_addr + ko, ones_addr - (big_addr + ko), 1024);
+            umma_f16_elect(d_tmem, ad, desc_advance(b_desc0, ko), idesc, (first && k == 0) ? 0u : 1u);
+          }
+          first = false;
+          umma_commit_elect(&gempty[mi]);
+#pragma unroll
+          for (int d = 0; d < 3; ++d) {
+            const int j = i + d;
+            const int lo = max(0, j - 2), hi = min(n_out - 1, j);
+            if (lane == 0) {
+              mbar_arrive(&empty[j]);
+              if (i == lo)
+                for (int e = hi - lo + 1; e < 3; ++e) mbar_arrive(&empty[j]);
+            }
+          }
+        }
+        fph ^= (1u << (n_out + 2)) - 1u;
+      }
+    }
+    umma_commit_elect(acc_full);
+  } else {
+    // ---------------------------------------------------------------- epilogue: add the four accumulators, one partial per CTA
+    const int quad = warp & 3;
+    mbar_wait(acc_full, 0, abort_flag, a.status, 260);
+    tc_fence_after_sync();
+    float* dst = a.partials + static_cast<long long>(blockIdx.x) * WT_PARTIAL_FLOATS;
+    const int m = quad * 32 + lane;
+    // which issuing warps produced anything (a grid with fewer tiles than warps leaves some accumulators unwritten)
+    int used = 0;
+    {
+      int total = 0;
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int s = item % a.nstrips;
+        const int h0 = s * a.rows_per_strip;
+        total += min(a.H, h0 + a.rows_per_strip) - h0;
+      }
+      used = total < WT_WARPS ? total : WT_WARPS;
+    }
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+      for (int w = 0; w < used; ++w) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(w * 64 + c0), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(r[j]);
+      }
+      float4* o = reinterpret_cast<float4*>(dst + m * 64 + c0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Sum the per-CTA partials of conv3x3_wgrad_thin_kernel in CTA order and emit the torch layouts
+// (see the kernel's comment): side 0: gw [64][cs][3][3], gb [64]; side 1: gw [cs][64][3][3], gb [cs].
+__global__ void conv3x3_wgrad_thin_reduce_kernel(const float* __restrict__ partials, int nparts, int side, int cs,
+                                                 float* __restrict__ gw, float* __restrict__ gb) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nw = 64 * cs * 9;
+  const int nb = side == 0 ? 64 : cs;
+  int row, col;
+  float* out;
+  if (idx < nw) {
+    int m, c, t;
+    if (side == 0) {          // idx = ((m * cs + c) * 9 + t)
+      t = idx % 9; c = (idx / 9) % cs; m = idx / (9 * cs);
+      col = t * 4 + c;
+    } else {                  // idx = ((c * 64 + m) * 9 + t)
+      t = idx % 9; m = (idx / 9) % 64; c = idx / (9 * 64);
+      col = (8 - t) * 4 + c;
+    }
+    row = m;
+    out = gw + idx;
+  } else if (idx < nw + nb) {
+    const int j = idx - nw;
+    if (gb == nullptr) return;
+    if (side == 0) { row = j; col = 36; } else { row = 64; col = 16 + j; }
+    out = gb + j;
+  } else {
+    return;
+  }
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partials[static_cast<long long>(p) * WT_PARTIAL_FLOATS + row * 64 + col];
+  *out = s;
+}
+
 static int padded_tmap(CUtensorMap* tm, const void* base, int NB, int H, int W, int boxw, int shrink_w) {
   // dims (C, W + 2 - shrink_w, H + 2, NB); strides of the full padded buffer.
   uint64_t dims[4] = {64, static_cast<uint64_t>(W + 2 - shrink_w), static_cast<uint64_t>(H + 2),
@@ -915,6 +1236,132 @@ extern "C" int jb_conv3x3_c64(const void* in_padded, const void* weights, const 
     if (e != cudaSuccess) return -3;
     k<<<grid, CV_THREADS, SMEM16, st>>>(tmIn, tmW, tmOut, tmAux, a);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Thin-input convolution: in_padded4 is [NB][H+2][W+2][4] bf16 (halo filled; W even), weights a single
+// [64][64] bf16 tile whose row n holds output channel n and whose column tap * 4 + c the weight of input
+// channel c at tap (ty, tx) = (tap / 3, tap % 3), i.e. out[p][n] = sum in[p + (ty - 1, tx - 1)][c] w[n][tap * 4 + c];
+// columns 36..63 are ignored.  Used for the first layer of a network (forward) and, with mirrored taps, for
+// the data gradient of a last layer with at most four output channels.  The epilogue arguments are those of
+// jb_conv3x3_c64 with 64 output channels.
+extern "C" int jb_conv3x3_thin_in(const void* in_padded4, const void* weights, const float* bias, const void* gelu_src,
+                                  void* dense_pre, void* padded_out, void* dense_out, int NB, int H, int W, int act,
+                                  const JbHalo* halo, unsigned int* done_counter, int* status, int sm_count, void* stream) {
+  if (W & 1) return -1;
+  if (dense_pre != nullptr && act != 1) return -1;
+  CUtensorMap tmIn, tmW;
+  {
+    // pixel pairs as the innermost 16-byte unit: (8 values, (W + 2) / 2 pairs, H + 2 rows, NB images)
+    uint64_t dims[4] = {8, static_cast<uint64_t>((W + 2) / 2), static_cast<uint64_t>(H + 2), static_cast<uint64_t>(NB)};
+    uint64_t strides[3] = {16, static_cast<uint64_t>(W + 2) * 8, static_cast<uint64_t>(H + 2) * (W + 2) * 8};
+    uint32_t box[4] = {8, CV_BOXW / 2, 1, 1};
+    if (make_tmap_bf16(&tmIn, in_padded4, 4, dims, strides, box, false) != 0) return -2;
+  }
+  {
+    uint64_t dims[2] = {64, 64};
+    uint64_t strides[1] = {128};
+    uint32_t box[2] = {64, 64};
+    if (make_tmap_bf16(&tmW, weights, 2, dims, strides, box) != 0) return -2;
+  }
+  ConvArgs a{};
+  a.NB = NB; a.H = H; a.W = W;
+  a.tiles_w = (W + CV_TW - 1) / CV_TW;
+  choose_strips(H, NB, a.tiles_w, sm_count, CV_CHUNK, &a.rows_per_strip, &a.nstrips);
+  a.cout_real = 64;
+  a.bias = bias;
+  a.gelu_src = static_cast<const __nv_bfloat16*>(gelu_src);
+  a.dense_pre = static_cast<__nv_bfloat16*>(dense_pre);
+  a.act = act;
+  a.padded_out = static_cast<__nv_bfloat16*>(padded_out);
+  a.dense_out = static_cast<__nv_bfloat16*>(dense_out);
+  a.done_counter = done_counter;
+  a.status = status;
+  if (halo != nullptr) {
+    for (int d = 0; d < 9; ++d) {
+      a.push.buf[d] = halo->push_buf[d];
+      a.push.flag[d] = static_cast<uint32_t*>(halo->push_flag[d]);
+      a.wait.flag[d] = static_cast<const uint32_t*>(halo->wait_flag[d]);
+    }
+    a.push.epoch = halo->push_epoch;
+    a.push.enabled = halo->push_enabled;
+    a.push.stride = halo->push_stride;
+    a.push.replay = halo->replay;
+    a.wait.epoch = halo->wait_epoch;
+    a.wait.enabled = halo->wait_enabled;
+    a.wait.stride = halo->wait_stride;
+    a.wait.replay = halo->replay;
+  }
+  CUtensorMap tmOut = tmW, tmAux = tmW;
+  const void* aux = gelu_src ? gelu_src : (dense_pre ? static_cast<const void*>(dense_pre) : static_cast<const void*>(dense_out));
+  const int n_aux = (gelu_src != nullptr) + (dense_pre != nullptr) + (dense_out != nullptr);
+  if (n_aux > 1) return -1;
+  if (padded_out != nullptr && padded_tmap(&tmOut, padded_out, NB, H, W, CV_TW, 1) != 0) return -2;
+  if (aux != nullptr) {
+    uint64_t dims[4] = {64, static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(NB)};
+    uint64_t strides[3] = {128, static_cast<uint64_t>(W) * 128, static_cast<uint64_t>(H) * W * 128};
+    uint32_t box[4] = {64, CV_TW, 1, 1};
+    if (make_tmap_bf16(&tmAux, aux, 4, dims, strides, box) != 0) return -2;
+  }
+  const int items = NB * a.tiles_w * a.nstrips;
+  const int grid = items < sm_count ? items : sm_count;
+  constexpr int SMEM = 8192 + ((CV_SLOTS * CV_THIN_SLOT_BYTES + 1023) & ~1023) + CV_MMA_WARPS * CV_STAGE_BYTES +
+                       2 * CV_STAGE_BYTES + 512 + 1024;
+  auto k = conv3x3_tc_kernel<64, 0, 1>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
+  k<<<grid, CV_THREADS, SMEM, static_cast<cudaStream_t>(stream)>>>(tmIn, tmW, tmOut, tmAux, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Number of fp32 scratch elements jb_conv3x3_wgrad_thin needs for a given SM count.
+extern "C" long long jb_conv3x3_wgrad_thin_scratch_floats(int sm_count) {
+  return static_cast<long long>(sm_count) * WT_PARTIAL_FLOATS;
+}
+
+// Weight (and bias) gradient of a layer with at most four channels on one side.
+//  big_padded  : [NB][H+2][W+2][64] bf16; its interior pixels are read
+//  small_padded: [NB][H+2][W+2][4] bf16 (halo filled; W even)
+//  side 0: the layer has `cs` input channels (small = layer input, big = gradient of its output):
+//          gw [64][cs][3][3], gb [64]
+//  side 1: the layer has `cs` output channels (small = gradient of its output, big = layer input):
+//          gw [cs][64][3][3], gb [cs]
+//  scratch: jb_conv3x3_wgrad_thin_scratch_floats(sm_count) floats.  gb may be null.
+extern "C" int jb_conv3x3_wgrad_thin(const void* big_padded, const void* small_padded, float* gw, float* gb,
+                                     float* scratch, int NB, int H, int W, int side, int cs, const JbHalo* halo,
+                                     int* status, int sm_count, void* stream) {
+  if ((W & 1) || cs < 1 || cs > 4 || (side != 0 && side != 1)) return -1;
+  CUtensorMap tmBig, tmSmall;
+  // hide the right border column of the big buffer so that pixels beyond W read as zero
+  if (padded_tmap(&tmBig, big_padded, NB, H, W, CV_TW, 1) != 0) return -2;
+  {
+    uint64_t dims[4] = {8, static_cast<uint64_t>((W + 2) / 2), static_cast<uint64_t>(H + 2), static_cast<uint64_t>(NB)};
+    uint64_t strides[3] = {16, static_cast<uint64_t>(W + 2) * 8, static_cast<uint64_t>(H + 2) * (W + 2) * 8};
+    uint32_t box[4] = {8, CV_BOXW / 2, 1, 1};
+    if (make_tmap_bf16(&tmSmall, small_padded, 4, dims, strides, box, false) != 0) return -2;
+  }
+  WgradThinArgs a{};
+  a.NB = NB; a.H = H; a.W = W;
+  a.tiles_w = (W + CV_TW - 1) / CV_TW;
+  choose_strips(H, NB, a.tiles_w, sm_count, CV_CHUNK, &a.rows_per_strip, &a.nstrips);
+  a.partials = scratch;
+  a.status = status;
+  if (halo != nullptr) {
+    for (int d = 0; d < 9; ++d) a.wait.flag[d] = static_cast<const uint32_t*>(halo->wait_flag[d]);
+    a.wait.epoch = halo->wait_epoch;
+    a.wait.enabled = halo->wait_enabled;
+    a.wait.stride = halo->wait_stride;
+    a.wait.replay = halo->replay;
+  }
+  const int items = NB * a.tiles_w * a.nstrips;
+  const int grid = items < sm_count ? items : sm_count;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  constexpr int SMEM = 2 * WT_WARPS * CV_STAGE_BYTES + 2048 + ((CV_SLOTS * CV_THIN_SLOT_BYTES + 1023) & ~1023) + 512 + 1024;
+  if (cudaFuncSetAttribute(conv3x3_wgrad_thin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+    return -3;
+  conv3x3_wgrad_thin_kernel<<<grid, WT_THREADS, SMEM, st>>>(tmBig, tmSmall, a);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  const int n = 64 * cs * 9 + (side == 0 ? 64 : cs);
+  conv3x3_wgrad_thin_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(scratch, grid, side, cs, gw, gb);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -22,6 +22,12 @@ import torch.multiprocessing as mp
 
 
 def _entry(rank: int, world: int, init_file: str, backend: str, fn: Callable, args: tuple, queue: Any) -> None:
+    # a rank that is still running after this long prints the stacks of all its threads (to the test's stderr):
+    # the place where a hung collective or a lost message blocks is then in the log instead of a bare timeout
+    import faulthandler
+
+    faulthandler.enable()            # a crash in native code prints the Python stack of the rank that died
+    faulthandler.dump_traceback_later(float(os.environ.get("JIGSAW_TEST_STACKS_AFTER", "90")), exit=False)
     try:
         os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"] = str(rank), str(world), str(rank)
         torch.set_num_threads(1)
@@ -35,6 +41,7 @@ def _entry(rank: int, world: int, init_file: str, backend: str, fn: Callable, ar
         if backend == "nccl":
             torch.cuda.synchronize()
         dist.barrier()
+        faulthandler.cancel_dump_traceback_later()
         queue.put((rank, None))
     except BaseException:  # noqa: BLE001 - report everything to the parent
         queue.put((rank, traceback.format_exc()))
@@ -59,11 +66,20 @@ def run_distributed(fn: Callable, world: int, *args: Any, backend: str = "gloo",
         try:
             import queue as _q
 
-            while len(results) < world:
+            import time
+
+            deadline = time.monotonic() + timeout
+            died = None
+            while len(results) < world and time.monotonic() < deadline:
                 try:
-                    rank, err = queue.get(timeout=timeout)
+                    rank, err = queue.get(timeout=2.0)
                 except _q.Empty:
-                    break
+                    # a rank that died in native code never reports: do not wait for the timeout
+                    dead = [(i, p.exitcode) for i, p in enumerate(procs) if p.exitcode not in (None, 0) and i not in results]
+                    if dead:
+                        died = dead
+                        break
+                    continue
                 results[rank] = err
                 if err is not None:
                     break
@@ -75,6 +91,8 @@ def run_distributed(fn: Callable, world: int, *args: Any, backend: str = "gloo",
                     p.terminate()
                     p.join(timeout=5)
     errors = {r: e for r, e in results.items() if e is not None}
+    if not errors and died:
+        raise AssertionError(f"ranks died without reporting (rank, exit code): {died}")
     if errors:
         rank, err = sorted(errors.items())[0]
         raise AssertionError(f"rank {rank} failed:\n{err}")
