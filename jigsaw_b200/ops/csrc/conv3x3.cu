@@ -208,7 +208,7 @@ __device__ __forceinline__ void conv_epilogue(const ConvArgs& a, float (&v)[CPW]
   if (a.act == 1) {
     float d[CPW];
 #pragma unroll
-    for (int j = 0; j < CPW; ++j) gelu_erf_with_grad(v[j], v[j], d[j]);
+    for (int j = 0; j < CPW; j += 2) gelu_erf_with_grad_x2(v[j], v[j + 1], v[j], v[j + 1], d[j], d[j + 1]);
     if (a.dense_pre != nullptr) {
       uint4* dst = reinterpret_cast<uint4*>(a.dense_pre + pix * 64 + c0);
 #pragma unroll
@@ -564,11 +564,11 @@ conv3x3_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constan
           const bool aux_is_pre = a.dense_pre != nullptr;
           if (a.act == 1 && !aux_is_pre) {
 #pragma unroll
-            for (int j = 0; j < CPW; ++j) v[j] = gelu_erf(v[j]);
+            for (int j = 0; j < CPW; j += 2) gelu_erf_x2(v[j], v[j + 1], v[j], v[j + 1]);
           } else if (a.act == 1) {
             float d[CPW];
 #pragma unroll
-            for (int j = 0; j < CPW; ++j) gelu_erf_with_grad(v[j], v[j], d[j]);
+            for (int j = 0; j < CPW; j += 2) gelu_erf_with_grad_x2(v[j], v[j + 1], v[j], v[j + 1], d[j], d[j + 1]);
 #pragma unroll
             for (int q = 0; q < CPW / 8; ++q) {
               aux_v[q].x = pack_bf16x2(d[q * 8 + 0], d[q * 8 + 1]);
