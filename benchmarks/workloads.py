@@ -251,9 +251,16 @@ def build_swin(lib, n, dev, scale):
     return model, loss_fn, tile(x), tile(y, patch), desc, batch
 
 
+DATA_PARALLEL = 1          # --dp N: N data-parallel replicas of the 3-D model (wrap_ddp with the joint hook)
+
+
 def build_unet3d(lib, n, dev, scale):
-    sh, sw = TILES[n]
-    mesh = lib.make_process_mesh({"sh": sh, "sw": sw, "col": 1})
+    dp = DATA_PARALLEL
+    sh, sw = TILES[n // dp]
+    if dp > 1:
+        mesh = lib.make_process_mesh({"dp": dp, "sh": sh, "sw": sw, "col": 1}, model_parallel_axes=("sh", "sw", "col"))
+    else:
+        mesh = lib.make_process_mesh({"sh": sh, "sw": sw, "col": 1})
     M = lib.modules
     size = {"small": 64, "default": 128, "full": 256}[scale]
     widths = (32, 64, 128)
@@ -275,8 +282,11 @@ def build_unet3d(lib, n, dev, scale):
         if i < 2:
             layers += [norm(ups[i]), nn.GELU()]
     model = nn.Sequential(*layers)
+    if dp > 1:
+        # every replica sees its own volume; DDP averages over dp and the joint hook folds the sum over the tile ranks in
+        model = lib.parallel.wrap_ddp(model, mesh, dp_key="dp", joint_hook=True)
     loss_fn = M.DistributedBCEWithLogitsLoss(reduce_groups=(mesh["sh"], mesh["sw"]))
-    g = torch.Generator().manual_seed(3)
+    g = torch.Generator().manual_seed(3 + (mesh["dp"].rank() if dp > 1 else 0))
     x = torch.randn(1, 1, size, size, size, generator=g)
     y = (torch.rand(1, 1, size, size, size, generator=g) > 0.5).float()
     h, w = size // sh, size // sw
@@ -284,8 +294,9 @@ def build_unet3d(lib, n, dev, scale):
     def tile(t):
         return t[..., mesh["sh"].rank() * h:(mesh["sh"].rank() + 1) * h, mesh["sw"].rank() * w:(mesh["sw"].rank() + 1) * w].contiguous()
 
-    desc = {"model": f"3-D enc-dec 1-32-64-128, {size}^3", "global_batch": 1, "seq_len": None, "parallelism": f"sh{sh} x sw{sw}"}
-    return model, loss_fn, tile(x), tile(y), desc, 1
+    desc = {"model": f"3-D enc-dec 1-32-64-128, {size}^3", "global_batch": dp, "seq_len": None,
+            "parallelism": (f"dp{dp} x " if dp > 1 else "") + f"sh{sh} x sw{sw}" + (", DDP with the joint hook" if dp > 1 else "")}
+    return model, loss_fn, tile(x), tile(y), desc, dp
 
 
 def main() -> None:
@@ -297,6 +308,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", default="default")
     ap.add_argument("--seq", choices=("ring", "ulysses"), default="ring", help="sequence parallelism of the ViT's attention")
+    ap.add_argument("--dp", type=int, default=1, help="unet3d only: data-parallel replicas (the tile grid uses gpus / dp ranks)")
     ap.add_argument("--mesh", default=None, help="ViT only: rows x columns of the mesh, e.g. 2x1 (default: 1x1, 1x2, 2x2, 4x2)")
     ap.add_argument("--graph", action="store_true",
                     help="replay the whole step as one CUDA graph (this framework only; GraphedStep)")
@@ -313,8 +325,9 @@ def main() -> None:
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     lib = load(args.impl)
-    global SEQUENCE_PARALLEL, MESH_OVERRIDE
+    global SEQUENCE_PARALLEL, MESH_OVERRIDE, DATA_PARALLEL
     SEQUENCE_PARALLEL = args.seq
+    DATA_PARALLEL = args.dp
     if args.mesh:
         r, c = (int(v) for v in args.mesh.lower().split("x"))
         if r * c != args.gpus:
