@@ -310,6 +310,8 @@ def main() -> None:
     ap.add_argument("--seq", choices=("ring", "ulysses"), default="ring", help="sequence parallelism of the ViT's attention")
     ap.add_argument("--dp", type=int, default=1, help="unet3d only: data-parallel replicas (the tile grid uses gpus / dp ranks)")
     ap.add_argument("--mesh", default=None, help="ViT only: rows x columns of the mesh, e.g. 2x1 (default: 1x1, 1x2, 2x2, 4x2)")
+    ap.add_argument("--profile", default=None, metavar="FILE",
+                    help="after the timed steps, run two more under torch.profiler and write rank 0's kernel table to FILE")
     ap.add_argument("--graph", action="store_true",
                     help="replay the whole step as one CUDA graph (this framework only; GraphedStep)")
     args = ap.parse_args()
@@ -396,6 +398,16 @@ def main() -> None:
                           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(ms), "impl": args.impl,
                           "dtype": "bf16", "data": "synthetic", "config": desc, "gpu_launches": launches,
                           "graph": graphed is not None, "loss": float(loss), "clocks": clocks, "dispatch": dispatch}), flush=True)
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            for _ in range(2):
+                run()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.profile, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
     if graphed is not None:
         graphed.close()                      # a live graph that holds collectives blocks the teardown
     dist.destroy_process_group()

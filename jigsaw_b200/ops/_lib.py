@@ -170,6 +170,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.jb_all_reduce_sum.restype = c_int
     L.jb_memcpy_async.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p]
     L.jb_memcpy_async.restype = c_int
+    L.jb_memcpy2d_async.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p]
+    L.jb_memcpy2d_async.restype = c_int
     L.jb_slot_acquire.argtypes = [POINTER(c_void_p), c_int, c_void_p, c_uint, c_uint, c_void_p, c_void_p, c_void_p]
     L.jb_slot_acquire.restype = c_int
     L.jb_slot_release.argtypes = [POINTER(c_void_p), c_int, c_uint, c_uint, c_void_p, c_void_p]

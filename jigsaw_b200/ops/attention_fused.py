@@ -26,7 +26,7 @@ from typing import Any
 import torch
 import torch.distributed as dist
 
-from . import _lib
+from . import _lib, symm
 
 
 @_lib.traced("jb.maybe_fused_merge")
@@ -78,8 +78,6 @@ def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     lse = torch.empty(bh, sq, dtype=torch.float32, device=q.device)
     status = None
     if bh > 0 and sq > 0:
-        from . import symm
-
         ar = symm.arena(q.device)
         status = ar.status
         rc = _lib.lib().jb_flash_attn_fwd(
@@ -156,50 +154,6 @@ def _ring_block(ar: Any, tag: tuple, nbytes: int) -> Any:
     return blk
 
 
-_side: dict[int, torch.cuda.Stream] = {}
-_epoch_words: dict[int, torch.Tensor] = {}
-
-
-def _push_to_peers(ar: Any, blk: Any, ranks: list, me: int, offset: int, nbytes: int) -> tuple[int, int, Any, Any]:
-    """Give every peer this rank's slot of ``blk`` (``nbytes`` at ``offset``, already written locally on the
-    current stream) and then raise this rank's flag in the peer's copy of the block.  Both travel by the copy
-    engines on a side stream: every staged byte crosses NVLink once per destination, no SM is used, and
-    the caller's attention kernel (launched next on the current stream) starts on its own part at once while
-    the pushes of all ranks are in flight.  Returns ``(epoch, stride, replay, done event)``; the caller makes
-    its stream wait for the event AFTER launching its kernel."""
-    L, dev = _lib.lib(), blk.tensor.device
-    epoch = ar.next_own_epoch(blk)
-    stride = ar.capture_stride or 0
-    replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
-    idx = dev.index
-    if idx not in _side:
-        _side[idx] = torch.cuda.Stream(dev)
-        _epoch_words[idx] = torch.zeros(64, dtype=torch.int32, device=dev)
-    side = _side[idx]
-    # the flag value as it must read on this replay: one word per block (the two blocks of a ring alternate)
-    word = _epoch_words[idx][(blk.offset // 1024) % 64:][:1]
-    one = (ctypes.c_void_p * 8)()
-    one[0] = word.data_ptr()
-    rc = L.jb_publish(one, 1, epoch, stride, replay, _lib.stream_ptr())
-    staged = torch.cuda.Event()
-    staged.record()
-    side.wait_event(staged)
-    with torch.cuda.stream(side):
-        st = _lib.stream_ptr()
-        for i, r in enumerate(ranks):
-            if i == me or rc != 0:
-                continue
-            rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + offset), ctypes.c_void_p(blk.ptr + offset), nbytes, st)
-            if rc == 0:
-                rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + 4 * me), ctypes.c_void_p(word.data_ptr()), 4, st)
-        done = torch.cuda.Event()
-        done.record()
-    if rc != 0:
-        raise RuntimeError(f"jigsaw_b200: pushing a staged block to the peers failed with code {rc}")
-    _lib.count_launches(1)
-    return epoch, stride, replay, done
-
-
 def _local_parts(blk: Any, P: int, base: int, slot: int, inner: int) -> Any:
     """Pointers to one operand (at ``inner`` inside a slot) in each of the ``P`` slots of this rank's block."""
     arr = (ctypes.c_void_p * 8)()
@@ -218,8 +172,6 @@ def _flag_ptrs(blk: Any, P: int, me: int) -> Any:
 class _RingFlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, group: Any) -> torch.Tensor:
-        from . import symm
-
         L, dev = _lib.lib(), q.device
         ar = symm.arena(dev)
         P, me = group.size(), group.rank()
@@ -233,7 +185,7 @@ class _RingFlashAttention(torch.autograd.Function):
         mine = blk.tensor[_HEADER + me * slot:_HEADER + (me + 1) * slot].view(torch.bfloat16).view(2, *k.shape)
         mine[0].copy_(k)                                      # any strides (e.g. a head-transposed view): one copy
         mine[1].copy_(v)
-        epoch, stride, replay, pushed = _push_to_peers(ar, blk, ranks, me, _HEADER + me * slot, slot)
+        epoch, stride, replay, pushed = symm.push_slot_to_peers(ar, blk, ranks, me, _HEADER + me * slot, slot)
         out = torch.empty_like(q3)
         lse = torch.empty(bh, s, dtype=torch.float32, device=dev)
         rc = L.jb_flash_attn_fwd_parts(
@@ -251,8 +203,6 @@ class _RingFlashAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        from . import symm
-
         q3, k, v, out, lse = ctx.saved_tensors
         group = ctx.group
         L, dev = _lib.lib(), q3.device
@@ -276,7 +226,7 @@ class _RingFlashAttention(torch.autograd.Function):
         rc = L.jb_flash_attn_delta(P_(out), P_(ops[1]), P_(rows[1]), bh * s, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher flash_attn_delta failed with code {rc}")
-        epoch, stride, replay, pushed = _push_to_peers(ar, blk, ranks, me, base, slot)
+        epoch, stride, replay, pushed = symm.push_slot_to_peers(ar, blk, ranks, me, base, slot)
         dq, dk, dv = (torch.empty(bh, s, 64, dtype=torch.bfloat16, device=dev) for _ in range(3))
         at = lambda i: _local_parts(blk, P, _HEADER, slot, i * n)  # noqa: E731
         rc = L.jb_flash_attn_bwd_parts(

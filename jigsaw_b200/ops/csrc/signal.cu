@@ -67,6 +67,16 @@ extern "C" int jb_memcpy_async(void* dst, const void* src, long long bytes, void
              : -4;
 }
 
+// The same for `rows` rows of `width` bytes each, `dpitch` / `spitch` bytes apart (a column block of a matrix).
+extern "C" int jb_memcpy2d_async(void* dst, long long dpitch, const void* src, long long spitch, long long width,
+                                 long long rows, void* stream) {
+  if (width <= 0 || rows <= 0) return -1;
+  return cudaMemcpy2DAsync(dst, static_cast<size_t>(dpitch), src, static_cast<size_t>(spitch), static_cast<size_t>(width),
+                           static_cast<size_t>(rows), cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? 0
+             : -4;
+}
+
 // Before producing content `new_epoch` into a buffer slot: wait until the (up to eight) local
 // acknowledgement words have reached the epoch of the slot's previous content, then record the new
 // epoch in `last_epoch` (a device word owned by the slot).

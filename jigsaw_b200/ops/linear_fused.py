@@ -7,14 +7,15 @@ transposing anything: ``dX = dY @ W`` (B operand MN-major) and ``dW = dY.T @ X``
 MN-major, fp32 output).  Returns ``None`` when the kernel does not apply; the caller then uses
 ``torch.nn.functional.linear``.
 
-``maybe_fused_gather_linear(x_local, w, b, group)`` fuses the all-gather of the activations
-into that GEMM: every rank drops its ``[M, K / P]`` block (cast to bf16) into a symmetric buffer
-and publishes an epoch flag; the TMA producer of the GEMM then reads the k-blocks of part ``p``
-straight from GPU ``p`` over NVLink, so the gathered ``[M, K]`` matrix is never materialised
-and the transfer overlaps the tensor-core work tile by tile.  The input gradient is the mirror
-image, GEMM -> reduce-scatter in one pass: the epilogue of ``dY @ W`` stores each tile into the
-inbox of the rank that owns those columns, and every rank sums the slabs it received.  (The
-weight gradient re-gathers ``x`` with NCCL and uses a local GEMM.)
+``maybe_fused_gather_linear(x_local, w, b, group)`` overlaps the all-gather of the activations
+with that GEMM: every rank writes its ``[M, K / P]`` block (cast to bf16) into its slot of a symmetric
+buffer, the copy engines push the slot into every peer's buffer followed by a flag, and the TMA
+producer of the GEMM reads the k-blocks of part ``p`` from LOCAL memory as soon as the flag of rank
+``p`` has arrived, so the transfer (each byte crosses NVLink once per destination, no SM involved) runs
+under the tensor-core work on the parts that are already there.  The input gradient is GEMM ->
+reduce-scatter in one pass: the epilogue of ``dY @ W`` stores each tile into the inbox of the rank that
+owns those columns, and every rank sums the slabs it received.  The weight gradient multiplies with the
+gathered activations saved by the forward pass (no second gather).
 
 Reference parity: the ``torch.matmul`` / ``F.linear`` calls of
 jigsaw/modules/linear/_distributed_matmul.py:100-110,159-177 (cuBLAS there) and the masked
@@ -242,58 +243,52 @@ class _GatherLinear(torch.autograd.Function):
         kp = x.shape[-1]
         M = x.numel() // kp
         N = w.shape[0]
-        blk = _staging_block(ar, ("gather_x", dev.index, M, kp, tuple(ranks)), _HEADER + M * kp * 2)
-        staged = blk.tensor[_HEADER:].view(torch.bfloat16)[: M * kp].view(M, kp)
-        staged.copy_(x.reshape(M, kp))                                   # cast + copy in one kernel
-        epoch = ar.next_own_epoch(blk)
-        stride = ar.capture_stride or 0
-        replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+        K = P * kp
+        # the gathered [M, K] matrix lives in every rank's block: this rank writes its own column block (cast + copy
+        # in one kernel) and the copy engines push it into the same columns of every peer, followed by a flag; the
+        # GEMM then reads ALL parts from local memory as their flags arrive, so each activation byte crosses NVLink
+        # once per destination
+        blk = _staging_block(ar, ("gather_x", dev.index, M, kp, tuple(ranks)), _HEADER + M * K * 2)
+        full = blk.tensor[_HEADER:_HEADER + M * K * 2].view(torch.bfloat16).view(M, K)
+        full[:, me * kp:(me + 1) * kp].copy_(x.reshape(M, kp))
+        epoch, stride, replay, pushed = symm.push_slot_to_peers(ar, blk, ranks, me, _HEADER + me * kp * 2, kp * 2,
+                                                                pitch=K * 2, rows=M)
         st = _lib.stream_ptr()
-        flags = (ctypes.c_void_p * 8)()
-        n = 0
-        for i, r in enumerate(ranks):
-            if i != me:
-                flags[n] = blk.peer_ptr(r) + 4 * me
-                n += 1
-        rc = L.jb_publish(flags, n, epoch, stride, replay, st)
         g = _lib.JbGather()
-        for i, r in enumerate(ranks):
-            g.a_part[i] = (blk.ptr if i == me else blk.peer_ptr(r)) + _HEADER
+        for i in range(P):
+            g.a_part[i] = blk.ptr + _HEADER + i * kp * 2
             g.flag[i] = None if i == me else blk.ptr + 4 * i
-        g.epoch, g.stride, g.replay, g.parts, g.k_part, g.lda_part = epoch, stride, replay, P, kp, kp
+        g.epoch, g.stride, g.replay, g.parts, g.k_part, g.lda_part = epoch, stride, replay, P, kp, K
         wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
         wb = wb if wb.is_contiguous() else wb.contiguous()
         bias = None if b is None else b.float().contiguous()
         y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-        if rc == 0:
-            rc = L.jb_gemm_bf16_gather(ctypes.byref(g), _p(wb), _p(y), _p(bias), M, N, wb.stride(0), y.stride(0), 0, 0,
-                                       _lib.sm_count(dev.index), _p(ar.status), st)
+        rc = L.jb_gemm_bf16_gather(ctypes.byref(g), _p(wb), _p(y), _p(bias), M, N, wb.stride(0), y.stride(0), 0, 0,
+                                   _lib.sm_count(dev.index), _p(ar.status), st)
+        torch.cuda.current_stream(dev).wait_event(pushed)
         if rc != 0:
             raise RuntimeError(f"jigsaw_b200 kernel launcher gemm_bf16_gather failed with code {rc}")
-        _lib.count_launches(2)
-        ctx.save_for_backward(staged.clone() if ctx.needs_input_grad[1] else None, wb)
+        _lib.count_launches(1)
+        # the weight gradient needs the gathered activations: keep a copy of the complete block (every part has
+        # arrived once the GEMM is done) instead of gathering again in the backward pass
+        ctx.save_for_backward(full.clone() if ctx.needs_input_grad[1] else None, wb)
         ctx.group, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = group, x.shape, x.dtype, w.dtype
         ctx.b_dtype = None if b is None else b.dtype
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
     def backward(ctx: Any, gy: torch.Tensor) -> tuple:
-        xb, wb = ctx.saved_tensors
+        x_full, wb = ctx.saved_tensors
         group = ctx.group
-        P = group.size()
         N = wb.shape[0]
         g = gy.reshape(-1, N)
         g = g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)
         g = g if g.is_contiguous() else g.contiguous()
-        M = g.shape[0]
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = _scatter_gemm(g, wb, group).view(ctx.x_shape).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
-            gathered = torch.empty(P, M, xb.shape[1], dtype=xb.dtype, device=xb.device)
-            dist.all_gather_into_tensor(gathered, xb, group=group)
-            x_full = gathered.permute(1, 0, 2).reshape(M, -1)
-            dw = gemm(g, x_full, a_mn=True, b_mn=True, out_dtype=torch.float32).to(ctx.w_dtype)
+            dw = gemm(g, x_full, a_mn=True, b_mn=True, out_dtype=torch.float32).to(ctx.w_dtype)   # [M, N]^T x [M, K]
         if ctx.b_dtype is not None and ctx.needs_input_grad[2]:
             db = g.sum(dim=0, dtype=torch.float32).to(ctx.b_dtype)
         return dx, dw, db, None

@@ -292,6 +292,59 @@ def arena(device: torch.device) -> PeerArena:
     return _arenas[idx]
 
 
+# --------------------------------------------------------------------------- all-gather by push
+_push_streams: dict[int, torch.cuda.Stream] = {}
+_epoch_words: dict[int, torch.Tensor] = {}
+
+
+def push_slot_to_peers(ar: "PeerArena", blk: Block, ranks: list, me: int, offset: int, nbytes: int, pitch: int = 0,
+                        rows: int = 1) -> tuple:
+    """Give every peer this rank's slot of ``blk`` (``nbytes`` at ``offset``, already written locally on the
+    current stream) and then raise this rank's flag in the peer's copy of the block.  Both travel by the copy
+    engines on a side stream: every staged byte crosses NVLink once per destination, no SM is used, and
+    the caller's attention kernel (launched next on the current stream) starts on its own part at once while
+    the pushes of all ranks are in flight.  Returns ``(epoch, stride, replay, done event)``; the caller makes
+    its stream wait for the event AFTER launching its kernel."""
+    from . import _lib
+
+    L, dev = _lib.lib(), blk.tensor.device
+    epoch = ar.next_own_epoch(blk)
+    stride = ar.capture_stride or 0
+    replay = ar.replay.data_ptr() if ar.capture_stride is not None else None
+    idx = dev.index
+    if idx not in _push_streams:
+        _push_streams[idx] = torch.cuda.Stream(dev)
+        _epoch_words[idx] = torch.zeros(64, dtype=torch.int32, device=dev)
+    side = _push_streams[idx]
+    # the flag value as it must read on this replay: one word per block (the two blocks of a ring alternate)
+    word = _epoch_words[idx][(blk.offset // 1024) % 64:][:1]
+    one = (ctypes.c_void_p * 8)()
+    one[0] = word.data_ptr()
+    rc = L.jb_publish(one, 1, epoch, stride, replay, _lib.stream_ptr())
+    staged = torch.cuda.Event()
+    staged.record()
+    side.wait_event(staged)
+    with torch.cuda.stream(side):
+        st = _lib.stream_ptr()
+        for i, r in enumerate(ranks):
+            if i == me or rc != 0:
+                continue
+            if rows > 1:        # a column block: `rows` pieces of `nbytes`, `pitch` bytes apart
+                rc = L.jb_memcpy2d_async(ctypes.c_void_p(blk.peer_ptr(r) + offset), pitch, ctypes.c_void_p(blk.ptr + offset),
+                                         pitch, nbytes, rows, st)
+            else:
+                rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + offset), ctypes.c_void_p(blk.ptr + offset), nbytes, st)
+            if rc == 0:
+                rc = L.jb_memcpy_async(ctypes.c_void_p(blk.peer_ptr(r) + 4 * me), ctypes.c_void_p(word.data_ptr()), 4, st)
+        done = torch.cuda.Event()
+        done.record()
+    if rc != 0:
+        raise RuntimeError(f"jigsaw_b200: pushing a staged block to the peers failed with code {rc}")
+    _lib.count_launches(1)
+    return epoch, stride, replay, done
+
+
+
 # --------------------------------------------------------------------------- neighbours
 def neighbour_table(group_h: dist.ProcessGroup | None, group_w: dist.ProcessGroup | None) -> list[int | None]:
     """World rank of the tile at ``(sy, sx)`` relative to this rank for the 3x3 neighbourhood
