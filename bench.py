@@ -77,7 +77,7 @@ class ClockSampler:
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None

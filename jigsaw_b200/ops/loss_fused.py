@@ -126,6 +126,8 @@ def maybe_fused_pair_loss_sum(a: torch.Tensor, b: torch.Tensor, kind: str, beta:
 def _pair_loss_sum(a: torch.Tensor, b: torch.Tensor, kind: str, beta: float) -> torch.Tensor | None:
     if not a.is_cuda:
         return None
+    if a.shape == b.shape and a.dim() > 4 and a.is_contiguous() and b.is_contiguous():
+        a, b = a.reshape(-1), b.reshape(-1)          # volumes and the like: element-wise, so one long row will do
     if a.shape != b.shape or a.dim() > 4 or a.dim() == 0 or a.numel() == 0:
         return _lib.decline("needs two tensors of the same shape with 1 to 4 dimensions")
     if a.dtype not in _OK or b.dtype not in _OK or torch._C._functorch.is_batchedtensor(a):
