@@ -24,7 +24,6 @@ import os
 import statistics
 import subprocess
 import sys
-import time
 
 import torch
 import torch.distributed as dist
@@ -192,25 +191,28 @@ def main() -> None:
         if e2e and run is not None:
             # The framework's input pipeline: every step's inputs travel from pinned host memory on a side
             # stream while the previous step computes (DevicePrefetcher), land in the graph's static inputs,
-            # and every step's loss is read back to the host, one step behind the launch so that the read
-            # does not stall the next launch.
+            # and every step's loss is read back to the host a few steps behind its launch, so that neither the
+            # read nor a late wake-up of one rank's host thread stalls the launches (the ranks wait for each
+            # other's halos inside every step, so one late rank would hold up all of them).
             from jigsaw_b200.data import DevicePrefetcher
 
-            host_loss = [torch.empty((), dtype=run.outputs.dtype).pin_memory() for _ in range(2)]
-            done = [torch.cuda.Event(), torch.cuda.Event()]
+            lag = 3                                    # steps between a launch and the read of its loss
+            host_loss = [torch.empty((), dtype=run.outputs.dtype).pin_memory() for _ in range(lag + 1)]
+            done = [torch.cuda.Event() for _ in range(lag + 1)]
             sizes["loss"] = run.outputs.element_size()
             batches = ((x_host, y_host) for _ in range(n_steps))
-            for i, (xb, yb) in enumerate(DevicePrefetcher(batches, dev, depth=2)):
+            for i, (xb, yb) in enumerate(DevicePrefetcher(batches, dev, depth=lag + 1)):
                 x_dev.copy_(xb)
                 y_dev.copy_(yb)
                 out = run.replay()
-                host_loss[i & 1].copy_(out, non_blocking=True)
-                done[i & 1].record()
-                if i > 0:
-                    done[(i - 1) & 1].synchronize()
-                    last = float(host_loss[(i - 1) & 1].item())
-            done[(n_steps - 1) & 1].synchronize()
-            last = float(host_loss[(n_steps - 1) & 1].item())
+                host_loss[i % (lag + 1)].copy_(out, non_blocking=True)
+                done[i % (lag + 1)].record()
+                if i >= lag:
+                    done[(i - lag) % (lag + 1)].synchronize()
+                    last = float(host_loss[(i - lag) % (lag + 1)].item())
+            for i in range(max(n_steps - lag, 0), n_steps):          # the losses still in flight
+                done[i % (lag + 1)].synchronize()
+                last = float(host_loss[i % (lag + 1)].item())
         for _ in range(0 if (e2e and run is not None) else n_steps):
             if e2e:
                 x = x_host.to(dev, non_blocking=True)

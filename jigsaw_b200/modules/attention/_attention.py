@@ -19,7 +19,6 @@ Reference parity: jigsaw/modules/attention/_attention.py:159-179 (core dtype), :
 
 from __future__ import annotations
 
-import os
 from typing import Any
 
 import torch

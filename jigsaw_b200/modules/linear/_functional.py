@@ -46,51 +46,99 @@ def _transport(comm: CommOp | str, device: torch.device) -> CommOp:
         return resolve_comm_op("auto", device)
 
 
+def _plan(h: int, w: int, group: dist.ProcessGroup, R: int, C: int, region_of: Any) -> tuple:
+    """Who reads what: ``(mine, want, plan_send, plan_recv)`` for a local block of ``h x w`` elements.
+    ``plan_send[p]`` is the part of my block that rank ``p`` reads, ``plan_recv[p]`` the part of rank
+    ``p``'s block that I read (both in global coordinates)."""
+    me = group.rank()
+    block = lambda p: ((p // C) * h, (p // C + 1) * h, (p % C) * w, (p % C + 1) * w)  # noqa: E731
+    mine, want = block(me), region_of(me)
+    plan_send, plan_recv = {}, {}
+    for p in range(R * C):
+        give = _overlap(region_of(p), mine)
+        if give is not None:
+            plan_send[p] = give
+        take = _overlap(want, block(p))
+        if take is not None:
+            plan_recv[p] = take
+    return mine, want, plan_send, plan_recv
+
+
+def _cut(t: torch.Tensor, part: Region, origin: Region) -> torch.Tensor:
+    return t[..., part[0] - origin[0]:part[1] - origin[0], part[2] - origin[2]:part[3] - origin[2]]
+
+
+def _fetch(x: torch.Tensor, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: Any) -> torch.Tensor:
+    x = x.contiguous()
+    mine, want, plan_send, plan_recv = _plan(x.shape[-2], x.shape[-1], group, R, C, region_of)
+    lead = x.shape[:-2]
+    out = x.new_empty(*lead, want[1] - want[0], want[3] - want[2])
+    sends = {p: _cut(x, give, mine).contiguous() for p, give in plan_send.items()}
+    recvs = {p: x.new_empty(*lead, take[1] - take[0], take[3] - take[2]) for p, take in plan_recv.items()}
+    sparse_exchange(sends, recvs, group, _transport(comm, x.device))
+    for p, take in plan_recv.items():
+        _cut(out, take, want).copy_(recvs[p])
+    return out
+
+
+def _scatter_add(g: torch.Tensor, h: int, w: int, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: Any) -> torch.Tensor:
+    """Adjoint of :func:`_fetch`: every piece of the region's gradient goes back to the owner of its
+    block, where the contributions of all readers are summed (in fp32 at least)."""
+    g = g.contiguous()
+    mine, want, plan_send, plan_recv = _plan(h, w, group, R, C, region_of)
+    lead = g.shape[:-2]
+    sends = {p: _cut(g, take, want).contiguous() for p, take in plan_recv.items()}
+    recvs = {p: g.new_empty(*lead, give[1] - give[0], give[3] - give[2]) for p, give in plan_send.items()}
+    sparse_exchange(sends, recvs, group, _transport(comm, g.device))
+    acc = torch.zeros(*lead, h, w, dtype=torch.promote_types(g.dtype, torch.float32), device=g.device)
+    for p, give in plan_send.items():
+        _cut(acc, give, mine).add_(recvs[p])
+    return acc.to(g.dtype)
+
+
 class _FetchRegion(torch.autograd.Function):
     """``region_of(rank)`` of a matrix whose last two dimensions are cut into ``R x C`` blocks over
     ``group`` (rank ``i * C + j`` holds block ``(i, j)``): every rank receives its region piece by piece
-    from the owners of the blocks it overlaps.  Backward: the adjoint scatter-add."""
+    from the owners of the blocks it overlaps.  Backward: the adjoint scatter-add (:class:`_ScatterRegion`),
+    itself differentiable; leading dimensions are batch, which is also the ``vmap`` rule."""
 
     @staticmethod
-    def forward(ctx: Any, x: torch.Tensor, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: Any) -> torch.Tensor:
-        x = x.contiguous()
-        h, w = x.shape[-2], x.shape[-1]
-        me = group.rank()
-        block = lambda p: ((p // C) * h, (p // C + 1) * h, (p % C) * w, (p % C + 1) * w)  # noqa: E731
-        mine, want = block(me), region_of(me)
-        lead = x.shape[:-2]
-        out = x.new_empty(*lead, want[1] - want[0], want[3] - want[2])
-        sends, recvs, places = {}, {}, {}
-        plan_send, plan_recv = {}, {}
-        for p in range(R * C):
-            give = _overlap(region_of(p), mine)                # part of my block that rank p reads
-            if give is not None:
-                plan_send[p] = give
-                sends[p] = x[..., give[0] - mine[0]:give[1] - mine[0], give[2] - mine[2]:give[3] - mine[2]].contiguous()
-            take = _overlap(want, block(p))                    # part of rank p's block that I read
-            if take is not None:
-                plan_recv[p] = take
-                recvs[p] = x.new_empty(*lead, take[1] - take[0], take[3] - take[2])
-                places[p] = (slice(take[0] - want[0], take[1] - want[0]), slice(take[2] - want[2], take[3] - want[2]))
-        comm = _transport(comm, x.device)
-        sparse_exchange(sends, recvs, group, comm)
-        for p, buf in recvs.items():
-            out[(..., *places[p])] = buf
-        ctx.group, ctx.comm, ctx.mine, ctx.want = group, comm, mine, want
-        ctx.plan_send, ctx.plan_recv, ctx.places, ctx.x_shape, ctx.x_dtype = plan_send, plan_recv, places, x.shape, x.dtype
-        return out
+    def forward(x: torch.Tensor, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: Any) -> torch.Tensor:
+        return _fetch(x, group, R, C, region_of, comm)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        x, ctx.group, ctx.R, ctx.C, ctx.region_of, ctx.comm = inputs
+        ctx.hw, ctx.x_dtype = (x.shape[-2], x.shape[-1]), x.dtype
 
     @staticmethod
     def backward(ctx: Any, g: torch.Tensor) -> tuple:
-        mine = ctx.mine
-        lead = ctx.x_shape[:-2]
-        sends = {p: g[(..., *ctx.places[p])].contiguous() for p in ctx.plan_recv}
-        recvs = {p: g.new_empty(*lead, give[1] - give[0], give[3] - give[2]) for p, give in ctx.plan_send.items()}
-        sparse_exchange(sends, recvs, ctx.group, ctx.comm)
-        acc = torch.zeros(ctx.x_shape, dtype=torch.promote_types(g.dtype, torch.float32), device=g.device)
-        for p, give in ctx.plan_send.items():
-            acc[..., give[0] - mine[0]:give[1] - mine[0], give[2] - mine[2]:give[3] - mine[2]] += recvs[p]
-        return acc.to(ctx.x_dtype), None, None, None, None, None
+        gx = _ScatterRegion.apply(g, ctx.hw[0], ctx.hw[1], ctx.group, ctx.R, ctx.C, ctx.region_of, ctx.comm)
+        return gx.to(ctx.x_dtype), None, None, None, None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: Any, R: int, C: int, region_of: Any, comm: Any) -> tuple:
+        xb = x if in_dims[0] is None else x.movedim(in_dims[0], 0)
+        return _FetchRegion.apply(xb, group, R, C, region_of, comm), (None if in_dims[0] is None else 0)
+
+
+class _ScatterRegion(torch.autograd.Function):
+    @staticmethod
+    def forward(g: torch.Tensor, h: int, w: int, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: Any) -> torch.Tensor:
+        return _scatter_add(g, h, w, group, R, C, region_of, comm)
+
+    @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: Any) -> None:
+        _, _, _, ctx.group, ctx.R, ctx.C, ctx.region_of, ctx.comm = inputs
+
+    @staticmethod
+    def backward(ctx: Any, gg: torch.Tensor) -> tuple:
+        return _FetchRegion.apply(gg, ctx.group, ctx.R, ctx.C, ctx.region_of, ctx.comm), None, None, None, None, None, None, None
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, g: torch.Tensor, h: int, w: int, group: Any, R: int, C: int, region_of: Any, comm: Any) -> tuple:
+        gb = g if in_dims[0] is None else g.movedim(in_dims[0], 0)
+        return _ScatterRegion.apply(gb, h, w, group, R, C, region_of, comm), (None if in_dims[0] is None else 0)
 
 
 def fetch_region(x: torch.Tensor, group: dist.ProcessGroup, R: int, C: int, region_of: Any, comm: CommOp | str = "auto") -> torch.Tensor:

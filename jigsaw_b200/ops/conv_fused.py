@@ -26,7 +26,6 @@ import ctypes
 from typing import Any
 
 import torch
-import torch.distributed as dist
 
 from . import _lib, symm
 

@@ -25,7 +25,6 @@ all-to-alls that move ``x`` blocks before them (jigsaw/_core/comm.py:430-455).
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Any
 
 import torch

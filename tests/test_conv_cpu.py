@@ -5,12 +5,11 @@ dilations, channel strategies and the transposed variants."""
 import pytest
 import torch
 
-from dist_utils import assert_close, merge, run_distributed, split
+from dist_utils import assert_close, run_distributed, split
 
 
 def _conv_case(mesh, nd, cin, cout, k, s, p, d, groups, transposed, channel_comm, size, seed):
     import jigsaw_b200 as jb
-    import torch.distributed as dist
 
     torch.manual_seed(seed)
     M = jb.modules

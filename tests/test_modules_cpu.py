@@ -5,7 +5,7 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from dist_utils import assert_close, merge, run_distributed, split
+from dist_utils import assert_close, run_distributed, split
 
 
 def _mesh_rc():
