@@ -136,10 +136,22 @@ def _axis_of(group: dist.ProcessGroup, mesh: Mapping[str, dist.ProcessGroup]) ->
 
 
 def _mesh_groups(mesh: Any) -> dict[str, dist.ProcessGroup]:
-    """Plain ``{axis: group}`` of the real axes of ``mesh`` (derived axes such as the flattened
-    model axis are not coordinates of a shard)."""
-    names = list(getattr(mesh, "axis_sizes", None) or mesh.keys())
-    return {n: mesh[n] for n in names}
+    """Plain ``{axis: group}`` of the real axes of ``mesh``.  Derived axes are not coordinates of a shard:
+    a ``ProcessMesh`` lists its real axes (``axis_sizes``); in a plain ``{name: group}`` mapping (which may
+    carry the flattened ``"model"`` group beside the axes it is made of) a group is derived when its
+    ranks contain all ranks of another non-trivial group, and a second name for the same ranks is dropped."""
+    sizes = getattr(mesh, "axis_sizes", None)
+    if sizes:
+        return {n: mesh[n] for n in sizes}
+    ranks = {n: frozenset(dist.get_process_group_ranks(g)) for n, g in mesh.items()}
+    real: dict[str, dist.ProcessGroup] = {}
+    for n in sorted(mesh, key=lambda name: name == "model"):      # the flattened group's name loses against an axis name
+        g = mesh[n]
+        derived = any(m != n and len(ranks[m]) > 1 and ranks[m] < ranks[n] for m in mesh)
+        repeated = any(ranks[m] == ranks[n] and len(ranks[n]) > 1 for m in real)
+        if not derived and not repeated:
+            real[n] = g
+    return real
 
 
 def _shard_file(coord: Mapping[str, int], stem: str = "shard") -> str:
@@ -152,6 +164,8 @@ def _describe(state: Mapping[str, torch.Tensor], layout: Layout, orders: dict, g
     entries: dict[str, dict] = {}
     for key, value in state.items():
         cuts = [(d, _axis_of(g, groups)) for d, g in layout[key]]
+        if len({a for _, a in cuts}) != len(cuts):
+            raise ValueError(f"{key}: a mesh axis cuts more than one dimension ({cuts}); such a layout cannot be stored")
         shape = list(value.shape)
         for d, axis in cuts:
             shape[d] *= groups[axis].size()

@@ -139,19 +139,11 @@ def flash_usable(q: torch.Tensor, k: torch.Tensor, dropout_p: float = 0.0) -> bo
 
 # ----------------------------------------------------------------------------- ring attention in one launch
 _HEADER = 256            # bytes of flag words in front of the staged tensors
-_rings: dict[tuple, list] = {}
 
 
 def _ring_block(ar: Any, tag: tuple, nbytes: int) -> Any:
-    """Two staging blocks per (shape, group), used alternately.  A rank stages its next payload only after
-    its previous attention kernel has finished, and that kernel needed every peer's flag of the same call;
-    so when a block is overwritten, the call that last used it (two calls ago) has completed on every rank."""
-    ring = _rings.get(tag)
-    if ring is None:
-        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
-    blk = ring[0][ring[1] & 1]
-    ring[1] += 1
-    return blk
+    """The next block of the two-deep staging ring ``tag`` (:meth:`symm.PeerArena.ring_block`)."""
+    return ar.ring_block(tag, nbytes)
 
 
 def _local_parts(blk: Any, P: int, base: int, slot: int, inner: int) -> Any:

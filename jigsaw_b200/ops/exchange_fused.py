@@ -17,17 +17,12 @@ import torch.distributed as dist
 from . import _lib, symm
 
 _HEADER = 256
-_rings: dict[tuple, list] = {}
 _side_streams: dict[int, "torch.cuda.Stream"] = {}
 
 
 def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
-    ring = _rings.get(tag)
-    if ring is None:
-        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
-    blk = ring[0][ring[1] & 1]
-    ring[1] += 1
-    return blk
+    """The next block of the two-deep staging ring ``tag`` (:meth:`symm.PeerArena.ring_block`)."""
+    return ar.ring_block(tag, nbytes)
 
 
 @_lib.traced("jb.maybe_fused_all_to_all")

@@ -167,20 +167,11 @@ def maybe_fused_matmul(a: torch.Tensor, b: torch.Tensor, a_t: bool = False, b_t:
 
 # ----------------------------------------------------------------------------- all-gather -> GEMM
 _HEADER = 256          # bytes of flag words in front of the staged block
-_rings: dict[tuple, list] = {}
 
 
 def _staging_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
-    """Two blocks per shape and group (the tag carries the group's ranks, so operations over different
-    groups never alternate on one ring), used alternately: a rank can run at most one gathered layer ahead of
-    its peers (it needs their flag of the current layer, which they publish after their previous
-    GEMM), so the block it overwrites is never one that a peer may still be reading."""
-    ring = _rings.get(tag)
-    if ring is None:
-        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
-    blk = ring[0][ring[1] & 1]
-    ring[1] += 1
-    return blk
+    """The next block of the two-deep staging ring ``tag`` (:meth:`symm.PeerArena.ring_block`)."""
+    return ar.ring_block(tag, nbytes)
 
 
 def scatter_gemm_launcher(L: Any) -> Any:

@@ -19,18 +19,11 @@ import torch.distributed as dist
 from . import _lib, symm
 
 _HEADER = 256
-_rings: dict[tuple, list] = {}
 
 
 def _ring_block(ar: "symm.PeerArena", tag: tuple, nbytes: int) -> "symm.Block":
-    """Two output blocks per shape, used alternately (a rank is at most one roll ahead of its
-    neighbours, so it never stores into a block that a neighbour is still copying out of)."""
-    ring = _rings.get(tag)
-    if ring is None:
-        ring = _rings[tag] = [[ar.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
-    blk = ring[0][ring[1] & 1]
-    ring[1] += 1
-    return blk
+    """The next block of the two-deep staging ring ``tag`` (:meth:`symm.PeerArena.ring_block`)."""
+    return ar.ring_block(tag, nbytes)
 
 
 def _axis(group: Any, shift: int, n: int) -> tuple[int, int, list[int], int]:

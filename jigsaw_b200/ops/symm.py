@@ -85,6 +85,8 @@ class PeerArena:
         self._capture_stride: int | None = None
         self._capture_slots: set[int] = set()
         self._capture_blocks: list[Block] = []
+        self._rings: dict[tuple, list] = {}
+        self._ring_uses: dict[tuple, int] = {}
         self._flags = None
         if self.symmetric:
             self._flags = self._new_symmetric(_MAX_SLOTS * _FLAG_WORDS * 4)
@@ -250,6 +252,28 @@ class PeerArena:
     @property
     def capture_stride(self) -> int | None:
         return self._capture_stride
+
+    def ring_block(self, tag: tuple, nbytes: int) -> Block:
+        """Two staging blocks per ``tag`` (geometry and ranks of the operation's group, so operations over
+        different groups never share a ring), used alternately.  A rank can run at most one such operation
+        ahead of its peers (it needs their flag of the current one, which they raise after finishing the
+        previous one), so the block it overwrites is never one that a peer may still be reading."""
+        ring = self._rings.get(tag)
+        if ring is None:
+            ring = self._rings[tag] = [[self.alloc(nbytes, tag=tag + (i,)) for i in range(2)], 0]
+        blk = ring[0][ring[1] & 1]
+        ring[1] += 1
+        self._ring_uses[tag] = self._ring_uses.get(tag, 0) + 1
+        return blk
+
+    def start_ring_count(self) -> None:
+        self._ring_uses = {}
+
+    def some_ring_used_an_odd_number_of_times(self) -> bool:
+        """Since :meth:`start_ring_count`.  A step that does so, replayed as a CUDA graph, ends and begins on
+        the SAME block of that ring, and the alternation argument of :meth:`ring_block` no longer separates
+        the last use of one replay from the first use of the next."""
+        return any(n & 1 for n in self._ring_uses.values())
 
     def flag_ptr(self, world_rank: int, slot: int, direction: int) -> int:
         return self._flags["ptrs"][world_rank] + (slot * _FLAG_WORDS + direction) * 4

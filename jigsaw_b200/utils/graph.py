@@ -12,6 +12,9 @@ as one graph removes that.  Two things make a captured step different from an ea
   launch captured with epoch ``e`` uses ``e + replays * EPOCH_STRIDE``.  The host-side epoch
   bookkeeping advances by the same stride per replay, so eager launches may follow replays
   (up to ``EPOCH_STRIDE`` productions of one buffer slot between two replays).
+* Staging blocks that peers write into are used in rings of two; a step that uses such a ring an odd number
+  of times would end and begin on the same block, so the capture then appends a one-element all-reduce
+  over all ranks that separates consecutive replays.
 
 The optimizer must be capturable (``jigsaw_b200.optim.FusedAdam``, or ``torch.optim.Adam(...,
 capturable=True)``; ``fused=True`` is fine).  A learning rate given as a float is frozen into the
@@ -50,8 +53,12 @@ class GraphedStep:
             for _ in range(max(warmup, 1)):
                 step_fn(*self.inputs)
             launches = _lib.LAUNCHES
+            self._arena.start_ring_count()
             step_fn(*self.inputs)
             self.launches_per_step = _lib.LAUNCHES - launches    # kernels of this package per replay
+            fenced = self._arena.some_ring_used_an_odd_number_of_times()
+            if fenced:
+                self._fence(device)                              # its staging block comes into being outside the capture
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self._graph = torch.cuda.CUDAGraph()
@@ -61,11 +68,31 @@ class GraphedStep:
             with torch.cuda.graph(self._graph):
                 self._arena.replay.add_(1)
                 self.outputs = step_fn(*self.inputs)
+                if fenced:
+                    self._fence(device)
         finally:
             self._slots = self._arena.end_capture()
         # Capturing advanced the host epochs of the produced slots without running anything;
         # replay n (counter = n) publishes captured + n * stride, which is what the host holds
         # after n calls of advance().
+
+    @staticmethod
+    def _fence(device: torch.device) -> None:
+        """A one-element sum over all ranks at the end of the captured step: a rank leaves it only after every
+        rank has entered it, i.e. after every rank's kernels of this replay are complete in stream order, so
+        the first operation of the next replay may overwrite a staging block the last one of this replay used."""
+        import torch.distributed as dist
+
+        if not dist.is_initialized() or dist.get_world_size() < 2:
+            return
+        from ..ops import reduce_fused
+
+        token = torch.zeros(4, dtype=torch.float32, device=device)
+        ranks = list(range(dist.get_world_size()))
+        if reduce_fused.usable([token], ranks):
+            reduce_fused._launch([token], ranks, 1.0, "fence")
+        else:
+            dist.all_reduce(token)
 
     def close(self) -> None:
         """Destroy the graph.  Call this before ``dist.destroy_process_group()``: a live graph

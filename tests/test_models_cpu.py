@@ -175,6 +175,33 @@ def test_sharded_checkpoint_across_meshes(tmp_path):
     run_distributed(_worker_checkpoint, 4, str(tmp_path))
 
 
+def _worker_checkpoint_plain_dict(rank, world, tmp):
+    """A plain ``{name: group}`` mapping that also carries the flattened model group (the form the
+    reference's ``process_mesh_dict`` has) names the same shards as the mesh object."""
+    import os
+
+    import jigsaw_b200 as jb
+    from jigsaw_b200 import checkpoint
+    from jigsaw_b200.models import ViT, ViTConfig
+
+    cfg = ViTConfig(image_size=(16, 32), depth=1, attn_backend="math")
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    jb.launch.set_all_seeds(40 + rank)
+    model = ViT(mesh, "cpu", cfg)
+    plain = {"model": mesh["model"], "row": mesh["row"], "col": mesh["col"]}
+    assert list(checkpoint._mesh_groups(plain)) == ["row", "col"]
+    checkpoint.save_sharded(model, plain, tmp)
+    assert sorted(f for f in os.listdir(tmp) if f.endswith(".pt")) == [f"shard-col{c}-row{r}.pt" for c in (0, 1) for r in (0, 1)]
+    other = ViT(mesh, "cpu", cfg)
+    checkpoint.load_sharded(other, plain, tmp)
+    for (k, a), b in zip(model.state_dict().items(), other.state_dict().values()):
+        assert_close(b, a, f"plain-dict checkpoint: {k}", 0, 0)
+
+
+def test_sharded_checkpoint_with_a_plain_group_dict(tmp_path):
+    run_distributed(_worker_checkpoint_plain_dict, 4, str(tmp_path))
+
+
 def _worker_reshard_hops(rank, world):
     """The layers of a ViT (patch convolution, layer norms, attention, block linears) carried
     2x2 -> 1x4 -> 4x1 -> 2x2 with ``reshard_parameters``: after every hop the gathered state equals the

@@ -302,6 +302,89 @@ def test_graphed_step_four_gpus():
     run_distributed(_worker_graphed_step, 4, (2, 2), backend="nccl", timeout=300)
 
 
+def _worker_graphed_vit(rank, world, mesh_shape, depth):
+    """A transformer step (patch embedding, LayerNorm, gathered linear layers, ring attention, cross-entropy
+    over sharded classes, replica gradient sums, fused Adam) replayed as a CUDA graph follows the eager run:
+    the copy-engine pushes, their flags and every in-kernel exchange take their epochs from the replay counter."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.models import ViT, ViTConfig
+    from jigsaw_b200.ops import _lib, symm
+    from jigsaw_b200.optim import FusedAdam
+    from jigsaw_b200.utils import GraphedStep
+
+    dev = torch.device("cuda", rank)
+    R, C = mesh_shape
+    mesh = jb.make_process_mesh({"row": R, "col": C})
+    row, col = mesh["row"], mesh["col"]
+    # 128 tokens per row rank, one 64-wide head per column rank; 10 classes per column rank keep the tiny
+    # classification head (8 rows) on the torch path
+    cfg = ViTConfig(image_size=(64, 256), in_channels=4, patch=8, dim=128, heads=2, depth=depth, num_classes=20)
+    loss_fn = jb.modules.DistributedCrossEntropyLoss(col, (row,))
+    g = torch.Generator().manual_seed(11)
+    xs, ys = [], []
+    for _ in range(4):
+        x = torch.randn(8, 4, 64, 256, generator=g)
+        x = x[:, col.rank() * 4 // C:(col.rank() + 1) * 4 // C, :, row.rank() * 256 // R:(row.rank() + 1) * 256 // R]
+        xs.append(x.contiguous().to(dev))
+        ys.append(torch.randint(0, 20, (8,), generator=g).to(dev))
+
+    def make():
+        torch.manual_seed(3 + mesh["model"].rank())
+        m = ViT(mesh, dev, cfg)
+        o = FusedAdam(m.parameters(), lr=1e-3)
+
+        def step(x, y):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = m(x)
+            loss = loss_fn(out.float(), y)
+            o.zero_grad(set_to_none=True)
+            loss.backward()
+            o.step()
+            return loss
+
+        return m, step
+
+    side = torch.cuda.Stream(dev)
+    order = [0, 0, 0, 0, 1, 2, 3, 1]
+    m1, eager = make()
+    with torch.cuda.stream(side):
+        ref = [float(eager(xs[i], ys[i])) for i in order]
+    m2, step2 = make()
+    xi, yi = xs[0].clone(), ys[0].clone()
+    before = _lib.dispatch_counts()
+    graphed = GraphedStep(step2, (xi, yi), warmup=3)
+    counts = _lib.dispatch_counts()
+    for name in (("ring_attention",) if R > 1 else ()) + (("gather_linear",) if C > 1 else ()) + ("layer_norm",):
+        assert counts.get(name, {}).get("fused", 0) > before.get(name, {}).get("fused", 0), (name, counts)
+    got = []
+    for i in order[4:]:
+        xi.copy_(xs[i])
+        yi.copy_(ys[i])
+        got.append(float(graphed.replay()))
+    torch.cuda.synchronize()
+    symm.arena(dev).check_status()
+    for a, b in zip(got, ref[4:]):
+        assert abs(a - b) <= 2e-3 * abs(b), (got, ref[4:])
+    for (n, p), q in zip(m1.named_parameters(), m2.parameters()):
+        assert_close(q, p, f"graphed ViT: {n}", 2e-2, 2e-2)
+    graphed.close()
+
+
+@pytest.mark.multigpu(2)
+def test_graphed_vit_step_ring_two_gpus():
+    run_distributed(_worker_graphed_vit, 2, (2, 1), 2, backend="nccl", timeout=300)
+
+
+@pytest.mark.multigpu(2)
+def test_graphed_vit_step_gathered_linear_two_gpus():
+    # depth 1 uses the staging ring of the gathered layers an odd number of times per step: the capture
+    # then ends with the fence that separates consecutive replays
+    run_distributed(_worker_graphed_vit, 2, (1, 2), 1, backend="nccl", timeout=300)
+
+
 def _worker_layer_norm(rank, world):
     """LayerNorm over a feature dimension cut over two GPUs: the fused kernels (statistics
     exchanged through peer memory) against the undivided torch op, twice in a row and in both
