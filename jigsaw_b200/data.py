@@ -65,24 +65,48 @@ def replica_sampler(dataset: Dataset, mesh: Mapping[str, dist.ProcessGroup], dp_
 
 
 class DevicePrefetcher:
-    """Iterate ``loader`` one batch ahead: host batch -> pinned staging buffers -> device copy on
+    """Iterate ``loader`` ``depth - 1`` batches ahead: host batch -> pinned staging buffers -> device copy on
     a side stream.  Yields tuples of device tensors that are safe to use on the current stream.
-    On a CPU device it just forwards the batches."""
+    On a CPU device it just forwards the batches.
 
-    def __init__(self, loader: Iterable, device: torch.device | str, depth: int = 2) -> None:
+    ``reuse_buffers=True`` copies into a fixed ring of ``depth + 1`` device buffers per tensor instead of
+    allocating fresh device tensors per batch: no allocator traffic in the loop (large batches otherwise
+    make the caching allocator grow, which synchronises the device).  A yielded tensor is then valid until
+    ``depth`` further batches have been drawn; clone what must live longer."""
+
+    def __init__(self, loader: Iterable, device: torch.device | str, depth: int = 2, reuse_buffers: bool = False) -> None:
         self.loader, self.device, self.depth = loader, torch.device(device), max(1, depth)
+        self.reuse_buffers = reuse_buffers
         self.bytes_copied = 0
         self._pinned: list[list[torch.Tensor]] = []
+        self._device: list[list[torch.Tensor]] = []
+        self._consumed: list["torch.cuda.Event | None"] = []
         self._stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
 
-    def _stage(self, slot: int, batch) -> tuple[tuple[torch.Tensor, ...], "torch.cuda.Event | None"]:
+    def _to_device(self, slot: int, j: int, src: torch.Tensor) -> torch.Tensor:
+        """Device copy of the pinned tensor ``src`` (on the side stream, which is current)."""
+        if not self.reuse_buffers:
+            return src.to(self.device, non_blocking=True)
+        ring = self._device[slot]
+        while len(ring) <= j:
+            ring.append(None)
+        if ring[j] is None or ring[j].shape != src.shape or ring[j].dtype != src.dtype:
+            ring[j] = torch.empty(src.shape, dtype=src.dtype, device=self.device)
+        ring[j].copy_(src, non_blocking=True)
+        return ring[j]
+
+    def _stage(self, slot: int, batch) -> tuple[tuple[torch.Tensor, ...], "torch.cuda.Event | None", int]:
         tensors = tuple(batch) if isinstance(batch, (tuple, list)) else (batch,)
         if self._stream is None:
-            return tuple(t if not torch.is_tensor(t) else t.to(self.device) for t in tensors), None
+            return tuple(t if not torch.is_tensor(t) else t.to(self.device) for t in tensors), None, slot
         while len(self._pinned) <= slot:
             self._pinned.append([])
+            self._device.append([])
+            self._consumed.append(None)
         stage = self._pinned[slot]
         out = []
+        if self.reuse_buffers and self._consumed[slot] is not None:
+            self._stream.wait_event(self._consumed[slot])   # the consumer's work on this slot's previous batch
         with torch.cuda.stream(self._stream):
             for j, t in enumerate(tensors):
                 if not torch.is_tensor(t):
@@ -91,18 +115,18 @@ class DevicePrefetcher:
                 if t.is_pinned():                      # already page-locked: copy straight from it
                     while len(stage) <= j:
                         stage.append(t)
-                    out.append(t.to(self.device, non_blocking=True))
+                    out.append(self._to_device(slot, j, t))
                     self.bytes_copied += t.numel() * t.element_size()
                     continue
                 if j >= len(stage) or stage[j].shape != t.shape or stage[j].dtype != t.dtype:
                     buf = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                     stage[j:j + 1] = [buf]
                 stage[j].copy_(t)
-                out.append(stage[j].to(self.device, non_blocking=True))
+                out.append(self._to_device(slot, j, stage[j]))
                 self.bytes_copied += t.numel() * t.element_size()
             ready = torch.cuda.Event()
             ready.record(self._stream)
-        return tuple(out), ready
+        return tuple(out), ready, slot
 
     def __iter__(self) -> Iterator[tuple[torch.Tensor, ...]]:
         queue: list = []
@@ -111,15 +135,23 @@ class DevicePrefetcher:
             queue.append(self._stage(slot % (self.depth + 1), batch))
             slot += 1
             if len(queue) > self.depth - 1:
-                yield self._release(queue.pop(0))
+                yield from self._hand_out(queue.pop(0))
         while queue:
-            yield self._release(queue.pop(0))
+            yield from self._hand_out(queue.pop(0))
 
-    def _release(self, item) -> tuple[torch.Tensor, ...]:
-        tensors, ready = item
-        if ready is not None:
-            torch.cuda.current_stream(self.device).wait_event(ready)
+    def _hand_out(self, item) -> Iterator[tuple[torch.Tensor, ...]]:
+        tensors, ready, slot = item
+        if ready is None:
+            yield tensors
+            return
+        current = torch.cuda.current_stream(self.device)
+        current.wait_event(ready)
+        if not self.reuse_buffers:
             for t in tensors:
                 if torch.is_tensor(t):
-                    t.record_stream(torch.cuda.current_stream(self.device))
-        return tensors
+                    t.record_stream(current)
+        yield tensors
+        if self.reuse_buffers:      # back from the consumer: everything it did with this batch is queued by now
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(self.device))
+            self._consumed[slot] = done
