@@ -163,7 +163,7 @@ def distributed_cross_entropy(
 ) -> torch.Tensor:
     """``F.cross_entropy`` on logits whose class dimension ``dim`` is split over
     ``channel_group``.  Targets are class indices (supports ``weight``, ``ignore_index``,
-    ``label_smoothing`` but not smoothing together with weight) or class probabilities
+    ``label_smoothing``, also together, with torch's rule for the combination) or class probabilities
     sharded like the logits (none of the three options)."""
     _check_reduction(reduction)
     dim = dim % input.dim()
@@ -190,16 +190,24 @@ def distributed_cross_entropy(
                 return elem.to(in_dtype)
             count = torch.full((), float(elem.numel()), device=elem.device)
             return reduce_scalar_loss(elem.sum(), count, reduction, reduce_groups).to(in_dtype)
-        if label_smoothing != 0.0 and weight is not None:
-            raise NotImplementedError("label_smoothing together with weight is not supported")
         picked, valid = _pick_target(logp, target, dim, channel_group, ignore_index)
         if label_smoothing != 0.0:
-            c_global = logp.shape[dim] * _gsize(channel_group)
-            smooth = logp.sum(dim=dim) * (label_smoothing / c_global)
+            c_local = logp.shape[dim]
+            c_global = c_local * _gsize(channel_group)
+            if weight is not None:           # torch's rule: both terms carry the class weights, the mean divides by sum w[y]
+                wg = weight.to(logp.dtype)
+                wt = torch.where(valid, wg[torch.where(valid, target, torch.zeros_like(target))], torch.zeros((), dtype=logp.dtype, device=logp.device))
+                shape = [1] * logp.dim()
+                shape[dim] = c_local
+                w_local = wg[_grank(channel_group) * c_local:(_grank(channel_group) + 1) * c_local].view(shape)
+                smooth = (logp * w_local).sum(dim=dim) * (label_smoothing / c_global)
+                picked = picked * wt
+            else:
+                wt = valid.to(logp.dtype)
+                smooth = logp.sum(dim=dim) * (label_smoothing / c_global)
             both = redundant_all_reduce(torch.stack((picked, smooth)), channel_group)
             elem = -((1.0 - label_smoothing) * both[0] + both[1])
             elem = torch.where(valid, elem, torch.zeros_like(elem))
-            wt = valid.to(logp.dtype)
         else:
             picked = redundant_all_reduce(picked, channel_group)
             if weight is not None:
