@@ -80,5 +80,5 @@ def global_shape(local_shape: Sequence[int], placement: Sequence[Shard]) -> tupl
 def check_divisible(value: int, parts: int, what: str) -> int:
     """Return ``value // parts`` or raise ``ValueError`` naming ``what``."""
     if parts < 1 or value % parts != 0:
-        raise ValueError(f"{what} ({value}) must be divisible by the group size ({parts})")
+        raise ValueError(f"{what}={value} must be divisible by the group size {parts}")
     return value // parts

@@ -96,8 +96,9 @@ class DistributedLinear(torch.nn.Module):
                 "model_group must span row_group x col_group or equal col_group"
             )
         check_divisible(self.in_dim, C, "in_dim")
-        check_divisible(self.out_dim, C, "out_dim")
         check_divisible(self.out_dim, row_split, "out_dim")
+        if self.out_dim % C:
+            raise ValueError(f"out_dim={self.out_dim} must be divisible by the column group size {C}, which shards the bias and the output columns")
         self.model_group, self.row_group, self.col_group = model_group, row_group, col_group
         self.col_split, self.row_split = C, row_split
         self.weight_replicated_over_rows = row_split == 1

@@ -64,8 +64,8 @@ class DistributedGroupNorm(torch.nn.Module):
         G = 1 if self.channel_group is None else self.channel_group.size()
         if self.num_groups % G or self.num_channels % G:
             raise ValueError(
-                f"num_groups ({self.num_groups}) and num_channels ({self.num_channels}) must be divisible by the "
-                f"channel group size ({G}) so that no normalization group straddles two shards"
+                f"num_groups={self.num_groups} and num_channels={self.num_channels} must be divisible by the "
+                f"channel group size {G} so that no normalization group straddles two shards"
             )
         self.local_groups = self.num_groups // G
         self.local_channels = self.num_channels // G
