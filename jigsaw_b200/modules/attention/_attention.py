@@ -403,6 +403,6 @@ class DistributedAttention(torch.nn.Module):
         return (
             f"in_dim={self.in_dim}, embed_dim={self.embed_dim}, out_dim={self.out_dim}, "
             f"heads={self.heads * self.channel_group.size()}, dropout_p={self.dropout_p}, qk_norm={self.qk_norm}, "
-            f"ring={self.ring}, ulysses={self.ulysses}, "
+            f"ring={self.ring}, " + ("ulysses=True, " if self.ulysses else "")
             + shard_repr(spatial=self.spatial_group, channel=self.channel_group)
         )

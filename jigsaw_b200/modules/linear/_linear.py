@@ -255,7 +255,7 @@ class _DistributedMatMul(torch.nn.Module):
         return 0
 
     def extra_repr(self) -> str:
-        return shard_repr(row=self.grid[0], col=self.grid[1])
+        return shard_repr(model=self.model_group)
 
 
 class DistributedMatMulXWT(_DistributedMatMul):

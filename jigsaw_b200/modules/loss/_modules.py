@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import torch
 
+from ..._core.shard_repr import shard_repr
 from . import _functional as LF
 
 
@@ -15,15 +16,11 @@ class _Loss(torch.nn.Module):
     def get_parameter_count(self) -> int:
         return 0
 
-    def _repr_groups(self) -> str:
-        sizes = tuple(1 if g is None else g.size() for g in LF._groups(getattr(self, "reduce_groups", None)))
-        s = f"reduction={self.reduction!r}, reduce={sizes}"
-        if hasattr(self, "channel_group"):
-            s += f", channel={LF._gsize(self.channel_group)}"
-        return s
-
     def extra_repr(self) -> str:
-        return self._repr_groups()
+        """Size of the class-sharding group (classification losses only), then of the reduction groups (one size
+        per group if a sequence was given)."""
+        fields = {"channel": self.channel_group} if hasattr(self, "channel_group") else {}
+        return shard_repr(**fields, reduce_groups=getattr(self, "reduce_groups", None))
 
 
 class DistributedNLLLoss(_Loss):

@@ -157,6 +157,8 @@ class DistributedGroupNorm(torch.nn.Module):
         return self.num_channels * (2 if self.bias is not None else 1)
 
     def extra_repr(self) -> str:
-        return f"{self.num_groups}, {self.num_channels}, eps={self.eps}, affine={self.affine}, " + shard_repr(
-            spatial=self.spatial_groups, channel=self.channel_group
-        )
+        tiles = 1
+        for g in self.spatial_groups:
+            tiles *= 1 if g is None else g.size()
+        return (f"{self.num_groups}, {self.num_channels}, eps={self.eps}, affine={self.affine}, bias={self.bias is not None}, "
+                + shard_repr(spatial=tiles, channel=self.channel_group))
