@@ -113,6 +113,21 @@ class PeerArena:
         self._segments.append(seg)
         return len(self._segments) - 1
 
+    def reserve(self, nbytes: int) -> None:
+        """Make sure a segment with ``nbytes`` of free room exists (collective over the world, like every growth
+        of the arena: mapping a segment into the peers is a rendezvous).  Growth happens when a request finds
+        no room, which is the same moment on every rank as long as all ranks issue the same sequence of
+        requests; a program whose ranks may diverge (data-dependent shapes, ranks that skip a layer) should
+        reserve its peak here, at a point all ranks pass, so that no later request has to grow."""
+        size = _round_up(nbytes, _ALIGN)
+        if any(seg["size"] - seg["used"] >= size for seg in self._segments):
+            return
+        i = self._new_segment(size)
+        self._segments[i]["tensor"].zero_()
+        if self.symmetric:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()
+
     def peer_base(self, segment: int, world_rank: int) -> int:
         ptrs = self._segments[segment]["ptrs"]
         return ptrs[world_rank if self.symmetric else 0]
@@ -122,7 +137,8 @@ class PeerArena:
         """A block of at least ``nbytes`` (1 KiB aligned).  A recycled block is only handed to a
         request with the same ``tag`` (callers tag padded buffers with their geometry, so the
         never-written zero border of a recycled buffer is still in the right place) and keeps
-        its contents unless ``zero``; fresh segments come zero-filled."""
+        its contents unless ``zero``; fresh segments come zero-filled.  A request that finds no room grows the
+        arena, which is collective (see :meth:`reserve`); every other request is local."""
         size = _round_up(nbytes, _ALIGN)
         pool = self._free.get((size, tag))
         if pool:
