@@ -11,6 +11,13 @@
 #   JB_BINDS      comma-separated bind mounts
 #   JB_VENV       virtual environment to activate
 #   JB_MODULES    modules to load first
+#   JB_PYTHON     interpreter that replaces a bare "python" / "python3" when no venv is set
+#   JB_ENV_FILE   extra --env-file handed to the container runtime
+#   JB_PASS_ENV   space-separated names of further variables to force into the container
+#
+# Options (before the command):
+#   --local N     no scheduler: start N ranks on this node with torchrun
+#   --dry-run     print the resolved environment and the command line instead of running it
 #
 # What jigsaw_b200.launch needs: SLURM_PROCID / SLURM_NTASKS / SLURM_LOCALID (srun) or RANK /
 # WORLD_SIZE / LOCAL_RANK (torchrun), and MASTER_ADDR / MASTER_PORT.  Under SLURM the two MASTER_
@@ -20,11 +27,19 @@ here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 root="$(dirname "$here")"
 
 local_ranks=0
-if [[ "${1:-}" == "--local" ]]; then
-    local_ranks="$2"; shift 2
-fi
+dry_run=0
+while [[ $# -gt 0 ]]; do
+    case "$1" in
+        --local)
+            if [[ ! "${2:-}" =~ ^[1-9][0-9]*$ ]]; then echo "run.sh: --local needs a positive rank count" >&2; exit 2; fi
+            local_ranks="$2"; shift 2 ;;
+        --dry-run) dry_run=1; shift ;;
+        --) shift; break ;;
+        *) break ;;
+    esac
+done
 if [[ $# -eq 0 ]]; then
-    echo "usage: run.sh [--local N] <command ...>" >&2; exit 2
+    echo "usage: run.sh [--local N] [--dry-run] <command ...>" >&2; exit 2
 fi
 
 site_file="${JB_SITE_FILE:-}"
@@ -59,12 +74,36 @@ if [[ "$local_ranks" -gt 0 ]]; then
     if [[ "$1" != "python" ]]; then echo "run.sh: --local expects 'python <script> ...'" >&2; exit 2; fi
 fi
 if [[ -n "${JB_VENV:-}" ]]; then
-    # shellcheck disable=SC1091
-    source "$JB_VENV/bin/activate"
+    if [[ ! -r "$JB_VENV/bin/activate" ]]; then echo "run.sh: JB_VENV=$JB_VENV has no bin/activate" >&2; exit 1; fi
+    if [[ "$dry_run" -eq 0 ]]; then
+        # shellcheck disable=SC1091
+        source "$JB_VENV/bin/activate"
+    fi
+elif [[ -n "${JB_PYTHON:-}" && ( "${cmd[0]}" == "python" || "${cmd[0]}" == "python3" ) ]]; then
+    cmd[0]="$JB_PYTHON"
 fi
 if [[ -n "${JB_SIF:-}" ]]; then
-    binds=()
-    if [[ -n "${JB_BINDS:-}" ]]; then binds=(--bind "$JB_BINDS"); fi
-    exec "${JB_RUNTIME:-apptainer}" exec --nv "${binds[@]}" --bind "$root" "$JB_SIF" "${cmd[@]}"
+    if [[ "$dry_run" -eq 0 && ! -r "$JB_SIF" ]]; then echo "run.sh: container image $JB_SIF is not readable" >&2; exit 1; fi
+    runtime="${JB_RUNTIME:-apptainer}"
+    if [[ "$dry_run" -eq 0 ]] && ! command -v "$runtime" >/dev/null 2>&1; then
+        echo "run.sh: container runtime '$runtime' not found (set JB_RUNTIME, or unset JB_SIF to run on the host)" >&2; exit 1
+    fi
+    binds=(--bind "$root")
+    IFS=',' read -r -a extra_binds <<< "${JB_BINDS:-}"
+    for b in "${extra_binds[@]}"; do [[ -n "$b" ]] && binds+=(--bind "$b"); done
+    env_file=()
+    [[ -n "${JB_ENV_FILE:-}" ]] && env_file=(--env-file "$JB_ENV_FILE")
+    # images may bake their own values into %environment, which beat plain passthrough: force ours with --env
+    forced=()
+    for v in MASTER_ADDR MASTER_PORT NCCL_NVLS_ENABLE TORCH_NCCL_ASYNC_ERROR_HANDLING CUDA_DEVICE_MAX_CONNECTIONS \
+             NCCL_DEBUG JIGSAW_STRICT_FUSED JIGSAW_LOG_LEVEL JIGSAW_LOG_DIR JIGSAW_LOG_FORMAT ${JB_PASS_ENV:-}; do
+        [[ -n "${!v:-}" ]] && forced+=(--env "$v=${!v}")
+    done
+    cmd=("$runtime" exec --nv "${binds[@]}" "${env_file[@]}" "${forced[@]}" --env "PYTHONPATH=$PYTHONPATH" "$JB_SIF" "${cmd[@]}")
+fi
+if [[ "$dry_run" -eq 1 ]]; then
+    for v in MASTER_ADDR MASTER_PORT NCCL_NVLS_ENABLE CUDA_DEVICE_MAX_CONNECTIONS PYTHONPATH; do echo "$v=${!v:-}"; done
+    printf 'exec:'; printf ' %q' "${cmd[@]}"; printf '\n'
+    exit 0
 fi
 exec "${cmd[@]}"
