@@ -192,6 +192,7 @@ def test_configuration_is_idempotent_reads_the_environment_and_writes_rank_files
 
 
 def test_warnings_are_routed_through_the_logger(captured):
+    logging.captureWarnings(False)          # an earlier configuration in this process may have left the hook half-installed
     log.configure_logging("DEBUG", as_json=True, install_excepthook=False, enable_faulthandler=False, capture_warnings=True, force=True)
     stream = io.StringIO()
     log.get_logger().handlers[0].stream = stream
