@@ -97,7 +97,8 @@ class ClockSampler:
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
             except ValueError:
                 continue
             for name, val in zip(names, f[5:9]):

@@ -384,7 +384,7 @@ def _fill(own: Mapping[str, torch.Tensor], tensors: Mapping[str, dict], layout: 
                     raise ValueError(f"{key}: dimension {d} of size {shape[d]} does not split {g.size()} ways")
                 n = shape[d] // g.size()
                 lo[d], hi[d] = g.rank() * n, (g.rank() + 1) * n
-            if [h - l for l, h in zip(lo, hi)] != list(target.shape):
+            if [h - low for low, h in zip(lo, hi)] != list(target.shape):
                 raise ValueError(f"{key}: global shape {shape} gives a block that does not fit the local {tuple(target.shape)}")
             # source blocks that overlap it
             src_cut = {axis: d for d, axis in entry["cuts"]}

@@ -44,10 +44,10 @@ def chunk_owner(send_op: SendOp, p: int, s: int, P: int, A: int) -> int:
     if P % A:
         raise ValueError(f"ring size {P} is not divisible by intra_size {A}")
     n = P // A
-    g, l = divmod(p, A)
+    g, local = divmod(p, A)
     og = (g + s // A) % n
     if send_op is SendOp.HYBRID:
-        return og * A + (l + s % A) % A
+        return og * A + (local + s % A) % A
     return og * A + s % A
 
 

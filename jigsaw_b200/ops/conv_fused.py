@@ -361,9 +361,9 @@ def _run_lazy_chain(source: torch.Tensor, layers: tuple, acts: tuple) -> torch.T
     kernel, because the chain's last epilogue writes the dense output without one."""
     from .. import parallel
 
-    kinds = chain_kinds([(l.in_channels, l.out_channels) for l in layers])
+    kinds = chain_kinds([(m.in_channels, m.out_channels) for m in layers])
     geom = geometry_for(source, *layers[0].spatial_groups)
-    raw = [t for l in layers for t in (l.weight, l.bias)]
+    raw = [t for m in layers for t in (m.weight, m.bias)]
     inner = list(acts[:-1]) + [False]
     ranks = parallel.overlapped_sum_plan(raw)
     if ranks is not None:
@@ -386,7 +386,7 @@ def lazy_conv2d(layer: Any, x: torch.Tensor) -> tuple[Any, torch.Tensor]:
     if isinstance(x, LazyConvChain) and x.pending:
         prev = x
         same_place = layer.spatial_groups == prev.layers[0].spatial_groups and prev.grad_mode == grad_mode
-        channels = [(l.in_channels, l.out_channels) for l in prev.layers] + [(layer.in_channels, layer.out_channels)]
+        channels = [(m.in_channels, m.out_channels) for m in prev.layers] + [(layer.in_channels, layer.out_channels)]
         if same_place and layer_is_eligible(layer, x) and chain_kinds(channels) is not None:
             shape = (x.shape[0], layer.out_channels, x.shape[2], x.shape[3])
             return prev.extended(layer, act, shape), x

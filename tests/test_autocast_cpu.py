@@ -11,7 +11,6 @@ Reference behaviours covered: tests/test_autocast.py:89-133 (linear), :135-260 (
 
 import contextlib
 
-import pytest
 import torch
 
 from dist_utils import assert_close, run_distributed

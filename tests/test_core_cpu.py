@@ -64,11 +64,15 @@ def test_launch_env_resolution(monkeypatch):
     assert (env.source, env.rank, env.world_size, env.master_addr, env.master_port) == ("single", 0, 1, "localhost", "29500")
     with pytest.raises(RuntimeError):
         launch.resolve_launch_env(strict=True)
-    monkeypatch.setenv("RANK", "3"); monkeypatch.setenv("WORLD_SIZE", "8"); monkeypatch.setenv("LOCAL_RANK", "1")
+    monkeypatch.setenv("RANK", "3")
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    monkeypatch.setenv("LOCAL_RANK", "1")
     monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
     env = launch.resolve_launch_env()
     assert (env.source, env.rank, env.world_size, env.local_rank, env.master_addr) == ("torchrun", 3, 8, 1, "127.0.0.1")
-    monkeypatch.setenv("SLURM_PROCID", "5"); monkeypatch.setenv("SLURM_NTASKS", "16"); monkeypatch.setenv("SLURM_LOCALID", "2")
+    monkeypatch.setenv("SLURM_PROCID", "5")
+    monkeypatch.setenv("SLURM_NTASKS", "16")
+    monkeypatch.setenv("SLURM_LOCALID", "2")
     env = launch.resolve_launch_env()      # SLURM wins over torchrun
     assert (env.source, env.rank, env.world_size, env.local_rank) == ("slurm", 5, 16, 2)
     launch.set_all_seeds(7)
@@ -82,7 +86,8 @@ def test_launch_env_resolution(monkeypatch):
 def test_logging_rank_filter_json_and_once(tmp_path, monkeypatch):
     from jigsaw_b200 import log
 
-    monkeypatch.setenv("RANK", "2"); monkeypatch.setenv("WORLD_SIZE", "4")
+    monkeypatch.setenv("RANK", "2")
+    monkeypatch.setenv("WORLD_SIZE", "4")
     logger = log.configure_logging("DEBUG", rank=2, log_dir=tmp_path, as_json=True, install_excepthook=False,
                                    enable_faulthandler=False, force=True)
     stream = io.StringIO()
@@ -96,11 +101,11 @@ def test_logging_rank_filter_json_and_once(tmp_path, monkeypatch):
         log.info("scoped away")
     with log.timed("block"):
         pass
-    lines = [json.loads(l) for l in stream.getvalue().splitlines()]
-    msgs = [l["msg"] for l in lines]
+    lines = [json.loads(row) for row in stream.getvalue().splitlines()]
+    msgs = [rec["msg"] for rec in lines]
     assert msgs[:3] == ["hello 1", "everyone", "only once"] and msgs.count("only once") == 1
     assert "not for me" not in msgs and "scoped away" not in msgs and any("block took" in m for m in msgs)
-    assert all(l["rank"] == 2 and l["world"] == 4 for l in lines)
+    assert all(rec["rank"] == 2 and rec["world"] == 4 for rec in lines)
     assert (tmp_path / "rank_0002.log").exists()
     with pytest.raises(ValueError):
         log.at("some")
@@ -230,13 +235,13 @@ def _worker_log_collectives(rank, world):
     assert log.assert_all_agree("depth", 12) is True
     assert log.assert_all_agree("seed", rank, fatal=False) is False          # every rank learns of it
     log.log_ranks("tile %d", rank, level=logging.INFO)
-    lines = [json.loads(l) for l in stream.getvalue().splitlines()]
+    lines = [json.loads(row) for row in stream.getvalue().splitlines()]
     if rank == 0:
-        assert any("ranks disagree on seed" in l["msg"] and "r2=2" in l["msg"] for l in lines)
-        dump = [l["msg"] for l in lines if l["msg"].startswith("rank dump")][0]
+        assert any("ranks disagree on seed" in rec["msg"] and "r2=2" in rec["msg"] for rec in lines)
+        dump = [rec["msg"] for rec in lines if rec["msg"].startswith("rank dump")][0]
         assert dump.index("[0] tile 0") < dump.index("[1] tile 1") < dump.index("[2] tile 2")
     else:
-        assert not any(l["msg"].startswith("rank dump") for l in lines)
+        assert not any(rec["msg"].startswith("rank dump") for rec in lines)
 
 
 def test_logging_collectives_on_ranks():

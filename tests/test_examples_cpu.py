@@ -30,7 +30,7 @@ def _load(name):
 
 def _worker_train(rank, world, name, kwargs, steps):
     losses = _load(name).main(steps=steps, **kwargs)
-    assert len(losses) == steps and all(l == l for l in losses)
+    assert len(losses) == steps and all(v == v for v in losses)
     assert sum(losses[-3:]) < sum(losses[:3]), (name, losses)
 
 

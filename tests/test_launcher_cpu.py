@@ -29,7 +29,7 @@ def test_slurm_allocation_gives_the_rendezvous_and_a_preset_reaches_the_containe
     out = _run(["--dry-run", "python", "train.py"], JB_SITE="hgx-b200", JB_SIF="/img.sif", JB_BINDS="/a,/b",
                SLURM_JOB_ID="123456", SLURM_JOB_NODELIST="n1", MASTER_ADDR="n1", NCCL_NVLS_ENABLE="0")
     assert out.returncode == 0, out.stderr
-    line = [l for l in out.stdout.splitlines() if l.startswith("exec:")][0]
+    line = [row for row in out.stdout.splitlines() if row.startswith("exec:")][0]
     assert line.startswith("exec: apptainer exec --nv --bind ")
     for piece in ("--bind /a --bind /b", "--env MASTER_ADDR=n1", "--env MASTER_PORT=23456", "--env NCCL_NVLS_ENABLE=0",
                   "--env NCCL_P2P_LEVEL=NVL", "--env JIGSAW_B200_ARENA_SEGMENT_GB=4", "/img.sif python train.py"):

@@ -29,7 +29,7 @@ def captured(monkeypatch):
     log._once_keys.clear()
 
     def lines():
-        return [json.loads(l) for l in stream.getvalue().splitlines()]
+        return [json.loads(row) for row in stream.getvalue().splitlines()]
 
     yield lines
     for h in list(logger.handlers):
@@ -52,12 +52,12 @@ def test_only_the_print_rank_speaks_by_default(captured, monkeypatch):
     log.info("hello %d", 1)
     _as(monkeypatch, 3, 4)
     log.info("suppressed")
-    assert [l["msg"] for l in captured()] == ["hello 1"]
+    assert [rec["msg"] for rec in captured()] == ["hello 1"]
     log.set_print_rank(3)
     log.info("now from 3")
     _as(monkeypatch, 0, 4)
     log.info("no longer from 0")
-    assert [l["msg"] for l in captured()] == ["hello 1", "now from 3"]
+    assert [rec["msg"] for rec in captured()] == ["hello 1", "now from 3"]
 
 
 def test_at_targets_an_int_a_list_and_all(captured, monkeypatch):
@@ -68,7 +68,7 @@ def test_at_targets_an_int_a_list_and_all(captured, monkeypatch):
     log.at(1).info("not mine")
     log.at([0, 3]).info("not mine either")
     log.info_all("everyone, whatever the print rank")
-    assert [l["msg"] for l in captured()] == ["int", "list", "all", "everyone, whatever the print rank"]
+    assert [rec["msg"] for rec in captured()] == ["int", "list", "all", "everyone, whatever the print rank"]
     with pytest.raises(ValueError):
         log.at("some")
 
@@ -83,7 +83,7 @@ def test_only_rank_scopes_plain_calls_and_restores_on_error(captured, monkeypatc
         with log.only_rank(1):
             raise RuntimeError
     log.info("outside again")
-    assert [l["msg"] for l in captured()] == ["inside"]
+    assert [rec["msg"] for rec in captured()] == ["inside"]
     assert log._state["scope"] is None
 
 
@@ -92,7 +92,7 @@ def test_log_once_fires_a_single_time_per_call_site(captured, monkeypatch):
     for _ in range(3):
         log.log_once("once")
     log.log_once("once")                    # another call site
-    assert [l["msg"] for l in captured()].count("once") == 2
+    assert [rec["msg"] for rec in captured()].count("once") == 2
 
 
 def test_records_carry_rank_metadata_and_levels(captured, monkeypatch):
@@ -104,8 +104,8 @@ def test_records_carry_rank_metadata_and_levels(captured, monkeypatch):
     except ValueError:
         log.at("all").exception("caught")
     got = captured()
-    assert [(l["rank"], l["world"]) for l in got] == [(3, 16)] * 3
-    assert [l["level"] for l in got] == ["DEBUG", "ERROR", "ERROR"]
+    assert [(rec["rank"], rec["world"]) for rec in got] == [(3, 16)] * 3
+    assert [rec["level"] for rec in got] == ["DEBUG", "ERROR", "ERROR"]
     assert "ValueError: boom" in got[-1]["exc"] and isinstance(got[0]["t"], float)
 
 
@@ -187,7 +187,7 @@ def test_configuration_is_idempotent_reads_the_environment_and_writes_rank_files
     for h in logger.handlers:
         h.flush()
     assert "for rank 1" in logger.handlers[0].stream.getvalue() and "addressed to rank 2" not in logger.handlers[0].stream.getvalue()
-    in_file = [json.loads(l)["msg"] for l in (tmp_path / "rank_0001.log").read_text().splitlines()]
+    in_file = [json.loads(row)["msg"] for row in (tmp_path / "rank_0001.log").read_text().splitlines()]
     assert len(in_file) == 2, "... but the per-rank file keeps every record of its rank"
 
 

@@ -484,7 +484,7 @@ def _worker_gather_linear(rank, world, mesh_axes):
     torch.manual_seed(0)
     dims = [256, 512, 256, 256]
     full = torch.nn.Sequential(*[torch.nn.Linear(dims[i], dims[i + 1], device=dev) for i in range(3)])
-    layers = torch.nn.Sequential(*[jb.modules.DistributedLinear.convert_to_jigsaw(l, mesh, dev) for l in full])
+    layers = torch.nn.Sequential(*[jb.modules.DistributedLinear.convert_to_jigsaw(lin, mesh, dev) for lin in full])
     cuts = {0: row, 1: col}
     from dist_utils import split
 

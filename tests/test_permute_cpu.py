@@ -14,7 +14,8 @@ from dist_utils import assert_close, run_distributed, split
 
 def _worker_permute(rank, world, R, C):
     import jigsaw_b200 as jb
-    mesh = jb.make_process_mesh({"row": R, "col": C}); row, col = mesh["row"], mesh["col"]
+    mesh = jb.make_process_mesh({"row": R, "col": C})
+    row, col = mesh["row"], mesh["col"]
     f = jb.modules.functional.distributed_permute
     torch.manual_seed(0)
     L = R * C * 2
