@@ -230,3 +230,118 @@ def synced_call(module: torch.nn.Module, *args: Any, **kwargs: Any) -> Any:
     if not routed:
         return module(*args, **kwargs)
     return torch.func.functional_call(module, routed, args, kwargs)
+
+
+class OverlappedGradSync:
+    """Sum the gradients of replicated parameters bucket by bucket WHILE the backward pass is still running.
+
+    The in-graph mode (:func:`sync_grad`) reduces inside the autograd graph, on the stream of the backward
+    pass: every reduction is on the critical path.  Inside this context the in-graph reduction is switched off
+    (as under :func:`no_grad_sync`); instead a hook fires when a marked parameter's gradient has been
+    accumulated, parameters are collected into buckets of about ``bucket_bytes`` per (replica groups, dtype),
+    and a full bucket is reduced at once:
+
+    * CUDA, fp32, at most eight copies: the peer-memory all-reduce kernel on a side stream
+      (:class:`jigsaw_b200.ops.reduce_fused.OverlappedReducer`), in place, bit-identical on every rank, while the
+      remaining gradient kernels keep the GPU busy;
+    * otherwise: an asynchronous ``all_reduce`` of the flattened bucket per group, copied back at the end.
+
+    Leaving the context (or :meth:`finish`) flushes the partial buckets and waits; the optimizer step follows.
+
+        with jb.parallel.OverlappedGradSync(model):
+            loss_fn(model(x), y).backward()
+        optimizer.step()
+
+    One backward pass per context: the hooks reduce what is in ``.grad`` when they fire, so for gradient
+    accumulation wrap only the LAST micro-batch (the earlier ones under :func:`no_grad_sync`).  Every rank must
+    run the same model, so that the hooks fire in the same order everywhere (the assumption DDP's buckets make).
+    Under the joint DDP hook, where DDP reduces, the context changes nothing.
+
+    Reference parity: the per-module blocking reduction of jigsaw/parallel/_sync.py:19-53 and the bucket hook of
+    jigsaw/parallel/_joint.py:215-279; the overlap outside DDP has no counterpart there.
+    """
+
+    def __init__(self, module_or_parameters: torch.nn.Module | Iterable[torch.Tensor], bucket_bytes: int = 1 << 20) -> None:
+        params = module_or_parameters.parameters() if isinstance(module_or_parameters, torch.nn.Module) else module_or_parameters
+        self.params = [p for p in params if p.requires_grad and replica_groups(p)]
+        self.bucket_bytes = int(bucket_bytes)
+        self._handles: list[Any] = []
+        self._buckets: dict[tuple, list[torch.Tensor]] = {}
+        self._pending: list[tuple] = []            # (flat, grads, works) of the library path
+        self._reducers: dict[tuple, Any] = {}
+        self.launched = 0                          # buckets reduced so far (for tests and logs)
+        self._active = False
+
+    # ------------------------------------------------------------------ context
+    def __enter__(self) -> "OverlappedGradSync":
+        global _deferred
+        if self._active:
+            raise RuntimeError("OverlappedGradSync is not re-entrant")
+        self._active = True
+        self._live = dist.is_initialized() and not _SYNC_DISABLED and active_joint_state() is None
+        _deferred += 1
+        if self._live:
+            for p in self.params:
+                self._handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
+        return self
+
+    def __exit__(self, exc_type: Any, exc: Any, tb: Any) -> None:
+        global _deferred
+        try:
+            if exc_type is None:
+                self.finish()
+        finally:
+            for h in self._handles:
+                h.remove()
+            self._handles.clear()
+            self._buckets.clear()
+            _deferred -= 1
+            self._active = False
+
+    # ------------------------------------------------------------------ hooks
+    def _on_grad(self, p: torch.Tensor) -> None:
+        if p.grad is None:
+            return
+        groups = replica_groups(p)
+        key = (groups, p.grad.dtype, p.grad.device)
+        bucket = self._buckets.setdefault(key, [])
+        bucket.append(p.grad)
+        if sum(g.numel() * g.element_size() for g in bucket) >= self.bucket_bytes:
+            self._reduce(key, self._buckets.pop(key))
+
+    def _reduce(self, key: tuple, grads: list[torch.Tensor]) -> None:
+        groups, dtype, device = key
+        self.launched += 1
+        if device.type == "cuda" and dtype == torch.float32:
+            from ..ops import reduce_fused
+
+            ranks = replica_rank_set(groups)
+            if len(ranks) <= 8 and reduce_fused.usable(grads, ranks) and all(g.is_contiguous() for g in grads):
+                red = self._reducers.get(tuple(ranks))
+                if red is None:
+                    red = self._reducers[tuple(ranks)] = reduce_fused.OverlappedReducer(device, ranks)
+                red.add(grads)                      # in place, on the side stream
+                return
+        with torch.no_grad():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            whole = merged_group(groups)
+            works = [dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=g, async_op=True) for g in ((whole,) if whole is not None else groups[:1])]
+            self._pending.append((flat, grads, works, () if whole is not None else groups[1:]))
+
+    def finish(self) -> None:
+        """Reduce the partial buckets and wait for everything that is in flight (collective)."""
+        for key in list(self._buckets):
+            self._reduce(key, self._buckets.pop(key))
+        for red in self._reducers.values():
+            red.finish()
+        with torch.no_grad():
+            for flat, grads, works, later in self._pending:
+                for w in works:
+                    w.wait()
+                for g in later:                     # further axes of a parameter replicated over several groups
+                    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=g)
+                offset = 0
+                for g in grads:
+                    g.copy_(flat[offset: offset + g.numel()].view_as(g))
+                    offset += g.numel()
+        self._pending.clear()

@@ -15,7 +15,7 @@ from dist_utils import assert_close, run_distributed, split
 EXPECTED = {
     "jigsaw_b200": {"ProcessMesh", "make_process_mesh", "checkpoint", "convert", "data", "models", "optim", "utils", "debug", "gather", "init", "launch", "log", "modules",
                     "parallel"},
-    "jigsaw_b200.parallel": {"JointCommHookState", "broadcast_replicas", "check_ddp", "clip_grad_norm_", "joint_comm_hook",
+    "jigsaw_b200.parallel": {"JointCommHookState", "OverlappedGradSync", "broadcast_replicas", "check_ddp", "clip_grad_norm_", "joint_comm_hook",
                              "mark_replicated", "no_grad_sync", "overlapped_sum_plan", "reduce_replica_grads", "register_joint_comm_hook",
                              "replica_groups", "sync_grad", "synced_call", "synced_parameters", "wrap_ddp"},
     "jigsaw_b200.modules.functional": {"confusion_to_metrics", "distributed_argmax", "distributed_binary_cross_entropy",

@@ -228,3 +228,68 @@ def _worker_accumulate(rank, world):
 
 def test_gradient_accumulation_with_one_reduction():
     run_distributed(_worker_accumulate, 4)
+
+
+def _worker_overlapped_sync(rank, world):
+    """Bucketed reduction under the backward pass gives the gradients of the in-graph mode whatever the bucket
+    size (up to the summation order of the transport, which depends on where an element sits in its bucket);
+    gradient accumulation wraps only the last micro-batch."""
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh({"sh": 2, "sw": 2, "col": 1})
+    P = jb.parallel
+
+    def build():
+        model = _tiny_model(mesh)
+        with torch.no_grad():
+            for i, p in enumerate(model.parameters()):
+                p.copy_(torch.randint(-2, 3, p.shape, generator=torch.Generator().manual_seed(100 + i)).float())
+        return model
+
+    def data(step):
+        g = torch.Generator().manual_seed(10 * rank + step)
+        return torch.randint(-2, 3, (1, 2, 4, 4), generator=g).float(), torch.randint(-2, 3, (1, 2, 4, 4), generator=g).float()
+
+    ref = build()
+    x, gy = data(0)
+    ref(x).backward(gy)
+    want = [p.grad.clone() for p in ref.parameters()]
+    for bucket_bytes in (1, 64, 1 << 20):
+        model = build()
+        with P.OverlappedGradSync(model, bucket_bytes=bucket_bytes) as sync:
+            model(x).backward(gy)
+        assert sync.launched >= (4 if bucket_bytes == 1 else 1)
+        for (n, p), w in zip(model.named_parameters(), want):
+            assert all_ok(torch.allclose(p.grad, w, rtol=1e-5, atol=1e-5 * float(w.abs().max()))), f"bucket {bucket_bytes}: {n}"
+    # accumulation over two micro-batches: the first under no_grad_sync, the second under the overlapped reduction
+    ref = build()
+    for step in range(2):
+        x, gy = data(step)
+        ref(x).backward(gy)
+    want = [p.grad.clone() for p in ref.parameters()]
+    model = build()
+    x, gy = data(0)
+    with P.no_grad_sync():
+        model(x).backward(gy)
+    x, gy = data(1)
+    with P.OverlappedGradSync(model, bucket_bytes=128):
+        model(x).backward(gy)
+    for (n, p), w in zip(model.named_parameters(), want):
+        assert all_ok(torch.allclose(p.grad, w, rtol=1e-5, atol=1e-5 * float(w.abs().max()))), f"accumulation: {n}: {float((p.grad - w).abs().max())} of {float(w.abs().max())}"
+    # after the context the in-graph mode is back
+    model = build()
+    x, gy = data(0)
+    model(x).backward(gy)
+    ref = build()
+    ref(x).backward(gy)
+    for p, q in zip(model.parameters(), ref.parameters()):
+        assert torch.equal(p.grad, q.grad)
+    with pytest.raises(RuntimeError):
+        sync = P.OverlappedGradSync(model)
+        with sync:
+            with sync:
+                pass
+
+
+def test_overlapped_grad_sync_matches_the_in_graph_mode():
+    run_distributed(_worker_overlapped_sync, 4)
