@@ -5,7 +5,7 @@ which in turn is pinned against the undivided torch layers by the CPU tests."""
 import pytest
 import torch
 
-from dist_utils import assert_close, run_distributed
+from dist_utils import all_ok, assert_close, run_distributed
 
 pytestmark = pytest.mark.gpu
 
@@ -915,3 +915,49 @@ def _worker_fused_softmax(rank, world):
 @pytest.mark.multigpu(2)
 def test_fused_softmax_two_gpus():
     run_distributed(_worker_fused_softmax, 2, backend="nccl", timeout=300)
+
+
+def _worker_overlapped_grad_sync(rank, world):
+    """``OverlappedGradSync`` on GPUs: buckets reduced by the peer-memory all-reduce on a side stream give the
+    gradients of the in-graph mode bit for bit (integer-valued data: every sum is exact)."""
+    import os
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import jigsaw_b200 as jb
+    from jigsaw_b200.ops import _lib, symm
+
+    dev = torch.device("cuda", rank)
+    mesh = jb.make_process_mesh({"sh": world, "sw": 1, "col": 1})
+    M = jb.modules
+
+    def build():
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(M.DistributedConv2d(2, 4, 3, dev, (mesh["sh"], mesh["sw"]), mesh["col"], padding=1),
+                                    M.DistributedConv2d(4, 2, 3, dev, (mesh["sh"], mesh["sw"]), mesh["col"], padding=1))
+        with torch.no_grad():
+            for i, p in enumerate(model.parameters()):
+                p.copy_(torch.randint(-2, 3, p.shape, generator=torch.Generator().manual_seed(100 + i)).float())
+        return model
+
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randint(-2, 3, (1, 2, 8, 8), generator=g).float().to(dev)
+    gy = torch.randint(-2, 3, (1, 2, 8, 8), generator=g).float().to(dev)
+    ref = build()
+    ref(x).backward(gy)
+    for bucket_bytes in (1, 1 << 20):
+        model = build()
+        before = _lib.dispatch_counts().get("all_reduce", {}).get("fused", 0)
+        launches = _lib.LAUNCHES
+        with jb.parallel.OverlappedGradSync(model, bucket_bytes=bucket_bytes) as sync:
+            model(x).backward(gy)
+        torch.cuda.synchronize()
+        symm.arena(dev).check_status(collective=True)
+        assert sync.launched >= 1 and _lib.LAUNCHES - launches >= sync.launched, "the buckets must go through the own all-reduce kernel"
+        assert _lib.dispatch_counts().get("all_reduce", {}).get("fused", 0) == before, "no blocking in-graph reduction inside the context"
+        for (n, p), q in zip(model.named_parameters(), ref.parameters()):
+            assert all_ok(torch.equal(p.grad, q.grad)), f"bucket {bucket_bytes}: {n}"
+
+
+@pytest.mark.multigpu(2)
+def test_overlapped_grad_sync_two_gpus():
+    run_distributed(_worker_overlapped_grad_sync, 2, backend="nccl", timeout=300)
