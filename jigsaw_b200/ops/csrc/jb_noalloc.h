@@ -4,7 +4,7 @@
 // and no allocator of its own); it exists for callers that are not allowed to allocate
 // device memory at the point where they need the result: code running inside a memory pool
 // that must not grow, a latency-critical loop that bans cudaMalloc because it synchronises
-// the device, or a host application that hands this library a fixed memory budget.
+// the device, or a host application that hands this library a fixed amount of device memory.
 //
 // jb_conv3x3_c64_wgrad_noalloc computes the same weight / bias gradient as
 // jb_conv3x3_c64_wgrad, but the per-CTA partial sums it needs as scratch live in a static

@@ -2,7 +2,7 @@
 
 Some callers of the kernel library may not allocate device memory where they need a result
 (a memory pool that must not grow, a loop that bans the device-wide synchronisation
-cudaMalloc implies, a host application with a fixed budget).  For them the library exports
+cudaMalloc implies, a host application with a fixed amount of device memory).  For them the library exports
 ``jb_conv3x3_c64_wgrad_noalloc``, whose scratch is a static device array inside the library
 image.  This test calls it through its exported C symbol, twice in a row (the scratch is
 shared between calls and keeps the previous contents), and compares weight and bias gradient
