@@ -1,8 +1,10 @@
 // Attention forward for head dimension 64 on tcgen05: O = softmax(scale * Q K^T) V and the row-wise
 // log-sum-exp, no mask, bf16 in / bf16 + fp32 out.  The keys and values may come in up to eight PARTS
-// that live on different GPUs (ring / sequence-parallel attention): the kernel walks over the parts
-// starting with its own, waits (bounded) for the flag of a part's owner before the first block of that
-// part, and loads the blocks by TMA straight from the owner's memory (no multicast).  The running
+// that belong to different GPUs (ring / sequence-parallel attention): the kernel walks over the parts
+// starting with its own, waits (bounded) for the arrival flag of a part before the first block of that
+// part, and loads its blocks by TMA (no multicast) through the part's own tensor map.  The callers let the
+// copy engines push every rank's part into a local staging slot, so each byte crosses NVLink once per
+// destination and the loads hit local memory; a map over a peer's memory works as well.  The running
 // maximum and sum stay in registers and the output accumulator stays in TMEM across all parts, so a
 // ring of P chunks is ONE launch and needs no merge step.
 //

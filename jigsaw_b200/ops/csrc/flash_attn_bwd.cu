@@ -8,9 +8,10 @@
 // S and dP are recomputed in both kernels so that no gradient needs atomics or a reduction: every
 // gradient block is produced completely by the one CTA that owns it.  That also carries ring attention:
 // the STREAMED operand pair (queries and output gradients for <0>, keys and values for <1>) may come in
-// up to eight parts that live on different GPUs; the kernel waits (bounded) for a part's flag and loads
-// its blocks by TMA from the owner's memory (no multicast), so the owner of a key block computes its
-// complete dK / dV by pulling every rank's queries, and nothing is sent back.
+// up to eight parts that belong to different GPUs; the kernel waits (bounded) for a part's arrival flag and
+// loads its blocks by TMA (no multicast) through the part's own tensor map (the callers have the copy engines
+// push every rank's part into a local staging slot), so the owner of a key block computes its complete
+// dK / dV from every rank's queries, and no gradient is sent back.
 //
 // Roles: warp 0 TMA producer, warp 1 UMMA issuer, warps 2-9 row warps (thread = one query row and one
 // half of the 128 key columns; no reduction along a row is needed in the backward pass).  P and dS go
