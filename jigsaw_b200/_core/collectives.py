@@ -29,6 +29,7 @@ import torch
 import torch.distributed as dist
 
 from .comm import CommOp, ring_shift
+from .vmap import to_front
 
 
 def _live(group: dist.ProcessGroup | None) -> bool:
@@ -62,7 +63,7 @@ def _batched_dim(x: torch.Tensor, bdim: int | None, dim: int) -> tuple[torch.Ten
     shifted behind it."""
     if bdim is None:
         return x, dim
-    return x.movedim(bdim, 0), dim + 1
+    return to_front(x, bdim), dim + 1
 
 
 class _AllGatherCat(torch.autograd.Function):

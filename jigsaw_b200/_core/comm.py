@@ -192,18 +192,6 @@ def ring_shift(
     return buffer, work
 
 
-def all_to_all_async(
-    outputs: list[torch.Tensor], inputs: list[torch.Tensor], group: dist.ProcessGroup, async_op: bool = True
-) -> dist.Work | None:
-    """List all-to-all (NCCL); thin wrapper kept for symmetry with the other transports."""
-    return dist.all_to_all(outputs, inputs, group=group, async_op=async_op)
-
-
-def comm_broadcast(
-    tensor: torch.Tensor, src_group_rank: int, group: dist.ProcessGroup, async_op: bool = False
-) -> dist.Work | None:
-    """Broadcast ``tensor`` in place from group rank ``src_group_rank``."""
-    return dist.broadcast(tensor, group_src=src_group_rank, group=group, async_op=async_op)
 
 
 def all_reduce_max(value: float | int, group: dist.ProcessGroup | None = None) -> float:
@@ -212,13 +200,3 @@ def all_reduce_max(value: float | int, group: dist.ProcessGroup | None = None) -
     t = torch.tensor([float(value)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
-
-
-def group_ranks(group: dist.ProcessGroup) -> tuple[int, ...]:
-    """Global ranks of ``group`` in group-rank order."""
-    return tuple(dist.get_process_group_ranks(group))
-
-
-def is_split(group: dist.ProcessGroup | None) -> bool:
-    """True for a group that really splits something (size > 1)."""
-    return group is not None and group.size() > 1

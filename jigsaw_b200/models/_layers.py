@@ -53,17 +53,6 @@ def mark_all(module: nn.Module, groups: Sequence[dist.ProcessGroup]) -> nn.Modul
     return module
 
 
-class Synced(nn.Module):
-    """A plain layer whose weights are replicated over the tile groups: the forward routes the
-    marked parameters through the in-graph gradient sum."""
-
-    def __init__(self, inner: nn.Module, groups: Sequence[dist.ProcessGroup]) -> None:
-        super().__init__()
-        self.inner = mark_all(inner, groups)
-
-    def forward(self, *args, **kwargs):
-        return parallel.synced_call(self.inner, *args, **kwargs)
-
 
 class ReplicatedLinear(nn.Linear):
     """``nn.Linear`` replicated over the tile groups (same parameter names as the sharded layer,

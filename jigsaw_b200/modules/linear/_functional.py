@@ -30,6 +30,7 @@ import torch.distributed as dist
 
 from ..._core.autocast import cast_to_autocast_dtype
 from ..._core.comm import CommOp, resolve_comm_op, sparse_exchange
+from ..._core.vmap import to_front
 
 Region = tuple[int, int, int, int]          # rows [r0, r1) and columns [c0, c1) of the global matrix
 
@@ -118,7 +119,7 @@ class _FetchRegion(torch.autograd.Function):
 
     @staticmethod
     def vmap(info: Any, in_dims: tuple, x: torch.Tensor, group: Any, R: int, C: int, region_of: Any, comm: Any) -> tuple:
-        xb = x if in_dims[0] is None else x.movedim(in_dims[0], 0)
+        xb = to_front(x, in_dims[0])
         return _FetchRegion.apply(xb, group, R, C, region_of, comm), (None if in_dims[0] is None else 0)
 
 
@@ -137,7 +138,7 @@ class _ScatterRegion(torch.autograd.Function):
 
     @staticmethod
     def vmap(info: Any, in_dims: tuple, g: torch.Tensor, h: int, w: int, group: Any, R: int, C: int, region_of: Any, comm: Any) -> tuple:
-        gb = g if in_dims[0] is None else g.movedim(in_dims[0], 0)
+        gb = to_front(g, in_dims[0])
         return _ScatterRegion.apply(gb, h, w, group, R, C, region_of, comm), (None if in_dims[0] is None else 0)
 
 

@@ -95,3 +95,28 @@ def _worker_ensemble(rank, world):
 
 def test_ensemble_of_stacked_weights():
     run_distributed(_worker_ensemble, 4)
+
+
+def _worker_nested_vmap(rank, world):
+    """The rules re-apply their Function to the stack, so nested ``vmap`` levels unwind one after the other:
+    two levels over a gather, a sum and a sharded linear layer equal the double loop."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200._core.collectives import all_gather_cat, all_reduce_sum
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    row, col = mesh["row"], mesh["col"]
+    x = torch.arange(2 * 3 * 4, dtype=torch.float64).view(2, 3, 4) + 100 * rank
+    for name, fn in (("gather", lambda t: all_gather_cat(t, row, 0)), ("sum", lambda t: all_reduce_sum(t, col))):
+        got = torch.vmap(torch.vmap(fn))(x)
+        want = torch.stack([torch.stack([fn(x[i, j]) for j in range(3)]) for i in range(2)])
+        assert_close(got, want, f"nested vmap over {name}", 0, 0)
+    torch.manual_seed(0)
+    lin = jb.modules.DistributedLinear(8, 12, "cpu", mesh["model"], row, col, dtype=torch.float64)
+    tokens = torch.randn(2, 3, 4, 4, dtype=torch.float64)            # (outer, inner, tokens / row, features / col)
+    got = torch.vmap(torch.vmap(lin))(tokens)
+    want = torch.stack([torch.stack([lin(tokens[i, j]) for j in range(3)]) for i in range(2)])
+    assert_close(got, want, "nested vmap over a sharded linear layer", 1e-12, 1e-12)
+
+
+def test_nested_vmap():
+    run_distributed(_worker_nested_vmap, 4)
