@@ -99,7 +99,15 @@ def _gather(x: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
     dim = plan.dim % x.dim()
     shape = list(x.shape)
     shape[dim] = plan.held
-    out = x.new_zeros(shape)
+    out = x.new_empty(shape)
+    # the owners' ranges tile the domain without gaps, so the held span is covered except where it reaches
+    # beyond the domain: only those two ends are zero-filled (no pass over the whole buffer)
+    lo, hi = plan.lo[me], plan.lo[me] + plan.held
+    below, above = min(max(0, lo), hi) - lo, hi - max(min(plan.total, hi), lo)
+    if below > 0:
+        out.narrow(dim, 0, below).zero_()
+    if above > 0:
+        out.narrow(dim, plan.held - above, above).zero_()
     sends: dict[int, torch.Tensor] = {}
     recvs: dict[int, torch.Tensor] = {}
     landing: list[tuple[int, int, torch.Tensor]] = []
@@ -129,7 +137,9 @@ def _reduce(y: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
     dim = plan.dim % y.dim()
     shape = list(y.shape)
     shape[dim] = plan.own
-    out = y.new_zeros(shape)
+    a, b = plan.overlap(me, me)
+    covers = b - a == plan.own              # my held span contains everything I own: start from that piece, not from zeros
+    out = y.narrow(dim, a - plan.lo[me], b - a).clone(memory_format=torch.contiguous_format) if covers else y.new_zeros(shape)
     sends: dict[int, torch.Tensor] = {}
     recvs: dict[int, torch.Tensor] = {}
     landing: list[tuple[int, int, torch.Tensor]] = []
@@ -138,7 +148,8 @@ def _reduce(y: torch.Tensor, plan: AxisPlan) -> torch.Tensor:
         if b > a:
             piece = y.narrow(dim, a - plan.lo[me], b - a)
             if q == me:
-                out.narrow(dim, a - me * plan.own, b - a).add_(piece)
+                if not covers:
+                    out.narrow(dim, a - me * plan.own, b - a).add_(piece)
             else:
                 sends[q] = piece.contiguous()
         if q != me:
