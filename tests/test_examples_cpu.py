@@ -72,13 +72,21 @@ def test_ddp_modes_agree_on_8_ranks():
     run_distributed(_worker_ddp_modes, 8)
 
 
+def _free_port() -> str:
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return str(sock.getsockname()[1])
+
+
 def test_torchrun_launch():
     env = {k: v for k, v in os.environ.items() if not k.startswith("SLURM_")}
     env["CUDA_VISIBLE_DEVICES"] = ""
     env["JIGSAW_LOG_LEVEL"] = "INFO"
     out = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
-         "--master-port", "29631", os.path.join(EXAMPLES, "domain_parallel.py"), "--steps", "3"],
+         "--master-port", _free_port(), os.path.join(EXAMPLES, "domain_parallel.py"), "--steps", "3"],
         env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     assert "step   0" in out.stderr + out.stdout
@@ -94,7 +102,7 @@ def test_cpu_gloo_cnn_workload_matches_undivided_model():
     script = os.path.join(os.path.dirname(EXAMPLES), "benchmarks", "cpu_cnn.py")
     out = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
-         "--master-port", "29633", script, "--steps", "2", "--image", "128"],
+         "--master-port", _free_port(), script, "--steps", "2", "--image", "128"],
         env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     line = [ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1]
