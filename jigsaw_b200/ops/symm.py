@@ -59,6 +59,14 @@ class Block:
     def peer_ptr(self, world_rank: int) -> int:
         return self.arena.peer_base(self.segment, world_rank) + self.offset
 
+    def check_range(self, offset: int, nbytes: int, pitch: int = 0, rows: int = 1) -> None:
+        """Raise unless ``rows`` pieces of ``nbytes`` bytes, ``pitch`` bytes apart, starting ``offset`` bytes into
+        the block, lie inside it.  Every copy into a peer's copy of a block is checked with this on the host before
+        it is enqueued: an address outside the block would land in whatever the peer keeps next to it."""
+        last = offset + (rows - 1) * pitch + nbytes
+        if offset < 0 or nbytes <= 0 or rows < 1 or (rows > 1 and pitch < nbytes) or last > self.nbytes:
+            raise ValueError(f"range (offset {offset}, {rows} x {nbytes} bytes, pitch {pitch}) does not fit a block of {self.nbytes} bytes")
+
     def view(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         return self.tensor.view(dtype)[: int(torch.Size(shape).numel())].view(shape)
 
@@ -348,6 +356,9 @@ def push_slot_to_peers(ar: "PeerArena", blk: Block, ranks: list, me: int, offset
     from . import _lib
 
     L, dev = _lib.lib(), blk.tensor.device
+    blk.check_range(offset, nbytes, pitch, rows)
+    if len(ranks) > 8 or not 0 <= me < len(ranks):
+        raise ValueError(f"a staged block is shared by at most 8 ranks and this rank must be one of them (got {len(ranks)}, index {me})")
     epoch = ar.next_own_epoch(blk)
     stride = ar.capture_stride or 0
     replay = ar.replay.data_ptr() if ar.capture_stride is not None else None

@@ -112,3 +112,16 @@ def test_kernel_status_is_agreed_over_ranks():
     from dist_utils import run_distributed
 
     run_distributed(_worker_status_agreement, 3, backend="gloo", timeout=120)
+
+
+def test_block_range_check():
+    """Host-side guard of every copy into a peer's copy of a block (pure arithmetic, no device needed)."""
+    from jigsaw_b200.ops.symm import Block
+
+    blk = Block(None, 0, 4096, 1 << 20, torch.empty(0))
+    blk.check_range(256, 1 << 10)
+    blk.check_range(256, 128, pitch=2048, rows=512)              # last row ends at 256 + 511 * 2048 + 128 = 1046912
+    blk.check_range(0, 1 << 20)
+    for bad in ((-1, 16, 0, 1), (0, 0, 0, 1), ((1 << 20) - 8, 16, 0, 1), (256, 128, 2048, 513), (0, 128, 64, 4), (0, 16, 0, 0)):
+        with pytest.raises(ValueError):
+            blk.check_range(*bad)
