@@ -202,13 +202,28 @@ class DistributedLinear(torch.nn.Module):
         self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, pm_row_key: str = "row", pm_col_key: str = "col",
         pm_model_key: str = "model",
     ) -> None:
-        # a projection built with model_group = col_group keeps its weight unsplit over rows
-        new_model = to_process_mesh_dict[pm_col_key] if self._model_is_col else to_process_mesh_dict[pm_model_key]
+        """Move the layer to another mesh (collective over both).  The target layout follows the meshes when they
+        describe this layer, i.e. when ``from_process_mesh_dict[pm_model_key]`` is the layer's model group: a
+        target whose model group is its column group (on a mesh with several rows) gives the column-only layout
+        (weight replicated over the rows and marked so), any other target the row x column layout.  When the
+        source mesh names another model group (a generic loop that hands every layer the whole mesh, although
+        this layer is the column-only projection of an attention block) the layer keeps its kind of layout."""
+        def same(a: dist.ProcessGroup, b: dist.ProcessGroup) -> bool:
+            return a is b or dist.get_process_group_ranks(a) == dist.get_process_group_ranks(b)
+
+        to_row, to_col = to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key]
+        from_model = from_process_mesh_dict.get(pm_model_key) if hasattr(from_process_mesh_dict, "get") else None
+        if from_model is not None and same(from_model, self.model_group) and pm_model_key in to_process_mesh_dict:
+            col_only = same(to_process_mesh_dict[pm_model_key], to_col) and to_row.size() > 1
+        else:
+            col_only = self._model_is_col
+        new_model = to_col if col_only else to_process_mesh_dict[pm_model_key]
         if (self.model_group is new_model and self.row_group is to_process_mesh_dict[pm_row_key]
                 and self.col_group is to_process_mesh_dict[pm_col_key]):
             return                                  # already there (a parent layer moved this one with itself)
         w, b = self.merge_weights(from_process_mesh_dict, pm_row_key, pm_col_key, pm_model_key)
         self._bind_groups(new_model, to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key])
+        self._model_is_col = col_only
         self.config = LinearConfig(new_model, linear_layer=True, device=self.device, comm=self.config.comm)
         self.weight = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))
         if self.bias is not None:
