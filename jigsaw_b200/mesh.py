@@ -89,6 +89,16 @@ def _model_axes_from(names: list[str], requested: Sequence[str] | None) -> list[
     return req
 
 
+def _resolve_device_type(device_type: str | None) -> str:
+    """The device type of the mesh: as given, else what the default group's backend serves (a gloo group
+    gets a CPU mesh even where GPUs are present; any other backend gets CUDA when it is available)."""
+    if device_type is not None:
+        return device_type
+    if dist.get_backend() == "gloo":
+        return "cpu"
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
 def make_process_mesh(
     axes: Mapping[str, int],
     *,
@@ -109,11 +119,7 @@ def make_process_mesh(
             "torch.distributed.init_process_group first"
         )
     check_backend()
-    if device_type is None:
-        if dist.get_backend() == "gloo":
-            device_type = "cpu"
-        else:
-            device_type = "cuda" if torch.cuda.is_available() else "cpu"
+    device_type = _resolve_device_type(device_type)
     world = dist.get_world_size()
     sizes = _sizes_from(axes, world)
     names = list(sizes)
