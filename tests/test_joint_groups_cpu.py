@@ -39,11 +39,9 @@ def test_groups_are_created_once_per_partition(monkeypatch):
 
     monkeypatch.setattr(_joint, "_partition_cache", {})
     monkeypatch.setattr(dist, "new_subgroups_by_enumeration", fake)
-    world = object()
-    monkeypatch.setattr(dist.group, "WORLD", world, raising=False)
     part = _joint._components(8, DP + ROW)
     a = _joint._group_for_partition(part)
     b = _joint._group_for_partition(_joint._components(8, [[0, 2, 4, 6], [1, 3, 5, 7]]))   # other lists, same partition
     assert a == b == "group 1" and made == [part]
     assert _joint._group_for_partition(DP) == "group 2" and made == [part, DP]
-    assert _joint._group_for_partition([list(range(8))]) is world and len(made) == 2        # every rank: the world, no new group
+    assert _joint._group_for_partition([list(range(8))]) is dist.group.WORLD and len(made) == 2   # every rank: the world, no new group
