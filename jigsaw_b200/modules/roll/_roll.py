@@ -95,13 +95,19 @@ class DistributedRoll(torch.nn.Module):
             raise ValueError("shifts and dims must have the same length")
         self.device, self.dtype = torch.device(device), dtype
         self.config = config or RollConfig(self.device)
+        if len(_tuple(distributed_dims)) != len(tuple(spatial_groups)):
+            raise ValueError("distributed_dims and spatial_groups must align: one process group (or None) per distributed dimension")
         self.reshard(distributed_dims, spatial_groups)
 
     def reshard(self, distributed_dims: Sequence[int], spatial_groups: Sequence[dist.ProcessGroup]) -> None:
         """Re-bind the module to other process groups."""
         distributed_dims, spatial_groups = _tuple(distributed_dims), tuple(spatial_groups)
         if len(distributed_dims) != len(spatial_groups):
-            raise ValueError("distributed_dims and spatial_groups must have the same length")
+            raise ValueError(f"distributed_dims and spatial_groups have mismatched lengths ({len(distributed_dims)} and {len(spatial_groups)})")
+        stray = [d for d in distributed_dims if d not in self.dims]
+        if stray:
+            raise ValueError(f"every distributed dimension must appear in dims={self.dims}: a dimension that is not rolled "
+                             f"needs no exchange (got {stray})")
         self.distributed_dims, self.spatial_groups = distributed_dims, spatial_groups
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
