@@ -129,11 +129,18 @@ class RingAttentionConfig:
             raise ValueError("offload=CPU keeps arrived chunks on the host, which needs save_scope=GLOBAL")
         if self.offload is Offload.CPU and self.device.type != "cuda":
             raise ValueError("offload=CPU needs a CUDA device")
-        if self.send_op in (SendOp.HYBRID, SendOp.HYBRID_BROADCAST) and self.intra_size < 1:
-            raise ValueError("hybrid topologies need intra_size >= 1")
+        if self.intra_size < 1:
+            raise ValueError(f"intra_size must be a positive number of ranks per intra group, got {intra_size}")
         self._layer_key: dict = {}
         self._comm_stream: Any = None
         self._offloader: Any = None
+
+    def __repr__(self) -> str:
+        """Every policy by name, so that a log line or an error message says how the ring is run."""
+        fields = ("send_in_forward", "send_op", "save_for_backward", "save_scope", "send_backward", "offload", "attn_backend")
+        policies = ", ".join(f"{name}={getattr(self, name).name}" for name in fields)
+        return (f"RingAttentionConfig(device={str(self.device)!r}, {policies}, intra_size={self.intra_size}, "
+                f"overlap_comm={self.overlap_comm}, comm={str(self.comm)!r}, outer_comm={str(self.outer_comm)!r})")
 
     @property
     def comm_stream(self) -> Any:
