@@ -31,56 +31,57 @@ def set_all_seeds(seed: int = 0) -> None:
 
 @dataclass(frozen=True)
 class LaunchEnv:
-    """Resolved launch parameters of this process."""
+    """Where this process sits in the job and how the ranks find each other."""
 
     rank: int
     world_size: int
     local_rank: int
     master_addr: str
     master_port: str
-    source: str  # "slurm" | "torchrun" | "single"
+    source: str  # which launcher's variables were found: "slurm", "torchrun" or "single"
+
+
+# launcher name -> the variables that carry (rank, world size, local rank); the first launcher whose rank
+# variable is set wins, so an srun step started from inside a torchrun shell is read as Slurm
+_LAUNCHERS = (
+    ("slurm", ("SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID")),
+    ("torchrun", ("RANK", "WORLD_SIZE", "LOCAL_RANK")),
+)
 
 
 def _first_slurm_host(nodelist: str) -> str:
-    out = subprocess.check_output(["scontrol", "show", "hostnames", nodelist])
-    return out.decode().splitlines()[0].strip()
+    hosts = subprocess.check_output(["scontrol", "show", "hostnames", nodelist]).decode().split()
+    return hosts[0]
 
 
 def resolve_launch_env(strict: bool = False) -> LaunchEnv:
-    """Read rank / world size / local rank from the environment.
+    """Work out rank, world size and local rank from the launcher's environment variables, and the rendezvous
+    address and port, which are also exported (``MASTER_ADDR`` / ``MASTER_PORT``) so that ``init_method="env://"``
+    finds them.
 
-    ``MASTER_ADDR`` (first SLURM node via ``scontrol`` when unset, else ``localhost``)
-    and ``MASTER_PORT`` (default 29500) are written back to ``os.environ`` so that
-    ``init_method="env://"`` works.  With ``strict`` a missing launcher raises
-    ``RuntimeError`` instead of assuming one process.
+    The address is taken as given, else it is the first host of the Slurm allocation (``scontrol show hostnames``),
+    else ``localhost``; the port defaults to 29500.  A launcher that sets only its rank variable gets a world of one
+    and local rank 0; a rank variable that is set but empty is an error of the launcher and raises ``ValueError``.
+    Without any launcher this is a single process, or a ``RuntimeError`` when ``strict`` is set.
     """
     env = os.environ
-    if env.get("SLURM_PROCID") is not None:
-        source = "slurm"
-        rank = int(env["SLURM_PROCID"])
-        world = int(env.get("SLURM_NTASKS") or 1)
-        local = int(env.get("SLURM_LOCALID") or 0)
-    elif env.get("RANK") is not None:
-        source = "torchrun"
-        rank = int(env["RANK"])
-        world = int(env.get("WORLD_SIZE") or 1)
-        local = int(env.get("LOCAL_RANK") or 0)
-    elif strict:
-        raise RuntimeError(
-            "No distributed launcher detected: expected SLURM_PROCID (srun) or RANK (torchrun) "
-            "in the environment. Launch with srun or torchrun, or pass strict=False for a "
-            "single-process run."
-        )
+    for source, (rank_var, world_var, local_var) in _LAUNCHERS:
+        if rank_var in env:
+            rank = int(env[rank_var])
+            world = int(env.get(world_var) or 1)
+            local = int(env.get(local_var) or 0)
+            break
     else:
+        if strict:
+            raise RuntimeError(
+                "No distributed launcher detected: expected SLURM_PROCID (srun) or RANK (torchrun) "
+                "in the environment. Launch with srun or torchrun, or pass strict=False for a "
+                "single-process run."
+            )
         source, rank, world, local = "single", 0, 1, 0
-
-    addr = env.get("MASTER_ADDR", "")
-    if not addr:
-        nodelist = env.get("SLURM_JOB_NODELIST", "")
-        addr = _first_slurm_host(nodelist) if nodelist else "localhost"
-    port = env.get("MASTER_PORT", "29500")
-    env["MASTER_ADDR"] = addr
-    env["MASTER_PORT"] = port
+    addr = env.get("MASTER_ADDR") or (_first_slurm_host(env["SLURM_JOB_NODELIST"]) if env.get("SLURM_JOB_NODELIST") else "localhost")
+    port = env.get("MASTER_PORT") or "29500"
+    env["MASTER_ADDR"], env["MASTER_PORT"] = addr, port
     return LaunchEnv(rank, world, local, addr, port, source)
 
 
