@@ -1,5 +1,14 @@
 """Distributed layers, losses, metrics and their configuration objects.
 
+Each sub-package holds one family and documents it: ``linear`` (tensor-parallel linear layers and block
+products), ``convolution`` (domain- and channel-parallel convolutions with halo exchange), ``attention`` (ring
+and Ulysses sequence parallelism), ``normalization``, ``activation``, ``roll``, ``permute``, ``loss`` and
+``metrics``; ``functional`` gathers the function forms.  The layer classes and configuration objects are also
+importable from here, and ``CommOp`` names the transport of the neighbour exchanges that most of them accept as
+``comm=``.  Every layer takes the process groups it is cut over as constructor arguments (``None`` meaning "not
+cut"), converts from and to its ``torch.nn`` counterpart, and can be moved between meshes with
+``reshard_parameters``.
+
 Reference parity: jigsaw/modules/__init__.py:61-112.
 """
 
@@ -41,52 +50,8 @@ from .metrics import DistributedSegmentationMetrics
 from .normalization import DistributedGroupNorm, DistributedLayerNorm
 from .roll import DistributedRoll, Roll, RollConfig
 
-__all__ = [
-    "Attention",
-    "DistributedAttention",
-    "DistributedConv1d",
-    "DistributedConv2d",
-    "DistributedConv3d",
-    "DistributedConvTranspose1d",
-    "DistributedConvTranspose2d",
-    "DistributedConvTranspose3d",
-    "DistributedGroupNorm",
-    "DistributedLayerNorm",
-    "DistributedLinear",
-    "DistributedMatMulXTW",
-    "DistributedMatMulXW",
-    "DistributedMatMulXWT",
-    "DistributedRoll",
-    "DistributedSoftmax",
-    "MatMulXTW",
-    "MatMulXW",
-    "MatMulXWT",
-    "Roll",
-    "DistributedBCELoss",
-    "DistributedBCEWithLogitsLoss",
-    "DistributedCrossEntropyLoss",
-    "DistributedL1Loss",
-    "DistributedMSELoss",
-    "DistributedNLLLoss",
-    "DistributedSmoothL1Loss",
-    "DistributedSegmentationMetrics",
-    "ConvNdConfig",
-    "ConvTransposeNdConfig",
-    "LinearConfig",
-    "RingAttentionConfig",
-    "RollConfig",
-    "CommOp",
-    "functional",
-    "activation",
-    "attention",
-    "convolution",
-    "linear",
-    "loss",
-    "metrics",
-    "normalization",
-    "permute",
-    "roll",
-]
+# everything imported above is public: the ten sub-packages, the layer and configuration classes, and CommOp
+__all__ = sorted(name for name in dir() if not name.startswith("_") and name != "set_module")
 
-set_module(globals(), [n for n in __all__ if n not in ("CommOp",)])
+set_module(globals(), [name for name in __all__ if name != "CommOp"])
 CommOp.__module__ = __name__
