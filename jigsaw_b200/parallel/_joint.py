@@ -200,7 +200,7 @@ def _require_hook(state: JointCommHookState) -> None:
         raise RuntimeError(
             "a JointCommHookState was built for this DDP but joint_comm_hook is not registered on "
             "it; without the hook the replicated gradients are never summed. Use "
-            "jigsaw.parallel.register_joint_comm_hook(ddp)."
+            "jigsaw_b200.parallel.register_joint_comm_hook(ddp)."
         )
 
 
