@@ -396,8 +396,11 @@ class DistributedAttention(torch.nn.Module):
         return t.reshape(3 * heads * hd, *rest).contiguous()
 
     def get_parameter_count(self) -> int:
-        """Parameters owned directly (the q/k norms); the projections report their own."""
-        return 4 * self.head_dim if self.qk_norm else 0
+        """Parameters this module answers for: the q/k norms, and the projections where they are plain
+        ``torch.nn.Linear`` (channel group of one rank); distributed projections report their own."""
+        plain = sum(p.numel() for proj in (self.qkv, self.head_concat) if isinstance(proj, torch.nn.Linear)
+                    for p in proj.parameters())
+        return plain + (4 * self.head_dim if self.qk_norm else 0)
 
     def extra_repr(self) -> str:
         return (
