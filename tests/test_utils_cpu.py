@@ -27,6 +27,47 @@ def test_preallocated_buffers_are_cached_per_call_site():
     assert not buffers._cache
 
 
+def test_buffer_cache_keys_and_growth():
+    """What tells two buffers apart: the calling line, the dtype, the device and the index; not the shape."""
+    from jigsaw_b200._core import buffers
+
+    buffers.clear_preallocated_buffers()
+    try:
+        first = buffers.preallocated_buffer((3, 3), torch.float32, "cpu")
+        second = buffers.preallocated_buffer((3, 3), torch.float32, "cpu")       # another line: its own storage
+        assert first.data_ptr() != second.data_ptr() and not first.any() and first.shape == (3, 3)
+        first.fill_(1.0)
+        second.fill_(2.0)
+        assert bool((first == 1.0).all()) and bool((second == 2.0).all())
+
+        def site(shape=(8,), dtype=torch.float32, device="cpu", index=0):
+            return buffers.preallocated_buffer(shape, dtype, device, index, depth=1)
+
+        before = len(buffers._cache)
+        a = site()
+        assert len(buffers._cache) == before + 1
+        for _ in range(50):
+            assert site().data_ptr() == a.data_ptr()                              # steady state: no new storage
+        assert len(buffers._cache) == before + 1
+        assert site(dtype=torch.float64).data_ptr() != a.data_ptr() and site(dtype=torch.float64).dtype == torch.float64
+        assert site(index=1).data_ptr() != a.data_ptr()
+        assert site(device="meta").device.type == "meta"
+        assert len(buffers._cache) == before + 4
+        # one entry serves every shape asked for at the line: grown once, then trimmed views of it
+        big = site((4, 16))
+        assert big.shape == (4, 16) and not big.any() and big.data_ptr() != a.data_ptr()
+        big.fill_(7.0)
+        small = site((2, 3))
+        assert small.data_ptr() == big.data_ptr() and float(small.sum()) == 42.0   # contents are the caller's business
+        assert float(site((2, 3), ).sum()) == 42.0
+        assert len(buffers._cache) == before + 4
+        volume = site((2, 3, 4))
+        volume[1, 2, 3] = 5.0
+        assert float(volume[1, 2, 3]) == 5.0 and volume.is_contiguous()
+    finally:
+        buffers.clear_preallocated_buffers()
+
+
 def test_offloader_is_transparent_on_cpu():
     from jigsaw_b200._core.offload import ActivationOffloader
 
