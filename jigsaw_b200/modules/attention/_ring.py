@@ -30,6 +30,7 @@ import torch
 import torch.distributed as dist
 
 from ..._core.comm import sparse_exchange
+from ..._core.vmap import to_front
 from ._config import Offload, RingAttentionConfig, SaveScope, SendBackward, SendForward, SendOp
 from ._cores import chunk_seed, merge_chunks, select_core
 
@@ -130,10 +131,15 @@ def _project_kv(x: torch.Tensor, w_qkv: torch.Tensor, heads: int) -> tuple[torch
 
 
 class _RingAttention(torch.autograd.Function):
+    """``forward`` leaves what the backward pass needs besides inputs and output (the circulated payload, the
+    log-sum-exp, the kept chunks, the dropout states) in ``stash``, a dict that the caller passes in empty;
+    ``setup_context`` moves it onto ``ctx``.  ``vmap`` puts the ensemble axis in front of the batch axes and
+    applies the Function once to the whole stack: the schedule only looks at the last three axes."""
+
     @staticmethod
     def forward(
-        ctx: Any, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, x: torch.Tensor | None, w_qkv: torch.Tensor | None,
-        scale: float, dropout_p: float, group: dist.ProcessGroup, cfg: RingAttentionConfig, save_chunks: bool,
+        q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, x: torch.Tensor | None, w_qkv: torch.Tensor | None,
+        scale: float, dropout_p: float, group: dist.ProcessGroup, cfg: RingAttentionConfig, save_chunks: bool, stash: dict,
     ) -> torch.Tensor:
         core = select_core(cfg.attn_backend)
         send_x = cfg.send_in_forward is SendForward.X and x is not None and w_qkv is not None
@@ -168,15 +174,36 @@ class _RingAttention(torch.autograd.Function):
             cfg.wait_offloads()
         result = out.to(q.dtype)
         if save_chunks:
-            ctx.save_for_backward(q, payload, result, lse, w_qkv if send_x else None)
-            ctx.saved_chunks = saved if keep_all else None
-            ctx.rng, ctx.scale, ctx.dropout_p = rng, scale, dropout_p
-            ctx.group, ctx.cfg, ctx.send_x, ctx.heads = group, cfg, send_x, heads
+            stash.update(payload=payload, lse=lse, saved_chunks=saved if keep_all else None, rng=rng, send_x=send_x, heads=heads)
         return result
 
     @staticmethod
+    def setup_context(ctx: Any, inputs: tuple, output: torch.Tensor) -> None:
+        q, _, _, _, w_qkv, scale, dropout_p, group, cfg, _, stash = inputs
+        if not stash:                                   # forward ran without grad mode: nothing was kept
+            return
+        ctx.save_for_backward(q, output, w_qkv if stash["send_x"] else None)
+        ctx.payload, ctx.lse, ctx.saved_chunks, ctx.rng = stash["payload"], stash["lse"], stash["saved_chunks"], stash["rng"]
+        ctx.send_x, ctx.heads = stash["send_x"], stash["heads"]
+        ctx.scale, ctx.dropout_p, ctx.group, ctx.cfg = scale, dropout_p, group, cfg
+        stash.clear()
+
+    @staticmethod
+    def vmap(info: Any, in_dims: tuple, q, k, v, x, w_qkv, scale, dropout_p, group, cfg, save_chunks, stash) -> tuple:
+        n = info.batch_size
+        if in_dims[4] is not None:
+            # one projection weight per member: K and V were projected per member by the caller and carry the
+            # gradient to ``x`` and the weights, so they circulate instead of the layer input
+            x = w_qkv = None
+        q, k, v = (to_front(t, d, n).contiguous() for t, d in zip((q, k, v), in_dims[:3]))
+        x = None if x is None else to_front(x, in_dims[3], n).contiguous()
+        out = _RingAttention.apply(q, k, v, x, w_qkv, scale, dropout_p, group, cfg, save_chunks, {})
+        return out, 0
+
+    @staticmethod
     def backward(ctx: Any, dout: torch.Tensor) -> tuple:
-        q, payload, out, lse, w_qkv = ctx.saved_tensors
+        q, out, w_qkv = ctx.saved_tensors
+        payload, lse = ctx.payload, ctx.lse
         cfg, group = ctx.cfg, ctx.group
         core = select_core(cfg.attn_backend)
         fetch = _Fetcher(payload, group, cfg)
@@ -227,8 +254,8 @@ class _RingAttention(torch.autograd.Function):
             dist.all_reduce(gathered, op=dist.ReduceOp.SUM, group=group)
             d_own = gathered[me]
         if ctx.send_x:
-            return dq.to(q.dtype), None, None, d_own.to(payload.dtype), dw.to(w_qkv.dtype), None, None, None, None, None
-        return dq.to(q.dtype), d_own[0].to(payload.dtype), d_own[1].to(payload.dtype), None, None, None, None, None, None, None
+            return dq.to(q.dtype), None, None, d_own.to(payload.dtype), dw.to(w_qkv.dtype), None, None, None, None, None, None
+        return dq.to(q.dtype), d_own[0].to(payload.dtype), d_own[1].to(payload.dtype), None, None, None, None, None, None, None, None
 
 
 def ring_attention(
@@ -250,7 +277,7 @@ def ring_attention(
         out = attention_fused.maybe_fused_ring_attention(q, k, v, scale, group, dropout_p)
         if out is not None:
             return out
-    return _RingAttention.apply(q, k, v, x, w_qkv, scale, dropout_p, group, cfg, torch.is_grad_enabled())
+    return _RingAttention.apply(q, k, v, x, w_qkv, scale, dropout_p, group, cfg, torch.is_grad_enabled(), {})
 
 
 _subgroup_cache: dict[tuple, tuple[dist.ProcessGroup, dist.ProcessGroup]] = {}

@@ -120,3 +120,54 @@ def _worker_nested_vmap(rank, world):
 
 def test_nested_vmap():
     run_distributed(_worker_nested_vmap, 4)
+
+
+def _worker_linear_members_nested(rank, world):
+    """Member weights at one ``vmap`` level and the input at another, in both orders, and member weights at both
+    levels (a grid of members): each equals the loops over the same members and inputs."""
+    import jigsaw_b200 as jb
+    from torch.func import functional_call, stack_module_state
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    row, col, model = mesh["row"], mesh["col"], mesh["model"]
+    E, B = 3, 2
+
+    def layer(seed):
+        jb.launch.set_all_seeds(seed * 13 + model.rank())
+        lin = jb.modules.DistributedLinear(8, 12, "cpu", model, row, col)
+        jb.parallel.broadcast_replicas(lin)
+        return lin
+
+    members = [layer(s) for s in range(E)]
+    base = layer(50)
+    params, _ = stack_module_state(members)
+    params = {k: v.detach().clone().requires_grad_(True) for k, v in params.items()}
+    x = torch.randn(E, B, 2, 5, 4, generator=torch.Generator().manual_seed(rank))
+
+    def call(p, xi):
+        return functional_call(base, p, (xi,))
+
+    want = torch.stack([torch.stack([m(xi) for xi in x[e]]) for e, m in enumerate(members)])
+    got = torch.vmap(lambda p, xe: torch.vmap(lambda xi: call(p, xi))(xe))(params, x)
+    assert_close(got, want, "members outside, inputs inside", 1e-5, 1e-6)
+    g = torch.randn(want.shape, generator=torch.Generator().manual_seed(9 + rank))
+    (got * g).sum().backward()
+    (want * g).sum().backward()
+    named = dict(base.named_parameters())
+    for n, p in params.items():
+        jb.parallel.mark_replicated(p, jb.parallel.replica_groups(named[n]))
+    jb.parallel.reduce_replica_grads(params.values())
+    for n, p in params.items():
+        assert_close(p.grad, torch.stack([dict(m.named_parameters())[n].grad for m in members]), f"gradient of {n}", 1e-4, 1e-5)
+    # inputs outside, members inside
+    got = torch.vmap(lambda xb: torch.vmap(call)(params, xb))(x.transpose(0, 1))
+    assert_close(got, want.transpose(0, 1), "inputs outside, members inside", 1e-5, 1e-6)
+    # a grid of members: weights batched at both levels
+    grid = {k: torch.stack([v.detach(), 2 * v.detach()], 1) for k, v in params.items()}          # (E, 2, ...)
+    got = torch.vmap(torch.vmap(call))(grid, x)
+    scaled = torch.stack([want[:, 0], 2 * torch.stack([m(x[e, 1]) for e, m in enumerate(members)])], 1)
+    assert_close(got, scaled, "members at both levels", 1e-5, 1e-6)
+
+
+def test_linear_member_weights_at_either_vmap_level():
+    run_distributed(_worker_linear_members_nested, 4)
