@@ -5,8 +5,8 @@ products), ``convolution`` (domain- and channel-parallel convolutions with halo 
 and Ulysses sequence parallelism), ``normalization``, ``activation``, ``roll``, ``permute``, ``loss`` and
 ``metrics``; ``functional`` gathers the function forms.  The layer classes and configuration objects are also
 importable from here, and ``CommOp`` names the transport of the neighbour exchanges that most of them accept as
-``comm=``.  Every layer takes the process groups it is cut over as constructor arguments (``None`` meaning "not
-cut"), converts from and to its ``torch.nn`` counterpart, and can be moved between meshes with
+``comm=``.  Every layer takes the process groups it is cut over as constructor arguments (for a spatial
+axis, a loss, a metric, a norm's spatial cut, a softmax and the block products ``None`` means "not cut"), converts from and to its ``torch.nn`` counterpart, and can be moved between meshes with
 ``reshard_parameters``.
 
 Reference parity: jigsaw/modules/__init__.py:61-112.

@@ -31,7 +31,7 @@ class LinearConfig:
 
     def __init__(
         self,
-        model_group: dist.ProcessGroup,
+        model_group: dist.ProcessGroup | None,
         *,
         linear_layer: bool = True,
         device: torch.device | str = "cuda",
@@ -40,7 +40,7 @@ class LinearConfig:
         self.device = torch.device(device)
         self.comm = resolve_comm_op(comm, self.device)
         self.linear_layer = linear_layer
-        self.model_size = model_group.size()
+        self.model_size = 1 if model_group is None else model_group.size()          # None: a single process
         self._layer_key = {"model group size": self.model_size, "linear_layer": linear_layer}
         self.vmapped = False
 

@@ -163,10 +163,15 @@ def _local_product(a: torch.Tensor, b: torch.Tensor, a_t: bool, b_t: bool) -> to
     return torch.matmul(a.transpose(-1, -2) if a_t else a, b.transpose(-1, -2) if b_t else b)
 
 
-def block_matmul(kind: str, x: torch.Tensor, w: torch.Tensor, group: dist.ProcessGroup, R: int, C: int,
+def block_matmul(kind: str, x: torch.Tensor, w: torch.Tensor, group: dist.ProcessGroup | None, R: int, C: int,
                  comm: CommOp | str = "auto") -> torch.Tensor:
-    """Generic block product for a bare model group (the ``DistributedMatMul*`` modules)."""
+    """Generic block product for a bare model group (the ``DistributedMatMul*`` modules).  ``group=None`` is a
+    single process that holds both operands whole."""
     x, w = cast_to_autocast_dtype(x, w)
+    if kind not in ("xwt", "xw", "xtw"):
+        raise ValueError(kind)
+    if group is None:
+        return _local_product(x, w, kind == "xtw", kind == "xwt")
     xh, xw_, wh, ww = x.shape[-2], x.shape[-1], w.shape[-2], w.shape[-1]
     if kind == "xwt":          # X (M/R, K/C), W (N/R, K/C): rows i of X, the N/C rows of W that make output block j
         n = wh * R // C

@@ -251,16 +251,17 @@ class DistributedLinear(torch.nn.Module):
 class _DistributedMatMul(torch.nn.Module):
     _kind = "xwt"
 
-    def __init__(self, device: torch.device | str, model_group: dist.ProcessGroup, config: LinearConfig | None = None,
+    def __init__(self, device: torch.device | str, model_group: dist.ProcessGroup | None, config: LinearConfig | None = None,
                  *, local_rank: int | None = None) -> None:
         super().__init__()
         if local_rank is not None:
             warnings.warn("local_rank is deprecated and ignored", DeprecationWarning, stacklevel=2)
         self.device = torch.device(device)
-        self.model_group = model_group
-        self.grid = default_grid(model_group.size())
+        self.model_group = model_group                      # None: a single process, no process group needed
+        size = 1 if model_group is None else model_group.size()
+        self.grid = default_grid(size)
         if config is not None:
-            check_config(config, {"model group size": model_group.size(), "linear_layer": False})
+            check_config(config, {"model group size": size, "linear_layer": False})
         self.config = config or LinearConfig(model_group, linear_layer=False, device=self.device)
 
     def forward(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
