@@ -114,3 +114,42 @@ def test_metrics_on_four_ranks(axes):
 
 def test_metrics_on_eight_ranks():
     run_distributed(_worker_metrics, 8, (("row", 4), ("col", 2)), timeout=300)
+
+
+def test_single_process_paths():
+    """No group at all: logits recognised by their extra axis, the explicit switch either way, a module without
+    parameters whose running matrix adds up over calls (reference: tests/modules/metrics/test_segmentation_local.py)."""
+    from jigsaw_b200.modules.metrics import DistributedSegmentationMetrics, distributed_confusion_matrix
+
+    gen = torch.Generator().manual_seed(0)
+    logits = torch.randn(N, C, 5, 3, generator=gen)
+    target = torch.randint(0, C, (N, 5, 3), generator=gen)
+    want = _ref_confusion(logits, target)
+    assert torch.equal(distributed_confusion_matrix(logits, target, C), want)
+    assert torch.equal(distributed_confusion_matrix(logits, target, C, pred_is_logits=True), want)
+    assert torch.equal(distributed_confusion_matrix(logits.argmax(1), target, C, pred_is_logits=False), want)
+    assert torch.equal(distributed_confusion_matrix(logits.argmax(1), target, C), want)               # indices: same rank as the target
+    moved = logits.movedim(1, -1)                                                                       # classes last
+    assert torch.equal(distributed_confusion_matrix(moved, target, C, dim=-1), want)
+    metric = DistributedSegmentationMetrics(C)
+    assert metric.get_parameter_count() == 0 and not list(metric.parameters()) and not metric.state_dict()
+    metric(logits, target)
+    metric.update(logits, target)
+    assert torch.equal(metric.confusion, 2 * want)
+    assert abs(float(metric.compute()["pixel_accuracy"]) - float(_ref_metrics(want)["pixel_accuracy"])) < 1e-12
+    metric.reset()
+    assert int(metric.confusion.sum()) == 0
+
+
+def _worker_one_group_for_a_sequence(rank, world):
+    import torch.distributed as dist
+    from jigsaw_b200.modules.metrics import distributed_confusion_matrix
+
+    gen = torch.Generator().manual_seed(0)
+    logits, target = torch.randn(N, C, 5, 3, generator=gen), torch.randint(0, C, (N, 5, 3), generator=gen)
+    got = distributed_confusion_matrix(logits, target, C, reduce_groups=dist.group.WORLD)               # a group, not a list of groups
+    assert torch.equal(got, world * _ref_confusion(logits, target))                                    # every rank held the same data
+
+
+def test_a_single_group_where_a_sequence_is_expected():
+    run_distributed(_worker_one_group_for_a_sequence, 2)
