@@ -289,3 +289,32 @@ def _worker_attention_reshard(rank, world):
 
 def test_attention_reshard_over_meshes():
     run_distributed(_worker_attention_reshard, 4)
+
+
+def _worker_ulysses_exchange(rank, world):
+    """The two exchanges of Ulysses on their own: sequence pieces become head pieces and back."""
+    import torch.distributed as dist
+    from jigsaw_b200.modules.attention._ulysses import heads_to_seq, seq_to_heads
+
+    group = dist.group.WORLD
+    b, s_local, heads, d = 2, 3, 2 * world, 5
+    x = torch.randn(b, s_local, heads, d, generator=torch.Generator().manual_seed(rank), dtype=torch.float64)
+    whole_seq = seq_to_heads(x, group)                                   # (b, s, heads / P, d)
+    assert tuple(whole_seq.shape) == (b, s_local * world, heads // world, d)
+    everyone = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(everyone, x)
+    mine = slice(rank * (heads // world), (rank + 1) * (heads // world))
+    want = torch.cat([piece[:, :, mine] for piece in everyone], dim=1)  # sequence in rank order, my window of heads
+    assert_close(whole_seq, want, "sequence gathered, heads scattered", 0, 0)
+    assert_close(heads_to_seq(whole_seq, group), x, "there and back", 0, 0)
+    stacked = torch.stack((x, 2 * x, 3 * x))                             # q, k, v in one exchange
+    got = seq_to_heads(stacked, group)
+    assert_close(got, torch.stack((want, 2 * want, 3 * want)), "stacked q, k, v", 0, 0)
+    leaf = x.clone().requires_grad_(True)
+    seed = torch.randn(whole_seq.shape, generator=torch.Generator().manual_seed(50 + rank), dtype=torch.float64)
+    (grad,) = torch.autograd.grad(seq_to_heads(leaf, group), leaf, seed)
+    assert_close(grad, heads_to_seq(seed, group), "the backward of one exchange is the other", 0, 0)
+
+
+def test_ulysses_exchanges_round_trip():
+    run_distributed(_worker_ulysses_exchange, 4)
