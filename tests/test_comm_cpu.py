@@ -78,3 +78,20 @@ def _worker_exchange(rank, world):
 @pytest.mark.parametrize("world", [2, 4])
 def test_sparse_exchange_and_ring_shift(world):
     run_distributed(_worker_exchange, world, timeout=300)
+
+
+def test_backend_names_that_are_accepted_and_refused(monkeypatch):
+    """The backend check reads the group's backend string: plain names, the per-device form of a group that runs
+    gloo on the CPU and NCCL on the GPUs, and anything else (which would take the NCCL code paths and hang)."""
+    import torch.distributed as dist
+    from jigsaw_b200._core import comm
+
+    for name, want in (("gloo", {"gloo"}), ("nccl", {"nccl"}), ("cpu:gloo,cuda:nccl", {"gloo", "nccl"})):
+        monkeypatch.setattr(dist, "get_backend", lambda group=None, name=name: name)
+        assert comm.check_backend() == want
+    monkeypatch.setattr(dist, "get_backend", lambda group=None: "gloo")
+    assert comm.get_device_of_process_group() == torch.device("cpu")
+    for name in ("mpi", "ucc", "cpu:gloo,cuda:ucc"):
+        monkeypatch.setattr(dist, "get_backend", lambda group=None, name=name: name)
+        with pytest.raises(RuntimeError, match="unsupported process-group backend"):
+            comm.check_backend()
