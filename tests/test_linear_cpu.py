@@ -157,3 +157,35 @@ def _worker_layouts(rank, world):
 
 def test_layouts_initialisation_conversion_and_training():
     run_distributed(_worker_layouts, 4, timeout=600)
+
+
+def _worker_config_mismatch(rank, world):
+    """A configuration object belongs to one kind of layer on one group size; a failed re-shard changes nothing
+    (reference: tests/modules/linear/test_config_checks.py:113-170)."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.linear import LinearConfig
+
+    m22, m14 = jb.make_process_mesh({"row": 2, "col": 2}), jb.make_process_mesh({"row": 1, "col": 4})
+    M, model, row, col = jb.modules, m22["model"], m22["row"], m22["col"]
+    refused = [
+        lambda: M.DistributedLinear(8, 8, "cpu", model, row, col, config=LinearConfig(row, device="cpu")),
+        lambda: M.DistributedLinear(8, 8, "cpu", model, row, col, config=LinearConfig(model, linear_layer=False, device="cpu")),
+        lambda: M.DistributedMatMulXW("cpu", model, LinearConfig(model, device="cpu")),
+        lambda: M.DistributedMatMulXTW("cpu", model, LinearConfig(row, linear_layer=False, device="cpu")),
+    ]
+    for build in refused:
+        with pytest.raises(ValueError, match="different layer"):
+            build()
+    M.DistributedLinear(8, 8, "cpu", model, row, col, config=LinearConfig(model, device="cpu", comm="isend"))
+    layer = M.DistributedLinear(6, 6, "cpu", model, row, col)
+    weight, bias, config = layer.weight, layer.bias, layer.config
+    with pytest.raises(ValueError, match="in_dim=6"):
+        layer.reshard_parameters(m22, m14)                       # refused before anything is gathered
+    assert layer.weight is weight and layer.bias is bias and layer.config is config and layer.model_group is model
+    x = torch.randn(3, 3)
+    assert tuple(layer(x).shape) == (3, 3)                        # and the layer still works on its old mesh
+    assert all_ok(True)
+
+
+def test_configurations_of_other_layers_and_failed_reshards():
+    run_distributed(_worker_config_mismatch, 4, timeout=300)
