@@ -65,9 +65,21 @@ def _worker_ring(rank, world):
     xr, y_ref, gy = _serial_and_grads(att, x)
     _compare(layer, att, x, xr, y_ref, gy, mesh, "ring send_in_forward=X")
     # no-grad forward keeps nothing
-    with torch.no_grad():
-        y = layer(split(x, {1: mesh["row"]}))
-    assert_close(y, split(y_ref, {1: mesh["row"]}), "ring no_grad", 1e-9, 1e-9)
+    from jigsaw_b200.modules.attention import _ring
+
+    kept = []
+    plain_setup = _ring._RingAttention.setup_context
+    _ring._RingAttention.setup_context = staticmethod(lambda ctx, inputs, output: (kept.append(dict(inputs[-1])), plain_setup(ctx, inputs, output))[1])
+    try:
+        layer(split(x, {1: mesh["row"]}).requires_grad_(True))
+        assert len(kept) == 1 and kept[0]["saved_chunks"] is not None and len(kept[0]["saved_chunks"]) == mesh["row"].size()
+        for mode in (torch.no_grad, torch.inference_mode):
+            with mode():
+                y = layer(split(x, {1: mesh["row"]}))
+            assert_close(y, split(y_ref, {1: mesh["row"]}), f"ring under {mode.__name__}", 1e-9, 1e-9)
+        assert kept[1:] == [{}, {}], "a forward pass without grad mode kept chunks for a backward pass that cannot come"
+    finally:
+        _ring._RingAttention.setup_context = plain_setup
     # guards
     with pytest.raises(ValueError):
         jb.modules.DistributedAttention(8, 16, 8, 4, 0, "cpu", mesh["col"], mesh["col"], ring=True)
