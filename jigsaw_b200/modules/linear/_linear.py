@@ -179,14 +179,14 @@ class DistributedLinear(torch.nn.Module):
                 self.bias.data = bias[j * nb : (j + 1) * nb].clone().to(self.device)
 
     def merge_weights(
-        self, from_process_mesh_dict: dict, row_kw: str = "row", col_kw: str = "col", model_kw: str = "model"
+        self, from_process_mesh: dict, row_kw: str = "row", col_kw: str = "col", model_kw: str = "model"
     ) -> tuple[torch.Tensor, torch.Tensor | None]:
         """Global weight and bias from the shards (collective over the row and column groups)."""
-        col = from_process_mesh_dict[col_kw]
+        col = from_process_mesh[col_kw]
         with torch.no_grad():
             w = gather_dim(self.weight.detach(), col, 1)
             if self.row_split > 1:
-                w = gather_dim(w, from_process_mesh_dict[row_kw], 0)
+                w = gather_dim(w, from_process_mesh[row_kw], 0)
             b = None if self.bias is None else gather_dim(self.bias.detach(), col, 0)
         return w, b
 
@@ -199,11 +199,11 @@ class DistributedLinear(torch.nn.Module):
         return layer
 
     def reshard_parameters(
-        self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, pm_row_key: str = "row", pm_col_key: str = "col",
+        self, from_process_mesh: dict, to_process_mesh: dict, pm_row_key: str = "row", pm_col_key: str = "col",
         pm_model_key: str = "model",
     ) -> None:
         """Move the layer to another mesh (collective over both).  The target layout follows the meshes when they
-        describe this layer, i.e. when ``from_process_mesh_dict[pm_model_key]`` is the layer's model group: a
+        describe this layer, i.e. when ``from_process_mesh[pm_model_key]`` is the layer's model group: a
         target whose model group is its column group (on a mesh with several rows) gives the column-only layout
         (weight replicated over the rows and marked so), any other target the row x column layout.  When the
         source mesh names another model group (a generic loop that hands every layer the whole mesh, although
@@ -211,18 +211,18 @@ class DistributedLinear(torch.nn.Module):
         def same(a: dist.ProcessGroup, b: dist.ProcessGroup) -> bool:
             return a is b or dist.get_process_group_ranks(a) == dist.get_process_group_ranks(b)
 
-        to_row, to_col = to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key]
-        from_model = from_process_mesh_dict.get(pm_model_key) if hasattr(from_process_mesh_dict, "get") else None
-        if from_model is not None and same(from_model, self.model_group) and pm_model_key in to_process_mesh_dict:
-            col_only = same(to_process_mesh_dict[pm_model_key], to_col) and to_row.size() > 1
+        to_row, to_col = to_process_mesh[pm_row_key], to_process_mesh[pm_col_key]
+        from_model = from_process_mesh.get(pm_model_key) if hasattr(from_process_mesh, "get") else None
+        if from_model is not None and same(from_model, self.model_group) and pm_model_key in to_process_mesh:
+            col_only = same(to_process_mesh[pm_model_key], to_col) and to_row.size() > 1
         else:
             col_only = self._model_is_col
-        new_model = to_col if col_only else to_process_mesh_dict[pm_model_key]
-        if (self.model_group is new_model and self.row_group is to_process_mesh_dict[pm_row_key]
-                and self.col_group is to_process_mesh_dict[pm_col_key]):
+        new_model = to_col if col_only else to_process_mesh[pm_model_key]
+        if (self.model_group is new_model and self.row_group is to_process_mesh[pm_row_key]
+                and self.col_group is to_process_mesh[pm_col_key]):
             return                                  # already there (a parent layer moved this one with itself)
-        w, b = self.merge_weights(from_process_mesh_dict, pm_row_key, pm_col_key, pm_model_key)
-        self._bind_groups(new_model, to_process_mesh_dict[pm_row_key], to_process_mesh_dict[pm_col_key])
+        w, b = self.merge_weights(from_process_mesh, pm_row_key, pm_col_key, pm_model_key)
+        self._bind_groups(new_model, to_process_mesh[pm_row_key], to_process_mesh[pm_col_key])
         self._model_is_col = col_only
         self.config = LinearConfig(new_model, linear_layer=True, device=self.device, comm=self.config.comm)
         self.weight = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))

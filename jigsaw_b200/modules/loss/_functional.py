@@ -104,18 +104,18 @@ def distributed_smooth_l1_loss(input, target, *, beta: float = 1.0, reduction: s
 
 
 # ----------------------------------------------------------------------------- binary cross-entropy
-def distributed_binary_cross_entropy(input, target, *, weight=None, reduction: str = "mean", reduce_groups=None) -> torch.Tensor:
+def distributed_binary_cross_entropy(probs, target, *, weight=None, reduction: str = "mean", reduce_groups=None) -> torch.Tensor:
     """``F.binary_cross_entropy`` (probabilities in) over a sharded tensor.  ``reduce_groups``
     must list EVERY group the tensor is split over, the channel group included."""
-    return _elementwise_loss(F.binary_cross_entropy, input, target, reduction, reduce_groups, weight=weight)
+    return _elementwise_loss(F.binary_cross_entropy, probs, target, reduction, reduce_groups, weight=weight)
 
 
 def distributed_binary_cross_entropy_with_logits(
-    input, target, *, weight=None, pos_weight=None, reduction: str = "mean", reduce_groups=None
+    logits, target, *, weight=None, pos_weight=None, reduction: str = "mean", reduce_groups=None
 ) -> torch.Tensor:
     """``F.binary_cross_entropy_with_logits`` over a sharded tensor (see the BCE note on groups)."""
     return _elementwise_loss(
-        F.binary_cross_entropy_with_logits, input, target, reduction, reduce_groups, weight=weight, pos_weight=pos_weight
+        F.binary_cross_entropy_with_logits, logits, target, reduction, reduce_groups, weight=weight, pos_weight=pos_weight
     )
 
 
@@ -135,15 +135,15 @@ def _pick_target(logp: torch.Tensor, target: torch.Tensor, dim: int, channel_gro
 
 
 def distributed_nll_loss(
-    input, target, *, weight=None, ignore_index: int = -100, reduction: str = "mean", dim: int = 1,
+    log_probs, target, *, weight=None, ignore_index: int = -100, reduction: str = "mean", dim: int = 1,
     channel_group=None, reduce_groups=None,
 ) -> torch.Tensor:
     """``F.nll_loss`` on log-probabilities whose class dimension ``dim`` is split over
     ``channel_group``; ``weight`` has the GLOBAL class count and is replicated."""
     _check_reduction(reduction)
-    dim = dim % input.dim()
-    in_dtype = input.dtype
-    logp = input.to(torch.promote_types(in_dtype, torch.float32))
+    dim = dim % log_probs.dim()
+    in_dtype = log_probs.dtype
+    logp = log_probs.to(torch.promote_types(in_dtype, torch.float32))
     picked, valid = _pick_target(logp, target, dim, channel_group, ignore_index)
     picked = redundant_all_reduce(picked, channel_group)
     if weight is not None:
@@ -158,7 +158,7 @@ def distributed_nll_loss(
 
 
 def distributed_cross_entropy(
-    input, target, *, weight=None, ignore_index: int = -100, reduction: str = "mean", label_smoothing: float = 0.0,
+    logits, target, *, weight=None, ignore_index: int = -100, reduction: str = "mean", label_smoothing: float = 0.0,
     dim: int = 1, channel_group=None, reduce_groups=None,
 ) -> torch.Tensor:
     """``F.cross_entropy`` on logits whose class dimension ``dim`` is split over
@@ -166,20 +166,20 @@ def distributed_cross_entropy(
     ``label_smoothing``, also together, with torch's rule for the combination) or class probabilities
     sharded like the logits (none of the three options)."""
     _check_reduction(reduction)
-    dim = dim % input.dim()
-    in_dtype = input.dtype
-    if input.is_cuda and not target.is_floating_point() and weight is None and label_smoothing == 0.0:
+    dim = dim % logits.dim()
+    in_dtype = logits.dtype
+    if logits.is_cuda and not target.is_floating_point() and weight is None and label_smoothing == 0.0:
         from ...ops import loss_fused
 
-        elem = loss_fused.maybe_fused_cross_entropy(input, target, dim, channel_group, ignore_index)
+        elem = loss_fused.maybe_fused_cross_entropy(logits, target, dim, channel_group, ignore_index)
         if elem is not None:
             if reduction == "none":
                 return elem.to(in_dtype)
             wt = (target != ignore_index).to(torch.float32)
             return reduce_scalar_loss(elem.sum(), wt.sum(), reduction, reduce_groups).to(in_dtype)
-    with torch.autocast(input.device.type, enabled=False):
-        logits = input.to(torch.promote_types(in_dtype, torch.float32))
-        logp = distributed_log_softmax(logits, dim, channel_group)
+    with torch.autocast(logits.device.type, enabled=False):
+        scores = logits.to(torch.promote_types(in_dtype, torch.float32))
+        logp = distributed_log_softmax(scores, dim, channel_group)
         if target.is_floating_point():
             if weight is not None or label_smoothing != 0.0 or ignore_index != -100:
                 raise NotImplementedError(

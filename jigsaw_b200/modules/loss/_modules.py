@@ -33,9 +33,9 @@ class DistributedNLLLoss(_Loss):
         self.register_buffer("weight", weight)
         self.ignore_index, self.reduction, self.dim = ignore_index, reduction, dim
 
-    def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    def forward(self, log_probs: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         return LF.distributed_nll_loss(
-            input, target, weight=self.weight, ignore_index=self.ignore_index, reduction=self.reduction,
+            log_probs, target, weight=self.weight, ignore_index=self.ignore_index, reduction=self.reduction,
             dim=self.dim, channel_group=self.channel_group, reduce_groups=self.reduce_groups,
         )
 
@@ -51,9 +51,9 @@ class DistributedCrossEntropyLoss(_Loss):
         self.ignore_index, self.reduction = ignore_index, reduction
         self.label_smoothing, self.dim = label_smoothing, dim
 
-    def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    def forward(self, logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         return LF.distributed_cross_entropy(
-            input, target, weight=self.weight, ignore_index=self.ignore_index, reduction=self.reduction,
+            logits, target, weight=self.weight, ignore_index=self.ignore_index, reduction=self.reduction,
             label_smoothing=self.label_smoothing, dim=self.dim, channel_group=self.channel_group,
             reduce_groups=self.reduce_groups,
         )
@@ -67,9 +67,9 @@ class DistributedBCELoss(_Loss):
         self.reduce_groups, self.reduction = reduce_groups, reduction
         self.register_buffer("weight", weight)
 
-    def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    def forward(self, probs: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         return LF.distributed_binary_cross_entropy(
-            input, target, weight=self.weight, reduction=self.reduction, reduce_groups=self.reduce_groups
+            probs, target, weight=self.weight, reduction=self.reduction, reduce_groups=self.reduce_groups
         )
 
 
@@ -82,9 +82,9 @@ class DistributedBCEWithLogitsLoss(_Loss):
         self.register_buffer("weight", weight)
         self.register_buffer("pos_weight", pos_weight)
 
-    def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    def forward(self, logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         return LF.distributed_binary_cross_entropy_with_logits(
-            input, target, weight=self.weight, pos_weight=self.pos_weight, reduction=self.reduction,
+            logits, target, weight=self.weight, pos_weight=self.pos_weight, reduction=self.reduction,
             reduce_groups=self.reduce_groups,
         )
 

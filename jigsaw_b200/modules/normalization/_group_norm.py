@@ -115,15 +115,18 @@ class DistributedGroupNorm(torch.nn.Module):
             if bias is not None and self.bias is not None:
                 self.bias.data = bias.detach()[r * n : (r + 1) * n].clone().to(self.device)
 
-    def merge_weights(self, process_mesh_dict: dict, col_kw: str = "col") -> tuple[torch.Tensor | None, torch.Tensor | None]:
-        g = process_mesh_dict[col_kw]
+    def merge_weights(self, from_process_mesh: dict, row_kw: str = "row", col_kw: str = "col",
+                      model_kw: str = "model") -> tuple[torch.Tensor | None, torch.Tensor | None]:
+        """All-gather the slices over the channel group (``row_kw`` and ``model_kw`` are accepted for a uniform
+        signature: the parameters are not cut over them)."""
+        g = from_process_mesh[col_kw]
         with torch.no_grad():
             w = None if self.weight is None else gather_dim(self.weight.detach(), g, 0)
             b = None if self.bias is None else gather_dim(self.bias.detach(), g, 0)
         return w, b
 
     def convert_to_torch(self, process_mesh_dict: dict, row_kw: str = "row", col_kw: str = "col", model_kw: str = "model") -> torch.nn.GroupNorm:
-        w, b = self.merge_weights(process_mesh_dict, col_kw)
+        w, b = self.merge_weights(process_mesh_dict, col_kw=col_kw)
         layer = torch.nn.GroupNorm(self.num_groups, self.num_channels, eps=self.eps, affine=self.affine, device=self.device)
         if w is not None:
             layer.weight.data = w
@@ -133,11 +136,11 @@ class DistributedGroupNorm(torch.nn.Module):
             layer.bias.data.zero_()
         return layer
 
-    def reshard_parameters(self, from_process_mesh_dict: dict, to_process_mesh_dict: dict, pm_row_key: str = "row",
+    def reshard_parameters(self, from_process_mesh: dict, to_process_mesh: dict, pm_row_key: str = "row",
                            pm_col_key: str = "col", pm_model_key: str = "model") -> None:
-        w, b = self.merge_weights(from_process_mesh_dict, pm_col_key)
-        self.channel_group = to_process_mesh_dict[pm_col_key]
-        self.spatial_groups = tuple(_as_list(to_process_mesh_dict[pm_row_key]))
+        w, b = self.merge_weights(from_process_mesh, col_kw=pm_col_key)
+        self.channel_group = to_process_mesh[pm_col_key]
+        self.spatial_groups = tuple(_as_list(to_process_mesh[pm_row_key]))
         self._resolve()
         if self.weight is not None:
             self.weight = torch.nn.Parameter(torch.empty(0, device=self.device, dtype=w.dtype))

@@ -31,6 +31,15 @@ def _entry(rank: int, world: int, init_file: str, backend: str, fn: Callable, ar
     try:
         os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"] = str(rank), str(world), str(rank)
         torch.set_num_threads(1)
+        # a rank forked from the server inherits its generators: seed them afresh, as a newly started interpreter does,
+        # so that ranks which forget to seed do differ from each other
+        import random
+        import sys
+
+        torch.seed()
+        random.seed()
+        if "numpy" in sys.modules:
+            sys.modules["numpy"].random.seed()
         if backend == "nccl":
             torch.cuda.set_device(rank)
             dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world,
@@ -53,9 +62,22 @@ def _entry(rank: int, world: int, init_file: str, backend: str, fn: Callable, ar
             pass
 
 
+def _context(backend: str) -> Any:
+    """How the ranks are started.  CPU ranks come from a fork server that has imported ``torch`` once (importing it
+    costs a rank about three seconds, most of a small test's run time); the server has run nothing, so its children
+    start from a clean state, and the library itself is imported by each rank (some tests set switches that are
+    read at import).  GPU ranks are spawned: a CUDA context must never be inherited.  ``JIGSAW_TEST_START=spawn``
+    spawns the CPU ranks as well."""
+    method = os.environ.get("JIGSAW_TEST_START", "spawn" if backend == "nccl" else "forkserver")
+    ctx = mp.get_context(method)
+    if method == "forkserver":
+        ctx.set_forkserver_preload(["torch", "torch.distributed"])
+    return ctx
+
+
 def run_distributed(fn: Callable, world: int, *args: Any, backend: str = "gloo", timeout: float = 240.0) -> None:
     """Spawn ``world`` ranks running ``fn(rank, world, *args)``; raise if any rank raised."""
-    ctx = mp.get_context("spawn")
+    ctx = _context(backend)
     queue = ctx.Queue()
     with tempfile.TemporaryDirectory() as tmp:
         init_file = os.path.join(tmp, "rendezvous")
