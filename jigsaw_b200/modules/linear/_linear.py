@@ -75,6 +75,7 @@ class DistributedLinear(torch.nn.Module):
             check_config(config, {"model group size": model_group.size(), "linear_layer": True})
         self.config = config or LinearConfig(model_group, linear_layer=True, device=self.device)
         self.global_weight_shape = (out_dim, in_dim)
+        self.global_bias_shape = (out_dim,) if bias else None
         self.weight = torch.nn.Parameter(
             torch.empty(out_dim // self.row_split, in_dim // self.col_split, device=self.device, dtype=dtype)
         )

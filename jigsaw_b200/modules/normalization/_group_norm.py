@@ -154,6 +154,15 @@ class DistributedGroupNorm(torch.nn.Module):
         cut = () if self.channel_group is None else ((0, self.channel_group),)
         return {"weight": cut, "bias": cut}
 
+    @property
+    def num_local_groups(self) -> int:
+        """Normalisation groups held by this rank (the reference's name of ``local_groups``)."""
+        return self.local_groups
+
+    @property
+    def num_local_channels(self) -> int:
+        return self.local_channels
+
     def get_parameter_count(self) -> int:
         if not self.affine:
             return 0

@@ -39,6 +39,7 @@ class DistributedLayerNorm(torch.nn.Module):
                 raise NotImplementedError("DistributedLayerNorm normalizes a single trailing dimension only")
             normalized_dim = int(tuple(normalized_dim)[0])
         self.normalized_dim = normalized_dim
+        self.local_rank = local_rank                      # kept as given; the layer takes its place from the groups
         self.device = torch.device(device)
         self.row_group, self.col_group = row_group, col_group
         self.eps = eps
@@ -52,6 +53,20 @@ class DistributedLayerNorm(torch.nn.Module):
             self.register_parameter("weight", None)
             self.register_parameter("bias", None)
         self._mark()
+
+    # the reference names the same things after what the groups cut (tokens, channels)
+    @property
+    def spatial_group(self) -> dist.ProcessGroup | None:
+        return self.row_group
+
+    @property
+    def channel_group(self) -> dist.ProcessGroup | None:
+        return self.col_group
+
+    @property
+    def local_dim(self) -> int:
+        """Features of the normalised axis held by this rank."""
+        return self.normalized_dim // (1 if self.col_group is None else self.col_group.size())
 
     def _mark(self) -> None:
         for p in self.parameters():

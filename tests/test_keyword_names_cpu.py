@@ -208,3 +208,26 @@ def test_methods_take_the_reference_keywords(cls_name):
 def test_functions_take_the_reference_keywords(fn_name):
     lost = _accepts(_find(fn_name), FUNCTIONS[fn_name])
     assert not lost, f"{fn_name}: keywords of the reference that are not accepted: {lost}"
+
+
+def _worker_attribute_names(rank, world):
+    """Attributes of the reference's layers that describe the cut (read by user code that sizes buffers or logs)."""
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    M, row, col = jb.modules, mesh["row"], mesh["col"]
+    ln = M.DistributedLayerNorm(8, mesh["model"].rank(), "cpu", row, col)
+    assert ln.local_dim == 4 and ln.spatial_group is row and ln.channel_group is col and ln.local_rank == mesh["model"].rank()
+    gn = M.DistributedGroupNorm(4, 8, "cpu", channel_group=col, spatial_group=row)
+    assert (gn.num_local_groups, gn.num_local_channels) == (2, 4)
+    lin = M.DistributedLinear(8, 12, "cpu", mesh["model"], row, col)
+    assert lin.global_weight_shape == (12, 8) and lin.global_bias_shape == (12,)
+    assert M.DistributedLinear(8, 12, "cpu", mesh["model"], row, col, bias=False).global_bias_shape is None
+
+
+def test_attributes_that_describe_the_cut():
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+
+    run_distributed(_worker_attribute_names, 4, timeout=120)
