@@ -16,7 +16,6 @@ Counterpart of the reference tutorial examples/domain_parallel.py.
 
 import sys
 
-import torch
 from torch import nn
 
 from _common import ddp_flags, denoising_batch, setup, shard, steps_flag, train

@@ -14,7 +14,7 @@ adjoints), test_layer_inputs.py (inputs of the wrong rank, configurations of ano
 import pytest
 import torch
 
-from dist_utils import all_ok, assert_close, merge, run_distributed, split
+from dist_utils import all_ok, assert_close, run_distributed, split
 from jigsaw_b200.modules.convolution import _args
 
 

@@ -138,7 +138,6 @@ def test_init_uses_global_fans():
 
 def _worker_mesh_gather_convert(rank, world):
     import jigsaw_b200 as jb
-    import torch.distributed as dist
     from jigsaw_b200.modules.attention import Attention
 
     with pytest.raises(ValueError):

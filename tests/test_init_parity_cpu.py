@@ -13,7 +13,6 @@ in one to three dimensions, overriding ``reset_parameters``).
 import math
 
 import pytest
-import torch
 
 from dist_utils import all_ok, run_distributed
 

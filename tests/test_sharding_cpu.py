@@ -14,7 +14,6 @@ tests/test_param_count.py (parameter counts with replicas counted once).
 
 import copy
 
-import pytest
 import torch
 
 from dist_utils import all_ok, assert_close, run_distributed, split
