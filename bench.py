@@ -145,7 +145,7 @@ def main() -> None:
         raise SystemExit("--gpus must be 1, 2, 4 or 8")
     rank, world, dev = init_dist(args.gpus)
     ph, pw = MESHES[args.gpus]
-    model, loss_fn, mesh = build(args.impl, (ph, pw), dev, args.model)
+    model, loss_fn, _mesh = build(args.impl, (ph, pw), dev, args.model)
     if args.impl == "ours":
         from jigsaw_b200.ops import _lib as _jb_lib
 

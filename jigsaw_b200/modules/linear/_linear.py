@@ -133,7 +133,7 @@ class DistributedLinear(torch.nn.Module):
         ``out * in / C`` elements in flight, never the whole matrix."""
         (w,) = cast_to_autocast_dtype(w)
         C, n = self.col_split, self.out_dim // self.col_split
-        h, k = w.shape
+        k = w.shape[1]
         if self.row_split > 1:
             # the weight is cut R x C over the model group (rank i * C + j holds block (i, j))
             return fetch_region(w, self.model_group, self.row_split, C, lambda p: ((p % C) * n, (p % C + 1) * n, 0, k * C),
