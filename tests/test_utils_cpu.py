@@ -135,6 +135,27 @@ def test_chunk_owner_schedules_visit_every_chunk_once():
             assert sorted(owners) == list(range(P)), (op, P, A, p, owners)
     with pytest.raises(ValueError):
         chunk_owner(SendOp.HYBRID, 0, 0, 6, 4)
+    # every ring size up to 12 with every intra size that divides it, all four schedules
+    for P in range(1, 13):
+        for A in [a for a in range(1, P + 1) if P % a == 0]:
+            for op in SendOp:
+                for p in range(P):
+                    owners = [chunk_owner(op, p, s, P, A) for s in range(P)]
+                    assert sorted(owners) == list(range(P)), (op, P, A, p, owners)
+                if op in (SendOp.RING, SendOp.HYBRID):
+                    # at each step the positions read from distinct owners: no owner serves two readers at once
+                    for step in range(P):
+                        assert len({chunk_owner(op, p, step, P, A) for p in range(P)}) == P, (op, P, A, step)
+                else:
+                    # the broadcast forms: at each step all positions of an intra group read one and the same owner
+                    for step in range(P):
+                        width = P if op is SendOp.BROADCAST else A
+                        for first in range(0, P, width):
+                            assert len({chunk_owner(op, p, step, P, A) for p in range(first, first + width)}) == 1
+                if op in (SendOp.HYBRID, SendOp.HYBRID_BROADCAST):
+                    # the first A steps stay inside the own intra group
+                    for p in range(P):
+                        assert all(chunk_owner(op, p, step, P, A) // A == p // A for step in range(A))
 
 
 def _worker_status_agreement(rank, world):
