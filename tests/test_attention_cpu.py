@@ -40,6 +40,24 @@ def _compare(layer, att, x, xr, y_ref, gy, mesh, what, tol=1e-9):
     assert_close(gq, att.qkv.weight.grad, f"{what}: dW_qkv", tol, tol)
 
 
+def _worker_ring_policies(rank, world, send_op):
+    """One schedule of visits with every way of keeping chunks, returning dK/dV and overlapping the exchange."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention, RingAttentionConfig
+
+    mesh = jb.make_process_mesh({"row": 4, "col": 1})
+    torch.manual_seed(0)
+    att = Attention(8, 16, 8, 4, "cpu", dtype=torch.float64, attn_backend="math")
+    x = torch.randn(2, 16, 8, dtype=torch.float64)
+    for scope, back, overlap in itertools.product(("local", "global"), ("send_dkv", "gather_dkv"), (False, True)):
+        cfg = RingAttentionConfig(device="cpu", send_in_forward="kv", send_op=send_op, save_scope=scope,
+                                  send_backward=back, intra_size=2, attn_backend="math", overlap_comm=overlap)
+        layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
+        att.zero_grad()
+        xr, y_ref, gy = _serial_and_grads(att, x)
+        _compare(layer, att, x, xr, y_ref, gy, mesh, f"ring {send_op}/{scope}/{back}/overlap={overlap}")
+
+
 def _worker_ring(rank, world):
     import jigsaw_b200 as jb
     from jigsaw_b200.modules.attention import Attention, RingAttentionConfig
@@ -48,16 +66,6 @@ def _worker_ring(rank, world):
     torch.manual_seed(0)
     att = Attention(8, 16, 8, 4, "cpu", dtype=torch.float64, attn_backend="math")
     x = torch.randn(2, 16, 8, dtype=torch.float64)
-    xr, y_ref, gy = _serial_and_grads(att, x)
-    combos = itertools.product(("ring", "broadcast", "hybrid", "hybrid_broadcast"), ("local", "global"),
-                               ("send_dkv", "gather_dkv"), (False, True))
-    for send_op, scope, back, overlap in combos:
-        cfg = RingAttentionConfig(device="cpu", send_in_forward="kv", send_op=send_op, save_scope=scope,
-                                  send_backward=back, intra_size=2, attn_backend="math", overlap_comm=overlap)
-        layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
-        att.zero_grad()
-        xr, y_ref, gy = _serial_and_grads(att, x)
-        _compare(layer, att, x, xr, y_ref, gy, mesh, f"ring {send_op}/{scope}/{back}/overlap={overlap}")
     # the layer input circulates and K/V are re-projected on arrival
     cfg = RingAttentionConfig(device="cpu", send_in_forward="x", attn_backend="math")
     layer = Attention.convert_to_jigsaw(att, mesh, "cpu", ring=True, config=cfg, attn_backend="math")
@@ -141,7 +149,12 @@ def _worker_heads(rank, world):
     assert "ring=False" in repr(conv) and conv.get_parameter_count() == 0
 
 
-def test_ring_attention_all_policies():
+@pytest.mark.parametrize("send_op", ["ring", "broadcast", "hybrid", "hybrid_broadcast"])
+def test_ring_attention_policies(send_op):
+    run_distributed(_worker_ring_policies, 4, send_op, timeout=400)
+
+
+def test_ring_with_circulating_input_without_grad_and_guards():
     run_distributed(_worker_ring, 4, timeout=400)
 
 
