@@ -22,7 +22,7 @@ def _dense(kind, X, W):
     return X.transpose(-1, -2) @ W
 
 
-def _worker_matmul_kinds(rank, world, comm):
+def _worker_matmul_kinds(rank, world, comm, kind):
     import jigsaw_b200 as jb
     from jigsaw_b200.modules.linear import LinearConfig
 
@@ -34,7 +34,7 @@ def _worker_matmul_kinds(rank, world, comm):
     M, K, N = 8 * R * C, 4 * R * C, 2 * R * C            # every dimension divides by R, C and R * C
     shapes = {"xwt": ((2, M, K), (2, N, K)), "xw": ((2, M, K), (2, K, N)), "xtw": ((2, K, M), (2, K, N))}
     classes = {"xwt": jb.modules.DistributedMatMulXWT, "xw": jb.modules.DistributedMatMulXW, "xtw": jb.modules.DistributedMatMulXTW}
-    for kind, (sx, sw) in shapes.items():
+    for kind, (sx, sw) in ((kind, shapes[kind]),):
         for frozen in (None, "x", "w"):
             X = torch.randn(*sx, dtype=torch.float64)
             W = torch.randn(*sw, dtype=torch.float64)
@@ -60,8 +60,9 @@ def _worker_matmul_kinds(rank, world, comm):
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("comm", ["batch_isend_irecv", "isend"])
-def test_matmul_kinds_on_reference_grids(world, comm):
-    run_distributed(_worker_matmul_kinds, world, comm, timeout=300)
+@pytest.mark.parametrize("kind", ["xwt", "xw", "xtw"])
+def test_matmul_kinds_on_reference_grids(kind, world, comm):
+    run_distributed(_worker_matmul_kinds, world, comm, kind, timeout=300)
 
 
 def _worker_linear_any_grid(rank, world, R, C):
