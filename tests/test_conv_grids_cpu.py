@@ -146,3 +146,50 @@ def _worker_frozen(rank, world):
 
 def test_frozen_operands_skip_their_collectives():
     run_distributed(_worker_frozen, 4, timeout=600)
+
+
+STRING_PADDINGS = {"valid_patchify": (2, 2, "valid", 1), "same_k1": (1, 1, "same", 1), "same_k3": (3, 1, "same", 1),
+                   "same_k3_dilated": (3, 1, "same", 2), "same_k5": (5, 1, "same", 1)}
+CHANNEL_COMMS = ("all_gather", "isend", "batch_isend_irecv")
+
+
+def _worker_string_padding(rank, world, axes, name):
+    """``padding="valid"`` / ``"same"`` on a layer cut in space and channels, with every way of moving channels,
+    against the undivided layer given the same string (reference: tests/modules/convolution/conv/
+    test_convolution_2d.py:755-824)."""
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh(axes)
+    mesh["sd"] = mesh["sh"] = None
+    mesh["sw"] = mesh["row"]
+    k, s, p, d = STRING_PADDINGS[name]
+    C = mesh["col"].size()
+    for channel_comm in CHANNEL_COMMS:
+        _conv_case(mesh, 2, 2 * C, 4 * C, k, s, p, d, 1, False, channel_comm, (6, 12 * mesh["row"].size()), 7)
+    _conv_case(mesh, 1, 2 * C, 4 * C, k, s, p, d, 1, False, "auto", (12 * mesh["row"].size(),), 8)
+
+
+@pytest.mark.parametrize("name", list(STRING_PADDINGS))
+def test_string_padding_on_2x2(name):
+    run_distributed(_worker_string_padding, 4, {"row": 2, "col": 2}, name, timeout=300)
+
+
+def _worker_rectangular(rank, world, axes):
+    """Meshes that are not powers of two: 2-way space x 3-way channels and the other way round, every way of moving
+    channels, plain and transposed (reference: test_convolution_2d.py:901-935)."""
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh(axes)
+    mesh["sd"] = mesh["sh"] = None
+    mesh["sw"] = mesh["row"]
+    R, C = mesh["row"].size(), mesh["col"].size()
+    for channel_comm in CHANNEL_COMMS:
+        _conv_case(mesh, 2, 2 * C, 3 * C, 3, 1, 1, 1, 1, False, channel_comm, (5, 4 * R), 11)
+        _conv_case(mesh, 2, 2 * C, 3 * C, 2, 2, 0, 1, 1, False, channel_comm, (4, 4 * R), 12)
+        _conv_case(mesh, 2, 2 * C, 3 * C, 4, 2, 1, 1, 1, True, channel_comm, (3, 2 * R), 13)
+    _conv_case(mesh, 2, 2 * C, 4 * C, 3, 1, 1, 1, C, False, "auto", (5, 4 * R), 14)                   # whole groups per rank
+
+
+@pytest.mark.parametrize("axes", [{"row": 2, "col": 3}, {"row": 3, "col": 2}], ids=["2x3", "3x2"])
+def test_rectangular_meshes_with_channel_split(axes):
+    run_distributed(_worker_rectangular, 6, axes, timeout=400)
