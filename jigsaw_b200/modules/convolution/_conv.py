@@ -72,7 +72,7 @@ class _DistributedConvBase(torch.nn.Module):
         n = self._n_spatial
         if self._transposed:
             if isinstance(padding, str):
-                raise ValueError("transposed convolutions take integer padding only")
+                raise NotImplementedError(f"transposed convolutions do not take string padding ({padding!r}): give the padding of each axis as a number")
             if any(o != 0 for o in ntuple(output_padding, n)):
                 raise NotImplementedError("output_padding is not supported by distributed transposed convolutions")
         self.groups = groups

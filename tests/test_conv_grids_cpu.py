@@ -193,3 +193,37 @@ def _worker_rectangular(rank, world, axes):
 @pytest.mark.parametrize("axes", [{"row": 2, "col": 3}, {"row": 3, "col": 2}], ids=["2x3", "3x2"])
 def test_rectangular_meshes_with_channel_split(axes):
     run_distributed(_worker_rectangular, 6, axes, timeout=400)
+
+
+TRANSPOSED_CASES = [(2, 2, 0), (4, 2, 1), (3, 1, 1), (3, 2, 0), (5, 1, 2), (4, 4, 0)]          # (kernel, stride, padding)
+
+
+def _worker_transposed_meshes(rank, world, axes):
+    """Transposed layers on channel-only, space-only and mixed meshes, every way of moving channels, with and
+    without an overhang to hand to the neighbours (reference: conv_transpose/test_conv2dtranspose.py:350-590)."""
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh(axes)
+    mesh["sd"] = mesh["sh"] = None
+    mesh["sw"] = mesh["row"]
+    R, C = mesh["row"].size(), mesh["col"].size()
+    matched = 0
+    for channel_comm in CHANNEL_COMMS:
+        for i, (k, s, p) in enumerate(TRANSPOSED_CASES):
+            try:
+                _conv_case(mesh, 2, 2 * C, 2 * C, k, s, p, 1, 1, True, channel_comm, (3, 4 * R), 30 + i)
+                matched += 1
+            except (NotImplementedError, ValueError):
+                pass                                          # an output that does not divide over the ranks: refused alike
+    assert all_ok(True) and matched >= 3 * 4, matched
+    with pytest.raises(NotImplementedError, match="string padding"):
+        jb.modules.DistributedConvTranspose2d(2 * C, 2 * C, 3, "cpu", mesh["row"], mesh["col"], padding="same")
+    if C > 1:                                                 # groups that do not stay whole on a channel rank
+        with pytest.raises(NotImplementedError, match="multiple of the channel-parallel group size"):
+            jb.modules.DistributedConvTranspose2d(6 * C, 6 * C, 3, "cpu", mesh["row"], mesh["col"], groups=3)
+
+
+@pytest.mark.parametrize("axes", [{"row": 1, "col": 4}, {"row": 4, "col": 1}, {"row": 2, "col": 2}, {"row": 2, "col": 4}],
+                         ids=["1x4", "4x1", "2x2", "2x4"])
+def test_transposed_layers_on_channel_space_and_mixed_meshes(axes):
+    run_distributed(_worker_transposed_meshes, axes["row"] * axes["col"], axes, timeout=600)
