@@ -278,7 +278,9 @@ class DistributedAttention(torch.nn.Module):
         if routed:
             return torch.func.functional_call(self, routed, (x,), {"attn_mask": attn_mask})
         if attn_mask is not None and (self.ring or self.ulysses):
-            raise NotImplementedError("attn_mask is supported only without ring / ulysses sequence parallelism")
+            kind = "ring" if self.ring else "ulysses"
+            raise ValueError(f"{kind} attention does not support attn_mask: a mask over the whole sequence cannot be "
+                             "applied to one chunk at a time; use ring=False, ulysses=False for masked (window) attention")
         core = attn_core_dtype(x)
         p = self.dropout_p if self.training else 0.0
         if self.ulysses and not self.ulysses_intra_size and not self.qk_norm and x.is_cuda and type(self.qkv) is torch.nn.Linear:

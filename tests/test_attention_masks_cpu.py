@@ -135,7 +135,7 @@ def _worker_distributed_masks(rank, world):
     mask = torch.ones(8, 8, dtype=torch.bool)
     for kw in ({"ring": True}, {"ring": False, "ulysses": True}):
         layer = Attention.convert_to_jigsaw(att, mesh, "cpu", attn_backend="math", **kw)
-        with pytest.raises(NotImplementedError, match="attn_mask"):
+        with pytest.raises(ValueError, match=("ring" if kw["ring"] else "ulysses") + " attention does not support"):
             layer(split(xs, {1: row, 2: col}), mask)
         layer(split(xs, {1: row, 2: col}))                            # and still runs without one
 
