@@ -31,6 +31,12 @@ import torch.distributed as dist
 from ..._core.comm import CommOp, sparse_exchange
 
 
+class UnevenSplitError(NotImplementedError, ValueError):
+    """The output of a layer does not divide evenly over the ranks of a split axis.  A ``NotImplementedError``
+    (uneven tiles are not supported; the reference raises that type) which is also a ``ValueError`` (the sizes
+    passed in are what is wrong)."""
+
+
 @dataclass(frozen=True)
 class AxisPlan:
     """Geometry of one split axis.  ``lo[q]`` is the global start of rank ``q``'s held span."""
@@ -65,7 +71,7 @@ def conv_axis_plan(
     extent = dilation * (kernel - 1) + 1
     global_out = (G * n_local + 2 * padding - extent) // stride + 1
     if global_out <= 0 or global_out % G != 0:
-        raise ValueError(
+        raise UnevenSplitError(
             f"global output size {global_out} along a split axis must be positive and divisible by the "
             f"spatial group size {G} (local input {n_local}, kernel {kernel}, stride {stride}, "
             f"padding {padding}, dilation {dilation})"
@@ -84,7 +90,7 @@ def conv_transpose_axis_plan(
     extent = dilation * (kernel - 1) + 1
     global_out = (G * n_local - 1) * stride - 2 * padding + extent
     if global_out <= 0 or global_out % G != 0:
-        raise ValueError(
+        raise UnevenSplitError(
             f"global output size {global_out} along a split axis must be positive and divisible by the "
             f"spatial group size {G} (local input {n_local}, kernel {kernel}, stride {stride}, padding {padding})"
         )

@@ -156,3 +156,19 @@ def _worker_inputs(rank, world):
 
 def test_inputs_of_the_wrong_rank_and_configurations_of_another_layer():
     run_distributed(_worker_inputs, 4, timeout=300)
+
+
+def test_uneven_split_is_both_kinds_of_error():
+    """An output that does not divide over the ranks is 'not supported' (the reference's type) and a wrong size."""
+    from jigsaw_b200.modules import CommOp
+    from jigsaw_b200.modules.convolution import _halo
+
+    class Four:
+        def size(self):
+            return 4
+
+    for make in (lambda: _halo.conv_axis_plan(-1, Four(), 8, 2, 1, 0, 1, CommOp.ISEND),
+                 lambda: _halo.conv_transpose_axis_plan(-1, Four(), 8, 3, 2, 0, 1, CommOp.ISEND)):
+        for kind in (NotImplementedError, ValueError, _halo.UnevenSplitError):
+            with pytest.raises(kind, match="divisible by the spatial group size"):
+                make()
