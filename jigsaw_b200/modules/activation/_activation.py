@@ -30,9 +30,13 @@ class DistributedSoftmax(torch.nn.Module):
         cls, model: torch.nn.Softmax, process_mesh_dict: dict, device: Any = None, row_kw: str = "row",
         col_kw: str = "col", model_kw: str = "model", **kwargs: Any,
     ) -> "DistributedSoftmax":
-        """The softmax dimension is taken to be the feature dimension, split over ``col_kw``."""
-        dim = -1 if model.dim is None else model.dim
-        return cls(kwargs.get("group", process_mesh_dict[col_kw]), dim)
+        """The softmax dimension is taken to be the feature dimension, split over ``col_kw``.  A ``Softmax`` built
+        without ``dim`` picks its axis from the rank of each input (torch's legacy rule), which a layer that must
+        know whether its axis is cut cannot follow: that one is refused."""
+        if model.dim is None:
+            raise NotImplementedError("a Softmax without an explicit dim cannot be converted: give it the dim it normalises, "
+                                      "or build DistributedSoftmax(group, dim) by hand")
+        return cls(kwargs.get("group", process_mesh_dict[col_kw]), model.dim)
 
     def convert_to_torch(self, *args: Any, **kwargs: Any) -> torch.nn.Softmax:
         return torch.nn.Softmax(dim=self.dim)

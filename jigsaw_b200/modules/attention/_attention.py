@@ -148,7 +148,7 @@ class Attention(torch.nn.Module):
             dropout_p=attention.dropout_p, qk_norm=attention.qk_norm, ring=ring, ulysses=ulysses,
             ulysses_intra_size=ulysses_intra_size, ulysses_inter_save_scope=ulysses_inter_save_scope,
             ulysses_inter_overlap=ulysses_inter_overlap, ulysses_inter_offload=ulysses_inter_offload,
-            attn_backend=attn_backend, dtype=attention.dtype, config=config,
+            attn_backend=attn_backend, dtype=attention.qkv.weight.dtype, config=config,        # the weights' dtype: the module may have been cast after it was built
             out_bias=attention.head_concat.bias is not None,
         )
         with torch.no_grad():
