@@ -338,7 +338,7 @@ class DistributedAttention(torch.nn.Module):
         C = channel.size()
         heads = self.heads * C
         out = Attention(self.in_dim, self.embed_dim, self.out_dim, heads, self.device, self.dropout_p, self.qk_norm,
-                        self.dtype, self.head_concat.bias is not None)
+                        self.qkv.weight.dtype, self.head_concat.bias is not None)
         with torch.no_grad():
             w = gather_dim(self.qkv.weight.data, channel, 1) if C > 1 else self.qkv.weight.data
             w = w.view(C, 3, self.heads, self.head_dim, self.in_dim).transpose(0, 1).reshape(3 * self.embed_dim, self.in_dim)

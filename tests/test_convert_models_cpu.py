@@ -139,3 +139,25 @@ def _worker_kinds(rank, world):
 
 def test_layer_kinds_one_by_one():
     run_distributed(_worker_kinds, 4, timeout=300)
+
+
+def _worker_cast_after_construction(rank, world):
+    """A module cast with ``.double()`` / ``.to(dtype)`` after it was built converts in the dtype of its weights, in
+    both directions."""
+    import jigsaw_b200 as jb
+    from jigsaw_b200.modules.attention import Attention
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    serial = Attention(8, 8, 8, 2, "cpu", attn_backend="math", qk_norm=True).double()        # built in float32, then cast
+    sharded = Attention.convert_to_jigsaw(serial, mesh, "cpu", attn_backend="math")
+    assert all(p.dtype == torch.float64 for p in sharded.parameters())
+    back = sharded.convert_to_torch(mesh)
+    assert all(p.dtype == torch.float64 for p in back.parameters())
+    assert_close(back.qkv.weight.data, serial.qkv.weight.data, "qkv weight there and back", 0, 0)
+    halved = Attention.convert_to_jigsaw(Attention(8, 8, 8, 2, "cpu").to(torch.bfloat16), mesh, "cpu")
+    assert all(p.dtype == torch.bfloat16 for p in halved.parameters())
+    assert all(p.dtype == torch.bfloat16 for p in halved.to(torch.float32).to(torch.bfloat16).convert_to_torch(mesh).parameters())
+
+
+def test_modules_cast_after_construction_convert_in_their_weights_dtype():
+    run_distributed(_worker_cast_after_construction, 4, timeout=300)
