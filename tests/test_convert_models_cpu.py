@@ -148,6 +148,7 @@ def _worker_cast_after_construction(rank, world):
     from jigsaw_b200.modules.attention import Attention
 
     mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    torch.manual_seed(0)                                                                      # the same module on every rank
     serial = Attention(8, 8, 8, 2, "cpu", attn_backend="math", qk_norm=True).double()        # built in float32, then cast
     sharded = Attention.convert_to_jigsaw(serial, mesh, "cpu", attn_backend="math")
     assert all(p.dtype == torch.float64 for p in sharded.parameters())
