@@ -29,7 +29,7 @@ from ... import parallel
 from ..._core.placement import gather_dim
 from ..._core.shard_repr import shard_repr
 from ..linear import DistributedLinear
-from ._config import AttnBackend, JIGSAW_TE_AVAILABLE, Offload, RingAttentionConfig, SaveBackward, SaveScope, SendForward, coerce_enum
+from ._config import AttnBackend, Offload, RingAttentionConfig, SaveBackward, SaveScope, SendForward, coerce_enum, resolve_backend
 from ._cores import MathCore
 from ._ring import hybrid_subgroups, ring_attention
 from ._ulysses import heads_to_seq, hierarchical_ulysses_attention, seq_to_heads
@@ -97,8 +97,7 @@ class Attention(torch.nn.Module):
         self.device, self.dtype = torch.device(device), dtype
         self.dropout_p, self.qk_norm = dropout_p, qk_norm
         self.attn_backend = coerce_enum(AttnBackend, attn_backend, "attn_backend")
-        if self.attn_backend is AttnBackend.TE and not JIGSAW_TE_AVAILABLE:
-            self.attn_backend = AttnBackend.SDPA
+        self.attn_backend = resolve_backend(self.attn_backend)
         self.scale = self.head_dim**-0.5
         self.qkv = torch.nn.Linear(in_dim, 3 * embed_dim, bias=False, device=self.device, dtype=dtype)
         self.head_concat = torch.nn.Linear(embed_dim, out_dim, bias=out_bias, device=self.device, dtype=dtype)
@@ -194,8 +193,7 @@ class DistributedAttention(torch.nn.Module):
         if ring and ulysses:
             raise ValueError("ring and ulysses are mutually exclusive")
         self.attn_backend = coerce_enum(AttnBackend, attn_backend, "attn_backend")
-        if self.attn_backend is AttnBackend.TE and not JIGSAW_TE_AVAILABLE:
-            self.attn_backend = AttnBackend.SDPA
+        self.attn_backend = resolve_backend(self.attn_backend)
         C, P = channel_group.size(), spatial_group.size()
         if heads % C:
             raise ValueError("heads is not divisible by channel group size")

@@ -93,6 +93,19 @@ except Exception:  # noqa: BLE001
     JIGSAW_TE_AVAILABLE = False
 
 
+def resolve_backend(backend: AttnBackend) -> AttnBackend:
+    """``TE`` stands for TransformerEngine's fused attention.  It is not used by this library: the request is
+    answered with the SDPA backend (the library's own flash kernels on a B200) and a warning, so that a configuration
+    written for an installation with TransformerEngine keeps running and says what it runs on."""
+    if backend is AttnBackend.TE and not JIGSAW_TE_AVAILABLE:
+        import warnings
+
+        warnings.warn("attn_backend='te' needs transformer_engine, which is not installed: falling back to 'sdpa'",
+                      UserWarning, stacklevel=3)
+        return AttnBackend.SDPA
+    return backend
+
+
 class RingAttentionConfig:
     """Validated bundle of ring-attention policies."""
 
@@ -119,8 +132,7 @@ class RingAttentionConfig:
         self.send_backward = coerce_enum(SendBackward, send_backward, "send_backward")
         self.offload = coerce_enum(Offload, offload, "offload")
         self.attn_backend = coerce_enum(AttnBackend, attn_backend, "attn_backend")
-        if self.attn_backend is AttnBackend.TE and not JIGSAW_TE_AVAILABLE:
-            self.attn_backend = AttnBackend.SDPA
+        self.attn_backend = resolve_backend(self.attn_backend)
         self.intra_size = int(intra_size)
         self.overlap_comm = bool(overlap_comm)
         self.comm = resolve_comm_op(comm, self.device)

@@ -44,7 +44,19 @@ def test_single_process_rules():
     # TransformerEngine is optional: without it the backend resolves to the default core
     assert A.JIGSAW_TE_AVAILABLE in (True, False)
     if not A.JIGSAW_TE_AVAILABLE:
-        assert Attention(8, 16, 8, 4, "cpu", attn_backend="te").attn_backend is A.AttnBackend.SDPA
+        import warnings
+
+        from jigsaw_b200.modules.attention import RingAttentionConfig
+
+        for build in (lambda: Attention(8, 16, 8, 4, "cpu", attn_backend="te"), lambda: RingAttentionConfig(device="cpu", attn_backend="TE")):
+            with warnings.catch_warnings(record=True) as seen:
+                warnings.simplefilter("always")
+                assert build().attn_backend is A.AttnBackend.SDPA
+            assert any(issubclass(w.category, UserWarning) and "falling back to 'sdpa'" in str(w.message) for w in seen)
+        with warnings.catch_warnings(record=True) as seen:                 # the other backends say nothing
+            warnings.simplefilter("always")
+            assert Attention(8, 16, 8, 4, "cpu", attn_backend="math").attn_backend is A.AttnBackend.MATH
+        assert not seen
 
 
 def _worker_policies(rank, world):
