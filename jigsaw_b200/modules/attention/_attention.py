@@ -190,6 +190,13 @@ class DistributedAttention(torch.nn.Module):
         self.ulysses_inter_save_scope = coerce_enum(SaveScope, ulysses_inter_save_scope, "ulysses_inter_save_scope")
         self.ulysses_inter_overlap = bool(ulysses_inter_overlap)
         self.ulysses_inter_offload = coerce_enum(Offload, ulysses_inter_offload, "ulysses_inter_offload")
+        if self.ulysses_inter_overlap and self.ulysses_intra_size and self.ulysses_inter_save_scope is SaveScope.GLOBAL:
+            import warnings
+
+            warnings.warn(
+                "ulysses_inter_overlap with ulysses_inter_save_scope=GLOBAL only overlaps the forward pass of the outer "
+                "K/V ring: GLOBAL keeps every chunk that arrived, so the backward pass fetches nothing that an overlap "
+                "could hide.  Use ulysses_inter_save_scope=LOCAL to overlap the backward pass as well.", stacklevel=2)
         if ring and ulysses:
             raise ValueError("ring and ulysses are mutually exclusive")
         self.attn_backend = coerce_enum(AttnBackend, attn_backend, "attn_backend")

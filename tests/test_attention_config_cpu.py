@@ -103,3 +103,29 @@ def _worker_policies(rank, world):
 
 def test_ring_policies_follow_the_layout():
     run_distributed(_worker_policies, 4, timeout=300)
+
+
+def _worker_outer_ring_overlap_warning(rank, world):
+    import warnings
+
+    import jigsaw_b200 as jb
+
+    mesh = jb.make_process_mesh({"row": 4, "col": 1})
+
+    def build(**kw):
+        with warnings.catch_warnings(record=True) as seen:
+            warnings.simplefilter("always")
+            jb.modules.DistributedAttention(8, 16, 8, 4, 0, "cpu", mesh["row"], mesh["col"], ulysses=True, ulysses_intra_size=2,
+                                            attn_backend="math", **kw)
+        return [str(w.message) for w in seen if issubclass(w.category, UserWarning)]
+
+    said = build(ulysses_inter_overlap=True, ulysses_inter_save_scope="global")
+    assert len(said) == 1 and "only overlaps the forward pass" in said[0] and "LOCAL" in said[0]
+    assert not build(ulysses_inter_overlap=True, ulysses_inter_save_scope="local")
+    assert not build(ulysses_inter_overlap=False, ulysses_inter_save_scope="global")
+
+
+def test_overlap_of_the_outer_ring_with_kept_chunks_says_what_it_overlaps():
+    from dist_utils import run_distributed
+
+    run_distributed(_worker_outer_ring_overlap_warning, 4, timeout=120)
