@@ -11,6 +11,7 @@ Reference behaviours covered: tests/test_autocast.py:89-133 (linear), :135-260 (
 
 import contextlib
 
+import pytest
 import torch
 
 from dist_utils import assert_close, run_distributed
@@ -18,10 +19,10 @@ from dist_utils import assert_close, run_distributed
 TOL = 3e-2
 
 
-def _run(model, x, autocast, seed=0):
+def _run(model, x, autocast, seed=0, half=torch.bfloat16):
     model.zero_grad(set_to_none=True)
     x = x.clone().detach().requires_grad_(True)
-    ctx = torch.autocast("cpu", dtype=torch.bfloat16) if autocast else contextlib.nullcontext()
+    ctx = torch.autocast("cpu", dtype=half) if autocast else contextlib.nullcontext()
     with ctx:
         y = model(x)
     g = torch.randn(y.shape, generator=torch.Generator().manual_seed(seed)).to(y.dtype)
@@ -30,8 +31,8 @@ def _run(model, x, autocast, seed=0):
     return y.detach(), x.grad.detach()
 
 
-def _check(name, model, x, out_dtype, tol=TOL):
-    y, dx = _run(model, x, True)
+def _check(name, model, x, out_dtype, tol=TOL, half=torch.bfloat16):
+    y, dx = _run(model, x, True, half=half)
     y_ref, dx_ref = _run(model, x, False)
     assert y.dtype == out_dtype, f"{name}: forward output is {y.dtype}, expected {out_dtype}"
     assert dx.dtype == x.dtype, f"{name}: input gradient is {dx.dtype}, not the input dtype {x.dtype}"
@@ -43,7 +44,7 @@ def _check(name, model, x, out_dtype, tol=TOL):
     assert_close(dx, dx_ref, f"{name}: input gradient", tol, tol * (float(dx_ref.abs().max()) + 1e-6))
 
 
-def _worker_autocast(rank, world):
+def _worker_autocast(rank, world, half):
     import jigsaw_b200 as jb
     from jigsaw_b200.modules.attention import RingAttentionConfig
 
@@ -53,27 +54,28 @@ def _worker_autocast(rank, world):
     torch.manual_seed(rank)
     for bias in (False, True):
         layer = M.DistributedLinear(10, 20, "cpu", model, row, col, bias=bias)
-        _check(f"linear bias={bias}", layer, torch.randn(1, 10, 5), torch.bfloat16)
+        _check(f"linear bias={bias}", layer, torch.randn(1, 10, 5), half, half=half)
     conv = M.DistributedConv2d(4, 8, 3, "cpu", row, col, padding=1)
-    _check("conv2d", conv, torch.randn(2, 2, 6, 4), torch.bfloat16)
+    _check("conv2d", conv, torch.randn(2, 2, 6, 4), half, half=half)
     convt = M.DistributedConvTranspose2d(4, 8, 2, "cpu", row, col, stride=2)
-    _check("conv transpose 2d", convt, torch.randn(2, 2, 6, 4), torch.bfloat16)
+    _check("conv transpose 2d", convt, torch.randn(2, 2, 6, 4), half, half=half)
     att = M.DistributedAttention(16, 16, 16, 4, col.rank(), "cpu", row, col, attn_backend="math")
-    _check("attention", att, torch.randn(2, 8, 8), torch.bfloat16, tol=6e-2)
+    _check("attention", att, torch.randn(2, 8, 8), half, tol=6e-2, half=half)
     cfg = RingAttentionConfig(device="cpu", attn_backend="math", send_in_forward="kv")
     ring = M.DistributedAttention(16, 16, 16, 4, col.rank(), "cpu", row, col, ring=True, attn_backend="math", config=cfg)
-    _check("ring attention", ring, torch.randn(2, 4, 8), torch.bfloat16, tol=6e-2)
+    _check("ring attention", ring, torch.randn(2, 4, 8), half, tol=6e-2, half=half)
     # fp32-list layers: fp32 out under autocast, also when fed bf16
     ln = M.DistributedLayerNorm(16, model.rank(), "cpu", row, col)
-    _check("layer norm", ln, torch.randn(2, 4, 8), torch.float32)
+    _check("layer norm", ln, torch.randn(2, 4, 8), torch.float32, half=half)
     ln0 = M.DistributedLayerNorm(16, model.rank(), "cpu", row, col, elementwise_affine=False)
-    _check("layer norm without parameters", ln0, torch.randn(2, 4, 8), torch.float32)
+    _check("layer norm without parameters", ln0, torch.randn(2, 4, 8), torch.float32, half=half)
     sm = M.DistributedSoftmax(col, dim=-1)
-    _check("softmax", sm, torch.randn(2, 4, 8), torch.float32)
-    with torch.autocast("cpu", dtype=torch.bfloat16):
-        assert ln(torch.randn(2, 4, 8).bfloat16()).dtype == torch.float32
-        assert sm(torch.randn(2, 4, 8).bfloat16()).dtype == torch.float32
+    _check("softmax", sm, torch.randn(2, 4, 8), torch.float32, half=half)
+    with torch.autocast("cpu", dtype=half):
+        assert ln(torch.randn(2, 4, 8).to(half)).dtype == torch.float32
+        assert sm(torch.randn(2, 4, 8).to(half)).dtype == torch.float32
 
 
-def test_autocast_contracts_on_four_ranks():
-    run_distributed(_worker_autocast, 4, timeout=300)
+@pytest.mark.parametrize("half", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_autocast_contracts_on_four_ranks(half):
+    run_distributed(_worker_autocast, 4, half, timeout=300)
