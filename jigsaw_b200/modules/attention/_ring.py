@@ -258,6 +258,13 @@ class _RingAttention(torch.autograd.Function):
         return dq.to(q.dtype), d_own[0].to(payload.dtype), d_own[1].to(payload.dtype), None, None, None, None, None, None, None, None
 
 
+def _under_vmap(t: torch.Tensor) -> bool:
+    try:
+        return bool(torch._C._functorch.is_batchedtensor(t))
+    except AttributeError:                       # a torch without that probe: let the fused path decide
+        return False
+
+
 def ring_attention(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, group: dist.ProcessGroup, cfg: RingAttentionConfig,
     dropout_p: float = 0.0, x: torch.Tensor | None = None, w_qkv: torch.Tensor | None = None,
@@ -271,7 +278,7 @@ def ring_attention(
     kernels pull each part from its owner, and circulating ``x`` instead of K / V is a transport
     choice that changes nothing in the result (K and V are differentiable outputs of the local
     projection), so ``cfg`` only matters to the chunked schedule below."""
-    if q.is_cuda:
+    if q.is_cuda and not _under_vmap(q):         # the fused launch has no batching rule: vmapped calls take the chunked schedule
         from ...ops import attention_fused
 
         out = attention_fused.maybe_fused_ring_attention(q, k, v, scale, group, dropout_p)
