@@ -54,9 +54,9 @@ def _dense_attention(q, k, v, scale: float, dropout_p: float, backend: AttnBacke
                 _math_autograd(q, k, v, scale, p, None)
         return _math_autograd(q, k, v, scale, p, attn_mask)
     if attn_mask is None and q.is_cuda:
-        from ...ops import attention_fused
+        from ...ops import _lib, attention_fused
 
-        if attention_fused.flash_usable(q, k, p) and v.dtype == torch.bfloat16:
+        if not _lib._any_batched((q, k, v)) and attention_fused.flash_usable(q, k, p) and v.dtype == torch.bfloat16:
             return attention_fused.FlashAttention.apply(q, k, v, scale)       # own tcgen05 kernels
     return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=p, scale=scale)
 

@@ -424,7 +424,10 @@ class _DistributedConvNd(_DistributedConvBase):
     def _try_fused(self, x: torch.Tensor) -> tuple[torch.Tensor | None, torch.Tensor]:
         if not x.is_cuda:
             return None, x
-        from ...ops import conv_fused
+        from ...ops import _lib, conv_fused
+
+        if _lib._any_batched((x, self.weight)):     # under torch.vmap: the kernels have no batching rules
+            return None, x
 
         if self._n_spatial != 2 or x.dim() != 4 or self._is_patchify():
             from ...ops.lazy_chain import materialize

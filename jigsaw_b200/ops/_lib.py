@@ -356,6 +356,14 @@ def record(name: str, fused: bool) -> None:
         raise FusedPathDeclined(f"{name} declined CUDA inputs: {_last_reason or 'outside the coverage of the kernel'}")
 
 
+def _any_batched(args: tuple) -> bool:
+    """True when one of ``args`` is a tensor that ``torch.vmap`` has wrapped."""
+    probe = getattr(getattr(torch._C, "_functorch", None), "is_batchedtensor", None)
+    if probe is None:
+        return False
+    return any(isinstance(a, torch.Tensor) and probe(a) for a in args)
+
+
 def audited(name: str):
     """Decorator of the ``maybe_fused_*`` entry points: counts, per operation, the calls that ran on the
     kernels and the calls with CUDA tensors that were declined, and raises on the latter under strict
@@ -373,7 +381,12 @@ def audited(name: str):
                 from .lazy_chain import materialize
 
                 args = tuple(materialize(a) for a in args)
-            out = fn(*args, **kwargs)
+            if _any_batched(args):
+                # the kernels take raw pointers and have no batching rules: a call under torch.vmap goes to the
+                # torch.distributed path, whose Functions carry them
+                out = decline("called under torch.vmap")
+            else:
+                out = fn(*args, **kwargs)
             if out is not None:
                 record(name, True)
                 return out
