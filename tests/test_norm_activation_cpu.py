@@ -91,3 +91,50 @@ def _worker_norms(rank, world):
 
 def test_norms_and_softmax_details():
     run_distributed(_worker_norms, 4, timeout=300)
+
+
+def _worker_norm_vmap(rank, world):
+    """Layer norm and softmax under ``vmap`` with the ensemble axis anywhere in the input, with and without affine
+    parameters, and with stacked member weights (reference: tests/modules/normalization/test_normalization_vmap.py,
+    tests/modules/activation/test_activation_vmap.py)."""
+    import jigsaw_b200 as jb
+    from torch.func import functional_call, stack_module_state
+
+    mesh = jb.make_process_mesh({"row": 2, "col": 2})
+    M, row, col = jb.modules, mesh["row"], mesh["col"]
+    gen = torch.Generator().manual_seed(11 + rank)
+    x = torch.randn(3, 2, 4, 8, generator=gen, dtype=torch.float64)                   # (members, batch, tokens / row, features / col)
+    for affine in (True, False):
+        jb.launch.set_all_seeds(5)
+        ln = M.DistributedLayerNorm(16, mesh["model"].rank(), "cpu", row, col, elementwise_affine=affine, dtype=torch.float64)
+        for in_dim in (0, 1, 2):
+            moved = x.movedim(0, in_dim).contiguous().requires_grad_(True)
+            got = torch.vmap(ln, in_dims=in_dim, out_dims=in_dim)(moved)
+            want = torch.stack([ln(m) for m in moved.unbind(in_dim)], dim=in_dim)
+            assert_close(got, want, f"layer norm affine={affine}, ensemble axis {in_dim}", 1e-12, 1e-12)
+            seed = torch.randn(want.shape, generator=torch.Generator().manual_seed(3), dtype=torch.float64)
+            (g,) = torch.autograd.grad(got, moved, seed, retain_graph=True)
+            (w,) = torch.autograd.grad(want, moved, seed)
+            assert_close(g, w, f"layer norm affine={affine}, ensemble axis {in_dim}: input gradient", 1e-10, 1e-12)
+        assert ln.get_parameter_count() == (32 if affine else 0)
+    members = []
+    for s in range(3):
+        jb.launch.set_all_seeds(20 + s)
+        m = M.DistributedLayerNorm(16, mesh["model"].rank(), "cpu", row, col, dtype=torch.float64)
+        with torch.no_grad():
+            for p in m.parameters():
+                p.add_(0.1 * torch.randn(p.shape, dtype=torch.float64))
+        jb.parallel.broadcast_replicas(m)
+        members.append(m)
+    params, buffers = stack_module_state(members)
+    got = torch.vmap(lambda p, b, xi: functional_call(members[0], (p, b), (xi,)))(params, buffers, x)
+    assert_close(got, torch.stack([m(xi) for m, xi in zip(members, x)]), "layer norm with member weights", 1e-12, 1e-12)
+    soft = M.DistributedSoftmax(col, dim=-1)
+    for in_dim in (0, 2):
+        moved = x.movedim(0, in_dim).contiguous()
+        got = torch.vmap(soft, in_dims=in_dim, out_dims=in_dim)(moved)
+        assert_close(got, torch.stack([soft(m) for m in moved.unbind(in_dim)], dim=in_dim), f"softmax, ensemble axis {in_dim}", 1e-12, 1e-12)
+
+
+def test_layer_norm_and_softmax_under_vmap_with_the_ensemble_axis_anywhere():
+    run_distributed(_worker_norm_vmap, 4, timeout=300)
