@@ -38,7 +38,7 @@ class LaunchEnv:
     local_rank: int
     master_addr: str
     master_port: str
-    source: str  # which launcher's variables were found: "slurm", "torchrun" or "single"
+    source: str  # which launcher's variables were found: "slurm", "torchrun", "mpirun" or "single"
 
 
 # launcher name -> the variables that carry (rank, world size, local rank); the first launcher whose rank
@@ -46,6 +46,7 @@ class LaunchEnv:
 _LAUNCHERS = (
     ("slurm", ("SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID")),
     ("torchrun", ("RANK", "WORLD_SIZE", "LOCAL_RANK")),
+    ("mpirun", ("OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_RANK")),      # Open MPI
 )
 
 
@@ -74,8 +75,8 @@ def resolve_launch_env(strict: bool = False) -> LaunchEnv:
     else:
         if strict:
             raise RuntimeError(
-                "No distributed launcher detected: expected SLURM_PROCID (srun) or RANK (torchrun) "
-                "in the environment. Launch with srun or torchrun, or pass strict=False for a "
+                "No distributed launcher detected: expected SLURM_PROCID (srun), RANK (torchrun) or "
+                "OMPI_COMM_WORLD_RANK (mpirun) in the environment. Launch with one of them, or pass strict=False for a "
                 "single-process run."
             )
         source, rank, world, local = "single", 0, 1, 0

@@ -15,7 +15,7 @@ import pytest
 from jigsaw_b200 import launch
 
 VARS = ("SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID", "SLURM_JOB_NODELIST", "RANK", "WORLD_SIZE", "LOCAL_RANK",
-        "MASTER_ADDR", "MASTER_PORT")
+        "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")
 
 
 @pytest.fixture(autouse=True)
@@ -104,3 +104,17 @@ def test_device_choice(monkeypatch, visible, local_rank, expected):
     assert (device.type, device.index) == ("cuda", expected) and selected == [expected]
     assert (got_local, rank, world) == (local_rank, 4 + local_rank, 8)   # the local rank is reported as launched
     assert started[0]["backend"] == "nccl" and started[0]["rank"] == 4 + local_rank and started[0]["world_size"] == 8
+
+
+def test_open_mpi_variables_come_last(monkeypatch):
+    """``mpirun`` (Open MPI) is read when neither Slurm nor torchrun variables are there; either of those wins."""
+    for name, value in (("OMPI_COMM_WORLD_RANK", "5"), ("OMPI_COMM_WORLD_SIZE", "8"), ("OMPI_COMM_WORLD_LOCAL_RANK", "1")):
+        monkeypatch.setenv(name, value)
+    env = launch.resolve_launch_env(strict=True)
+    assert (env.source, env.rank, env.world_size, env.local_rank) == ("mpirun", 5, 8, 1)
+    assert (env.master_addr, env.master_port) == ("localhost", "29500")
+    monkeypatch.setenv("RANK", "2")
+    monkeypatch.setenv("WORLD_SIZE", "4")
+    assert launch.resolve_launch_env().source == "torchrun"
+    monkeypatch.setenv("SLURM_PROCID", "3")
+    assert launch.resolve_launch_env().source == "slurm"
